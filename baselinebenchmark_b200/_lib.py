@@ -1,0 +1,88 @@
+"""ctypes binding of libmoba_b200.so (the C ABI declared in include/moba_b200.h).
+
+The library is the product; there is no Python or CPU fallback.  Importing this
+module never compiles anything: a missing library is an error that names the
+build command.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libmoba_b200.so"
+
+ATTEND_TCGEN05 = 0
+ATTEND_MMA_SYNC = 1
+
+#: every symbol include/moba_b200.h declares
+SYMBOLS = (
+    "moba_b200_abi_version", "moba_b200_strerror", "moba_problem_check", "moba_problem_dims",
+    "moba_workspace_size", "moba_forward", "moba_workspace_size_host", "moba_forward_host",
+    "moba_chunk_metadata", "moba_chunk_means", "moba_gate_topk", "moba_compact_routes",
+    "moba_attend", "moba_merge", "moba_attend_tile_rows",
+)
+
+
+class Problem(C.Structure):
+    """struct moba_problem"""
+    _fields_ = [
+        ("total_tokens", C.c_int64), ("batch", C.c_int32), ("num_q_heads", C.c_int32),
+        ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("max_seqlen", C.c_int32),
+        ("chunk_size", C.c_int32), ("topk", C.c_int32), ("attend_impl", C.c_int32),
+        ("q_stride_token", C.c_int64), ("q_stride_head", C.c_int64),
+        ("k_stride_token", C.c_int64), ("k_stride_head", C.c_int64),
+        ("v_stride_token", C.c_int64), ("v_stride_head", C.c_int64),
+        ("o_stride_token", C.c_int64), ("o_stride_head", C.c_int64),
+    ]
+
+
+class Dims(C.Structure):
+    """struct moba_dims"""
+    _fields_ = [
+        ("chunks_per_seq", C.c_int32), ("slots", C.c_int32), ("hist", C.c_int32),
+        ("partials", C.c_int32), ("rows", C.c_int64), ("lists", C.c_int64),
+    ]
+
+
+class MobaError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"moba_b200 error {code}: {message}")
+        self.code = code
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads the shared library once; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m baselinebenchmark_b200.build` "
+                "(nvcc, sm_100a).  There is no fallback implementation.")
+        handle = C.CDLL(str(LIB_PATH))
+        handle.moba_b200_strerror.restype = C.c_char_p
+        handle.moba_b200_strerror.argtypes = [C.c_int]
+        vp, i32p, sz = C.c_void_p, C.c_void_p, C.c_size_t
+        pp = C.POINTER(Problem)
+        handle.moba_problem_check.argtypes = [pp]
+        handle.moba_problem_dims.argtypes = [pp, C.POINTER(Dims)]
+        handle.moba_workspace_size.argtypes = [pp, C.POINTER(sz)]
+        handle.moba_workspace_size_host.argtypes = [pp, C.POINTER(sz)]
+        handle.moba_forward.argtypes = [pp, vp, vp, vp, i32p, vp, vp, i32p, vp, sz, vp]
+        handle.moba_forward_host.argtypes = [pp, vp, vp, vp, i32p, vp, vp, i32p, vp, sz, vp]
+        handle.moba_chunk_metadata.argtypes = [pp, i32p, i32p, i32p, vp, vp]
+        handle.moba_chunk_means.argtypes = [pp, vp, i32p, vp, vp]
+        handle.moba_gate_topk.argtypes = [pp, vp, vp, i32p, i32p, i32p, vp]
+        handle.moba_compact_routes.argtypes = [pp, i32p, i32p, i32p, i32p, i32p, i32p, i32p, vp, C.c_int32, vp]
+        handle.moba_attend.argtypes = [pp, vp, vp, vp, i32p, i32p, i32p, i32p, i32p, vp, vp, i32p, vp]
+        handle.moba_merge.argtypes = [pp, vp, vp, i32p, vp, vp, vp]
+        handle.moba_attend_tile_rows.argtypes = [C.c_int]
+        _lib = handle
+    return _lib
+
+
+def check(code: int) -> None:
+    if code != 0:
+        raise MobaError(code, lib().moba_b200_strerror(code).decode())

@@ -1,0 +1,330 @@
+// C ABI of the MoBA forward (declared in include/moba_b200.h): argument
+// validation, workspace carving and the launch sequence.  Host-side only.
+//
+// Mirrors backends/_mthreads/ops/moba/parallel.py:253-457 of the reference:
+// the checks of parallel_moba (:410-443) and the dataflow of
+// _moba_attn_varlen_inference (:283-374), with all ranks handled in one pass
+// and every scratch buffer taken from a caller-owned workspace.
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+using namespace moba;
+
+namespace {
+
+constexpr size_t kAlign = 256;
+inline size_t align_up(size_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
+
+int check_problem(const moba_problem_t* p) {
+  if (p == nullptr) return MOBA_E_NULL;
+  if (p->total_tokens <= 0 || p->batch <= 0 || p->num_q_heads <= 0 || p->num_kv_heads <= 0 || p->head_dim <= 0)
+    return MOBA_E_SHAPE;                                   // parallel.py:440-441
+  if (p->num_q_heads % p->num_kv_heads != 0) return MOBA_E_SHAPE;          // :442-443
+  if (p->max_seqlen <= 0 || p->chunk_size <= 0) return MOBA_E_SHAPE;       // :428-431
+  if (p->topk < 1 || p->topk > kMaxTopk) return MOBA_E_TOPK;               // :432-437
+  if (p->head_dim > 256) return MOBA_E_SHAPE;                              // :445-446
+  if (p->head_dim != kHeadDim) return MOBA_E_UNSUPPORTED;
+  if (p->num_q_heads / p->num_kv_heads > 128) return MOBA_E_UNSUPPORTED;
+  if (p->attend_impl != MOBA_ATTEND_TCGEN05 && p->attend_impl != MOBA_ATTEND_MMA_SYNC) return MOBA_E_UNSUPPORTED;
+  const int64_t strides[8] = {p->q_stride_token, p->q_stride_head, p->k_stride_token, p->k_stride_head,
+                              p->v_stride_token, p->v_stride_head, p->o_stride_token, p->o_stride_head};
+  for (int i = 0; i < 8; ++i) {
+    if (strides[i] <= 0) return MOBA_E_SHAPE;
+    if (strides[i] % 8 != 0) return MOBA_E_ALIGN;          // 16-byte vector and TMA accesses
+  }
+  const int64_t mc = (p->max_seqlen + (int64_t)p->chunk_size - 1) / p->chunk_size;
+  if (mc * p->batch > (int64_t)1 << 24) return MOBA_E_UNSUPPORTED;
+  if (mc > 16384) return MOBA_E_UNSUPPORTED;               // per-CTA list tables live in shared memory
+  const int64_t hist = (p->topk - 1 < mc - 1) ? p->topk - 1 : mc - 1;
+  const int64_t np = (hist > 0 ? hist : 0) + 1;
+  // entry ids (row * partials + rank) are int32, like the reference's int32 offsets (routing.py:1094-1100)
+  if (p->total_tokens * p->num_q_heads * np >= ((int64_t)1 << 31)) return MOBA_E_UNSUPPORTED;
+  return MOBA_OK;
+}
+
+Params make_params(const moba_problem_t* p) {
+  Params r;
+  r.T = p->total_tokens;
+  r.B = p->batch;
+  r.Hq = p->num_q_heads;
+  r.Hkv = p->num_kv_heads;
+  r.G = r.Hq / r.Hkv;
+  r.D = p->head_dim;
+  r.max_seqlen = p->max_seqlen;
+  r.C = p->chunk_size;
+  r.topk = p->topk;
+  r.mc = (int)((p->max_seqlen + (int64_t)p->chunk_size - 1) / p->chunk_size);
+  r.slots = r.B * r.mc;
+  r.hist = (r.topk - 1 < r.mc - 1) ? r.topk - 1 : r.mc - 1;       // parallel.py:303
+  if (r.hist < 0) r.hist = 0;
+  r.NP = r.hist + 1;
+  r.rows = r.T * r.Hq;
+  r.lists = (int64_t)r.slots * r.Hkv;
+  r.sq_t = p->q_stride_token; r.sq_h = p->q_stride_head;
+  r.sk_t = p->k_stride_token; r.sk_h = p->k_stride_head;
+  r.sv_t = p->v_stride_token; r.sv_h = p->v_stride_head;
+  r.so_t = p->o_stride_token; r.so_h = p->o_stride_head;
+  return r;
+}
+
+// Carves the workspace; with base == nullptr only sizes are computed.
+struct Workspace {
+  __nv_bfloat16* means;
+  int32_t* selected;
+  int32_t* list_counts;      // [lists] + work counter + status, zeroed per call in one memset
+  int32_t* work_counter;
+  int32_t* status;
+  int32_t* list_offsets;
+  int32_t* tile_prefix;
+  int32_t* cursors;
+  int32_t* row_list;
+  float* partial_out;
+  float* partial_lse;
+  size_t zero_bytes;
+  size_t total;
+};
+
+Workspace carve(const Params& r, void* base) {
+  Workspace w;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    void* ptr = base ? static_cast<char*>(base) + off : nullptr;
+    off += align_up(bytes);
+    return ptr;
+  };
+  const size_t lists = (size_t)r.lists;
+  w.zero_bytes = (lists + 64) * sizeof(int32_t);
+  w.list_counts = static_cast<int32_t*>(take(w.zero_bytes));
+  w.work_counter = w.list_counts ? w.list_counts + lists : nullptr;
+  w.status = w.list_counts ? w.list_counts + lists + 1 : nullptr;
+  w.list_offsets = static_cast<int32_t*>(take((lists + 1) * sizeof(int32_t)));
+  w.tile_prefix = static_cast<int32_t*>(take((lists + 1) * sizeof(int32_t)));
+  w.cursors = static_cast<int32_t*>(take(lists * sizeof(int32_t)));
+  w.means = static_cast<__nv_bfloat16*>(take((size_t)r.slots * r.Hkv * kHeadDim * 2));
+  w.selected = static_cast<int32_t*>(take((size_t)r.hist * r.rows * sizeof(int32_t)));
+  w.row_list = static_cast<int32_t*>(take((size_t)r.hist * r.rows * sizeof(int32_t)));
+  w.partial_lse = static_cast<float*>(take((size_t)r.rows * r.NP * sizeof(float)));
+  w.partial_out = static_cast<float*>(take((size_t)r.rows * r.NP * kHeadDim * sizeof(float)));
+  w.total = off;
+  return w;
+}
+
+int tile_rows_of(int impl) { return impl == MOBA_ATTEND_MMA_SYNC ? kMmaTileRows : kTc5TileRows; }
+
+int attend_dispatch(const moba_problem_t* p, const Params& r, const void* q, const void* k, const void* v,
+                    const int32_t* cu, const int32_t* list_counts, const int32_t* list_offsets,
+                    const int32_t* tile_prefix, const int32_t* row_list, float* partial_out,
+                    float* partial_lse, int32_t* work_counter, int32_t* status, cudaStream_t st) {
+  const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(q);
+  const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(k);
+  const __nv_bfloat16* vb = static_cast<const __nv_bfloat16*>(v);
+  if (p->attend_impl == MOBA_ATTEND_MMA_SYNC)
+    return (int)launch_attend_mma(r, qb, kb, vb, cu, list_counts, list_offsets, tile_prefix, row_list,
+                                  partial_out, partial_lse, work_counter, st);
+  return (int)launch_attend_tc5(r, qb, kb, vb, cu, list_counts, list_offsets, tile_prefix, row_list,
+                                partial_out, partial_lse, work_counter, status, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+int moba_b200_abi_version(void) { return 1; }
+
+const char* moba_b200_strerror(int code) {
+  switch (code) {
+    case MOBA_OK: return "ok";
+    case MOBA_E_SHAPE: return "q, k, v, cu_seqlens or the integer arguments have an invalid shape or value";
+    case MOBA_E_UNSUPPORTED: return "configuration outside this build (bf16, head_dim 128, contiguous innermost dim)";
+    case MOBA_E_WORKSPACE: return "workspace is null or too small";
+    case MOBA_E_NULL: return "a required pointer is null";
+    case MOBA_E_TOPK: return "moba_topk must be in 1..64";
+    case MOBA_E_ALIGN: return "pointers and strides must be multiples of 16 bytes";
+    case MOBA_E_DEVICE: return "needs an sm_100 device and a driver that exports cuTensorMapEncodeTiled";
+    default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
+  }
+}
+
+int moba_problem_check(const moba_problem_t* p) { return check_problem(p); }
+
+int moba_problem_dims(const moba_problem_t* p, moba_dims_t* d) {
+  const int rc = check_problem(p);
+  if (rc != MOBA_OK) return rc;
+  if (d == nullptr) return MOBA_E_NULL;
+  const Params r = make_params(p);
+  d->chunks_per_seq = r.mc;
+  d->slots = r.slots;
+  d->hist = (p->topk - 1 < r.mc - 1) ? p->topk - 1 : r.mc - 1;
+  d->partials = r.NP;
+  d->rows = r.rows;
+  d->lists = r.lists;
+  return MOBA_OK;
+}
+
+int moba_attend_tile_rows(int impl) { return tile_rows_of(impl); }
+
+int moba_workspace_size(const moba_problem_t* p, size_t* bytes) {
+  const int rc = check_problem(p);
+  if (rc != MOBA_OK) return rc;
+  if (bytes == nullptr) return MOBA_E_NULL;
+  *bytes = carve(make_params(p), nullptr).total;
+  return MOBA_OK;
+}
+
+int moba_chunk_metadata(const moba_problem_t* p, const int32_t* cu, int32_t* cu_chunk, int32_t* chunk_end,
+                        int8_t* valid, void* stream) {
+  const int rc = check_problem(p);
+  if (rc != MOBA_OK) return rc;
+  if (!cu || !cu_chunk || !chunk_end || !valid) return MOBA_E_NULL;
+  return (int)launch_chunk_metadata(make_params(p), cu, cu_chunk, chunk_end, valid, (cudaStream_t)stream);
+}
+
+int moba_chunk_means(const moba_problem_t* p, const void* k, const int32_t* cu, void* means, void* stream) {
+  const int rc = check_problem(p);
+  if (rc != MOBA_OK) return rc;
+  if (!k || !cu || !means) return MOBA_E_NULL;
+  return (int)launch_chunk_means(make_params(p), static_cast<const __nv_bfloat16*>(k), cu,
+                                 static_cast<__nv_bfloat16*>(means), (cudaStream_t)stream);
+}
+
+int moba_gate_topk(const moba_problem_t* p, const void* q, const void* means, const int32_t* cu,
+                   int32_t* selected, int32_t* list_counts, void* stream) {
+  const int rc = check_problem(p);
+  if (rc != MOBA_OK) return rc;
+  if (!q || !means || !cu || !selected) return MOBA_E_NULL;
+  const Params r = make_params(p);
+  if (r.hist <= 0) return MOBA_OK;
+  return (int)launch_gate_topk(r, static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(means),
+                               cu, selected, list_counts, (cudaStream_t)stream);
+}
+
+int moba_compact_routes(const moba_problem_t* p, const int32_t* cu, const int32_t* selected,
+                        const int32_t* list_counts, int32_t* list_offsets, int32_t* tile_prefix,
+                        int32_t* cursors, int32_t* row_list, float* partial_lse, int32_t tile_rows,
+                        void* stream) {
+  const int rc = check_problem(p);
+  if (rc != MOBA_OK) return rc;
+  if (!cu || !selected || !list_counts || !list_offsets || !tile_prefix || !cursors || !row_list || !partial_lse)
+    return MOBA_E_NULL;
+  if (tile_rows <= 0) return MOBA_E_SHAPE;
+  const Params r = make_params(p);
+  if (r.hist <= 0) return MOBA_OK;
+  return (int)launch_compact(r, cu, selected, list_counts, list_offsets, tile_prefix, cursors, row_list,
+                             partial_lse, tile_rows, (cudaStream_t)stream);
+}
+
+int moba_attend(const moba_problem_t* p, const void* q, const void* k, const void* v, const int32_t* cu,
+                const int32_t* list_counts, const int32_t* list_offsets, const int32_t* tile_prefix,
+                const int32_t* row_list, float* partial_out, float* partial_lse, int32_t* work_counter,
+                void* stream) {
+  const int rc = check_problem(p);
+  if (rc != MOBA_OK) return rc;
+  if (!q || !k || !v || !cu || !partial_out || !partial_lse || !work_counter) return MOBA_E_NULL;
+  const Params r = make_params(p);
+  if (r.hist > 0 && (!list_counts || !list_offsets || !tile_prefix || !row_list)) return MOBA_E_NULL;
+  return attend_dispatch(p, r, q, k, v, cu, list_counts, list_offsets, tile_prefix, row_list, partial_out,
+                         partial_lse, work_counter, work_counter + 1, (cudaStream_t)stream);
+}
+
+int moba_merge(const moba_problem_t* p, const float* partial_out, const float* partial_lse,
+               const int32_t* status, void* out, float* lse_out, void* stream) {
+  const int rc = check_problem(p);
+  if (rc != MOBA_OK) return rc;
+  if (!partial_out || !partial_lse || !out) return MOBA_E_NULL;
+  return (int)launch_merge(make_params(p), partial_out, partial_lse, status, static_cast<__nv_bfloat16*>(out),
+                           lse_out, (cudaStream_t)stream);
+}
+
+int moba_forward(const moba_problem_t* p, const void* q, const void* k, const void* v, const int32_t* cu,
+                 void* out, float* lse_out, int32_t* selected_out, void* workspace, size_t workspace_bytes,
+                 void* stream) {
+  const int rc = check_problem(p);
+  if (rc != MOBA_OK) return rc;
+  if (!q || !k || !v || !cu || !out) return MOBA_E_NULL;
+  const uintptr_t ptrs[5] = {(uintptr_t)q, (uintptr_t)k, (uintptr_t)v, (uintptr_t)out, (uintptr_t)workspace};
+  for (int i = 0; i < 5; ++i)
+    if (ptrs[i] % 16 != 0) return MOBA_E_ALIGN;
+  const Params r = make_params(p);
+  if (workspace == nullptr) return MOBA_E_WORKSPACE;
+  const Workspace w = carve(r, workspace);
+  if (workspace_bytes < w.total) return MOBA_E_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaMemsetAsync(w.list_counts, 0, w.zero_bytes, st);
+  if (e != cudaSuccess) return (int)e;
+  const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(q);
+  const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(k);
+  if (r.hist > 0) {
+    int32_t* sel = selected_out ? selected_out : w.selected;
+    if ((e = launch_chunk_means(r, kb, cu, w.means, st)) != cudaSuccess) return (int)e;
+    if ((e = launch_gate_topk(r, qb, w.means, cu, sel, w.list_counts, st)) != cudaSuccess) return (int)e;
+    if ((e = launch_compact(r, cu, sel, w.list_counts, w.list_offsets, w.tile_prefix, w.cursors, w.row_list,
+                            w.partial_lse, tile_rows_of(p->attend_impl), st)) != cudaSuccess)
+      return (int)e;
+  }
+  const int arc = attend_dispatch(p, r, q, k, v, cu, w.list_counts, w.list_offsets, w.tile_prefix, w.row_list,
+                                  w.partial_out, w.partial_lse, w.work_counter, w.status, st);
+  if (arc != 0) return arc;
+  e = launch_merge(r, w.partial_out, w.partial_lse, w.status, static_cast<__nv_bfloat16*>(out), lse_out, st);
+  return (int)e;
+}
+
+int moba_workspace_size_host(const moba_problem_t* p, size_t* bytes) {
+  size_t core = 0;
+  const int rc = moba_workspace_size(p, &core);
+  if (rc != MOBA_OK) return rc;
+  const Params r = make_params(p);
+  size_t extra = align_up((size_t)r.T * r.Hq * kHeadDim * 2) * 2 +      // q, out
+                 align_up((size_t)r.T * r.Hkv * kHeadDim * 2) * 2 +     // k, v
+                 align_up((size_t)(r.B + 1) * 4) +                      // cu_seqlens
+                 align_up((size_t)r.rows * 4);                          // lse
+  *bytes = core + extra;
+  return MOBA_OK;
+}
+
+int moba_forward_host(const moba_problem_t* p, const void* q_host, const void* k_host, const void* v_host,
+                      const int32_t* cu_host, void* out_host, float* lse_out_host, int32_t* selected_out_host,
+                      void* workspace, size_t workspace_bytes, void* stream) {
+  size_t need = 0, core = 0;
+  int rc = moba_workspace_size_host(p, &need);
+  if (rc != MOBA_OK) return rc;
+  moba_workspace_size(p, &core);
+  if (!q_host || !k_host || !v_host || !cu_host || !out_host) return MOBA_E_NULL;
+  if (workspace == nullptr || workspace_bytes < need) return MOBA_E_WORKSPACE;
+  const Params r = make_params(p);
+  // host tensors are taken as contiguous [T, H, D]
+  if (r.sq_h != kHeadDim || r.sq_t != (int64_t)r.Hq * kHeadDim || r.sk_h != kHeadDim ||
+      r.sk_t != (int64_t)r.Hkv * kHeadDim || r.sv_h != kHeadDim || r.sv_t != (int64_t)r.Hkv * kHeadDim ||
+      r.so_h != kHeadDim || r.so_t != (int64_t)r.Hq * kHeadDim)
+    return MOBA_E_UNSUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+  char* base = static_cast<char*>(workspace) + core;
+  const size_t qbytes = (size_t)r.T * r.Hq * kHeadDim * 2, kbytes = (size_t)r.T * r.Hkv * kHeadDim * 2;
+  char* dq = base;               base += align_up(qbytes);
+  char* dout = base;             base += align_up(qbytes);
+  char* dk = base;               base += align_up(kbytes);
+  char* dv = base;               base += align_up(kbytes);
+  int32_t* dcu = (int32_t*)base; base += align_up((size_t)(r.B + 1) * 4);
+  float* dlse = (float*)base;
+  cudaError_t e;
+  if ((e = cudaMemcpyAsync(dq, q_host, qbytes, cudaMemcpyHostToDevice, st)) != cudaSuccess) return (int)e;
+  if ((e = cudaMemcpyAsync(dk, k_host, kbytes, cudaMemcpyHostToDevice, st)) != cudaSuccess) return (int)e;
+  if ((e = cudaMemcpyAsync(dv, v_host, kbytes, cudaMemcpyHostToDevice, st)) != cudaSuccess) return (int)e;
+  if ((e = cudaMemcpyAsync(dcu, cu_host, (size_t)(r.B + 1) * 4, cudaMemcpyHostToDevice, st)) != cudaSuccess)
+    return (int)e;
+  const Workspace w = carve(r, workspace);
+  rc = moba_forward(p, dq, dk, dv, dcu, dout, lse_out_host ? dlse : nullptr, nullptr, workspace, core, stream);
+  if (rc != MOBA_OK) return rc;
+  if ((e = cudaMemcpyAsync(out_host, dout, qbytes, cudaMemcpyDeviceToHost, st)) != cudaSuccess) return (int)e;
+  if (lse_out_host &&
+      (e = cudaMemcpyAsync(lse_out_host, dlse, (size_t)r.rows * 4, cudaMemcpyDeviceToHost, st)) != cudaSuccess)
+    return (int)e;
+  if (selected_out_host && r.hist > 0 &&
+      (e = cudaMemcpyAsync(selected_out_host, w.selected, (size_t)r.hist * r.rows * 4, cudaMemcpyDeviceToHost, st)) !=
+          cudaSuccess)
+    return (int)e;
+  return MOBA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,147 @@
+// Shared declarations of the MoBA forward kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "moba_b200.h"
+
+namespace moba {
+
+constexpr int kHeadDim = 128;            // the build is specialised for D = 128
+constexpr int kMeanLanes = 32;           // row accumulators of a chunk mean
+constexpr int kMaxTopk = 64;             // parallel.py:436
+
+// Launch-time view of a problem, passed to kernels by value.
+struct Params {
+  int64_t T;
+  int B, Hq, Hkv, G, D;
+  int max_seqlen, C, topk;
+  int mc, slots, hist, NP;               // NP = partial results per row
+  int64_t rows, lists;
+  int64_t sq_t, sq_h, sk_t, sk_h, sv_t, sv_h, so_t, so_h;
+};
+
+__host__ inline int cdiv_i(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
+
+__device__ __forceinline__ float bf16_lo(uint32_t x) { return __uint_as_float(x << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t x) { return __uint_as_float(x & 0xffff0000u); }
+
+// Chunk slot geometry (routing.py:565-579).
+struct Slot {
+  int start, end;        // token range [start, end)
+  bool historical;       // may be selected by later queries
+};
+__device__ __forceinline__ Slot slot_of(const int32_t* __restrict__ cu, int b, int j, int C) {
+  const int s0 = cu[b], s1 = cu[b + 1];
+  Slot s;
+  const long long st = (long long)s0 + (long long)j * C;
+  s.start = st < s1 ? (int)st : s1;
+  const long long en = (long long)s.start + C;
+  s.end = en < s1 ? (int)en : s1;
+  s.historical = s.end < s1;
+  return s;
+}
+
+// Work item of the dense stage.
+struct Item {
+  int valid;             // 0: nothing to do
+  int causal;            // 1: own chunk, rows are consecutive tokens of one head
+  int nrows;             // rows in this item (<= tile rows)
+  int row_start;         // routed: first index into row_list
+  int tok0;              // own: first query token
+  int head;              // own: query head
+  int kv_head;
+  int kv_tok0;           // first key token
+  int kv_len;            // keys to visit
+};
+
+// Decode work item `i`.  Routed items come first (list-major, tiles of
+// `tile_rows` rows), own-chunk items follow with the longest tiles first.
+__device__ __forceinline__ Item decode_item(const Params& p, int i, int n_routed, int tile_rows,
+                                            const int32_t* __restrict__ cu,
+                                            const int32_t* __restrict__ list_counts,
+                                            const int32_t* __restrict__ list_offsets,
+                                            const int32_t* __restrict__ tile_prefix) {
+  Item it;
+  it.valid = 0;
+  if (i < n_routed) {
+    int lo = 0, hi = (int)p.lists;           // last l with tile_prefix[l] <= i
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (tile_prefix[mid] <= i) lo = mid; else hi = mid;
+    }
+    const int l = lo;
+    const int tile = i - tile_prefix[l];
+    const int slot = l / p.Hkv;
+    const int b = slot / p.mc, j = slot - b * p.mc;
+    it.valid = 1;
+    it.causal = 0;
+    it.row_start = list_offsets[l] + tile * tile_rows;
+    const int left = list_counts[l] - tile * tile_rows;
+    it.nrows = left < tile_rows ? left : tile_rows;
+    it.kv_head = l - slot * p.Hkv;
+    it.kv_tok0 = cu[b] + j * p.C;
+    it.kv_len = p.C;
+    it.tok0 = 0;
+    it.head = 0;
+    return it;
+  }
+  const int tiles_per_chunk = (p.C + tile_rows - 1) / tile_rows;
+  const int per_tile = p.slots * p.Hq;
+  int idx = i - n_routed;
+  const int ti = tiles_per_chunk - 1 - idx / per_tile;
+  idx -= (idx / per_tile) * per_tile;
+  const int slot = idx / p.Hq;
+  const int h = idx - slot * p.Hq;
+  const int b = slot / p.mc, j = slot - b * p.mc;
+  const Slot s = slot_of(cu, b, j, p.C);
+  const int tok0 = s.start + ti * tile_rows;
+  if (ti < 0 || tok0 >= s.end) return it;
+  it.valid = 1;
+  it.causal = 1;
+  it.tok0 = tok0;
+  it.nrows = s.end - tok0 < tile_rows ? s.end - tok0 : tile_rows;
+  it.head = h;
+  it.kv_head = h / p.G;
+  it.kv_tok0 = s.start;
+  it.kv_len = tok0 + it.nrows - s.start;
+  it.row_start = 0;
+  return it;
+}
+
+__host__ __device__ inline int own_item_count(int slots, int Hq, int C, int tile_rows) {
+  return slots * Hq * ((C + tile_rows - 1) / tile_rows);
+}
+
+// ---- launchers implemented in the kernel files -----------------------------
+cudaError_t launch_chunk_metadata(const Params& p, const int32_t* cu, int32_t* cu_chunk,
+                                  int32_t* chunk_end, int8_t* valid, cudaStream_t st);
+cudaError_t launch_chunk_means(const Params& p, const __nv_bfloat16* k, const int32_t* cu,
+                               __nv_bfloat16* means, cudaStream_t st);
+cudaError_t launch_gate_topk(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* means,
+                             const int32_t* cu, int32_t* selected, int32_t* list_counts,
+                             cudaStream_t st);
+cudaError_t launch_compact(const Params& p, const int32_t* cu, const int32_t* selected,
+                           const int32_t* list_counts, int32_t* list_offsets, int32_t* tile_prefix,
+                           int32_t* cursors, int32_t* row_list, float* partial_lse, int tile_rows,
+                           cudaStream_t st);
+cudaError_t launch_merge(const Params& p, const float* partial_out, const float* partial_lse,
+                         const int32_t* status, __nv_bfloat16* out, float* lse_out, cudaStream_t st);
+
+constexpr int kMmaTileRows = 128;        // rows per work item, mma.sync kernel
+constexpr int kTc5TileRows = 256;        // rows per work item, tcgen05 kernel (two 128-row MMA tiles)
+
+cudaError_t launch_attend_mma(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* k,
+                              const __nv_bfloat16* v, const int32_t* cu, const int32_t* list_counts,
+                              const int32_t* list_offsets, const int32_t* tile_prefix,
+                              const int32_t* row_list, float* partial_out, float* partial_lse,
+                              int32_t* work_counter, cudaStream_t st);
+cudaError_t launch_attend_tc5(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* k,
+                              const __nv_bfloat16* v, const int32_t* cu, const int32_t* list_counts,
+                              const int32_t* list_offsets, const int32_t* tile_prefix,
+                              const int32_t* row_list, float* partial_out, float* partial_lse,
+                              int32_t* work_counter, int32_t* status, cudaStream_t st);
+
+}  // namespace moba

@@ -1,0 +1,263 @@
+// Gating stage of MoBA: chunk slot tables, mean-pooled keys, q.mean scores with
+// the causal chunk mask and a per-(token, head) top-k.
+//
+// Replaces, for the inference path of the reference,
+//   _dense_chunk_metadata_kernel            backends/_mthreads/ops/moba/routing.py:553-592
+//   _dense_chunk_mean_kernel                routing.py:690-737
+//   _chunk_topk_batched_streaming_kernel    routing.py:1056-1182
+//
+// The stage is bound by HBM traffic (K and Q are read once); the arithmetic
+// runs on CUDA cores in one fixed fp32 summation order so that the selection
+// is reproducible bit for bit by a CPU restatement:
+//   mean : row r of a chunk is added to accumulator r % 32 in increasing r, the
+//          32 accumulators are added in increasing index, the total is divided
+//          by C and rounded to bf16 (round to nearest even);
+//   score: bf16*bf16 products are exact in fp32; 16 lanes each add their 8
+//          products left to right, then a halving tree (lane l + lane l^8, ^4,
+//          ^2, ^1) combines the lanes.
+#include "common.cuh"
+
+namespace moba {
+
+// ---------------------------------------------------------------------------
+// slot tables
+// ---------------------------------------------------------------------------
+__global__ void chunk_metadata_kernel(Params p, const int32_t* __restrict__ cu,
+                                      int32_t* __restrict__ cu_chunk,
+                                      int32_t* __restrict__ chunk_end,
+                                      int8_t* __restrict__ valid) {
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s == 0) cu_chunk[p.slots] = cu[p.B];
+  if (s >= p.slots) return;
+  const int b = s / p.mc, j = s - b * p.mc;
+  const Slot sl = slot_of(cu, b, j, p.C);
+  cu_chunk[s] = sl.start;
+  chunk_end[s] = sl.historical ? sl.end : 0;
+  valid[s] = sl.historical ? 1 : 0;
+}
+
+cudaError_t launch_chunk_metadata(const Params& p, const int32_t* cu, int32_t* cu_chunk,
+                                  int32_t* chunk_end, int8_t* valid, cudaStream_t st) {
+  const int threads = 256;
+  chunk_metadata_kernel<<<cdiv_i(p.slots, threads), threads, 0, st>>>(p, cu, cu_chunk, chunk_end, valid);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// chunk means: one CTA per (slot, kv head), 32 row lanes x 16 dim lanes.
+// A warp covers two consecutive rows of one kv head with 16-byte loads.
+// ---------------------------------------------------------------------------
+constexpr int kMeanThreads = kMeanLanes * (kHeadDim / 8);   // 512
+
+__global__ void __launch_bounds__(kMeanThreads)
+chunk_mean_kernel(Params p, const __nv_bfloat16* __restrict__ k, const int32_t* __restrict__ cu,
+                  __nv_bfloat16* __restrict__ means) {
+  const int slot = blockIdx.x, hk = blockIdx.y;
+  const int b = slot / p.mc, j = slot - b * p.mc;
+  const Slot sl = slot_of(cu, b, j, p.C);
+  const int dl = threadIdx.x & 15;        // dims 8*dl .. 8*dl+7
+  const int rl = threadIdx.x >> 4;        // row lane 0..31
+  __nv_bfloat16* dst = means + ((int64_t)slot * p.Hkv + hk) * kHeadDim;
+
+  __shared__ float part[kMeanLanes][kHeadDim + 4];
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+
+  if (sl.historical) {                     // historical chunks are always full: C rows
+    const __nv_bfloat16* base = k + (int64_t)sl.start * p.sk_t + (int64_t)hk * p.sk_h + dl * 8;
+    int r = rl;
+    // four rows in flight per thread, accumulated in increasing r
+    for (; r + 3 * kMeanLanes < p.C; r += 4 * kMeanLanes) {
+      uint4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        x[u] = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)(r + u * kMeanLanes) * p.sk_t));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        acc[0] += bf16_lo(x[u].x); acc[1] += bf16_hi(x[u].x);
+        acc[2] += bf16_lo(x[u].y); acc[3] += bf16_hi(x[u].y);
+        acc[4] += bf16_lo(x[u].z); acc[5] += bf16_hi(x[u].z);
+        acc[6] += bf16_lo(x[u].w); acc[7] += bf16_hi(x[u].w);
+      }
+    }
+    for (; r < p.C; r += kMeanLanes) {
+      const uint4 x = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)r * p.sk_t));
+      acc[0] += bf16_lo(x.x); acc[1] += bf16_hi(x.x);
+      acc[2] += bf16_lo(x.y); acc[3] += bf16_hi(x.y);
+      acc[4] += bf16_lo(x.z); acc[5] += bf16_hi(x.z);
+      acc[6] += bf16_lo(x.w); acc[7] += bf16_hi(x.w);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) part[rl][dl * 8 + i] = acc[i];
+  __syncthreads();
+  if (threadIdx.x < kHeadDim) {
+    float tot = part[0][threadIdx.x];
+#pragma unroll
+    for (int a = 1; a < kMeanLanes; ++a) tot += part[a][threadIdx.x];
+    const float mean = sl.historical ? __fdiv_rn(tot, (float)p.C) : 0.f;
+    dst[threadIdx.x] = __float2bfloat16_rn(mean);
+  }
+}
+
+cudaError_t launch_chunk_means(const Params& p, const __nv_bfloat16* k, const int32_t* cu,
+                               __nv_bfloat16* means, cudaStream_t st) {
+  dim3 grid(p.slots, p.Hkv);
+  chunk_mean_kernel<<<grid, kMeanThreads, 0, st>>>(p, k, cu, means);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// scores + mask + top-k
+//   grid (token tiles of one sequence, kv head, sequence); 256 threads = 16 row
+//   groups of 16 lanes.  The CTA stages the bf16 means of its kv head for a
+//   tile of candidate chunks in shared memory; every row group then scores its
+//   rows against them and keeps the `hist` largest packed keys
+//   (order-preserving score bits << 32 | 0xFFFFFFFF - slot, routing.py:1151-1153)
+//   by repeated arg-max, which makes ties fall to the lower slot.
+// ---------------------------------------------------------------------------
+constexpr int kGateThreads = 256;
+constexpr int kGateGroups = kGateThreads / 16;
+constexpr int kGateRows = 128;            // (token, head) rows per CTA
+constexpr int kCandTile = 128;            // candidate chunks staged per pass
+
+__device__ __forceinline__ uint32_t float_key(float x) {      // routing.py:778-784
+  const uint32_t b = __float_as_uint(x);
+  return b ^ ((b & 0x80000000u) ? 0xFFFFFFFFu : 0x80000000u);
+}
+
+__global__ void __launch_bounds__(kGateThreads)
+gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__ q,
+                 const __nv_bfloat16* __restrict__ means, const int32_t* __restrict__ cu,
+                 int32_t* __restrict__ selected, int32_t* __restrict__ list_counts) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int hist = p.hist;
+  // layout: means tile | cand[groups][kCandTile] | wins[groups][hist] | best[rows][hist] | counts[mc]
+  uint4* means_s = reinterpret_cast<uint4*>(smem_raw);                              // kCandTile*16 uint4
+  unsigned long long* cand_s = reinterpret_cast<unsigned long long*>(means_s + kCandTile * 16);
+  unsigned long long* wins_s = cand_s + kGateGroups * kCandTile;
+  unsigned long long* best_s = wins_s + kGateGroups * hist;
+  int32_t* cnt_s = reinterpret_cast<int32_t*>(best_s + (size_t)kGateRows * hist);
+
+  const int b = blockIdx.z, hk = blockIdx.y;
+  const int s0 = cu[b], s1 = cu[b + 1];
+  const int tok_lo = s0 + blockIdx.x * tokens_per_cta;
+  if (tok_lo >= s1) return;
+  const int ntok = min(tokens_per_cta, s1 - tok_lo);
+  const int nrows = ntok * p.G;
+  const int grp = threadIdx.x >> 4, lane = threadIdx.x & 15;
+  const unsigned gmask = 0xFFFFu << (threadIdx.x & 16);       // the 16 lanes of this group
+
+  for (int i = threadIdx.x; i < p.mc; i += kGateThreads) cnt_s[i] = 0;
+  for (int i = threadIdx.x; i < kGateRows * hist; i += kGateThreads) best_s[i] = 0ull;
+  // candidates of the last token of the tile bound the chunks to stage
+  const int max_cand = (tok_lo + ntok - 1 - s0) / p.C;
+  const int slot0 = b * p.mc;
+  unsigned long long* cand = cand_s + grp * kCandTile;
+  unsigned long long* wins = wins_s + grp * hist;
+
+  for (int c0 = 0; c0 < max_cand; c0 += kCandTile) {
+    const int ct = min(kCandTile, max_cand - c0);
+    __syncthreads();                                          // previous tile fully consumed
+    for (int i = threadIdx.x; i < ct * 16; i += kGateThreads) {
+      const int c = i >> 4, part = i & 15;
+      means_s[i] = __ldg(reinterpret_cast<const uint4*>(
+          means + ((int64_t)(slot0 + c0 + c) * p.Hkv + hk) * kHeadDim + part * 8));
+    }
+    __syncthreads();
+    for (int row = grp; row < nrows; row += kGateGroups) {    // row = token-major, head-minor
+      const int tl = row / p.G, hl = row - tl * p.G;
+      const int tok = tok_lo + tl;
+      const int cend = min(ct, (tok - s0) / p.C - c0);        // this row's candidates in the tile
+      if (cend <= 0) continue;                                // uniform over the 16 lanes
+      float qf[8];
+      {
+        const uint4 x = __ldg(reinterpret_cast<const uint4*>(
+            q + (int64_t)tok * p.sq_t + (int64_t)(hk * p.G + hl) * p.sq_h + lane * 8));
+        qf[0] = bf16_lo(x.x); qf[1] = bf16_hi(x.x); qf[2] = bf16_lo(x.y); qf[3] = bf16_hi(x.y);
+        qf[4] = bf16_lo(x.z); qf[5] = bf16_hi(x.z); qf[6] = bf16_lo(x.w); qf[7] = bf16_hi(x.w);
+      }
+      for (int c = 0; c < cend; ++c) {
+        const uint4 m = means_s[c * 16 + lane];
+        float s = qf[0] * bf16_lo(m.x);
+        s = __fmaf_rn(qf[1], bf16_hi(m.x), s);
+        s = __fmaf_rn(qf[2], bf16_lo(m.y), s);
+        s = __fmaf_rn(qf[3], bf16_hi(m.y), s);
+        s = __fmaf_rn(qf[4], bf16_lo(m.z), s);
+        s = __fmaf_rn(qf[5], bf16_hi(m.z), s);
+        s = __fmaf_rn(qf[6], bf16_lo(m.w), s);
+        s = __fmaf_rn(qf[7], bf16_hi(m.w), s);
+        s = __fadd_rn(s, __shfl_xor_sync(gmask, s, 8));
+        s = __fadd_rn(s, __shfl_xor_sync(gmask, s, 4));
+        s = __fadd_rn(s, __shfl_xor_sync(gmask, s, 2));
+        s = __fadd_rn(s, __shfl_xor_sync(gmask, s, 1));
+        if (lane == (c & 15))
+          cand[c] = ((unsigned long long)float_key(s) << 32) |
+                    (unsigned long long)(0xFFFFFFFFu - (uint32_t)(slot0 + c0 + c));
+      }
+      unsigned long long* best = best_s + (size_t)row * hist;
+      for (int i = lane; i < hist; i += 16) wins[i] = 0ull;
+      __syncwarp(gmask);
+      // the `hist` largest of best[0..hist) U cand[0..cend), by repeated arg-max
+      for (int r = 0; r < hist; ++r) {
+        unsigned long long mine = 0ull;
+        int mine_i = -1;
+        for (int i = lane; i < hist + cend; i += 16) {
+          const unsigned long long kk = i < hist ? best[i] : cand[i - hist];
+          if (kk > mine) { mine = kk; mine_i = i; }
+        }
+        unsigned long long top = mine;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+          const unsigned long long other = __shfl_xor_sync(gmask, top, o);
+          top = other > top ? other : top;
+        }
+        if (top == 0ull) break;                               // fewer than hist candidates
+        if (mine == top) {                                    // keys are unique: exactly one owner
+          if (mine_i < hist) best[mine_i] = 0ull; else cand[mine_i - hist] = 0ull;
+          wins[r] = top;
+        }
+        __syncwarp(gmask);
+      }
+      __syncwarp(gmask);
+      for (int i = lane; i < hist; i += 16) best[i] = wins[i];
+      __syncwarp(gmask);
+    }
+  }
+  __syncthreads();
+  // selected[r][head][tok]: `ntok` consecutive ints per (rank, head)
+  for (int i = threadIdx.x; i < hist * nrows; i += kGateThreads) {
+    const int r = i / nrows, rem = i - r * nrows;
+    const int hl = rem / ntok, tl = rem - hl * ntok;
+    const unsigned long long w = best_s[(size_t)(tl * p.G + hl) * hist + r];
+    const int slot = w ? (int)(0xFFFFFFFFu - (uint32_t)(w & 0xFFFFFFFFull)) : -1;
+    selected[((int64_t)r * p.Hq + (hk * p.G + hl)) * p.T + tok_lo + tl] = slot;
+    if (slot >= 0) atomicAdd(&cnt_s[slot - slot0], 1);
+  }
+  __syncthreads();
+  if (list_counts != nullptr)
+    for (int c = threadIdx.x; c < p.mc; c += kGateThreads)
+      if (cnt_s[c] > 0) atomicAdd(&list_counts[(int64_t)(slot0 + c) * p.Hkv + hk], cnt_s[c]);
+}
+
+static size_t gate_smem_bytes(const Params& p) {
+  return (size_t)kCandTile * 16 * sizeof(uint4) + (size_t)kGateGroups * kCandTile * 8 +
+         (size_t)kGateGroups * p.hist * 8 + (size_t)kGateRows * p.hist * 8 + (size_t)p.mc * 4;
+}
+
+cudaError_t launch_gate_topk(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* means,
+                             const int32_t* cu, int32_t* selected, int32_t* list_counts,
+                             cudaStream_t st) {
+  int tokens_per_cta = kGateRows / p.G;
+  if (tokens_per_cta < 1) tokens_per_cta = 1;
+  const size_t smem = gate_smem_bytes(p);
+  if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
+  cudaError_t e = cudaFuncSetAttribute(gate_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  dim3 grid(cdiv_i(p.max_seqlen, tokens_per_cta), p.Hkv, p.B);
+  gate_topk_kernel<<<grid, kGateThreads, smem, st>>>(p, tokens_per_cta, q, means, cu, selected, list_counts);
+  return cudaGetLastError();
+}
+
+}  // namespace moba

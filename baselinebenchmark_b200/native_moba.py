@@ -1,0 +1,11 @@
+"""Counterpart of backends/_mthreads/ops/moba/native_moba.py for harness code
+that asks the package whether its native sparse path is eligible
+(benchmarks/moba_compare.py:130, :203 call ``native_moba._supported(q)``)."""
+import torch
+
+
+def _supported(q: torch.Tensor) -> bool:
+    """True where the tcgen05 dense stage runs: CUDA bf16, head_dim 128, sm_100."""
+    if q.device.type != "cuda" or q.dtype != torch.bfloat16 or q.shape[-1] != 128:
+        return False
+    return torch.cuda.get_device_capability(q.device)[0] == 10

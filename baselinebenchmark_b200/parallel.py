@@ -1,0 +1,153 @@
+"""Host-side mirror of the reference operator
+``parallel_moba(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)``
+(backends/_mthreads/ops/moba/parallel.py:377-457) on top of the C ABI.
+
+Same seven positional arguments, same validation order and exception types as
+parallel.py:410-443, same caller contract for the inference path
+(parallel.py:270-274): ``cu_seqlens`` starts at 0, increases strictly and ends
+at ``q.shape[0]``; ``max_seqlen`` is at least the longest sequence; neither is
+read back to the host.  torch is used for device memory and the current stream
+only; all computation happens inside libmoba_b200.so and there is no fallback:
+an unsupported configuration raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+__all__ = ["parallel_moba", "moba_attn_varlen", "moba_forward", "make_problem", "workspace_bytes"]
+
+_workspaces: dict = {}
+
+
+def _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk) -> None:
+    """parallel.py:410-446, message for message where it matters to callers."""
+    if q.ndim != 3 or k.ndim != 3 or v.ndim != 3:
+        raise ValueError("q, k, and v must have shape [tokens, heads, head_dim]")
+    if k.shape != v.shape:
+        raise ValueError(f"k and v must have identical shapes, got {k.shape} and {v.shape}")
+    if q.shape[0] != k.shape[0] or q.shape[2] != k.shape[2]:
+        raise ValueError(
+            f"q and k/v must have the same token count and head dimension, got q={q.shape}, k={k.shape}")
+    if q.device != k.device or q.device != v.device or q.device.type != "cuda":
+        raise ValueError("q, k, and v must be accelerator tensors on the same device")
+    if q.dtype != k.dtype or q.dtype != v.dtype:
+        raise TypeError("q, k, and v must have the same dtype")
+    if q.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError(f"only float16 and bfloat16 are supported, got {q.dtype}")
+    if cu_seqlens.ndim != 1 or cu_seqlens.numel() < 2:
+        raise ValueError("cu_seqlens must be a one-dimensional tensor of length >= 2")
+    if cu_seqlens.device != q.device or cu_seqlens.dtype != torch.int32:
+        raise TypeError("cu_seqlens must be an int32 tensor on the q device")
+    if not isinstance(max_seqlen, int) or max_seqlen <= 0:
+        raise ValueError(f"max_seqlen must be a positive int, got {max_seqlen}")
+    if not isinstance(moba_chunk_size, int) or moba_chunk_size <= 0:
+        raise ValueError(f"moba_chunk_size must be a positive int, got {moba_chunk_size}")
+    if not isinstance(moba_topk, int) or moba_topk < 1:
+        raise ValueError(f"moba_topk must be a positive int, got {moba_topk}")
+    if moba_topk > 64:
+        raise ValueError(f"moba_topk must be <= 64 to match FlashMoBA, got {moba_topk}")
+    if q.shape[0] == 0 or q.shape[1] == 0 or k.shape[1] == 0 or q.shape[2] == 0:
+        raise ValueError("q, k, and v dimensions must be non-zero")
+    if q.shape[1] % k.shape[1] != 0:
+        raise ValueError(f"q heads ({q.shape[1]}) must be divisible by kv heads ({k.shape[1]})")
+    if q.shape[2] > 256:
+        raise ValueError(f"head_dim must be <= 256 to match FlashMoBA, got {q.shape[2]}")
+    # limits of this build (no fallback by design)
+    if q.dtype != torch.bfloat16 or q.shape[2] != 128:
+        raise NotImplementedError("this build supports bfloat16 with head_dim 128 only")
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if t.stride(2) != 1:
+            raise NotImplementedError(f"{name} must be contiguous in its last dimension")
+
+
+def make_problem(q, k, v, out, cu_seqlens, max_seqlen, chunk, topk, attend_impl=_lib.ATTEND_TCGEN05):
+    return _lib.Problem(
+        total_tokens=q.shape[0], batch=cu_seqlens.numel() - 1, num_q_heads=q.shape[1],
+        num_kv_heads=k.shape[1], head_dim=q.shape[2], max_seqlen=max_seqlen, chunk_size=chunk,
+        topk=topk, attend_impl=attend_impl,
+        q_stride_token=q.stride(0), q_stride_head=q.stride(1),
+        k_stride_token=k.stride(0), k_stride_head=k.stride(1),
+        v_stride_token=v.stride(0), v_stride_head=v.stride(1),
+        o_stride_token=out.stride(0), o_stride_head=out.stride(1))
+
+
+def workspace_bytes(problem) -> int:
+    size = C.c_size_t(0)
+    _lib.check(_lib.lib().moba_workspace_size(C.byref(problem), C.byref(size)))
+    return int(size.value)
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """One grow-only scratch buffer per device, reused stream-ordered across calls."""
+    ws = _workspaces.get(device)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _workspaces[device] = ws
+    return ws
+
+
+def moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, *,
+                 return_lse: bool = False, return_selected: bool = False,
+                 attend_impl: int = _lib.ATTEND_TCGEN05, workspace: Optional[torch.Tensor] = None
+                 ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """Runs the operator and optionally returns the final LSE [Hq, T] (fp32) and
+    the routing decision selected[hist, Hq, T] (int32, -1 padded)."""
+    _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)
+    out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    prob = make_problem(q, k, v, out, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, attend_impl)
+    dims = _lib.Dims()
+    _lib.check(_lib.lib().moba_problem_dims(C.byref(prob), C.byref(dims)))
+    need = workspace_bytes(prob)
+    ws = workspace if workspace is not None else _workspace(q.device, need)
+    if ws.numel() * ws.element_size() < need:
+        raise ValueError(f"workspace too small: {ws.numel() * ws.element_size()} < {need} bytes")
+    lse = torch.empty((q.shape[1], q.shape[0]), dtype=torch.float32, device=q.device) if return_lse else None
+    sel = None
+    if return_selected:
+        sel = torch.empty((max(dims.hist, 0), q.shape[1], q.shape[0]), dtype=torch.int32, device=q.device)
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+        rc = _lib.lib().moba_forward(
+            C.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(),
+            lse.data_ptr() if lse is not None else None,
+            sel.data_ptr() if sel is not None and sel.numel() else None,
+            ws.data_ptr(), ws.numel() * ws.element_size(), stream)
+    _lib.check(rc)
+    return out, lse, sel
+
+
+def parallel_moba(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor,
+                  max_seqlen: int, moba_chunk_size: int, moba_topk: int) -> torch.Tensor:
+    """Causal variable-length MoBA forward, signature of parallel.py:377-385.
+
+    Only the inference path exists here: like the reference it is taken when
+    autograd is off (parallel.py:448); with autograd on this raises instead of
+    silently returning a tensor without a graph.
+    """
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        raise NotImplementedError("the B200 build implements the inference forward only; "
+                                  "call under torch.no_grad() / torch.inference_mode()")
+    return moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)[0]
+
+
+@torch.library.custom_op("moba_b200::moba_attn_varlen", mutates_args=(), device_types="cuda")
+def _moba_attn_varlen_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor,
+                         max_seqlen: int, moba_chunk_size: int, moba_topk: int) -> torch.Tensor:
+    return moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)[0]
+
+
+@_moba_attn_varlen_op.register_fake
+def _(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk):
+    return torch.empty_like(q)
+
+
+def moba_attn_varlen(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk):
+    """The operator under the name the benchmark contract uses; a registered
+    torch custom op (``torch.ops.moba_b200.moba_attn_varlen``)."""
+    _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)
+    return _moba_attn_varlen_op(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)

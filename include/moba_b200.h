@@ -1,0 +1,173 @@
+/*
+ * moba_b200 -- C ABI of the B200 (sm_100a) MoBA causal-prefill forward.
+ *
+ * Drop-in boundary for the operator the reference exposes as
+ *   parallel_moba(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)
+ *   (backends/_mthreads/ops/moba/parallel.py:377-457, inference body :253-374).
+ *
+ * Conventions
+ *   - plain pointers and sizes only; every device pointer must belong to the
+ *     CUDA device that is current on the calling thread;
+ *   - every entry point is stream ordered on `stream` (a cudaStream_t passed as
+ *     void*), performs no device-to-host read and no allocation, so a caller
+ *     may capture it in a CUDA graph, exactly like the reference path
+ *     (parallel.py:262-275);
+ *   - return value: 0 success, < 0 invalid argument (MOBA_E_*), > 0 a
+ *     cudaError_t raised by a launch or a copy.  Nothing throws or aborts;
+ *   - tensors are bf16, head_dim 128, innermost dimension contiguous; token and
+ *     head strides are given in elements (the reference kernels also take
+ *     strides, attention.py:431-439).  Anything else returns
+ *     MOBA_E_UNSUPPORTED: there is no fallback path.
+ */
+#ifndef MOBA_B200_H_
+#define MOBA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  MOBA_OK = 0,
+  MOBA_E_SHAPE = -1,        /* parallel.py:410-443 ValueError cases              */
+  MOBA_E_UNSUPPORTED = -2,  /* dtype / head_dim / stride outside the build       */
+  MOBA_E_WORKSPACE = -3,    /* workspace pointer null or too small               */
+  MOBA_E_NULL = -4,         /* a required pointer is null                        */
+  MOBA_E_TOPK = -5,         /* moba_topk outside 1..64 (parallel.py:434-437)     */
+  MOBA_E_ALIGN = -6,        /* base pointer or stride not 16-byte aligned        */
+  MOBA_E_DEVICE = -7        /* not an sm_100 device, or driver entry point missing */
+};
+
+/* Which implementation of the dense stage moba_attend/moba_forward run. */
+enum {
+  MOBA_ATTEND_TCGEN05 = 0,  /* tcgen05.mma + TMEM accumulators + TMA K/V tiles   */
+  MOBA_ATTEND_MMA_SYNC = 1  /* legacy mma.sync tensor path, kept as cross-check  */
+};
+
+/* Problem description.  Mirrors the arguments of parallel_moba
+ * (parallel.py:377-385) plus the strides its kernels receive. */
+typedef struct moba_problem {
+  int64_t total_tokens;     /* T = q.shape[0] = cu_seqlens[batch]                */
+  int32_t batch;            /* B = len(cu_seqlens) - 1                           */
+  int32_t num_q_heads;      /* Hq                                                */
+  int32_t num_kv_heads;     /* Hkv, Hq % Hkv == 0                                */
+  int32_t head_dim;         /* D (128)                                           */
+  int32_t max_seqlen;       /* >= the longest sequence                           */
+  int32_t chunk_size;       /* moba_chunk_size                                   */
+  int32_t topk;             /* moba_topk, counts the query's own chunk           */
+  int32_t attend_impl;      /* MOBA_ATTEND_*                                     */
+  int64_t q_stride_token, q_stride_head;   /* elements                           */
+  int64_t k_stride_token, k_stride_head;
+  int64_t v_stride_token, v_stride_head;
+  int64_t o_stride_token, o_stride_head;
+} moba_problem_t;
+
+/* Derived sizes: mc = ceil(max_seqlen / chunk), slots = B*mc,
+ * hist = min(topk-1, mc-1)  (parallel.py:303, routing.py:604-605). */
+typedef struct moba_dims {
+  int32_t chunks_per_seq;   /* mc                                                */
+  int32_t slots;            /* B * mc                                            */
+  int32_t hist;             /* historical chunks selected per query, may be <= 0 */
+  int32_t partials;         /* max(hist,0) + 1 partial results per (token, head) */
+  int64_t rows;             /* T * Hq                                            */
+  int64_t lists;            /* slots * Hkv routed query lists                    */
+} moba_dims_t;
+
+int moba_b200_abi_version(void);
+const char* moba_b200_strerror(int code);
+
+/* Validation of parallel.py:410-443 without touching the device. */
+int moba_problem_check(const moba_problem_t* p);
+int moba_problem_dims(const moba_problem_t* p, moba_dims_t* dims);
+
+/* Bytes of caller-owned scratch that moba_forward needs for `p`.  Replaces the
+ * per-call torch allocations of parallel.py:283-374 (table of buffers:
+ * routing.py:1653-1658, attention.py:418-419, :727-728). */
+int moba_workspace_size(const moba_problem_t* p, size_t* bytes);
+
+/* The whole operator: replaces _moba_attn_varlen_inference (parallel.py:253-374).
+ *   q [T,Hq,D], k,v [T,Hkv,D], out [T,Hq,D] bf16 on device; cu_seqlens int32[B+1] on device.
+ *   lse_out       optional fp32 [Hq,T]   (natural log, layout of attention.py:419)
+ *   selected_out  optional int32 [hist,Hq,T] (layout of routing.py:1221-1226);
+ *                 when null the selection lives in the workspace only. */
+int moba_forward(const moba_problem_t* p, const void* q, const void* k, const void* v,
+                 const int32_t* cu_seqlens, void* out, float* lse_out, int32_t* selected_out,
+                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* Same call with HOST buffers (pinned memory recommended): copies q, k, v and
+ * cu_seqlens to staging buffers inside `workspace`, runs moba_forward, copies
+ * `out` (and lse_out / selected_out when given) back, all on `stream`.  The
+ * caller synchronises the stream.  Use moba_workspace_size_host for sizing. */
+int moba_workspace_size_host(const moba_problem_t* p, size_t* bytes);
+int moba_forward_host(const moba_problem_t* p, const void* q_host, const void* k_host,
+                      const void* v_host, const int32_t* cu_seqlens_host, void* out_host,
+                      float* lse_out_host, int32_t* selected_out_host,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- staged entry points (unit tests, context-parallel driver) ------------ */
+
+/* Chunk slot tables: replaces _build_dense_chunk_metadata_triton
+ * (routing.py:595-632).  cu_chunk int32[slots+1], chunk_end int32[slots],
+ * valid_hist int8[slots]. */
+int moba_chunk_metadata(const moba_problem_t* p, const int32_t* cu_seqlens, int32_t* cu_chunk,
+                        int32_t* chunk_end, int8_t* valid_hist, void* stream);
+
+/* Mean-pooled keys: replaces _compute_dense_chunk_means_triton
+ * (routing.py:740-775).  means bf16 [slots,Hkv,D], zeros for slots that are
+ * not historical. */
+int moba_chunk_means(const moba_problem_t* p, const void* k, const int32_t* cu_seqlens,
+                     void* means, void* stream);
+
+/* Scores + causal chunk mask + top-k: replaces
+ * _compute_selected_chunks_batched_streaming_triton (routing.py:1185-1262).
+ * selected int32 [hist,Hq,T]; list_counts int32[lists] (optional) receives the
+ * number of (token, head) rows routed to every (slot, kv head) list and must be
+ * zero on entry. */
+int moba_gate_topk(const moba_problem_t* p, const void* q, const void* means,
+                   const int32_t* cu_seqlens, int32_t* selected, int32_t* list_counts,
+                   void* stream);
+
+/* Grouping of the routed rows: replaces _build_sparse_routes_device_triton
+ * (routing.py:1642-1718), grouped by (slot, kv head) instead of (slot, q head)
+ * so the query heads of a GQA group share one K/V stream.
+ *   list_offsets  int32[lists+1]  exclusive prefix of list_counts
+ *   tile_prefix   int32[lists+1]  exclusive prefix of ceil(count / tile_rows)
+ *   row_list      int32[hist*T*Hq] entry ids  (t*Hq + h) * partials + rank + 1
+ *   partial_lse   fp32 [T*Hq, partials]; entries of ranks that selected nothing
+ *                 are set to -inf here
+ *   cursors       int32[lists] scratch */
+int moba_compact_routes(const moba_problem_t* p, const int32_t* cu_seqlens,
+                        const int32_t* selected, const int32_t* list_counts,
+                        int32_t* list_offsets, int32_t* tile_prefix, int32_t* cursors,
+                        int32_t* row_list, float* partial_lse, int32_t tile_rows, void* stream);
+
+/* Dense stage: own-chunk causal attention (replaces _varlen_attn_fwd_kernel,
+ * attention.py:53-160) and the routed historical-chunk attention (replaces
+ * native_moba.routed / _routed_gqa_attn_fwd_kernel, native_moba.py:120-135,
+ * attention.py:610-707) in one persistent launch.  Writes normalised fp32
+ * partial outputs [T*Hq, partials, D] and their natural-log LSE.
+ *   work_counter int32[2] must be zero on entry: [0] is the item counter, [1]
+ *   receives a non-zero status if a bounded device-side wait gave up. */
+int moba_attend(const moba_problem_t* p, const void* q, const void* k, const void* v,
+                const int32_t* cu_seqlens, const int32_t* list_counts,
+                const int32_t* list_offsets, const int32_t* tile_prefix,
+                const int32_t* row_list, float* partial_out, float* partial_lse,
+                int32_t* work_counter, void* stream);
+
+/* LSE-weighted combine: replaces _fused_merge_softmax_triton
+ * (attention.py:892-945), all partials of a row in one pass, fp32 throughout,
+ * one rounding to bf16.  `status` (optional) is work_counter + 1 of moba_attend:
+ * when it is non-zero the output is filled with NaN instead of partial data. */
+int moba_merge(const moba_problem_t* p, const float* partial_out, const float* partial_lse,
+               const int32_t* status, void* out, float* lse_out, void* stream);
+
+/* Rows per routed work item that the selected attend implementation wants
+ * (the tile_rows argument of moba_compact_routes). */
+int moba_attend_tile_rows(int attend_impl);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOBA_B200_H_ */

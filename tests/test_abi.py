@@ -1,0 +1,139 @@
+"""CPU: the C-ABI library builds, loads and exports every symbol that
+include/moba_b200.h declares; argument validation follows parallel.py:410-443.
+No compute entry point is called here."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+from baselinebenchmark_b200 import _lib, build, parallel
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build()
+    return _lib.lib()
+
+
+def _problem(**kw):
+    base = dict(total_tokens=4096, batch=1, num_q_heads=8, num_kv_heads=8, head_dim=128, max_seqlen=4096,
+                chunk_size=512, topk=3, attend_impl=0, q_stride_token=1024, q_stride_head=128,
+                k_stride_token=1024, k_stride_head=128, v_stride_token=1024, v_stride_head=128,
+                o_stride_token=1024, o_stride_head=128)
+    base.update(kw)
+    return _lib.Problem(**base)
+
+
+def test_header_symbols_are_exported(lib):
+    header = (ROOT / "include" / "moba_b200.h").read_text()
+    declared = set(re.findall(r"^(?:int|const char\*)\s+(moba_\w+)\s*\(", header, flags=re.M))
+    assert declared == set(_lib.SYMBOLS)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.moba_b200_abi_version() == 1
+
+
+def test_problem_check_codes(lib):
+    ok = _problem()
+    assert lib.moba_problem_check(C.byref(ok)) == 0
+    assert lib.moba_problem_check(C.byref(_problem(num_q_heads=6, num_kv_heads=4))) == -1   # not divisible
+    assert lib.moba_problem_check(C.byref(_problem(topk=0))) == -5
+    assert lib.moba_problem_check(C.byref(_problem(topk=65))) == -5
+    assert lib.moba_problem_check(C.byref(_problem(head_dim=64))) == -2                     # outside the build
+    assert lib.moba_problem_check(C.byref(_problem(head_dim=512))) == -1                    # parallel.py:445
+    assert lib.moba_problem_check(C.byref(_problem(max_seqlen=0))) == -1
+    assert lib.moba_problem_check(C.byref(_problem(q_stride_head=132))) == -6
+    assert lib.moba_problem_check(None) == -4
+    assert b"topk" in lib.moba_b200_strerror(-5)
+
+
+def test_dims_follow_reference_formulas(lib):
+    d = _lib.Dims()
+    assert lib.moba_problem_dims(C.byref(_problem()), C.byref(d)) == 0
+    assert (d.chunks_per_seq, d.slots, d.hist, d.partials, d.rows, d.lists) == (8, 8, 2, 3, 4096 * 8, 64)
+    assert lib.moba_problem_dims(C.byref(_problem(topk=1)), C.byref(d)) == 0
+    assert (d.hist, d.partials) == (0, 1)
+    assert lib.moba_problem_dims(C.byref(_problem(max_seqlen=300, topk=64)), C.byref(d)) == 0
+    assert (d.chunks_per_seq, d.hist) == (1, 0)                                             # parallel.py:303
+
+
+def test_workspace_size_and_null_handling(lib):
+    size = C.c_size_t(0)
+    assert lib.moba_workspace_size(C.byref(_problem()), C.byref(size)) == 0
+    assert size.value > 4096 * 8 * 3 * 128 * 4
+    assert lib.moba_workspace_size(C.byref(_problem()), None) == -4
+    # null tensors are rejected before anything touches a device
+    assert lib.moba_forward(C.byref(_problem()), None, None, None, None, None, None, None, None, 0, None) == -4
+    assert lib.moba_attend_tile_rows(_lib.ATTEND_TCGEN05) == 256
+    assert lib.moba_attend_tile_rows(_lib.ATTEND_MMA_SYNC) == 128
+
+
+def _cpu_args(t=64, hq=4, hkv=2, d=128, dtype=torch.bfloat16):
+    q = torch.zeros(t, hq, d, dtype=dtype)
+    k = torch.zeros(t, hkv, d, dtype=dtype)
+    return q, k, k.clone(), torch.tensor([0, t], dtype=torch.int32)
+
+
+def test_host_validation_mirrors_reference():
+    q, k, v, cu = _cpu_args()
+    with pytest.raises(ValueError, match="accelerator tensors"):
+        parallel.parallel_moba(q, k, v, cu, 64, 32, 2)          # CPU tensors, parallel.py:416-417
+    with pytest.raises(ValueError, match="shape \\[tokens, heads, head_dim\\]"):
+        parallel.parallel_moba(q[0], k, v, cu, 64, 32, 2)
+    with pytest.raises(ValueError, match="identical shapes"):
+        parallel.parallel_moba(q, k, v[:, :1], cu, 64, 32, 2)
+    with pytest.raises(ValueError, match="same token count"):
+        parallel.parallel_moba(q[:32], k, v, cu, 64, 32, 2)
+
+
+def test_host_validation_value_checks(monkeypatch):
+    """Checks that come after the device check, exercised on fake 'cuda' metadata."""
+    q, k, v, cu = _cpu_args()
+
+    class Dev:
+        type = "cuda"
+
+        def __eq__(self, other):
+            return True
+
+        def __ne__(self, other):
+            return False
+
+    class T:
+        def __init__(self, t):
+            self._t = t
+            self.device = Dev()
+
+        def __getattr__(self, name):
+            return getattr(self._t, name)
+
+    fq, fk, fv, fcu = T(q), T(k), T(v), T(cu)
+    with pytest.raises(TypeError, match="same dtype"):
+        parallel._validate(fq, T(k.half()), fv, fcu, 64, 32, 2)
+    with pytest.raises(TypeError, match="only float16 and bfloat16"):
+        parallel._validate(T(q.float()), T(k.float()), T(v.float()), fcu, 64, 32, 2)
+    with pytest.raises(TypeError, match="int32"):
+        parallel._validate(fq, fk, fv, T(cu.long()), 64, 32, 2)
+    with pytest.raises(ValueError, match="max_seqlen"):
+        parallel._validate(fq, fk, fv, fcu, 0, 32, 2)
+    with pytest.raises(ValueError, match="moba_chunk_size"):
+        parallel._validate(fq, fk, fv, fcu, 64, 0, 2)
+    with pytest.raises(ValueError, match="moba_topk must be a positive int"):
+        parallel._validate(fq, fk, fv, fcu, 64, 32, 0)
+    with pytest.raises(ValueError, match="<= 64"):
+        parallel._validate(fq, fk, fv, fcu, 64, 32, 65)
+    with pytest.raises(ValueError, match="divisible"):
+        parallel._validate(T(q[:, :3]), fk, fv, fcu, 64, 32, 2)
+    with pytest.raises(NotImplementedError):
+        parallel._validate(T(q.half()), T(k.half()), T(v.half()), fcu, 64, 32, 2)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "libmoba_b200.so")
+    with pytest.raises(ImportError, match="no fallback"):
+        _lib.lib()
