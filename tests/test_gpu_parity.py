@@ -1,0 +1,320 @@
+"""GPU parity tests: every stage of the CUDA path, called through the C ABI,
+against the CPU oracle on the same seeded inputs.
+
+Routing (slot tables, chunk means, selected chunks) must be bit-exact.
+Outputs must be within max-abs 2e-2 and mean-abs 2e-3 of the fp32 evaluation of
+the same selection (BASELINE.json north_star); the reference's own limits are
+max < 0.04, mean < 4e-4 against float64 (test_moba_topk.py:117-118)."""
+import glob
+import zlib
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from baselinebenchmark_b200 import _lib, parallel
+from oracle import moba_oracle as O
+from tests import gpu_util as G
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS, MEAN_ABS = 2e-2, 2e-3
+IMPLS = [pytest.param(_lib.ATTEND_TCGEN05, id="tcgen05"), pytest.param(_lib.ATTEND_MMA_SYNC, id="mma_sync")]
+GOLDEN = sorted(glob.glob(str(Path(__file__).parent / "golden" / "routing_*.npz")))
+
+# (name, seq_lens, Hq, Hkv, chunk, topk, max_seqlen or None)
+SMALL_CASES = [
+    ("mha_c128", (1024,), 4, 4, 128, 3, None),
+    ("gqa_varlen", (700, 333, 1290), 8, 2, 128, 4, None),
+    ("tail_one_token", (513, 257), 4, 2, 256, 3, None),
+    ("chunk_boundaries", (127, 128, 129), 4, 4, 64, 8, None),
+    ("short_seqs_one_chunk", (100, 60), 4, 1, 128, 8, None),
+    ("slack_maxlen", (520, 130), 8, 2, 64, 5, 1024),
+    ("k64_saturated", (512, 512), 4, 2, 32, 64, None),
+    ("k1_local_only", (600, 300), 4, 2, 128, 1, None),
+    ("many_chunks_k64", (4161,), 4, 2, 16, 64, None),
+    ("mqa", (900,), 8, 1, 128, 3, None),
+]
+
+
+def _case_inputs(lens, hq, hkv, chunk, seed):
+    return O.make_inputs(list(lens), hq, hkv, 128, chunk, seed)
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=lambda p: p.split("routing_")[-1][:-4])
+def test_golden_routing_through_cuda(path):
+    """Reference-generated golden vectors (D = 128 cases) through the CUDA gating stage."""
+    z = np.load(path)
+    if int(z["d"]) != 128:
+        pytest.skip("fixture has head_dim != 128")
+    q = torch.from_numpy(z["q_bits"]).view(torch.bfloat16).cuda()
+    k = torch.from_numpy(z["k_bits"]).view(torch.bfloat16).cuda()
+    cu = torch.from_numpy(z["cu_seqlens"]).cuda()
+    prob, _ = G.problem_for(q, k, k, cu, int(z["max_seqlen"]), int(z["chunk"]), int(z["topk"]))
+    cu_chunk, chunk_end, valid = G.metadata(prob, cu)
+    np.testing.assert_array_equal(cu_chunk.cpu().numpy(), z["cu_chunk"])
+    np.testing.assert_array_equal(chunk_end.cpu().numpy(), z["chunk_end"])
+    np.testing.assert_array_equal(valid.cpu().numpy(), z["valid_hist"])
+    m = G.means(prob, k, cu)
+    np.testing.assert_array_equal(m.cpu().view(torch.int16).numpy(), z["means_rne_bits"])
+    sel, _ = G.gate(prob, q, m, cu)
+    np.testing.assert_array_equal(sel.cpu().numpy(), z["selected_ref"])
+
+
+@pytest.mark.parametrize("case", SMALL_CASES, ids=lambda c: c[0])
+def test_routing_bit_exact(case):
+    name, lens, hq, hkv, chunk, topk, max_len = case
+    q, k, v, cu = _case_inputs(lens, hq, hkv, chunk, seed=zlib.crc32(name.encode()) % 1000)
+    max_seqlen = max_len or max(lens)
+    cu_chunk_o, chunk_end_o, valid_o, mc = O.chunk_slots(cu, max_seqlen, chunk)
+    hist = O.historical_topk(topk, mc)
+    qd, kd, vd = G.to_dev(q, k, v)
+    cud = torch.from_numpy(cu).cuda()
+    prob, _ = G.problem_for(qd, kd, vd, cud, max_seqlen, chunk, topk)
+    cu_chunk, chunk_end, valid = G.metadata(prob, cud)
+    np.testing.assert_array_equal(cu_chunk.cpu().numpy(), cu_chunk_o)
+    np.testing.assert_array_equal(chunk_end.cpu().numpy(), chunk_end_o)
+    np.testing.assert_array_equal(valid.cpu().numpy(), valid_o)
+    means_o = O.chunk_means(k, cu_chunk_o, valid_o, chunk)
+    m = G.means(prob, kd, cud)
+    assert torch.equal(m.cpu().view(torch.int16), means_o.view(torch.int16))
+    if hist <= 0:
+        return
+    sel_o = O.select_chunks(q, means_o, cu, max_seqlen, chunk, hist)
+    sel, counts = G.gate(prob, qd, m, cud)
+    np.testing.assert_array_equal(sel.cpu().numpy(), sel_o)
+    # list sizes: rows routed to each (slot, kv head)
+    g = hq // hkv
+    want = np.zeros((len(valid_o), hkv), dtype=np.int64)
+    for h in range(hq):
+        ids = sel_o[:, h, :].ravel()
+        np.add.at(want[:, h // g], ids[ids >= 0], 1)
+    np.testing.assert_array_equal(counts.cpu().numpy().reshape(-1, hkv), want)
+    # compaction: every routed (row, rank) appears exactly once, in the list of its slot
+    for tile_rows in (128, 256):
+        offsets, tiles, row_list, plse = G.compact(prob, cud, sel, counts, tile_rows)
+        offsets, tiles, row_list = offsets.cpu().numpy(), tiles.cpu().numpy(), row_list.cpu().numpy()
+        assert offsets[0] == 0 and offsets[-1] == (sel_o >= 0).sum()
+        np.testing.assert_array_equal(np.diff(offsets), want.ravel())
+        np.testing.assert_array_equal(np.diff(tiles), -(-want.ravel() // tile_rows))
+        npart = hist + 1
+        used = row_list[:offsets[-1]]
+        assert len(np.unique(used)) == len(used)
+        rank = used % npart - 1
+        row = used // npart
+        tok, head = row // hq, row % hq
+        slot_of_entry = sel_o[rank, head, tok]
+        list_id = np.repeat(np.arange(len(want.ravel())), want.ravel())
+        np.testing.assert_array_equal(slot_of_entry * hkv + head // g, list_id)
+        # ranks without a chunk are marked -inf for the merge
+        plse = plse.cpu().numpy().reshape(-1, npart)
+        empty = np.transpose(sel_o < 0, (2, 1, 0)).reshape(-1, hist)        # [row, rank]
+        assert np.all(np.isneginf(plse[:, 1:][empty])) and np.all(plse[:, 1:][~empty] == 0)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("case", SMALL_CASES, ids=lambda c: c[0])
+def test_forward_matches_fp32_evaluation(case, impl):
+    name, lens, hq, hkv, chunk, topk, max_len = case
+    q, k, v, cu = _case_inputs(lens, hq, hkv, chunk, seed=zlib.crc32(name.encode()) % 1000)
+    max_seqlen = max_len or max(lens)
+    ref, ref_lse, sel_o = O.moba_forward(q, k, v, cu, max_seqlen, chunk, topk, dtype=torch.float32)
+    qd, kd, vd = G.to_dev(q, k, v)
+    out, lse, sel = parallel.moba_forward(qd, kd, vd, torch.from_numpy(cu).cuda(), max_seqlen, chunk, topk,
+                                          return_lse=True, return_selected=True, attend_impl=impl)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(sel.cpu().numpy(), sel_o)
+    assert torch.isfinite(out.float()).all()
+    mx, mean = G.rel_stats(out.cpu(), ref)
+    assert mx < MAX_ABS and mean < MEAN_ABS, (mx, mean)
+    assert (lse.cpu() - ref_lse).abs().max().item() < 2e-3
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_topk1_chunk_local_exact(impl):
+    """test_moba_topk.py:30-57 with head_dim 128: exact equality required."""
+    lengths, chunk = (192, 129), 64
+    total = sum(lengths)
+    q = torch.zeros(total, 4, 128, dtype=torch.bfloat16)
+    k = torch.zeros(total, 2, 128, dtype=torch.bfloat16)
+    v = torch.empty_like(k)
+    expected = torch.empty_like(q)
+    full = torch.empty_like(q)
+    start = 0
+    for b, n in enumerate(lengths):
+        for pos in range(n):
+            val = (pos // chunk + 1) * (1 if b == 0 else -1)
+            v[start + pos].fill_(val)
+            expected[start + pos].fill_(val)
+        for pos in range(n):
+            full[start + pos] = v[start:start + pos + 1].float().mean(0).repeat_interleave(2, dim=0).bfloat16()
+        start += n
+    cu = torch.tensor([0, lengths[0], total], dtype=torch.int32).cuda()
+    out = parallel.moba_forward(q.cuda(), k.cuda(), v.cuda(), cu, max(lengths), chunk, 1, attend_impl=impl)[0].cpu()
+    torch.testing.assert_close(out, expected, rtol=0, atol=0)
+    assert (out.float() - full.float()).abs().max().item() > 0.5
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("lengths,topk", [((257, 193), 2), ((257, 193), 64), ((4161,), 64)])
+def test_separated_scores_against_float64(lengths, topk, impl):
+    """test_moba_topk.py:60-118 with head_dim 128, limits max < 0.04, mean < 4e-4."""
+    chunk, hq, hkv, dim = 64, 4, 2, 128
+    total = sum(lengths)
+    qc = torch.full((total, hq, dim), 0.125, dtype=torch.bfloat16)
+    qc[:, 1::2] *= -1
+    kc = torch.empty(total, hkv, dim, dtype=torch.bfloat16)
+    start = 0
+    for n in lengths:
+        for pos in range(n):
+            kc[start + pos].fill_((pos // chunk + 1) / 128)
+        start += n
+    vc = torch.randn(total, hkv, dim, generator=torch.Generator().manual_seed(42)).bfloat16()
+    bounds = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+    out = parallel.moba_forward(qc.cuda(), kc.cuda(), vc.cuda(), torch.from_numpy(bounds).cuda(), max(lengths),
+                                chunk, topk, attend_impl=impl)[0].cpu().double()
+    errors = []
+    for b, n in enumerate(lengths):
+        s = int(bounds[b])
+        keys, values = kc[s:s + n], vc[s:s + n].double()
+        means = torch.stack([keys[t:t + chunk].double().mean(0).bfloat16().double() for t in range(0, n, chunk)])
+        positions = {0, n - 1}
+        positions.update(range(0, n, max(1, n // 32)))
+        for edge in range(chunk, n, chunk):
+            positions.update((edge - 1, edge))
+        for pos in sorted(positions):
+            cur = pos // chunk
+            for head in range(hq):
+                kvh = head // (hq // hkv)
+                query = qc[s + pos, head].double()
+                scores = means[:cur, kvh] @ query
+                chosen = torch.topk(scores, min(topk - 1, cur)).indices.tolist()
+                idx = [i for blk in chosen for i in range(blk * chunk, (blk + 1) * chunk)]
+                idx += list(range(cur * chunk, pos + 1))
+                logits = (keys[idx, kvh].double() @ query) * dim ** -0.5
+                errors.append((out[s + pos, head] - logits.softmax(0) @ values[idx, kvh]).abs())
+    diff = torch.stack(errors)
+    assert torch.isfinite(diff).all()
+    assert diff.max().item() < 0.04 and diff.mean().item() < 4e-4
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_config0_full(impl):
+    """BASELINE.json configs[0]: 4096 tokens, 8/8 heads, chunk 512, top-k 3."""
+    cfg = O.CONFIGS[0]
+    lens = O.config_lengths(0)
+    q, k, v, cu = O.make_inputs(lens, cfg["hq"], cfg["hkv"], cfg["d"], cfg["chunk"], seed=42)
+    ref, ref_lse, sel_o = O.moba_forward(q, k, v, cu, max(lens), cfg["chunk"], cfg["topk"])
+    out, lse, sel = parallel.moba_forward(*G.to_dev(q, k, v), torch.from_numpy(cu).cuda(), max(lens), cfg["chunk"],
+                                          cfg["topk"], return_lse=True, return_selected=True, attend_impl=impl)
+    np.testing.assert_array_equal(sel.cpu().numpy(), sel_o)
+    mx, mean = G.rel_stats(out.cpu(), ref)
+    assert mx < MAX_ABS and mean < MEAN_ABS, (mx, mean)
+    assert (lse.cpu() - ref_lse).abs().max().item() < 2e-3
+
+
+def _sampled_check(q, k, v, cu, max_seqlen, chunk, topk, out, sel, nsample, seed):
+    """Routing bit-exact on sampled tokens (all heads); outputs of sampled rows vs float64."""
+    rng = np.random.default_rng(seed)
+    t_total, hq, _ = q.shape
+    toks = set(rng.integers(0, t_total, nsample).tolist())
+    for b in range(len(cu) - 1):                                    # sequence and chunk edges
+        toks.update({int(cu[b]), int(cu[b + 1]) - 1})
+        for e in range(int(cu[b]) + chunk, int(cu[b + 1]), chunk * max(1, (int(cu[b + 1]) - int(cu[b])) // chunk // 4)):
+            toks.update({e - 1, e})
+    toks = sorted(toks)
+    cu_chunk, _, valid, mc = O.chunk_slots(cu, max_seqlen, chunk)
+    hist = O.historical_topk(topk, mc)
+    means = O.chunk_means(k, cu_chunk, valid, chunk)
+    sel_o = O.select_chunks(q, means, cu, max_seqlen, chunk, hist, rows=toks)
+    np.testing.assert_array_equal(sel[:, :, toks], sel_o[:, :, toks])
+    rows = [(t, int(h)) for t in toks[:: max(1, len(toks) // 48)] for h in rng.integers(0, hq, 2)]
+    ref, _ = O.attend_rows(q, k, v, cu, max_seqlen, chunk, sel_o, rows)
+    got = torch.stack([out[t, h] for t, h in rows]).double()
+    diff = (got - ref).abs()
+    return diff.max().item(), diff.mean().item()
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_config1_varlen_sampled(impl):
+    """BASELINE.json configs[1]: 4 seeded lengths in [1024, 8192], 32/32 heads, chunk 512, top-k 3."""
+    cfg = O.CONFIGS[1]
+    lens = O.config_lengths(1)
+    q, k, v, cu = O.make_inputs(lens, cfg["hq"], cfg["hkv"], cfg["d"], cfg["chunk"], seed=43)
+    out, _, sel = parallel.moba_forward(*G.to_dev(q, k, v), torch.from_numpy(cu).cuda(), max(lens), cfg["chunk"],
+                                        cfg["topk"], return_selected=True, attend_impl=impl)
+    assert torch.isfinite(out.float()).all()
+    mx, mean = _sampled_check(q, k, v, cu, max(lens), cfg["chunk"], cfg["topk"], out.cpu(), sel.cpu().numpy(), 96, 1)
+    assert mx < MAX_ABS and mean < MEAN_ABS, (mx, mean)
+
+
+def test_config2_long_gqa_sampled():
+    """BASELINE.json configs[2]: 32768 tokens, 32/8 heads, chunk 4096, top-k 12 (every earlier chunk is selected)."""
+    cfg = O.CONFIGS[2]
+    lens = O.config_lengths(2)
+    q, k, v, cu = O.make_inputs(lens, cfg["hq"], cfg["hkv"], cfg["d"], cfg["chunk"], seed=44)
+    out, _, sel = parallel.moba_forward(*G.to_dev(q, k, v), torch.from_numpy(cu).cuda(), max(lens), cfg["chunk"],
+                                        cfg["topk"], return_selected=True)
+    assert torch.isfinite(out.float()).all()
+    sel = sel.cpu().numpy()
+    # hist = 7 = all earlier chunks: the selected set of a query in chunk j is {0..j-1}
+    for j in (1, 3, 7):
+        got = np.sort(sel[:, 5, j * 4096 + 17])
+        assert got[got >= 0].tolist() == list(range(j))
+    mx, mean = _sampled_check(q, k, v, cu, max(lens), cfg["chunk"], cfg["topk"], out.cpu(), sel, 48, 2)
+    assert mx < MAX_ABS and mean < MEAN_ABS, (mx, mean)
+
+
+def test_implementations_agree_and_are_deterministic():
+    q, k, v, cu = _case_inputs((2048, 1111), 8, 2, 256, seed=5)
+    args = (*G.to_dev(q, k, v), torch.from_numpy(cu).cuda(), 2048, 256, 4)
+    a = parallel.moba_forward(*args, attend_impl=_lib.ATTEND_TCGEN05)[0]
+    b = parallel.moba_forward(*args, attend_impl=_lib.ATTEND_TCGEN05)[0]
+    c = parallel.moba_forward(*args, attend_impl=_lib.ATTEND_MMA_SYNC)[0]
+    assert torch.equal(a, b)                                    # run-to-run bit identical
+    assert (a.float() - c.float()).abs().max().item() < 2e-2
+
+
+def test_causality_and_batch_isolation():
+    """SEMANTICS.md:38: changing Q/K/V after a prefix, and a later sequence, leaves the prefix outputs unchanged."""
+    lens = (1500, 900)
+    q, k, v, cu = _case_inputs(lens, 8, 2, 128, seed=9)
+    cud = torch.from_numpy(cu).cuda()
+    base = parallel.moba_forward(*G.to_dev(q, k, v), cud, 1500, 128, 4)[0].cpu()
+    cut = 777
+    q2, k2, v2 = q.clone(), k.clone(), v.clone()
+    g = torch.Generator().manual_seed(1)
+    for t in (q2, k2, v2):
+        t[cut:] = torch.randn(t[cut:].shape, generator=g).bfloat16()
+    pert = parallel.moba_forward(*G.to_dev(q2, k2, v2), cud, 1500, 128, 4)[0].cpu()
+    assert torch.equal(base[:cut], pert[:cut])
+    assert not torch.equal(base[cut:], pert[cut:])
+
+
+def test_strided_inputs():
+    """q/k/v given as slices of a fused projection (token stride larger than heads*dim)."""
+    t, hq, hkv = 1024, 8, 2
+    g = torch.Generator().manual_seed(3)
+    fused = torch.randn(t, hq + 2 * hkv, 128, generator=g).bfloat16().cuda()
+    q, k, v = fused[:, :hq], fused[:, hq:hq + hkv], fused[:, hq + hkv:]
+    cu = torch.tensor([0, 600, t], dtype=torch.int32).cuda()
+    a = parallel.moba_forward(q, k, v, cu, 600, 128, 3)[0]
+    b = parallel.moba_forward(q.contiguous(), k.contiguous(), v.contiguous(), cu, 600, 128, 3)[0]
+    assert torch.equal(a, b)
+
+
+def test_public_operator_names():
+    import baselinebenchmark_b200 as pkg
+    from baselinebenchmark_b200 import native_moba
+    q, k, v, cu = _case_inputs((512,), 4, 2, 128, seed=11)
+    qd, kd, vd = G.to_dev(q, k, v)
+    cud = torch.from_numpy(cu).cuda()
+    with torch.inference_mode():
+        a = pkg.parallel_moba(qd, kd, vd, cud, 512, 128, 3)
+        b = pkg.moba_attn_varlen(qd, kd, vd, cud, 512, 128, 3)
+        c = torch.ops.moba_b200.moba_attn_varlen(qd, kd, vd, cud, 512, 128, 3)
+    assert torch.equal(a, b) and torch.equal(a, c)
+    assert native_moba._supported(qd)
+    with pytest.raises(NotImplementedError):
+        pkg.parallel_moba(qd.half(), kd.half(), vd.half(), cud, 512, 128, 3)
