@@ -237,9 +237,9 @@ int moba_merge(const moba_problem_t* p, const float* partial_out, const float* p
                            lse_out, (cudaStream_t)stream);
 }
 
-int moba_forward(const moba_problem_t* p, const void* q, const void* k, const void* v, const int32_t* cu,
-                 void* out, float* lse_out, int32_t* selected_out, void* workspace, size_t workspace_bytes,
-                 void* stream) {
+static int forward_impl(const moba_problem_t* p, const void* q, const void* k, const void* v, const int32_t* cu,
+                        void* out, float* lse_out, int32_t* selected_out, void* workspace, size_t workspace_bytes,
+                        void* stream, void* const* events) {
   const int rc = check_problem(p);
   if (rc != MOBA_OK) return rc;
   if (!q || !k || !v || !cu || !out) return MOBA_E_NULL;
@@ -251,23 +251,46 @@ int moba_forward(const moba_problem_t* p, const void* q, const void* k, const vo
   const Workspace w = carve(r, workspace);
   if (workspace_bytes < w.total) return MOBA_E_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
-  cudaError_t e = cudaMemsetAsync(w.list_counts, 0, w.zero_bytes, st);
-  if (e != cudaSuccess) return (int)e;
+  cudaError_t e;
+  auto mark = [&](int i) -> cudaError_t {
+    return (events && events[i]) ? cudaEventRecord((cudaEvent_t)events[i], st) : cudaSuccess;
+  };
+  if ((e = mark(0)) != cudaSuccess) return (int)e;
+  if ((e = cudaMemsetAsync(w.list_counts, 0, w.zero_bytes, st)) != cudaSuccess) return (int)e;
   const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(q);
   const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(k);
   if (r.hist > 0) {
     int32_t* sel = selected_out ? selected_out : w.selected;
     if ((e = launch_chunk_means(r, kb, cu, w.means, st)) != cudaSuccess) return (int)e;
+    if ((e = mark(1)) != cudaSuccess) return (int)e;
     if ((e = launch_gate_topk(r, qb, w.means, cu, sel, w.list_counts, st)) != cudaSuccess) return (int)e;
+    if ((e = mark(2)) != cudaSuccess) return (int)e;
     if ((e = launch_compact(r, cu, sel, w.list_counts, w.list_offsets, w.tile_prefix, w.cursors, w.row_list,
                             w.partial_lse, tile_rows_of(p->attend_impl), st)) != cudaSuccess)
       return (int)e;
+  } else {
+    if ((e = mark(1)) != cudaSuccess || (e = mark(2)) != cudaSuccess) return (int)e;
   }
+  if ((e = mark(3)) != cudaSuccess) return (int)e;
   const int arc = attend_dispatch(p, r, q, k, v, cu, w.list_counts, w.list_offsets, w.tile_prefix, w.row_list,
                                   w.partial_out, w.partial_lse, w.work_counter, w.status, st);
   if (arc != 0) return arc;
+  if ((e = mark(4)) != cudaSuccess) return (int)e;
   e = launch_merge(r, w.partial_out, w.partial_lse, w.status, static_cast<__nv_bfloat16*>(out), lse_out, st);
-  return (int)e;
+  if (e != cudaSuccess) return (int)e;
+  return (int)mark(5);
+}
+
+int moba_forward(const moba_problem_t* p, const void* q, const void* k, const void* v, const int32_t* cu,
+                 void* out, float* lse_out, int32_t* selected_out, void* workspace, size_t workspace_bytes,
+                 void* stream) {
+  return forward_impl(p, q, k, v, cu, out, lse_out, selected_out, workspace, workspace_bytes, stream, nullptr);
+}
+
+int moba_forward_events(const moba_problem_t* p, const void* q, const void* k, const void* v, const int32_t* cu,
+                        void* out, float* lse_out, int32_t* selected_out, void* workspace,
+                        size_t workspace_bytes, void* stream, void* const* events) {
+  return forward_impl(p, q, k, v, cu, out, lse_out, selected_out, workspace, workspace_bytes, stream, events);
 }
 
 int moba_workspace_size_host(const moba_problem_t* p, size_t* bytes) {

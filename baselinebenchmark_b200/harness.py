@@ -1,0 +1,171 @@
+"""Latency harness for the operator, CUDA edition of the reference's
+benchmarks/moba_compare.py protocol: inputs built outside the timed region
+(seed 42, randn, moba_compare.py:103-109), one untimed first call, `--warmup`
+calls, then `--rounds` x `--iterations` timed calls with perf_counter + device
+synchronisation per call (:111-128); median / mean / p99 per case in one JSON
+report (:39-44).  Like the original it performs no correctness check.
+
+    python -m baselinebenchmark_b200.harness --case cfg2 --rounds 1 --iterations 3
+    python -m baselinebenchmark_b200.harness --suite --output results.json
+
+`--suite` runs the reference's case list (moba_compare.py:59-99) restricted to
+what this build supports (bf16, head_dim 128); the rest is reported as skipped.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+import time
+from dataclasses import asdict, dataclass
+from itertools import accumulate
+
+import torch
+
+from . import native_moba
+from .parallel import parallel_moba
+
+
+@dataclass(frozen=True)
+class Case:
+    name: str
+    seq_lens: tuple
+    q_heads: int = 16
+    kv_heads: int = 16
+    head_dim: int = 128
+    chunk_size: int = 128
+    topk: int = 8
+    dtype: str = "bfloat16"
+    key_offsets: bool = False      # BASELINE.json configs add a per-chunk offset to the keys
+
+
+BASELINE_CASES = {
+    "cfg0": Case("cfg0", (4096,), 8, 8, 128, 512, 3, key_offsets=True),
+    "cfg1": Case("cfg1", (6144, 2560, 7168, 3584), 32, 32, 128, 512, 3, key_offsets=True),
+    "cfg2": Case("cfg2", (32768,), 32, 8, 128, 4096, 12, key_offsets=True),
+    "cfg3-unit": Case("cfg3-unit", (131072,), 4, 1, 128, 4096, 8, key_offsets=True),
+}
+
+
+def reference_suite():
+    """The workload list of benchmarks/moba_compare.py:59-99 (same shapes, same names)."""
+    cases = [Case(f"length-{n}", (n, n)) for n in (512, 2048, 4096, 8192, 16384)]
+    cases += [Case(f"batch-{b}", (4096,) * b) for b in (1, 4)]
+    cases += [Case(f"dim-{d}", (4096, 4096), head_dim=d) for d in (64, 96, 256)]
+    cases += [Case(f"chunk-{c}", (4096, 4096), chunk_size=c) for c in (64, 256, 512)]
+    cases += [Case(f"topk-{k}", (4096, 4096), topk=k) for k in (2, 4, 16)]
+    cases += [Case("gqa-16q-4kv", (4096, 4096), kv_heads=4), Case("mqa-16q-1kv", (4096, 4096), kv_heads=1),
+              Case("heads-4", (4096, 4096), q_heads=4, kv_heads=4)]
+    cases += [Case("fp16-d128", (4096, 4096), dtype="float16"),
+              Case("fp16-d64", (4096, 4096), head_dim=64, dtype="float16"),
+              Case("fp16-gqa", (4096, 4096), kv_heads=4, dtype="float16")]
+    cases += [Case("chunk-boundaries", (127, 128, 129), q_heads=4, kv_heads=4), Case("one-token-tail", (4097, 4097)),
+              Case("varlen-gqa", (200, 400, 648), q_heads=8, kv_heads=2), Case("varlen-long", (1023, 4097, 8191)),
+              Case("fp16-varlen", (127, 513, 2049), q_heads=8, kv_heads=2, head_dim=64, dtype="float16")]
+    cases += [Case(f"long-gqa-{n}", (n,), q_heads=32, kv_heads=8) for n in (32768, 65536)]
+    cases += [Case(f"long-c{c}-k{k}", (32768,), q_heads=32, kv_heads=8, chunk_size=c, topk=k)
+              for c, k in ((512, 8), (1024, 8), (512, 16))]
+    cases += [Case("tokens16k-b1", (16384,)), Case("tokens16k-b8", (2048,) * 8),
+              Case("tokens16k-varlen", (1024, 2048, 4096, 9216))]
+    cases += [Case(f"length-{n}", (n, n)) for n in (4096, 8192, 16384, 32768, 65536)]
+    cases += [Case("topk-1", (4096, 4096), topk=1), Case("topk64-saturated", (512, 512), topk=64),
+              Case("topk64-long-gqa", (32768,), q_heads=32, kv_heads=8, topk=64)]
+    unique = {}
+    for case in cases:
+        key = (case.seq_lens, case.q_heads, case.kv_heads, case.head_dim, case.chunk_size, case.topk, case.dtype)
+        unique.setdefault(key, case)
+    return list(unique.values())
+
+
+def summary(samples):
+    out = {"mean_ms": statistics.mean(samples), "median_ms": statistics.median(samples), "count": len(samples)}
+    if len(samples) >= 100:
+        out["p99_ms"] = sorted(samples)[int(0.99 * (len(samples) - 1))]
+    return out
+
+
+def make_inputs(case: Case, device):
+    torch.manual_seed(42)
+    dtype = getattr(torch, case.dtype)
+    total = sum(case.seq_lens)
+    q = torch.randn(total, case.q_heads, case.head_dim, device=device, dtype=dtype)
+    k = torch.randn(total, case.kv_heads, case.head_dim, device=device, dtype=dtype)
+    v = torch.randn_like(k)
+    if case.key_offsets:
+        start = 0
+        for n in case.seq_lens:
+            nck = -(-n // case.chunk_size)
+            off = (torch.randn(nck, case.kv_heads, case.head_dim, device=device) * 0.5).to(dtype)
+            k[start:start + n] += off.repeat_interleave(case.chunk_size, 0)[:n]
+            start += n
+    cu = torch.tensor([0, *accumulate(case.seq_lens)], device=device, dtype=torch.int32)
+    return q, k, v, cu
+
+
+def supported(case: Case) -> bool:
+    return case.dtype == "bfloat16" and case.head_dim == 128
+
+
+def run_case(case: Case, args, device):
+    if not supported(case):
+        return {**asdict(case), "status": "skipped", "reason": "this build: bfloat16, head_dim 128"}
+    q, k, v, cu = make_inputs(case, device)
+    call = (q, k, v, cu, max(case.seq_lens), case.chunk_size, case.topk)
+    with torch.inference_mode():
+        parallel_moba(*call)
+        torch.cuda.synchronize()
+        samples = []
+        for _ in range(args.rounds):
+            for _ in range(args.warmup):
+                parallel_moba(*call)
+            torch.cuda.synchronize()
+            for _ in range(args.iterations):
+                t0 = time.perf_counter()
+                result = parallel_moba(*call)
+                torch.cuda.synchronize()
+                samples.append((time.perf_counter() - t0) * 1e3)
+                del result
+    tokens = sum(case.seq_lens)
+    stats = summary(samples)
+    return {**asdict(case), "status": "measured", "q_shape": list(q.shape), "kv_shape": list(k.shape),
+            "native_sparse_path_eligible": bool(native_moba._supported(q)) and case.topk > 1
+            and max(case.seq_lens) > case.chunk_size,
+            "latency": stats, "tokens_per_s": tokens / (stats["median_ms"] * 1e-3)}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--case", action="append", choices=sorted(BASELINE_CASES), help="BASELINE.json workload(s)")
+    ap.add_argument("--suite", action="store_true", help="the reference's 40-case list")
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--iterations", type=int, default=25)
+    ap.add_argument("--rounds", type=int, default=4)
+    ap.add_argument("--output")
+    args = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        raise SystemExit("needs a CUDA device")
+    device = torch.device("cuda", torch.cuda.current_device())
+    cases = [BASELINE_CASES[c] for c in (args.case or [])] + (reference_suite() if args.suite else [])
+    if not cases:
+        cases = [BASELINE_CASES["cfg0"]]
+    report = {"schema_version": 4, "timing": "perf_counter + device synchronize per call; inference only",
+              "correctness_checked": False, "device": torch.cuda.get_device_name(device),
+              "arguments": {"warmup": args.warmup, "iterations": args.iterations, "rounds": args.rounds},
+              "cases": []}
+    for case in cases:
+        res = run_case(case, args, device)
+        report["cases"].append(res)
+        lat = res.get("latency", {})
+        print(f"{case.name:>20}  {res['status']:>8}  median {lat.get('median_ms', float('nan')):9.4f} ms", flush=True)
+        torch.cuda.empty_cache()
+    text = json.dumps(report, indent=2)
+    if args.output:
+        with open(args.output, "w") as f:
+            f.write(text + "\n")
+    return report
+
+
+if __name__ == "__main__":
+    main()
+    sys.exit(0)

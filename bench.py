@@ -1,0 +1,368 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 MoBA prefill forward.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: under torchrun)
+    python bench.py --impl reference --gpus N --steps K --warmup W
+
+Workload (BASELINE.json configs[3], "batched GQA prefill sharded by (sequence,
+KV-head group)"): every GPU holds 16 independent (sequence, KV-head group)
+units = 2 sequences of 131072 tokens with 32 query / 8 KV heads, head_dim 128,
+bf16, chunk 4096, top-k 8, causal.  At 8 GPUs that is the whole config (128
+units); fewer GPUs run the same per-GPU share (weak scaling), no collective.
+One step = one call of the operator on the rank's share.  Inputs are synthetic:
+q, k, v ~ N(0,1) plus a N(0, 0.5^2) offset per (sequence, chunk, kv head) on the
+keys, generated on the device from a seed.
+
+Printed JSON (one line, rank 0): tokens/s with inputs resident in HBM (`value`),
+the same through the C ABI with pinned HOST buffers (`e2e`), the dense-stage
+roofline from CUDA events recorded between the kernels of the timed steps, the
+CPU baseline, clocks sampled during the timed region, and the 32K GQA prefill
+(configs[2]) as an extra measurement under `also`.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SEQ_LEN = 131072
+SEQS_PER_GPU = 2
+HQ, HKV, D, CHUNK, TOPK = 32, 8, 128, 4096, 8
+KERNELS_PER_STEP = 6      # chunk_mean, gate_topk, scan_lists, scatter_routes, attend, merge
+
+
+def cdiv(a, b):
+    return (a + b - 1) // b
+
+
+def attention_flops(seq_lens, hq, d, chunk, topk):
+    pairs = 0
+    for n in seq_lens:
+        for j in range(cdiv(n, chunk)):
+            ln = min(chunk, n - j * chunk)
+            pairs += ln * (ln + 1) // 2 + ln * min(topk - 1, j) * chunk
+    return 4.0 * d * hq * pairs
+
+
+def peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        p = json.loads(f.read_text())
+        return dict(burst=float(p["bf16_tflops"]), sustained=float(p["bf16_tflops_sustained"]),
+                    hbm=float(p["hbm_gbs"]), source="measured")
+    return dict(burst=1590.0, sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_inputs_device(seq_lens, hq, hkv, d, chunk, seed, device):
+    g = torch.Generator(device=device).manual_seed(seed)
+    total = sum(seq_lens)
+    q = torch.randn(total, hq, d, generator=g, device=device, dtype=torch.float32).bfloat16()
+    k = torch.empty(total, hkv, d, device=device, dtype=torch.bfloat16)
+    v = torch.randn(total, hkv, d, generator=g, device=device, dtype=torch.float32).bfloat16()
+    start = 0
+    for n in seq_lens:                      # keys: N(0,1) + one offset vector per (chunk, kv head)
+        kk = torch.randn(n, hkv, d, generator=g, device=device, dtype=torch.float32)
+        off = torch.randn(cdiv(n, chunk), hkv, d, generator=g, device=device, dtype=torch.float32) * 0.5
+        kk += off.repeat_interleave(chunk, 0)[:n]
+        k[start:start + n] = kk.bfloat16()
+        start += n
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(seq_lens)]), dtype=torch.int32, device=device)
+    return q, k, v, cu
+
+
+class Runner:
+    """Holds problem, workspace and events for repeated calls through the C ABI."""
+
+    def __init__(self, q, k, v, cu, max_seqlen, chunk, topk):
+        from baselinebenchmark_b200 import _lib, parallel
+        self.lib, self._lib = _lib.lib(), _lib
+        self.q, self.k, self.v, self.cu = q, k, v, cu
+        self.out = torch.empty_like(q)
+        self.prob = parallel.make_problem(q, k, v, self.out, cu, max_seqlen, chunk, topk)
+        self.ws = torch.empty(parallel.workspace_bytes(self.prob), dtype=torch.uint8, device=q.device)
+
+    def step(self, events=None):
+        stream = torch.cuda.current_stream().cuda_stream
+        if events is None:
+            rc = self.lib.moba_forward(C.byref(self.prob), self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(),
+                                       self.cu.data_ptr(), self.out.data_ptr(), None, None, self.ws.data_ptr(),
+                                       self.ws.numel(), stream)
+        else:
+            arr = (C.c_void_p * 6)(*[e.cuda_event for e in events])
+            rc = self.lib.moba_forward_events(C.byref(self.prob), self.q.data_ptr(), self.k.data_ptr(),
+                                              self.v.data_ptr(), self.cu.data_ptr(), self.out.data_ptr(), None, None,
+                                              self.ws.data_ptr(), self.ws.numel(), stream, arr)
+        self._lib.check(rc)
+
+
+def new_events(n):
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
+    for e in evs:
+        e.record()                          # materialises the cudaEvent_t handle
+    return evs
+
+
+def timed_steps(runner, steps, warmup, barrier):
+    for _ in range(warmup):
+        runner.step()
+    per_step = [new_events(6) for _ in range(steps)]
+    torch.cuda.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    for evs in per_step:
+        runner.step(evs)
+    torch.cuda.synchronize()
+    barrier()
+    total_ms = per_step[0][0].elapsed_time(per_step[-1][5])
+    stage_ms = [[evs[i].elapsed_time(evs[i + 1]) for i in range(5)] for evs in per_step]
+    return total_ms, np.asarray(stage_ms).mean(0)
+
+
+class HostRunner:
+    """The same operator through moba_forward_host: pinned host tensors in, pinned host result out."""
+
+    def __init__(self, runner, q, k, v, cu):
+        from baselinebenchmark_b200 import _lib
+        self.lib, self._lib, self.prob = _lib.lib(), _lib, runner.prob
+        size = C.c_size_t(0)
+        _lib.check(self.lib.moba_workspace_size_host(C.byref(self.prob), C.byref(size)))
+        self.ws = torch.empty(size.value, dtype=torch.uint8, device=q.device)
+        self.hq, self.hk, self.hv = (t.cpu().pin_memory() for t in (q, k, v))
+        self.hcu = cu.cpu().pin_memory()
+        self.hout = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+        self.h2d = sum(t.numel() * t.element_size() for t in (self.hq, self.hk, self.hv, self.hcu))
+        self.d2h = self.hout.numel() * self.hout.element_size()
+
+    def step(self):
+        rc = self.lib.moba_forward_host(C.byref(self.prob), self.hq.data_ptr(), self.hk.data_ptr(), self.hv.data_ptr(),
+                                        self.hcu.data_ptr(), self.hout.data_ptr(), None, None, self.ws.data_ptr(),
+                                        self.ws.numel(), torch.cuda.current_stream().cuda_stream)
+        self._lib.check(rc)
+
+
+def cpu_sample(threads):
+    """CPU baseline on a bounded sample of the workload: one (sequence, KV-head
+    group) unit with 4 of its 32 query chunks evaluated (chunks 3, 11, 19, 27:
+    6.0 selected chunks per query on average, 6.1 in the full unit)."""
+    from oracle import moba_cpu, moba_oracle
+    torch.set_num_threads(threads)
+    q, k, v, cu = moba_oracle.make_inputs([SEQ_LEN], HQ // HKV, 1, D, CHUNK, seed=7)
+    chunks = (3, 11, 19, 27)
+    t0 = time.perf_counter()
+    _, done = moba_cpu.moba_forward_cpu(q, k, v, cu, SEQ_LEN, CHUNK, TOPK, query_chunks=chunks)
+    dt = time.perf_counter() - t0
+    # a benchmark token carries all 32 query heads; the sample evaluated 4 of them
+    tokens_equiv = int(done.sum()) * (HQ // HKV) / HQ
+    return tokens_equiv / dt, dt, ("one (sequence, KV-group) unit: 131072 keys, 4 query heads, query chunks "
+                                   "3/11/19/27 of 32 evaluated (16384 tokens x 4 heads)")
+
+
+def reference_arm(args, rank):
+    """The reference has no CPU implementation of this path and its kernels need a
+    vendor device; the arm times the oracle's PyTorch-CPU port on the host cores."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    rates, secs = [], []
+    sample = ""
+    for i in range(args.warmup + args.steps):
+        r, dt, sample = cpu_sample(threads)
+        if i >= args.warmup:
+            rates.append(r); secs.append(dt)
+    value = sum(rates) / len(rates)
+    line = {
+        "impl": "reference", "metric": "MoBA prefill tokens/s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * sum(secs) / len(secs), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {"workload": "BASELINE.json configs[3] share: 16 (sequence, KV-head group) units per GPU = 2 sequences "
+                        "x 131072 tokens, 32 q / 8 kv heads, head_dim 128, chunk 4096, top-k 8, causal "
+                        f"({16 * n_gpus} of 128 units at {n_gpus} GPU(s))",
+            "tokens_per_gpu": SEQ_LEN * SEQS_PER_GPU, "parallelism": f"units x{n_gpus}, no collective",
+            "l2": "inputs (3 GiB per GPU) exceed the 126 MB L2"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-also", action="store_true", help="skip the configs[2] extra measurement")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        reference_arm(args, rank)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    from baselinebenchmark_b200 import build
+    build.build()
+    seq_lens = [SEQ_LEN] * SEQS_PER_GPU
+    q, k, v, cu = make_inputs_device(seq_lens, HQ, HKV, D, CHUNK, 45000 + rank, dev)
+    runner = Runner(q, k, v, cu, SEQ_LEN, CHUNK, TOPK)
+    with ClockSampler(local) as clocks:
+        total_ms, stage_ms = timed_steps(runner, args.steps, args.warmup, barrier)
+    total_ms = max_over_ranks(total_ms)
+    attend_ms = max_over_ranks(float(stage_ms[3]))
+    tokens = world * sum(seq_lens) * args.steps
+    value = tokens / (total_ms * 1e-3)
+    flops = attention_flops(seq_lens, HQ, D, CHUNK, TOPK)
+    pk = peaks()
+
+    # end to end: pinned host buffers in, pinned host result out, copies inside the timed region
+    host = HostRunner(runner, q, k, v, cu)
+    host.step()
+    torch.cuda.synchronize()
+    barrier()
+    e0, e1 = new_events(2)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.e2e_steps):
+        host.step()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+    e2e_value = world * sum(seq_lens) * args.e2e_steps / (e2e_ms * 1e-3)
+    h2d, d2h = host.h2d, host.d2h
+    del host
+
+    also = {}
+    if not args.no_also and rank == 0:
+        del runner, q, k, v
+        torch.cuda.empty_cache()
+        q2, k2, v2, cu2 = make_inputs_device([32768], 32, 8, 128, 4096, 44, dev)
+        r2 = Runner(q2, k2, v2, cu2, 32768, 4096, 12)
+        ms2, st2 = timed_steps(r2, 20, 5, lambda: None)
+        ms2 /= 20
+        f2 = attention_flops([32768], 32, 128, 4096, 12)
+        also["configs[2] 32K GQA prefill (1 GPU, 32768 tokens, 32/8 heads, chunk 4096, top-k 12)"] = {
+            "ms_per_call": ms2, "tokens_per_s": 32768 / (ms2 * 1e-3), "tflops": f2 / (ms2 * 1e-3) / 1e12,
+            "frac_of_measured_burst_peak": f2 / (ms2 * 1e-3) / 1e12 / pk["burst"],
+            "dense_stage_ms": float(st2[3]), "dense_stage_tflops": f2 / (float(st2[3]) * 1e-3) / 1e12,
+            "stage_ms": {"means": float(st2[0]), "gate_topk": float(st2[1]), "compact": float(st2[2]),
+                         "attend": float(st2[3]), "merge": float(st2[4])}}
+    barrier()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        rate, dt, sample = cpu_sample(threads)
+        cpu = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample,
+               "seconds": dt}
+
+    if rank == 0:
+        achieved = flops / (attend_ms * 1e-3) / 1e12
+        line = {
+            "metric": "MoBA prefill tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(world),
+            "tflops_effective": flops * world * args.steps / (total_ms * 1e-3) / 1e12,
+            "frac_of_bf16_peak": flops * args.steps / (total_ms * 1e-3) / 1e12 / pk["sustained"],
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / args.e2e_steps, "steps": args.e2e_steps},
+            "gpu_launches": KERNELS_PER_STEP * args.steps,
+            "roofline": {"kernel": "attend_tc5_kernel", "bound": "tensor", "achieved": achieved,
+                         "peak": pk["sustained"], "unit": "TFLOP/s", "frac": achieved / pk["sustained"],
+                         "peak_kind": f"{pk['source']} cuBLAS bf16, sustained (kernel timed inside a long step); "
+                                      f"burst {pk['burst']}", "frac_of_burst": achieved / pk["burst"],
+                         "flops_per_launch": flops, "ms_per_launch": attend_ms, "traffic": None},
+            "stage_ms": {"means": float(stage_ms[0]), "gate_topk": float(stage_ms[1]), "compact": float(stage_ms[2]),
+                         "attend": float(stage_ms[3]), "merge": float(stage_ms[4])},
+            "cpu_baseline": cpu, "clocks": clocks.summary(), "also": also,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -96,6 +96,16 @@ int moba_forward(const moba_problem_t* p, const void* q, const void* k, const vo
                  const int32_t* cu_seqlens, void* out, float* lse_out, int32_t* selected_out,
                  void* workspace, size_t workspace_bytes, void* stream);
 
+/* moba_forward with CUDA events (cudaEvent_t, may be null) recorded on `stream`
+ * between the stages, for per-kernel timing without a profiler:
+ *   [0] before the first launch   [1] after the chunk means   [2] after scores/top-k
+ *   [3] after the compaction      [4] after the dense stage   [5] after the merge
+ * The reference has no such hook: its harness times the whole call with
+ * perf_counter (benchmarks/moba_compare.py:111-128). */
+int moba_forward_events(const moba_problem_t* p, const void* q, const void* k, const void* v,
+                        const int32_t* cu_seqlens, void* out, float* lse_out, int32_t* selected_out,
+                        void* workspace, size_t workspace_bytes, void* stream, void* const* events);
+
 /* Same call with HOST buffers (pinned memory recommended): copies q, k, v and
  * cu_seqlens to staging buffers inside `workspace`, runs moba_forward, copies
  * `out` (and lse_out / selected_out when given) back, all on `stream`.  The
