@@ -7,9 +7,11 @@ build command.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libmoba_b200.so"
+#: MOBA_B200_LIB selects another build of the same library (A/B runs of kernel variants)
+LIB_PATH = Path(os.environ.get("MOBA_B200_LIB") or Path(__file__).resolve().parent / "libmoba_b200.so")
 
 ATTEND_TCGEN05 = 0
 ATTEND_MMA_SYNC = 1

@@ -19,8 +19,8 @@
 //
 // Warp roles (384 threads):
 //   warp 0      TMA producer: K and V tiles of 128 keys, two stages each
-//   warp 1      MMA issuer (one lane): S = Q.K^T into TMEM, O += P.V with P read
-//               from TMEM; owns the TMEM allocation
+//   warp 1      MMA issuer: S = Q.K^T into TMEM, O += P.V with P read from TMEM; the
+//               warp runs convergent, one elected lane issues; owns the TMEM allocation
 //   warps 4-7   softmax of tile A: one thread per row (TMEM lane)
 //   warps 8-11  softmax of tile B
 //   all warps   gather of the Q rows into 128B-swizzled shared memory
@@ -62,24 +62,200 @@ struct Ctrl {
 
 constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + 6 * kTileBytes + sizeof(Ctrl);
 
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Pairs of score columns whose exponential is evaluated with the cubic on the
+// FMA pipe instead of the special-function unit: kPolyPairs out of every 8.
+// The special-function unit sustains 16 ex2 per clock and SM, which is exactly
+// the rate two 128x128 MMAs per 1024 cycles would ask of it.
+#ifndef MOBA_POLY_PAIRS
+#define MOBA_POLY_PAIRS 3
+#endif
+constexpr int kPolyPairs = MOBA_POLY_PAIRS;
+
+// Optional cycle accounting (build with -DMOBA_TC5_TRACE): sums over all CTAs are
+// added to status[2 + i]; status must then point at 64 zeroed ints.
+#ifdef MOBA_TC5_TRACE
+#define TRACE_T0(var) const long long var = clock64()
+#define TRACE_BASE(args) reinterpret_cast<unsigned long long*>(((uintptr_t)((args).status + 2) + 7) & ~(uintptr_t)7)
+#define TRACE_ADD(args, slot, t0) atomicAdd(TRACE_BASE(args) + (slot), (unsigned long long)(clock64() - (t0)))
+#else
+#define TRACE_T0(var)
+#define TRACE_ADD(args, slot, t0)
+#endif
+
+struct KernelArgs {
+  const __nv_bfloat16* q;
+  const int32_t* cu;
+  const int32_t* list_counts;
+  const int32_t* list_offsets;
+  const int32_t* tile_prefix;
+  const int32_t* row_list;
+  float* partial_out;
+  float* partial_lse;
+  int32_t* work_counter;
+  int32_t* status;
+};
+
+// Common head of an item, executed by all 384 threads: draw the next item,
+// resolve its rows and gather the Q rows into the two swizzled Q tiles.
+// Returns false when the queue is empty (or the kernel is aborting).
+__device__ __forceinline__ bool next_item(const Params& p, const KernelArgs& a, Ctrl& c, unsigned char* smem,
+                                          int n_routed, int n_items, Item& it) {
+  for (;;) {
+    __syncthreads();                       // every role has finished the previous item
+    if (threadIdx.x == 0) c.item = c.abort ? 0x7fffffff : atomicAdd(a.work_counter, 1);
+    __syncthreads();
+    const int idx = c.item;
+    if (idx >= n_items) return false;
+    it = decode_item(p, idx, n_routed, 2 * kTileM, a.cu, a.list_counts, a.list_offsets, a.tile_prefix);
+    if (it.valid) break;
+  }
+  for (int r = threadIdx.x; r < 2 * kTileM; r += kThreads) {
+    int32_t e = -1;
+    int64_t off = 0;
+    if (r < it.nrows) {
+      if (it.causal) {
+        e = (int32_t)(((int64_t)(it.tok0 + r) * p.Hq + it.head) * p.NP);
+        off = (int64_t)(it.tok0 + r) * p.sq_t + (int64_t)it.head * p.sq_h;
+      } else {
+        e = a.row_list[it.row_start + r];
+        const int64_t row = e / p.NP;
+        const int64_t t = row / p.Hq;
+        off = t * p.sq_t + (row - t * p.Hq) * p.sq_h;
+      }
+    }
+    c.entry[r] = e;
+    c.qoff[r] = off;
+  }
+  __syncthreads();
+  // gather Q rows into two [2][128][64] blocks with the 128-byte swizzle TMA would produce
+#pragma unroll 1
+  for (int i0 = threadIdx.x; i0 < 2 * kTileM * 16; i0 += 4 * kThreads) {
+    uint4 val[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * kThreads;
+      val[u] = make_uint4(0, 0, 0, 0);
+      if (i < 2 * kTileM * 16) {
+        const int r = i >> 4, ch = i & 15;
+        if (c.entry[r] >= 0) val[u] = __ldg(reinterpret_cast<const uint4*>(a.q + c.qoff[r] + ch * 8));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * kThreads;
+      if (i < 2 * kTileM * 16) {
+        const int r = i >> 4, ch = i & 15;
+        const uint32_t dst = (uint32_t)((r >> 7) * kTileBytes + (ch >> 3) * kHalfBytes + (r & 127) * 128 +
+                                        (((ch & 7) ^ (r & 7)) << 4));
+        *reinterpret_cast<uint4*>(smem + dst) = val[u];
+      }
+    }
+  }
+  fence_proxy_async_smem();
+  __syncthreads();
+  return true;
+}
+
+// One softmax step of one row: S (128 fp32 columns of this thread's TMEM lane)
+// -> P (bf16, written over the first 64 columns), running max / sum updated.
+template <bool kMasked>
+__device__ __forceinline__ void softmax_row(uint32_t tS, uint32_t tO, int j, int key0, int lim, float sl2,
+                                            float& m_ref, float& l) {
+  uint32_t v[128];
+  tmem_ld128(tS, v);
+  tmem_wait_ld();
+  if (kMasked) {
+#pragma unroll
+    for (int i = 0; i < 128; ++i) v[i] = (key0 + i < lim) ? v[i] : 0xff800000u;   // -inf
+  }
+  float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 128; i += 8) {
+    mx0 = max3(mx0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+    mx1 = max3(mx1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+    mx2 = max3(mx2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+    mx3 = max3(mx3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+  }
+  const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+  const float m_new = fmaxf(m_ref, mx * sl2);
+  if (__any_sync(0xffffffffu, m_new > m_ref + 8.f)) {
+    const float alpha = (m_new == -INFINITY) ? 1.f : ex2_approx(m_ref - m_new);
+    if (j > 0) {
+      uint32_t o[32];
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        tmem_ld32(tO + ch * 32, o);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+        tmem_st32(tO + ch * 32, o);
+      }
+    }
+    l *= alpha;
+    m_ref = m_new;
+  }
+  const uint64_t scale2 = pack2(sl2, sl2);
+  const uint64_t negm2 = pack2(-m_ref, -m_ref);
+  uint64_t sum_a = 0, sum_b = 0;           // two packed accumulators = four running sums
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int e = ch * 32 + 2 * i;
+      const uint64_t x = fma2(pack2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])), scale2, negm2);
+      uint64_t pr;
+      if ((i & 7) < kPolyPairs) {
+        pr = ex2_poly2(x);
+      } else {
+        pr = pack2(ex2_approx(lo2(x)), ex2_approx(hi2(x)));
+      }
+      if (i & 1) sum_b = add2(sum_b, pr); else sum_a = add2(sum_a, pr);
+      pk[i] = pack_bf16(lo2(pr), hi2(pr));
+    }
+    tmem_st16(tS + ch * 16, pk);
+  }
+  const uint64_t sum = add2(sum_a, sum_b);
+  l += lo2(sum) + hi2(sum);
+  tmem_wait_st();
+}
+
+// Descriptor words.  Low word: start address >> 4 | (leading byte offset >> 4) << 16;
+// high word (constant): stride byte offset 1024 >> 4 | version 1 << 14 | SWIZZLE_128B (2) << 29.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+  return ((addr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
+}
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint64_t desc64(uint32_t lo) { return ((uint64_t)kDescHi << 32) | lo; }
+
+// S_X = Q_X . K^T for one K tile: 8 k-steps of 16 dims; X and STAGE are compile-time
+// so every descriptor is the base word plus an immediate.
+template <int X, int STAGE>
+__device__ __forceinline__ void issue_qk(uint32_t tmem, uint32_t dq, uint32_t dk) {
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    constexpr int kHalf = kHalfBytes >> 4, kTile = kTileBytes >> 4;
+    const uint32_t koff = (uint32_t)((ks >> 2) * kHalf + (ks & 3) * 2);
+    mma_ss(tmem + X * kBN, desc64(dq + X * kTile + koff), desc64(dk + STAGE * kTile + koff), kIdescQK, ks > 0);
+  }
+}
+// O_X (+)= P_X . V for one V tile: 8 k-steps of 16 keys, P read from tensor memory.
+template <int X, int STAGE>
+__device__ __forceinline__ void issue_pv(uint32_t tmem, uint32_t dv, bool first) {
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks)
+    mma_ts(tmem + 256 + X * kHeadDim, tmem + X * kBN + ks * 8,
+           desc64(dv + STAGE * (kTileBytes >> 4) + ks * (2048 >> 4)), kIdescPV, (!first) || ks > 0);
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
-                  const __grid_constant__ CUtensorMap tmap_v, const __nv_bfloat16* __restrict__ q,
-                  const int32_t* __restrict__ cu, const int32_t* __restrict__ list_counts,
-                  const int32_t* __restrict__ list_offsets, const int32_t* __restrict__ tile_prefix,
-                  const int32_t* __restrict__ row_list, float* __restrict__ partial_out,
-                  float* __restrict__ partial_lse, int32_t* __restrict__ work_counter,
-                  int32_t* __restrict__ status) {
+                  const __grid_constant__ CUtensorMap tmap_v, const KernelArgs a) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sQ = smem_u32(smem);                       // tile A, tile B
@@ -87,7 +263,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
   const uint32_t sV = sK + 2 * kTileBytes;                  // 2 stages
   Ctrl& c = *reinterpret_cast<Ctrl*>(smem + 6 * kTileBytes);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;   // warp index, uniform
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -113,249 +289,184 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
   tc_fence_after();
   const uint32_t tmem = c.tmem_slot;
 
-  const int n_routed = p.hist > 0 ? tile_prefix[p.lists] : 0;
+  const int n_routed = p.hist > 0 ? a.tile_prefix[p.lists] : 0;
   const int n_items = n_routed + own_item_count(p.slots, p.Hq, p.C, 2 * kTileM);
-  const float sl2 = rsqrtf((float)kHeadDim) * 1.4426950408889634f;
+  Item it;
 
-  // running pipeline counters; every role advances its own copy identically
-  uint32_t kc = 0, vc = 0;                 // K / V tiles produced or consumed so far
-  uint32_t sph = 0, oph = 0;               // softmax: s_full / o_full phases of its tile
-  uint32_t pph0 = 0, pph1 = 0;             // MMA: p_full phases of tile A / B
-
-  for (;;) {
-    __syncthreads();                       // every role has finished the previous item
-    if (threadIdx.x == 0) c.item = c.abort ? 0x7fffffff : atomicAdd(work_counter, 1);
-    __syncthreads();
-    const int idx = c.item;
-    if (idx >= n_items) break;
-    const Item it = decode_item(p, idx, n_routed, 2 * kTileM, cu, list_counts, list_offsets, tile_prefix);
-    if (!it.valid) continue;
-
-    for (int r = threadIdx.x; r < 2 * kTileM; r += kThreads) {
-      int32_t e = -1;
-      int64_t off = 0;
-      if (r < it.nrows) {
-        if (it.causal) {
-          e = (int32_t)(((int64_t)(it.tok0 + r) * p.Hq + it.head) * p.NP);
-          off = (int64_t)(it.tok0 + r) * p.sq_t + (int64_t)it.head * p.sq_h;
-        } else {
-          e = row_list[it.row_start + r];
-          const int64_t row = e / p.NP;
-          const int64_t t = row / p.Hq;
-          off = t * p.sq_t + (row - t * p.Hq) * p.sq_h;
-        }
-      }
-      c.entry[r] = e;
-      c.qoff[r] = off;
-    }
-    __syncthreads();
-    // gather Q rows into two [2][128][64] blocks with the 128-byte swizzle TMA would produce
-    for (int i0 = threadIdx.x; i0 < 2 * kTileM * 16; i0 += 4 * kThreads) {
-      uint4 val[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i = i0 + u * kThreads;
-        val[u] = make_uint4(0, 0, 0, 0);
-        if (i < 2 * kTileM * 16) {
-          const int r = i >> 4, ch = i & 15;
-          if (c.entry[r] >= 0) val[u] = __ldg(reinterpret_cast<const uint4*>(q + c.qoff[r] + ch * 8));
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i = i0 + u * kThreads;
-        if (i < 2 * kTileM * 16) {
-          const int r = i >> 4, ch = i & 15;
-          const uint32_t dst = (uint32_t)((r >> 7) * kTileBytes + (ch >> 3) * kHalfBytes + (r & 127) * 128 +
-                                          (((ch & 7) ^ (r & 7)) << 4));
-          *reinterpret_cast<uint4*>(smem + dst) = val[u];
-        }
-      }
-    }
-    fence_proxy_async_smem();
-    __syncthreads();
-
-    const int ntiles = (it.kv_len + kBN - 1) / kBN;
-
-    if (warp == 0) {
-      // ------------------------------------------------------------ TMA producer
-      if (lane == 0) {
+  if (warp < 4) {
+    // =============================================== warps 0-3: TMA producer, MMA issuer, two spare warps
+    setmaxnreg_dec_64();
+    uint32_t kc = 0, vc = 0;               // K / V tiles produced (warp 0) or consumed (warp 1) so far
+    uint32_t pph0 = 0, pph1 = 0;           // p_full phases of tile A / B
+    // warp-uniform copies of the TMEM base and of the low words of the shared-memory
+    // descriptors of the first Q / K / V block (every other block or k-step is a
+    // compile-time offset from these), and the lane that issues
+    const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+    const uint32_t dq = __shfl_sync(0xffffffffu, desc_lo(sQ, 16), 0);
+    const uint32_t dk = __shfl_sync(0xffffffffu, desc_lo(sK, 16), 0);
+    const uint32_t dv = __shfl_sync(0xffffffffu, desc_lo(sV, kHalfBytes), 0);
+    const uint32_t el = elect_one();
+    while (next_item(p, a, c, smem, n_routed, n_items, it)) {
+      const int ntiles = (it.kv_len + kBN - 1) / kBN;
+      if (warp == 0 && lane == 0) {
         for (int j = 0; j < ntiles; ++j) {
           const int tok = it.kv_tok0 + j * kBN;
           {
             const uint32_t s = kc & 1;
-            if (!mbar_wait(smem_u32(&c.k_empty[s]), ((kc >> 1) & 1) ^ 1)) { atomicExch(status, ST_PRODUCER); c.abort = 1; break; }
+            if (!mbar_wait(smem_u32(&c.k_empty[s]), ((kc >> 1) & 1) ^ 1)) { atomicExch(a.status, ST_PRODUCER); c.abort = 1; break; }
             const uint32_t bar = smem_u32(&c.k_full[s]);
+#ifdef MOBA_EXPERIMENT_NO_TMA
+            if (j >= 2) { mbar_arrive(bar); } else
+#endif
+            {
             mbar_expect_tx(bar, kTileBytes);
             tma_load_3d(sK + s * kTileBytes, &tmap_k, bar, 0, it.kv_head, tok);
             tma_load_3d(sK + s * kTileBytes + kHalfBytes, &tmap_k, bar, 64, it.kv_head, tok);
+            }
             ++kc;
           }
           {
             const uint32_t s = vc & 1;
-            if (!mbar_wait(smem_u32(&c.v_empty[s]), ((vc >> 1) & 1) ^ 1)) { atomicExch(status, ST_PRODUCER); c.abort = 1; break; }
+            if (!mbar_wait(smem_u32(&c.v_empty[s]), ((vc >> 1) & 1) ^ 1)) { atomicExch(a.status, ST_PRODUCER); c.abort = 1; break; }
             const uint32_t bar = smem_u32(&c.v_full[s]);
+#ifdef MOBA_EXPERIMENT_NO_TMA
+            if (j >= 2) { mbar_arrive(bar); } else
+#endif
+            {
             mbar_expect_tx(bar, kTileBytes);
             tma_load_3d(sV + s * kTileBytes, &tmap_v, bar, 0, it.kv_head, tok);
             tma_load_3d(sV + s * kTileBytes + kHalfBytes, &tmap_v, bar, 64, it.kv_head, tok);
+            }
             ++vc;
           }
         }
-      }
-      __syncwarp();
-    } else if (warp == 1) {
-      // ------------------------------------------------------------ MMA issuer
-      if (lane == 0) {
+      } else if (warp == 1) {
+        // MMA issuer.  The whole warp runs this code so that addresses and descriptors
+        // stay warp-uniform (uniform registers); one elected lane executes the
+        // tcgen05 instructions.  Issued from a single-lane branch instead, every MMA
+        // costs a dozen dependent vector instructions and the issuer starves for
+        // issue slots next to the softmax warps of its scheduler partition.
         bool ok = true;
-        auto issue_qk = [&](int x, uint32_t stage) {
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint32_t koff = (uint32_t)((ks >> 2) * kHalfBytes + (ks & 3) * 32);
-            mma_ss(tmem + x * kBN, smem_desc_sw128(sQ + x * kTileBytes + koff, 16, 1024),
-                   smem_desc_sw128(sK + stage * kTileBytes + koff, 16, 1024), kIdescQK, ks > 0);
-          }
-        };
-        auto issue_pv = [&](int x, uint32_t stage, bool first) {
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            mma_ts(tmem + 256 + x * kHeadDim, tmem + x * kBN + ks * 8,
-                   smem_desc_sw128(sV + stage * kTileBytes + ks * 2048, kHalfBytes, 1024), kIdescPV,
-                   (!first) || ks > 0);
-        };
+        TRACE_T0(t_item);
         tc_fence_after();
-        ok = mbar_wait(smem_u32(&c.k_full[kc & 1]), (kc >> 1) & 1);
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.k_full[kc & 1]), (kc >> 1) & 1));
         if (ok) {
           tc_fence_after();
-          issue_qk(0, kc & 1);
-          tc_commit(smem_u32(&c.s_full[0]));
-          issue_qk(1, kc & 1);
-          tc_commit(smem_u32(&c.s_full[1]));
-          tc_commit(smem_u32(&c.k_empty[kc & 1]));
-          ++kc;
-        }
-        for (int j = 0; ok && j < ntiles; ++j) {
-          const bool more = j + 1 < ntiles;
-          ok = mbar_wait(smem_u32(&c.v_full[vc & 1]), (vc >> 1) & 1);
-          if (!ok) break;
-          ok = mbar_wait(smem_u32(&c.p_full[0]), pph0);
-          if (!ok) break;
-          pph0 ^= 1;
-          tc_fence_after();
-          issue_pv(0, vc & 1, j == 0);
-          if (more) {
-            ok = mbar_wait(smem_u32(&c.k_full[kc & 1]), (kc >> 1) & 1);
-            if (!ok) break;
-            tc_fence_after();
-            issue_qk(0, kc & 1);
-            tc_commit(smem_u32(&c.s_full[0]));
-          } else {
-            tc_commit(smem_u32(&c.o_full[0]));
-          }
-          ok = mbar_wait(smem_u32(&c.p_full[1]), pph1);
-          if (!ok) break;
-          pph1 ^= 1;
-          tc_fence_after();
-          issue_pv(1, vc & 1, j == 0);
-          tc_commit(smem_u32(&c.v_empty[vc & 1]));
-          ++vc;
-          if (more) {
-            issue_qk(1, kc & 1);
+          if (el) {
+            if (kc & 1) { issue_qk<0, 1>(tm, dq, dk); tc_commit(smem_u32(&c.s_full[0])); issue_qk<1, 1>(tm, dq, dk); }
+            else        { issue_qk<0, 0>(tm, dq, dk); tc_commit(smem_u32(&c.s_full[0])); issue_qk<1, 0>(tm, dq, dk); }
             tc_commit(smem_u32(&c.s_full[1]));
             tc_commit(smem_u32(&c.k_empty[kc & 1]));
-            ++kc;
-          } else {
-            tc_commit(smem_u32(&c.o_full[1]));
           }
+          __syncwarp();
+          ++kc;
         }
-        if (!ok) { atomicExch(status, ST_MMA); c.abort = 1; }
+        // K tile j+1 and V tile j always sit in opposite stages (kc == vc + 1 here)
+        for (int j = 0; ok && j < ntiles; ++j) {
+          const bool more = j + 1 < ntiles;
+          const uint32_t vs = vc & 1, ks = vs ^ 1;
+          TRACE_T0(t_v);
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.v_full[vs]), (vc >> 1) & 1));
+          if (!ok) break;
+          if (lane == 0) TRACE_ADD(a, 0, t_v);
+          TRACE_T0(t_pa);
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.p_full[0]), pph0));
+          if (!ok) break;
+          if (lane == 0) TRACE_ADD(a, 1, t_pa);
+          pph0 ^= 1;
+          tc_fence_after();
+          if (el) { if (vs) issue_pv<0, 1>(tm, dv, j == 0); else issue_pv<0, 0>(tm, dv, j == 0); }
+          __syncwarp();
+          if (more) {
+            TRACE_T0(t_k);
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.k_full[ks]), (kc >> 1) & 1));
+            if (!ok) break;
+            if (lane == 0) TRACE_ADD(a, 2, t_k);
+            tc_fence_after();
+            if (el) {
+              if (ks) issue_qk<0, 1>(tm, dq, dk); else issue_qk<0, 0>(tm, dq, dk);
+              tc_commit(smem_u32(&c.s_full[0]));
+            }
+          } else if (el) {
+            tc_commit(smem_u32(&c.o_full[0]));
+          }
+          __syncwarp();
+          TRACE_T0(t_pb);
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.p_full[1]), pph1));
+          if (!ok) break;
+          if (lane == 0) TRACE_ADD(a, 3, t_pb);
+          pph1 ^= 1;
+          tc_fence_after();
+          if (el) {
+            if (vs) issue_pv<1, 1>(tm, dv, j == 0); else issue_pv<1, 0>(tm, dv, j == 0);
+            tc_commit(smem_u32(&c.v_empty[vs]));
+            if (more) {
+              if (ks) issue_qk<1, 1>(tm, dq, dk); else issue_qk<1, 0>(tm, dq, dk);
+              tc_commit(smem_u32(&c.s_full[1]));
+              tc_commit(smem_u32(&c.k_empty[ks]));
+            } else {
+              tc_commit(smem_u32(&c.o_full[1]));
+            }
+          }
+          __syncwarp();
+          ++vc;
+          if (more) ++kc;
+        }
+        if (!ok && lane == 0) { atomicExch(a.status, ST_MMA); c.abort = 1; }
+        if (lane == 0) TRACE_ADD(a, 4, t_item);
       }
       __syncwarp();
-    } else if (warp >= 4) {
-      // ------------------------------------------------------------ softmax + epilogue
-      const int x = (warp - 4) >> 2;                       // 0: tile A, 1: tile B
-      const int row = (warp & 3) * 32 + lane;              // row inside the tile = TMEM lane
-      const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-      const uint32_t tS = tmem + lane_base + x * kBN;
-      const uint32_t tO = tmem + lane_base + 256 + x * kHeadDim;
+    }
+  } else {
+    // =============================================== warps 4-11: softmax + epilogue, one thread per row
+    setmaxnreg_inc_216();
+    const int x = (warp - 4) >> 2;                       // 0: tile A, 1: tile B
+    const int row = (warp & 3) * 32 + lane;              // row inside the tile = TMEM lane
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + lane_base + x * kBN;
+    const uint32_t tO = tmem + lane_base + 256 + x * kHeadDim;
+    const float sl2 = rsqrtf((float)kHeadDim) * 1.4426950408889634f;
+    uint32_t sph = 0, oph = 0;                           // s_full / o_full phases of this tile
+#ifdef MOBA_TC5_TRACE
+    long long t_next = clock64();
+    const long long t_kernel = t_next;
+#endif
+    while (next_item(p, a, c, smem, n_routed, n_items, it)) {
+#ifdef MOBA_TC5_TRACE
+      if (threadIdx.x == 128) { TRACE_ADD(a, 8, t_next); atomicAdd(TRACE_BASE(a) + 9, 1ull); }
+#endif
+      const int ntiles = (it.kv_len + kBN - 1) / kBN;
       const int qpos = it.tok0 + x * kTileM + row;
+      const int lim = it.causal ? min(it.kv_len, qpos - it.kv_tok0 + 1) : it.kv_len;   // keys < lim are visible
       float m_ref = -INFINITY, l = 0.f;
       bool ok = true;
-      uint32_t v[32];
-      for (int j = 0; j < ntiles; ++j) {
-        ok = mbar_wait(smem_u32(&c.s_full[x]), sph);
+      for (int j = 0; ok && j < ntiles; ++j) {
+        TRACE_T0(t_s);
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.s_full[x]), sph));   // warp-uniform exit
         if (!ok) break;
+        if (threadIdx.x == 128) TRACE_ADD(a, 5, t_s);
+        TRACE_T0(t_c);
         sph ^= 1;
         tc_fence_after();
         const int key0 = j * kBN;
         const bool masked = key0 + kBN > it.kv_len ||
                             (it.causal && it.kv_tok0 + key0 + kBN - 1 > it.tok0 + x * kTileM);
-        const int lim = it.causal ? min(it.kv_len, qpos - it.kv_tok0 + 1) : it.kv_len;   // keys < lim are visible
-        // pass 1: row maximum
-        float mx = -INFINITY;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          tmem_ld32(tS + ch * 32, v);
-          tmem_wait_ld();
-          if (masked) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              mx = (key0 + ch * 32 + i < lim) ? fmaxf(mx, __uint_as_float(v[i])) : mx;
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-          }
-        }
-        const float m_new = fmaxf(m_ref, mx * sl2);
-        const bool grow = m_new > m_ref + 8.f;
-        if (__any_sync(0xffffffffu, grow)) {
-          const float alpha = (m_new == -INFINITY) ? 1.f : ex2(m_ref - m_new);
-          if (j > 0) {
-#pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
-              tmem_ld32(tO + ch * 32, v);
-              tmem_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-              tmem_st32(tO + ch * 32, v);
-            }
-            tmem_wait_st();
-          }
-          l *= alpha;
-          m_ref = m_new;
-        }
-        // pass 2: P = exp2(S * sl2 - m_ref), bf16, written over the first 64 columns of S
-        const float neg_m = -m_ref;
-        float rs = 0.f;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          tmem_ld32(tS + ch * 32, v);
-          tmem_wait_ld();
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float p0 = ex2(fmaf(__uint_as_float(v[2 * i]), sl2, neg_m));
-            float p1 = ex2(fmaf(__uint_as_float(v[2 * i + 1]), sl2, neg_m));
-            if (masked) {
-              p0 = (key0 + ch * 32 + 2 * i < lim) ? p0 : 0.f;
-              p1 = (key0 + ch * 32 + 2 * i + 1 < lim) ? p1 : 0.f;
-            }
-            rs += p0 + p1;
-            pk[i] = pack_bf16(p0, p1);
-          }
-          tmem_st16(tS + ch * 16, pk);
-        }
-        l += rs;
-        tmem_wait_st();
+        if (masked) softmax_row<true>(tS, tO, j, key0, lim, sl2, m_ref, l);
+        else softmax_row<false>(tS, tO, j, key0, lim, sl2, m_ref, l);
         tc_fence_before();
         mbar_arrive(smem_u32(&c.p_full[x]));
+        if (threadIdx.x == 128) TRACE_ADD(a, 6, t_c);
       }
+      TRACE_T0(t_e);
       if (ok) ok = mbar_wait(smem_u32(&c.o_full[x]), oph);
+      ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         oph ^= 1;
         tc_fence_after();
         const int32_t e = c.entry[x * kTileM + row];
         const float inv = 1.f / l;
-        float* dst = partial_out + (int64_t)(e >= 0 ? e : 0) * kHeadDim;
+        float* dst = a.partial_out + (int64_t)(e >= 0 ? e : 0) * kHeadDim;
+        uint32_t v[32];
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
           tmem_ld32(tO + ch * 32, v);
@@ -368,13 +479,20 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
                               __uint_as_float(v[4 * i + 2]) * inv, __uint_as_float(v[4 * i + 3]) * inv);
           }
         }
-        if (e >= 0) partial_lse[e] = (m_ref + log2f(l)) * 0.6931471805599453f;
+        if (e >= 0) a.partial_lse[e] = (m_ref + log2f(l)) * 0.6931471805599453f;
         tc_fence_before();
+        if (threadIdx.x == 128) TRACE_ADD(a, 7, t_e);
       } else {
-        atomicExch(status, ST_SOFTMAX);
+        atomicExch(a.status, ST_SOFTMAX);
         c.abort = 1;
       }
+#ifdef MOBA_TC5_TRACE
+      t_next = clock64();
+#endif
     }
+#ifdef MOBA_TC5_TRACE
+    if (threadIdx.x == 128) TRACE_ADD(a, 10, t_kernel);
+#endif
   }
 
   // teardown: all roles are past their last wait; give in-flight copies time to
@@ -434,8 +552,9 @@ cudaError_t launch_attend_tc5(const Params& p, const __nv_bfloat16* q, const __n
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  attend_tc5_kernel<<<sms, kThreads, kSmemBytes, st>>>(p, mk, mv, q, cu, list_counts, list_offsets, tile_prefix,
-                                                      row_list, partial_out, partial_lse, work_counter, status);
+  const KernelArgs args{q, cu, list_counts, list_offsets, tile_prefix, row_list, partial_out, partial_lse,
+                        work_counter, status};
+  attend_tc5_kernel<<<sms, kThreads, kSmemBytes, st>>>(p, mk, mv, args);
   return cudaGetLastError();
 }
 

@@ -151,6 +151,83 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 
+// 32 lanes x 128 / 64 consecutive 32-bit columns in one instruction.
+#define MOBA_R8(v, b) "=r"(v[b]), "=r"(v[b + 1]), "=r"(v[b + 2]), "=r"(v[b + 3]), "=r"(v[b + 4]), "=r"(v[b + 5]), "=r"(v[b + 6]), "=r"(v[b + 7])
+__device__ __forceinline__ void tmem_ld128(uint32_t taddr, uint32_t (&r)[128]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x128.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63, "
+      "%64, %65, %66, %67, %68, %69, %70, %71, %72, %73, %74, %75, %76, %77, %78, %79, "
+      "%80, %81, %82, %83, %84, %85, %86, %87, %88, %89, %90, %91, %92, %93, %94, %95, "
+      "%96, %97, %98, %99, %100, %101, %102, %103, %104, %105, %106, %107, %108, %109, %110, %111, "
+      "%112, %113, %114, %115, %116, %117, %118, %119, %120, %121, %122, %123, %124, %125, %126, %127}, [%128];"
+      : MOBA_R8(r, 0), MOBA_R8(r, 8), MOBA_R8(r, 16), MOBA_R8(r, 24), MOBA_R8(r, 32), MOBA_R8(r, 40),
+        MOBA_R8(r, 48), MOBA_R8(r, 56), MOBA_R8(r, 64), MOBA_R8(r, 72), MOBA_R8(r, 80), MOBA_R8(r, 88),
+        MOBA_R8(r, 96), MOBA_R8(r, 104), MOBA_R8(r, 112), MOBA_R8(r, 120)
+      : "r"(taddr)
+      : "memory");
+}
+#undef MOBA_R8
+
+// ---- packed fp32 arithmetic (two floats in one 64-bit register) ------------------
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  return ((uint64_t)__float_as_uint(hi) << 32) | (uint64_t)__float_as_uint(lo);
+}
+__device__ __forceinline__ float lo2(uint64_t v) { return __uint_as_float((uint32_t)v); }
+__device__ __forceinline__ float hi2(uint64_t v) { return __uint_as_float((uint32_t)(v >> 32)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// 2^x (x <= 100; below -126 saturates to about 1e-38) on the FMA pipe: n = rint(x) through the 1.5*2^23 trick,
+// f = x - n in [-0.5, 0.5], cubic for 2^f (relative error 7.5e-5, far below the
+// bf16 rounding the result goes through), exponent patched with an integer add.
+__device__ __forceinline__ uint64_t ex2_poly2(uint64_t x) {
+  const uint64_t magic = pack2(12582912.f, 12582912.f);
+  x = pack2(fmaxf(lo2(x), -126.f), fmaxf(hi2(x), -126.f));
+  const uint64_t t = add2(x, magic);
+  const uint64_t f = sub2(x, sub2(t, magic));
+  uint64_t p = fma2(f, pack2(0.055171530693769455f, 0.055171530693769455f),
+                    pack2(0.24261100590229034f, 0.24261100590229034f));
+  p = fma2(p, f, pack2(0.6932609677314758f, 0.6932609677314758f));
+  p = fma2(p, f, pack2(0.9999280571937561f, 0.9999280571937561f));
+  const uint32_t r0 = (uint32_t)p + ((uint32_t)t << 23);
+  const uint32_t r1 = (uint32_t)(p >> 32) + ((uint32_t)(t >> 32) << 23);
+  return ((uint64_t)r1 << 32) | r0;
+}
+// One lane of a converged warp (the same lane on every call).
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred;
+}
+__device__ __forceinline__ void setmaxnreg_dec_64() { asm volatile("setmaxnreg.dec.sync.aligned.u32 64;"); }
+__device__ __forceinline__ void setmaxnreg_inc_216() { asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); }
+
 // ---- UMMA descriptors -------------------------------------------------------------
 // Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field = 1:
 //   bits  0-13 start address >> 4      bits 16-29 leading byte offset >> 4
