@@ -72,7 +72,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // The special-function unit sustains 16 ex2 per clock and SM, which is exactly
 // the rate two 128x128 MMAs per 1024 cycles would ask of it.
 #ifndef MOBA_POLY_PAIRS
-#define MOBA_POLY_PAIRS 3
+#define MOBA_POLY_PAIRS 2
 #endif
 constexpr int kPolyPairs = MOBA_POLY_PAIRS;
 
@@ -295,7 +295,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
 
   if (warp < 4) {
     // =============================================== warps 0-3: TMA producer, MMA issuer, two spare warps
-    setmaxnreg_dec_64();
+    setmaxnreg_dec<64>();
     uint32_t kc = 0, vc = 0;               // K / V tiles produced (warp 0) or consumed (warp 1) so far
     uint32_t pph0 = 0, pph1 = 0;           // p_full phases of tile A / B
     // warp-uniform copies of the TMEM base and of the low words of the shared-memory
@@ -315,28 +315,18 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
             const uint32_t s = kc & 1;
             if (!mbar_wait(smem_u32(&c.k_empty[s]), ((kc >> 1) & 1) ^ 1)) { atomicExch(a.status, ST_PRODUCER); c.abort = 1; break; }
             const uint32_t bar = smem_u32(&c.k_full[s]);
-#ifdef MOBA_EXPERIMENT_NO_TMA
-            if (j >= 2) { mbar_arrive(bar); } else
-#endif
-            {
             mbar_expect_tx(bar, kTileBytes);
             tma_load_3d(sK + s * kTileBytes, &tmap_k, bar, 0, it.kv_head, tok);
             tma_load_3d(sK + s * kTileBytes + kHalfBytes, &tmap_k, bar, 64, it.kv_head, tok);
-            }
             ++kc;
           }
           {
             const uint32_t s = vc & 1;
             if (!mbar_wait(smem_u32(&c.v_empty[s]), ((vc >> 1) & 1) ^ 1)) { atomicExch(a.status, ST_PRODUCER); c.abort = 1; break; }
             const uint32_t bar = smem_u32(&c.v_full[s]);
-#ifdef MOBA_EXPERIMENT_NO_TMA
-            if (j >= 2) { mbar_arrive(bar); } else
-#endif
-            {
             mbar_expect_tx(bar, kTileBytes);
             tma_load_3d(sV + s * kTileBytes, &tmap_v, bar, 0, it.kv_head, tok);
             tma_load_3d(sV + s * kTileBytes + kHalfBytes, &tmap_v, bar, 64, it.kv_head, tok);
-            }
             ++vc;
           }
         }
@@ -419,7 +409,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     }
   } else {
     // =============================================== warps 4-11: softmax + epilogue, one thread per row
-    setmaxnreg_inc_216();
+    setmaxnreg_inc<216>();
     const int x = (warp - 4) >> 2;                       // 0: tile A, 1: tile B
     const int row = (warp & 3) * 32 + lane;              // row inside the tile = TMEM lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;

@@ -170,6 +170,18 @@ __device__ __forceinline__ void tmem_ld128(uint32_t taddr, uint32_t (&r)[128]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+      : MOBA_R8(r, 0), MOBA_R8(r, 8), MOBA_R8(r, 16), MOBA_R8(r, 24), MOBA_R8(r, 32), MOBA_R8(r, 40),
+        MOBA_R8(r, 48), MOBA_R8(r, 56)
+      : "r"(taddr)
+      : "memory");
+}
 #undef MOBA_R8
 
 // ---- packed fp32 arithmetic (two floats in one 64-bit register) ------------------
@@ -225,8 +237,9 @@ __device__ __forceinline__ uint32_t elect_one() {
   asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
   return pred;
 }
-__device__ __forceinline__ void setmaxnreg_dec_64() { asm volatile("setmaxnreg.dec.sync.aligned.u32 64;"); }
-__device__ __forceinline__ void setmaxnreg_inc_216() { asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); }
+// Register budget of the calling warpgroup (all four warps execute it).
+template <int N> __device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 
 // ---- UMMA descriptors -------------------------------------------------------------
 // Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field = 1:
