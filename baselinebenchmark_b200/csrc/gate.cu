@@ -12,9 +12,9 @@
 //   mean : row r of a chunk is added to accumulator r % 32 in increasing r, the
 //          32 accumulators are added in increasing index, the total is divided
 //          by C and rounded to bf16 (round to nearest even);
-//   score: bf16*bf16 products are exact in fp32; 16 lanes each add their 8
-//          products left to right, then a halving tree (lane l + lane l^8, ^4,
-//          ^2, ^1) combines the lanes.
+//   score: bf16*bf16 products are exact in fp32; each of the 16 blocks of 8
+//          dims is added left to right, then a halving tree (block l + block
+//          l+8, then l + l+4, l + l+2, l + l+1) combines the block sums.
 #include "common.cuh"
 
 namespace moba {
@@ -110,21 +110,40 @@ cudaError_t launch_chunk_means(const Params& p, const __nv_bfloat16* k, const in
 
 // ---------------------------------------------------------------------------
 // scores + mask + top-k
-//   grid (token tiles of one sequence, kv head, sequence); 256 threads = 16 row
-//   groups of 16 lanes.  The CTA stages the bf16 means of its kv head for a
-//   tile of candidate chunks in shared memory; every row group then scores its
+//   grid (token tiles of one sequence, kv head, sequence); 256 threads = 64 row
+//   groups of 4 lanes.  The CTA stages the means of its kv head for a tile of
+//   candidate chunks in shared memory as fp32; every row group then scores its
 //   rows against them and keeps the `hist` largest packed keys
 //   (order-preserving score bits << 32 | 0xFFFFFFFF - slot, routing.py:1151-1153)
 //   by repeated arg-max, which makes ties fall to the lower slot.
+//   Lane t of a group owns the 8-dim blocks t, t+4, t+8, t+12, so the first two
+//   levels of the halving tree (block l + block l+8, then l + l+4) stay inside
+//   the lane and only the last two cross lanes: same summation order as 16
+//   lanes with one block each, a quarter of the shuffles.
 // ---------------------------------------------------------------------------
 constexpr int kGateThreads = 256;
-constexpr int kGateGroups = kGateThreads / 16;
+constexpr int kGateGroups = kGateThreads / 4;
 constexpr int kGateRows = 128;            // (token, head) rows per CTA
-constexpr int kCandTile = 128;            // candidate chunks staged per pass
+constexpr int kCandTile = 32;             // candidate chunks staged per pass
 
 __device__ __forceinline__ uint32_t float_key(float x) {      // routing.py:778-784
   const uint32_t b = __float_as_uint(x);
   return b ^ ((b & 0x80000000u) ? 0xFFFFFFFFu : 0x80000000u);
+}
+__device__ __forceinline__ float dot8(const float (&q)[8], const float4 a, const float4 b) {
+  float s = q[0] * a.x;
+  s = __fmaf_rn(q[1], a.y, s);
+  s = __fmaf_rn(q[2], a.z, s);
+  s = __fmaf_rn(q[3], a.w, s);
+  s = __fmaf_rn(q[4], b.x, s);
+  s = __fmaf_rn(q[5], b.y, s);
+  s = __fmaf_rn(q[6], b.z, s);
+  s = __fmaf_rn(q[7], b.w, s);
+  return s;
+}
+__device__ __forceinline__ void unpack8(const uint4 x, float (&f)[8]) {
+  f[0] = bf16_lo(x.x); f[1] = bf16_hi(x.x); f[2] = bf16_lo(x.y); f[3] = bf16_hi(x.y);
+  f[4] = bf16_lo(x.z); f[5] = bf16_hi(x.z); f[6] = bf16_lo(x.w); f[7] = bf16_hi(x.w);
 }
 
 __global__ void __launch_bounds__(kGateThreads)
@@ -133,9 +152,9 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
                  int32_t* __restrict__ selected, int32_t* __restrict__ list_counts) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int hist = p.hist;
-  // layout: means tile | cand[groups][kCandTile] | wins[groups][hist] | best[rows][hist] | counts[mc]
-  uint4* means_s = reinterpret_cast<uint4*>(smem_raw);                              // kCandTile*16 uint4
-  unsigned long long* cand_s = reinterpret_cast<unsigned long long*>(means_s + kCandTile * 16);
+  // layout: means tile fp32 | cand[groups][kCandTile] | wins[groups][hist] | best[rows][hist] | counts[mc]
+  float4* means_s = reinterpret_cast<float4*>(smem_raw);                            // kCandTile * 32 float4
+  unsigned long long* cand_s = reinterpret_cast<unsigned long long*>(means_s + kCandTile * 32);
   unsigned long long* wins_s = cand_s + kGateGroups * kCandTile;
   unsigned long long* best_s = wins_s + kGateGroups * hist;
   int32_t* cnt_s = reinterpret_cast<int32_t*>(best_s + (size_t)kGateRows * hist);
@@ -146,8 +165,8 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
   if (tok_lo >= s1) return;
   const int ntok = min(tokens_per_cta, s1 - tok_lo);
   const int nrows = ntok * p.G;
-  const int grp = threadIdx.x >> 4, lane = threadIdx.x & 15;
-  const unsigned gmask = 0xFFFFu << (threadIdx.x & 16);       // the 16 lanes of this group
+  const int grp = threadIdx.x >> 2, t = threadIdx.x & 3;
+  const unsigned gmask = 0xFu << (threadIdx.x & 28);          // the 4 lanes of this group
 
   for (int i = threadIdx.x; i < p.mc; i += kGateThreads) cnt_s[i] = 0;
   for (int i = threadIdx.x; i < kGateRows * hist; i += kGateThreads) best_s[i] = 0ull;
@@ -162,54 +181,53 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
     __syncthreads();                                          // previous tile fully consumed
     for (int i = threadIdx.x; i < ct * 16; i += kGateThreads) {
       const int c = i >> 4, part = i & 15;
-      means_s[i] = __ldg(reinterpret_cast<const uint4*>(
+      const uint4 x = __ldg(reinterpret_cast<const uint4*>(
           means + ((int64_t)(slot0 + c0 + c) * p.Hkv + hk) * kHeadDim + part * 8));
+      float f[8];
+      unpack8(x, f);
+      means_s[c * 32 + part * 2] = make_float4(f[0], f[1], f[2], f[3]);
+      means_s[c * 32 + part * 2 + 1] = make_float4(f[4], f[5], f[6], f[7]);
     }
     __syncthreads();
     for (int row = grp; row < nrows; row += kGateGroups) {    // row = token-major, head-minor
       const int tl = row / p.G, hl = row - tl * p.G;
       const int tok = tok_lo + tl;
       const int cend = min(ct, (tok - s0) / p.C - c0);        // this row's candidates in the tile
-      if (cend <= 0) continue;                                // uniform over the 16 lanes
-      float qf[8];
+      if (cend <= 0) continue;                                // uniform over the 4 lanes
+      float qf[4][8];
       {
-        const uint4 x = __ldg(reinterpret_cast<const uint4*>(
-            q + (int64_t)tok * p.sq_t + (int64_t)(hk * p.G + hl) * p.sq_h + lane * 8));
-        qf[0] = bf16_lo(x.x); qf[1] = bf16_hi(x.x); qf[2] = bf16_lo(x.y); qf[3] = bf16_hi(x.y);
-        qf[4] = bf16_lo(x.z); qf[5] = bf16_hi(x.z); qf[6] = bf16_lo(x.w); qf[7] = bf16_hi(x.w);
+        const __nv_bfloat16* qrow = q + (int64_t)tok * p.sq_t + (int64_t)(hk * p.G + hl) * p.sq_h;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          unpack8(__ldg(reinterpret_cast<const uint4*>(qrow + (t + 4 * k) * 8)), qf[k]);
       }
       for (int c = 0; c < cend; ++c) {
-        const uint4 m = means_s[c * 16 + lane];
-        float s = qf[0] * bf16_lo(m.x);
-        s = __fmaf_rn(qf[1], bf16_hi(m.x), s);
-        s = __fmaf_rn(qf[2], bf16_lo(m.y), s);
-        s = __fmaf_rn(qf[3], bf16_hi(m.y), s);
-        s = __fmaf_rn(qf[4], bf16_lo(m.z), s);
-        s = __fmaf_rn(qf[5], bf16_hi(m.z), s);
-        s = __fmaf_rn(qf[6], bf16_lo(m.w), s);
-        s = __fmaf_rn(qf[7], bf16_hi(m.w), s);
-        s = __fadd_rn(s, __shfl_xor_sync(gmask, s, 8));
-        s = __fadd_rn(s, __shfl_xor_sync(gmask, s, 4));
+        const float4* m = means_s + c * 32;
+        float acc[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[k] = dot8(qf[k], m[(t + 4 * k) * 2], m[(t + 4 * k) * 2 + 1]);
+        // halving tree over the 16 block sums: (l, l+8), (l, l+4) in-lane, (l, l+2), (l, l+1) across lanes
+        float s = __fadd_rn(__fadd_rn(acc[0], acc[2]), __fadd_rn(acc[1], acc[3]));
         s = __fadd_rn(s, __shfl_xor_sync(gmask, s, 2));
         s = __fadd_rn(s, __shfl_xor_sync(gmask, s, 1));
-        if (lane == (c & 15))
+        if (t == (c & 3))
           cand[c] = ((unsigned long long)float_key(s) << 32) |
                     (unsigned long long)(0xFFFFFFFFu - (uint32_t)(slot0 + c0 + c));
       }
       unsigned long long* best = best_s + (size_t)row * hist;
-      for (int i = lane; i < hist; i += 16) wins[i] = 0ull;
+      for (int i = t; i < hist; i += 4) wins[i] = 0ull;
       __syncwarp(gmask);
       // the `hist` largest of best[0..hist) U cand[0..cend), by repeated arg-max
       for (int r = 0; r < hist; ++r) {
         unsigned long long mine = 0ull;
         int mine_i = -1;
-        for (int i = lane; i < hist + cend; i += 16) {
+        for (int i = t; i < hist + cend; i += 4) {
           const unsigned long long kk = i < hist ? best[i] : cand[i - hist];
           if (kk > mine) { mine = kk; mine_i = i; }
         }
         unsigned long long top = mine;
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) {
+        for (int o = 2; o > 0; o >>= 1) {
           const unsigned long long other = __shfl_xor_sync(gmask, top, o);
           top = other > top ? other : top;
         }
@@ -221,7 +239,7 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
         __syncwarp(gmask);
       }
       __syncwarp(gmask);
-      for (int i = lane; i < hist; i += 16) best[i] = wins[i];
+      for (int i = t; i < hist; i += 4) best[i] = wins[i];
       __syncwarp(gmask);
     }
   }
@@ -242,7 +260,7 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
 }
 
 static size_t gate_smem_bytes(const Params& p) {
-  return (size_t)kCandTile * 16 * sizeof(uint4) + (size_t)kGateGroups * kCandTile * 8 +
+  return (size_t)kCandTile * 32 * sizeof(float4) + (size_t)kGateGroups * kCandTile * 8 +
          (size_t)kGateGroups * p.hist * 8 + (size_t)kGateRows * p.hist * 8 + (size_t)p.mc * 4;
 }
 
