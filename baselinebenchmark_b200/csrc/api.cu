@@ -34,19 +34,26 @@ int check_problem(const moba_problem_t* p) {
     if (strides[i] <= 0) return MOBA_E_SHAPE;
     if (strides[i] % 8 != 0) return MOBA_E_ALIGN;          // 16-byte vector and TMA accesses
   }
+  if (p->q_tokens < 0 || p->q_token_begin < 0) return MOBA_E_SHAPE;
+  if (p->q_tokens > 0 && p->q_token_begin + p->q_tokens > p->total_tokens) return MOBA_E_SHAPE;
+  if (p->q_tokens == 0 && p->q_token_begin != 0) return MOBA_E_SHAPE;
+  if (p->total_tokens >= ((int64_t)1 << 31)) return MOBA_E_UNSUPPORTED;
   const int64_t mc = (p->max_seqlen + (int64_t)p->chunk_size - 1) / p->chunk_size;
   if (mc * p->batch > (int64_t)1 << 24) return MOBA_E_UNSUPPORTED;
   if (mc > 16384) return MOBA_E_UNSUPPORTED;               // per-CTA list tables live in shared memory
   const int64_t hist = (p->topk - 1 < mc - 1) ? p->topk - 1 : mc - 1;
   const int64_t np = (hist > 0 ? hist : 0) + 1;
   // entry ids (row * partials + rank) are int32, like the reference's int32 offsets (routing.py:1094-1100)
-  if (p->total_tokens * p->num_q_heads * np >= ((int64_t)1 << 31)) return MOBA_E_UNSUPPORTED;
+  const int64_t tq = p->q_tokens > 0 ? p->q_tokens : p->total_tokens;
+  if (tq * p->num_q_heads * np >= ((int64_t)1 << 31)) return MOBA_E_UNSUPPORTED;
   return MOBA_OK;
 }
 
 Params make_params(const moba_problem_t* p) {
   Params r;
   r.T = p->total_tokens;
+  r.Tq = p->q_tokens > 0 ? p->q_tokens : p->total_tokens;
+  r.win_lo = p->q_tokens > 0 ? (int)p->q_token_begin : 0;
   r.B = p->batch;
   r.Hq = p->num_q_heads;
   r.Hkv = p->num_kv_heads;
@@ -60,7 +67,7 @@ Params make_params(const moba_problem_t* p) {
   r.hist = (r.topk - 1 < r.mc - 1) ? r.topk - 1 : r.mc - 1;       // parallel.py:303
   if (r.hist < 0) r.hist = 0;
   r.NP = r.hist + 1;
-  r.rows = r.T * r.Hq;
+  r.rows = r.Tq * r.Hq;
   r.lists = (int64_t)r.slots * r.Hkv;
   r.sq_t = p->q_stride_token; r.sq_h = p->q_stride_head;
   r.sk_t = p->k_stride_token; r.sk_h = p->k_stride_head;
@@ -131,7 +138,7 @@ int attend_dispatch(const moba_problem_t* p, const Params& r, const void* q, con
 
 extern "C" {
 
-int moba_b200_abi_version(void) { return 1; }
+int moba_b200_abi_version(void) { return 2; }
 
 const char* moba_b200_strerror(int code) {
   switch (code) {
@@ -316,6 +323,7 @@ int moba_forward_host(const moba_problem_t* p, const void* q_host, const void* k
   if (!q_host || !k_host || !v_host || !cu_host || !out_host) return MOBA_E_NULL;
   if (workspace == nullptr || workspace_bytes < need) return MOBA_E_WORKSPACE;
   const Params r = make_params(p);
+  if (r.Tq != r.T) return MOBA_E_UNSUPPORTED;             // the host variant runs whole problems
   // host tensors are taken as contiguous [T, H, D]
   if (r.sq_h != kHeadDim || r.sq_t != (int64_t)r.Hq * kHeadDim || r.sk_h != kHeadDim ||
       r.sk_t != (int64_t)r.Hkv * kHeadDim || r.sv_h != kHeadDim || r.sv_t != (int64_t)r.Hkv * kHeadDim ||

@@ -109,9 +109,9 @@ attend_mma_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bflo
       int64_t off = 0;
       if (r < it.nrows) {
         if (it.causal) {
-          const int64_t row = (int64_t)(it.tok0 + r) * p.Hq + it.head;
-          e = (int32_t)(row * p.NP);
-          off = (int64_t)(it.tok0 + r) * p.sq_t + (int64_t)it.head * p.sq_h;
+          const int64_t tl = it.tok0 - p.win_lo + r;          // window-relative token
+          e = (int32_t)((tl * p.Hq + it.head) * p.NP);
+          off = tl * p.sq_t + (int64_t)it.head * p.sq_h;
         } else {
           e = row_list[it.row_start + r];
           const int64_t row = e / p.NP;

@@ -119,8 +119,9 @@ __device__ __forceinline__ bool next_item(const Params& p, const KernelArgs& a, 
     int64_t off = 0;
     if (r < it.nrows) {
       if (it.causal) {
-        e = (int32_t)(((int64_t)(it.tok0 + r) * p.Hq + it.head) * p.NP);
-        off = (int64_t)(it.tok0 + r) * p.sq_t + (int64_t)it.head * p.sq_h;
+        const int64_t tl = it.tok0 - p.win_lo + r;            // window-relative token
+        e = (int32_t)((tl * p.Hq + it.head) * p.NP);
+        off = tl * p.sq_t + (int64_t)it.head * p.sq_h;
       } else {
         e = a.row_list[it.row_start + r];
         const int64_t row = e / p.NP;

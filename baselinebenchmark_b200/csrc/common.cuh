@@ -15,7 +15,9 @@ constexpr int kMaxTopk = 64;             // parallel.py:436
 
 // Launch-time view of a problem, passed to kernels by value.
 struct Params {
-  int64_t T;
+  int64_t T;                             // tokens of k / v (and of cu_seqlens)
+  int64_t Tq;                            // query tokens: the window [win_lo, win_lo + Tq) of the packed tokens
+  int win_lo;                            // q, out, selected and the partials are indexed by token - win_lo
   int B, Hq, Hkv, G, D;
   int max_seqlen, C, topk;
   int mc, slots, hist, NP;               // NP = partial results per row
@@ -99,6 +101,8 @@ __device__ __forceinline__ Item decode_item(const Params& p, int i, int n_routed
   const Slot s = slot_of(cu, b, j, p.C);
   const int tok0 = s.start + ti * tile_rows;
   if (ti < 0 || tok0 >= s.end) return it;
+  // the query window starts and ends on slot boundaries: a tile is inside or outside
+  if (tok0 < p.win_lo || tok0 >= p.win_lo + p.Tq) return it;
   it.valid = 1;
   it.causal = 1;
   it.tok0 = tok0;

@@ -161,9 +161,11 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
 
   const int b = blockIdx.z, hk = blockIdx.y;
   const int s0 = cu[b], s1 = cu[b + 1];
-  const int tok_lo = s0 + blockIdx.x * tokens_per_cta;
-  if (tok_lo >= s1) return;
-  const int ntok = min(tokens_per_cta, s1 - tok_lo);
+  // tokens of this CTA, clipped to the sequence and to the query window
+  const int tok_lo = max(s0 + blockIdx.x * tokens_per_cta, p.win_lo);
+  const int tok_hi = min(min(s0 + (blockIdx.x + 1) * tokens_per_cta, s1), p.win_lo + (int)p.Tq);
+  if (tok_lo >= tok_hi) return;
+  const int ntok = tok_hi - tok_lo;
   const int nrows = ntok * p.G;
   const int grp = threadIdx.x >> 2, t = threadIdx.x & 3;
   const unsigned gmask = 0xFu << (threadIdx.x & 28);          // the 4 lanes of this group
@@ -196,7 +198,7 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
       if (cend <= 0) continue;                                // uniform over the 4 lanes
       float qf[4][8];
       {
-        const __nv_bfloat16* qrow = q + (int64_t)tok * p.sq_t + (int64_t)(hk * p.G + hl) * p.sq_h;
+        const __nv_bfloat16* qrow = q + (int64_t)(tok - p.win_lo) * p.sq_t + (int64_t)(hk * p.G + hl) * p.sq_h;
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           unpack8(__ldg(reinterpret_cast<const uint4*>(qrow + (t + 4 * k) * 8)), qf[k]);
@@ -250,7 +252,7 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
     const int hl = rem / ntok, tl = rem - hl * ntok;
     const unsigned long long w = best_s[(size_t)(tl * p.G + hl) * hist + r];
     const int slot = w ? (int)(0xFFFFFFFFu - (uint32_t)(w & 0xFFFFFFFFull)) : -1;
-    selected[((int64_t)r * p.Hq + (hk * p.G + hl)) * p.T + tok_lo + tl] = slot;
+    selected[((int64_t)r * p.Hq + (hk * p.G + hl)) * p.Tq + (tok_lo - p.win_lo) + tl] = slot;
     if (slot >= 0) atomicAdd(&cnt_s[slot - slot0], 1);
   }
   __syncthreads();

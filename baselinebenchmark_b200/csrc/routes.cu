@@ -81,9 +81,11 @@ scatter_routes_kernel(Params p, const int32_t* __restrict__ cu, const int32_t* _
   int32_t* base_s = sm + p.mc;       // [mc] first position reserved for this CTA
   const int b = blockIdx.z, hk = blockIdx.y;
   const int s0 = cu[b], s1 = cu[b + 1];
-  const int tok_lo = s0 + blockIdx.x * kScatterTokens;
-  if (tok_lo >= s1) return;
-  const int ntok = min(kScatterTokens, s1 - tok_lo);
+  const int tok_lo = max(s0 + blockIdx.x * kScatterTokens, p.win_lo);
+  const int tok_hi = min(min(s0 + (blockIdx.x + 1) * kScatterTokens, s1), p.win_lo + (int)p.Tq);
+  if (tok_lo >= tok_hi) return;
+  const int ntok = tok_hi - tok_lo;
+  const int loc = tok_lo - p.win_lo;             // window-relative token of the first row
   const int slot0 = b * p.mc;
   const int n = p.hist * p.G * ntok;             // entries (rank, head, token), token fastest
   for (int i = threadIdx.x; i < p.mc; i += kScatterThreads) cnt_s[i] = 0;
@@ -91,7 +93,7 @@ scatter_routes_kernel(Params p, const int32_t* __restrict__ cu, const int32_t* _
   for (int i = threadIdx.x; i < n; i += kScatterThreads) {
     const int tl = i % ntok, rh = i / ntok;
     const int hl = rh % p.G, r = rh / p.G;
-    const int slot = selected[((int64_t)r * p.Hq + hk * p.G + hl) * p.T + tok_lo + tl];
+    const int slot = selected[((int64_t)r * p.Hq + hk * p.G + hl) * p.Tq + loc + tl];
     if (slot >= 0) atomicAdd(&cnt_s[slot - slot0], 1);
   }
   __syncthreads();
@@ -105,8 +107,8 @@ scatter_routes_kernel(Params p, const int32_t* __restrict__ cu, const int32_t* _
     const int tl = i % ntok, rh = i / ntok;
     const int hl = rh % p.G, r = rh / p.G;
     const int head = hk * p.G + hl;
-    const int slot = selected[((int64_t)r * p.Hq + head) * p.T + tok_lo + tl];
-    const int64_t entry = ((int64_t)(tok_lo + tl) * p.Hq + head) * p.NP + r + 1;
+    const int slot = selected[((int64_t)r * p.Hq + head) * p.Tq + loc + tl];
+    const int64_t entry = ((int64_t)(loc + tl) * p.Hq + head) * p.NP + r + 1;
     if (slot >= 0) {
       const int c = slot - slot0;
       const int pos = offsets[(int64_t)slot * p.Hkv + hk] + base_s[c] + atomicAdd(&cnt_s[c], 1);
@@ -174,7 +176,7 @@ merge_kernel(Params p, const float* __restrict__ partial_out, const float* __res
     pk.x = *reinterpret_cast<uint32_t*>(&lo);
     pk.y = *reinterpret_cast<uint32_t*>(&hi);
     *reinterpret_cast<uint2*>(out + t * p.so_t + (int64_t)h * p.so_h + lane * 4) = pk;
-    if (lse_out != nullptr && lane == 0) lse_out[(int64_t)h * p.T + t] = logf(tot) + mx;
+    if (lse_out != nullptr && lane == 0) lse_out[(int64_t)h * p.Tq + t] = logf(tot) + mx;
   }
 }
 

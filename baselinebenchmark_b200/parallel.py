@@ -24,13 +24,14 @@ __all__ = ["parallel_moba", "moba_attn_varlen", "moba_forward", "make_problem", 
 _workspaces: dict = {}
 
 
-def _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk) -> None:
-    """parallel.py:410-446, message for message where it matters to callers."""
+def _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, windowed: bool = False) -> None:
+    """parallel.py:410-446, message for message where it matters to callers.
+    `windowed`: q holds a window of the packed tokens, so its token count may differ from k's."""
     if q.ndim != 3 or k.ndim != 3 or v.ndim != 3:
         raise ValueError("q, k, and v must have shape [tokens, heads, head_dim]")
     if k.shape != v.shape:
         raise ValueError(f"k and v must have identical shapes, got {k.shape} and {v.shape}")
-    if q.shape[0] != k.shape[0] or q.shape[2] != k.shape[2]:
+    if (q.shape[0] != k.shape[0] and not windowed) or q.shape[2] != k.shape[2]:
         raise ValueError(
             f"q and k/v must have the same token count and head dimension, got q={q.shape}, k={k.shape}")
     if q.device != k.device or q.device != v.device or q.device.type != "cuda":
@@ -65,9 +66,13 @@ def _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk) -> No
             raise NotImplementedError(f"{name} must be contiguous in its last dimension")
 
 
-def make_problem(q, k, v, out, cu_seqlens, max_seqlen, chunk, topk, attend_impl=_lib.ATTEND_TCGEN05):
+def make_problem(q, k, v, out, cu_seqlens, max_seqlen, chunk, topk, attend_impl=_lib.ATTEND_TCGEN05,
+                 q_token_begin=None):
+    """struct moba_problem for these tensors.  With `q_token_begin` set, q/out hold the
+    packed tokens [q_token_begin, q_token_begin + q.shape[0]) and k/v all of them."""
     return _lib.Problem(
-        total_tokens=q.shape[0], batch=cu_seqlens.numel() - 1, num_q_heads=q.shape[1],
+        q_token_begin=q_token_begin or 0, q_tokens=q.shape[0] if q_token_begin is not None else 0,
+        total_tokens=k.shape[0], batch=cu_seqlens.numel() - 1, num_q_heads=q.shape[1],
         num_kv_heads=k.shape[1], head_dim=q.shape[2], max_seqlen=max_seqlen, chunk_size=chunk,
         topk=topk, attend_impl=attend_impl,
         q_stride_token=q.stride(0), q_stride_head=q.stride(1),
@@ -93,13 +98,20 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 
 def moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, *,
                  return_lse: bool = False, return_selected: bool = False,
-                 attend_impl: int = _lib.ATTEND_TCGEN05, workspace: Optional[torch.Tensor] = None
+                 attend_impl: int = _lib.ATTEND_TCGEN05, workspace: Optional[torch.Tensor] = None,
+                 q_token_begin: Optional[int] = None
                  ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
     """Runs the operator and optionally returns the final LSE [Hq, T] (fp32) and
-    the routing decision selected[hist, Hq, T] (int32, -1 padded)."""
-    _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)
+    the routing decision selected[hist, Hq, T] (int32, -1 padded).
+
+    `q_token_begin` (context parallelism): q holds only the packed tokens
+    [q_token_begin, q_token_begin + q.shape[0]), a window that starts and ends on
+    chunk boundaries, while k, v and cu_seqlens describe every token; outputs
+    cover the window."""
+    _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, windowed=q_token_begin is not None)
     out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
-    prob = make_problem(q, k, v, out, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, attend_impl)
+    prob = make_problem(q, k, v, out, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, attend_impl,
+                        q_token_begin)
     dims = _lib.Dims()
     _lib.check(_lib.lib().moba_problem_dims(C.byref(prob), C.byref(dims)))
     need = workspace_bytes(prob)

@@ -62,6 +62,14 @@ typedef struct moba_problem {
   int64_t k_stride_token, k_stride_head;
   int64_t v_stride_token, v_stride_head;
   int64_t o_stride_token, o_stride_head;
+  /* Query window, for context-parallel callers (the reference has none: it is
+   * rendered with enable_cp=False, native_moba.py:69).  With q_tokens > 0 only
+   * the packed tokens [q_token_begin, q_token_begin + q_tokens) are queries:
+   * q, out, lse_out and selected_out then hold q_tokens tokens (token 0 of q is
+   * packed token q_token_begin) while k, v and cu_seqlens still describe all
+   * total_tokens.  The window must start and end on chunk boundaries of its
+   * sequences (or at sequence ends).  q_tokens == 0: every token is a query. */
+  int64_t q_token_begin, q_tokens;
 } moba_problem_t;
 
 /* Derived sizes: mc = ceil(max_seqlen / chunk), slots = B*mc,
@@ -71,7 +79,7 @@ typedef struct moba_dims {
   int32_t slots;            /* B * mc                                            */
   int32_t hist;             /* historical chunks selected per query, may be <= 0 */
   int32_t partials;         /* max(hist,0) + 1 partial results per (token, head) */
-  int64_t rows;             /* T * Hq                                            */
+  int64_t rows;             /* query tokens * Hq                                 */
   int64_t lists;            /* slots * Hkv routed query lists                    */
 } moba_dims_t;
 

@@ -34,7 +34,7 @@ def test_header_symbols_are_exported(lib):
     assert declared == set(_lib.SYMBOLS)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.moba_b200_abi_version() == 1
+    assert lib.moba_b200_abi_version() == 2
 
 
 def test_problem_check_codes(lib):

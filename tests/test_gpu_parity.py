@@ -318,3 +318,21 @@ def test_public_operator_names():
     assert native_moba._supported(qd)
     with pytest.raises(NotImplementedError):
         pkg.parallel_moba(qd.half(), kd.half(), vd.half(), cud, 512, 128, 3)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_query_window_equals_full_run(impl):
+    """Context-parallel building block: the operator run on a chunk-aligned query
+    window, with K/V of the whole sequence, returns exactly the rows of the full run."""
+    lens = (2048, 1280)
+    q, k, v, cu = _case_inputs(lens, 8, 2, 128, seed=21)
+    qd, kd, vd = G.to_dev(q, k, v)
+    cud = torch.from_numpy(cu).cuda()
+    full, full_lse, full_sel = parallel.moba_forward(qd, kd, vd, cud, 2048, 128, 4, return_lse=True,
+                                                     return_selected=True, attend_impl=impl)
+    for lo, hi in [(0, 1024), (1024, 2048), (2048, 2048 + 1280), (512, 2560)]:
+        out, lse, sel = parallel.moba_forward(qd[lo:hi].contiguous(), kd, vd, cud, 2048, 128, 4, return_lse=True,
+                                              return_selected=True, attend_impl=impl, q_token_begin=lo)
+        assert torch.equal(sel, full_sel[:, :, lo:hi])
+        assert torch.equal(out, full[lo:hi])
+        assert torch.equal(lse, full_lse[:, lo:hi])
