@@ -236,7 +236,7 @@ def reference_arm(args, rank):
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def workload_config(n_gpus):
@@ -247,7 +247,21 @@ def workload_config(n_gpus):
             "l2": "inputs (3 GiB per GPU) exceed the 126 MB L2"}
 
 
+_JSON_FD = None
+
+
+def emit(line: dict) -> None:
+    """The one JSON line goes to the original stdout; everything else that
+    libraries print there (NCCL's version banner) is sent to stderr."""
+    data = (json.dumps(line) + "\n").encode()
+    os.write(_JSON_FD if _JSON_FD is not None else 1, data)
+
+
 def main():
+    global _JSON_FD
+    sys.stdout.flush()
+    _JSON_FD = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
@@ -359,7 +373,7 @@ def main():
                          "attend": float(stage_ms[3]), "merge": float(stage_ms[4])},
             "cpu_baseline": cpu, "clocks": clocks.summary(), "also": also,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if dist is not None:
         dist.destroy_process_group()
 
