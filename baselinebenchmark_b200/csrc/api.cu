@@ -134,6 +134,32 @@ int attend_dispatch(const moba_problem_t* p, const Params& r, const void* q, con
                                 partial_out, partial_lse, work_counter, status, st);
 }
 
+// ---- host-buffer variant: side streams and window bookkeeping ----------------
+constexpr int kHostWindowsPerSeq = 8;     // query windows a sequence is cut into
+constexpr int kHostMaxUnits = 256;        // [0, prefix] pairs kept alive in the workspace
+
+struct HostStreams {
+  cudaStream_t h2d, d2h;
+};
+// Two copy streams per device, created on first use and kept for the process.
+HostStreams* host_streams() {
+  static HostStreams streams[64];
+  static bool ready[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!ready[dev]) {
+    if (cudaStreamCreateWithFlags(&streams[dev].h2d, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    if (cudaStreamCreateWithFlags(&streams[dev].d2h, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    ready[dev] = true;
+  }
+  return &streams[dev];
+}
+
+__global__ void set_pair_kernel(int32_t* dst, int32_t a, int32_t b) {
+  dst[0] = a;
+  dst[1] = b;
+}
+
 }  // namespace
 
 extern "C" {
@@ -304,10 +330,12 @@ int moba_workspace_size_host(const moba_problem_t* p, size_t* bytes) {
   size_t core = 0;
   const int rc = moba_workspace_size(p, &core);
   if (rc != MOBA_OK) return rc;
+  if (bytes == nullptr) return MOBA_E_NULL;
   const Params r = make_params(p);
   size_t extra = align_up((size_t)r.T * r.Hq * kHeadDim * 2) * 2 +      // q, out
                  align_up((size_t)r.T * r.Hkv * kHeadDim * 2) * 2 +     // k, v
                  align_up((size_t)(r.B + 1) * 4) +                      // cu_seqlens
+                 align_up((size_t)kHostMaxUnits * 2 * 4) +              // [0, prefix] pairs of the windows
                  align_up((size_t)r.rows * 4);                          // lse
   *bytes = core + extra;
   return MOBA_OK;
@@ -331,31 +359,95 @@ int moba_forward_host(const moba_problem_t* p, const void* q_host, const void* k
     return MOBA_E_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
   char* base = static_cast<char*>(workspace) + core;
-  const size_t qbytes = (size_t)r.T * r.Hq * kHeadDim * 2, kbytes = (size_t)r.T * r.Hkv * kHeadDim * 2;
+  const size_t qrow = (size_t)r.Hq * kHeadDim * 2, krow = (size_t)r.Hkv * kHeadDim * 2;
+  const size_t qbytes = (size_t)r.T * qrow, kbytes = (size_t)r.T * krow;
   char* dq = base;               base += align_up(qbytes);
   char* dout = base;             base += align_up(qbytes);
   char* dk = base;               base += align_up(kbytes);
   char* dv = base;               base += align_up(kbytes);
   int32_t* dcu = (int32_t*)base; base += align_up((size_t)(r.B + 1) * 4);
+  int32_t* dpairs = (int32_t*)base; base += align_up((size_t)kHostMaxUnits * 2 * 4);
   float* dlse = (float*)base;
   cudaError_t e;
-  if ((e = cudaMemcpyAsync(dq, q_host, qbytes, cudaMemcpyHostToDevice, st)) != cudaSuccess) return (int)e;
-  if ((e = cudaMemcpyAsync(dk, k_host, kbytes, cudaMemcpyHostToDevice, st)) != cudaSuccess) return (int)e;
-  if ((e = cudaMemcpyAsync(dv, v_host, kbytes, cudaMemcpyHostToDevice, st)) != cudaSuccess) return (int)e;
-  if ((e = cudaMemcpyAsync(dcu, cu_host, (size_t)(r.B + 1) * 4, cudaMemcpyHostToDevice, st)) != cudaSuccess)
-    return (int)e;
-  const Workspace w = carve(r, workspace);
-  rc = moba_forward(p, dq, dk, dv, dcu, dout, lse_out_host ? dlse : nullptr, nullptr, workspace, core, stream);
-  if (rc != MOBA_OK) return rc;
-  if ((e = cudaMemcpyAsync(out_host, dout, qbytes, cudaMemcpyDeviceToHost, st)) != cudaSuccess) return (int)e;
-  if (lse_out_host &&
-      (e = cudaMemcpyAsync(lse_out_host, dlse, (size_t)r.rows * 4, cudaMemcpyDeviceToHost, st)) != cudaSuccess)
-    return (int)e;
-  if (selected_out_host && r.hist > 0 &&
-      (e = cudaMemcpyAsync(selected_out_host, w.selected, (size_t)r.hist * r.rows * 4, cudaMemcpyDeviceToHost, st)) !=
-          cudaSuccess)
-    return (int)e;
-  return MOBA_OK;
+
+  if (lse_out_host || selected_out_host) {
+    // one call on the whole batch: the extra outputs keep their whole-batch layouts
+    if ((e = cudaMemcpyAsync(dq, q_host, qbytes, cudaMemcpyHostToDevice, st)) != cudaSuccess) return (int)e;
+    if ((e = cudaMemcpyAsync(dk, k_host, kbytes, cudaMemcpyHostToDevice, st)) != cudaSuccess) return (int)e;
+    if ((e = cudaMemcpyAsync(dv, v_host, kbytes, cudaMemcpyHostToDevice, st)) != cudaSuccess) return (int)e;
+    if ((e = cudaMemcpyAsync(dcu, cu_host, (size_t)(r.B + 1) * 4, cudaMemcpyHostToDevice, st)) != cudaSuccess)
+      return (int)e;
+    const Workspace w = carve(r, workspace);
+    rc = moba_forward(p, dq, dk, dv, dcu, dout, lse_out_host ? dlse : nullptr, nullptr, workspace, core, stream);
+    if (rc != MOBA_OK) return rc;
+    if ((e = cudaMemcpyAsync(out_host, dout, qbytes, cudaMemcpyDeviceToHost, st)) != cudaSuccess) return (int)e;
+    if (lse_out_host &&
+        (e = cudaMemcpyAsync(lse_out_host, dlse, (size_t)r.rows * 4, cudaMemcpyDeviceToHost, st)) != cudaSuccess)
+      return (int)e;
+    if (selected_out_host && r.hist > 0 &&
+        (e = cudaMemcpyAsync(selected_out_host, w.selected, (size_t)r.hist * r.rows * 4, cudaMemcpyDeviceToHost,
+                             st)) != cudaSuccess)
+      return (int)e;
+    return MOBA_OK;
+  }
+
+  // Pipelined path.  A query only sees keys at or before its own position, so a
+  // sequence can be processed in chunk-aligned query windows, window w needing K/V
+  // of the sequence only up to the end of w: copy window w+1 in and window w-1 out
+  // on two side streams while window w computes.  All copies are contiguous.
+  HostStreams* hs = host_streams();
+  if (hs == nullptr) return (int)cudaErrorUnknown;
+  cudaEvent_t ev;
+  if ((e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming)) != cudaSuccess) return (int)e;
+  // side streams start after everything already queued on the caller's stream
+  cudaEventRecord(ev, st);
+  cudaStreamWaitEvent(hs->h2d, ev, 0);
+  cudaStreamWaitEvent(hs->d2h, ev, 0);
+  cudaEventDestroy(ev);
+  int unit = 0;
+  int status = MOBA_OK;
+  for (int b = 0; b < r.B && status == MOBA_OK; ++b) {
+    const int64_t s0 = cu_host[b], s1 = cu_host[b + 1];
+    const int64_t nchunks = (s1 - s0 + r.C - 1) / r.C;
+    int64_t per = (nchunks + kHostWindowsPerSeq - 1) / kHostWindowsPerSeq;      // chunks per window
+    if ((int64_t)r.B * kHostWindowsPerSeq > kHostMaxUnits) per = nchunks;        // many sequences: one window each
+    if (per < 1) per = 1;
+    for (int64_t c0 = 0; c0 < nchunks && status == MOBA_OK; c0 += per, ++unit) {
+      const int64_t lo = s0 + c0 * r.C;
+      const int64_t hi = (c0 + per) * r.C < s1 - s0 ? s0 + (c0 + per) * r.C : s1;
+      cudaEvent_t ev_in, ev_out;
+      if ((e = cudaEventCreateWithFlags(&ev_in, cudaEventDisableTiming)) != cudaSuccess) return (int)e;
+      if ((e = cudaEventCreateWithFlags(&ev_out, cudaEventDisableTiming)) != cudaSuccess) return (int)e;
+      cudaMemcpyAsync(dq + lo * qrow, (const char*)q_host + lo * qrow, (hi - lo) * qrow, cudaMemcpyHostToDevice, hs->h2d);
+      cudaMemcpyAsync(dk + lo * krow, (const char*)k_host + lo * krow, (hi - lo) * krow, cudaMemcpyHostToDevice, hs->h2d);
+      e = cudaMemcpyAsync(dv + lo * krow, (const char*)v_host + lo * krow, (hi - lo) * krow, cudaMemcpyHostToDevice, hs->h2d);
+      if (e != cudaSuccess) return (int)e;
+      cudaEventRecord(ev_in, hs->h2d);
+      cudaStreamWaitEvent(st, ev_in, 0);
+      // the window as a problem of its own: the prefix [s0, hi) is the sequence
+      moba_problem_t sub = *p;
+      sub.total_tokens = hi - s0;
+      sub.batch = 1;
+      sub.q_token_begin = lo - s0;
+      sub.q_tokens = hi - lo;
+      int32_t* pair = dpairs + 2 * (unit % kHostMaxUnits);
+      set_pair_kernel<<<1, 1, 0, st>>>(pair, 0, (int32_t)(hi - s0));
+      status = moba_forward(&sub, dq + lo * qrow, dk + s0 * krow, dv + s0 * krow, pair, dout + lo * qrow, nullptr,
+                            nullptr, workspace, core, stream);
+      cudaEventRecord(ev_out, st);
+      cudaStreamWaitEvent(hs->d2h, ev_out, 0);
+      cudaMemcpyAsync((char*)out_host + lo * qrow, dout + lo * qrow, (hi - lo) * qrow, cudaMemcpyDeviceToHost, hs->d2h);
+      cudaEventDestroy(ev_in);
+      cudaEventDestroy(ev_out);
+    }
+  }
+  // the caller's stream completes when the last copy out has
+  if ((e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming)) != cudaSuccess) return (int)e;
+  cudaEventRecord(ev, hs->d2h);
+  cudaStreamWaitEvent(st, ev, 0);
+  cudaEventDestroy(ev);
+  if (status != MOBA_OK) return status;
+  return (int)cudaGetLastError();
 }
 
 }  // extern "C"

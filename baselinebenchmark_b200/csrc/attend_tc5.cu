@@ -19,6 +19,7 @@
 //
 // Warp roles (384 threads):
 //   warp 0      TMA producer: K and V tiles of 128 keys, two stages each
+//   warp 2      draws, decodes and resolves the next work item while the current one runs
 //   warp 1      MMA issuer: S = Q.K^T into TMEM, O += P.V with P read from TMEM; the
 //               warp runs convergent, one elected lane issues; owns the TMEM allocation
 //   warps 4-7   softmax of tile A: one thread per row (TMEM lane)
@@ -53,11 +54,13 @@ struct Ctrl {
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
   uint64_t s_full[2], p_full[2], o_full[2];
   uint32_t tmem_slot;
-  int32_t item;
   volatile int32_t abort;
-  int32_t pad;
-  int64_t qoff[2 * kTileM];
-  int32_t entry[2 * kTileM];
+  // Work items are drawn and resolved one item ahead by a spare warp: slot (n & 1)
+  // holds item n, its output entries and the offsets of its Q rows.
+  Item item[2];
+  int32_t done[2];
+  int64_t qoff[2][2 * kTileM];
+  int32_t entry[2][2 * kTileM];
 };
 
 constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + 6 * kTileBytes + sizeof(Ctrl);
@@ -100,21 +103,26 @@ struct KernelArgs {
   int32_t* status;
 };
 
-// Common head of an item, executed by all 384 threads: draw the next item,
-// resolve its rows and gather the Q rows into the two swizzled Q tiles.
-// Returns false when the queue is empty (or the kernel is aborting).
-__device__ __forceinline__ bool next_item(const Params& p, const KernelArgs& a, Ctrl& c, unsigned char* smem,
-                                          int n_routed, int n_items, Item& it) {
+// Runs in one spare warp while the other warps work on the current item: draws the
+// next item from the global queue (skipping empty own-chunk tiles), decodes it and
+// resolves its rows (output entry and Q row offset) into prefetch slot `slot`.
+__device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs& a, Ctrl& c, int slot,
+                                              int n_routed, int n_items) {
+  const int lane = threadIdx.x & 31;
+  Item it;
+  it.valid = 0;
+  int done = 0;
   for (;;) {
-    __syncthreads();                       // every role has finished the previous item
-    if (threadIdx.x == 0) c.item = c.abort ? 0x7fffffff : atomicAdd(a.work_counter, 1);
-    __syncthreads();
-    const int idx = c.item;
-    if (idx >= n_items) return false;
+    int idx = 0;
+    if (lane == 0) idx = c.abort ? 0x7fffffff : atomicAdd(a.work_counter, 1);
+    idx = __shfl_sync(0xffffffffu, idx, 0);
+    if (idx >= n_items) { done = 1; break; }
     it = decode_item(p, idx, n_routed, 2 * kTileM, a.cu, a.list_counts, a.list_offsets, a.tile_prefix);
     if (it.valid) break;
   }
-  for (int r = threadIdx.x; r < 2 * kTileM; r += kThreads) {
+  if (lane == 0) { c.item[slot] = it; c.done[slot] = done; }
+  if (done) return;
+  for (int r = lane; r < 2 * kTileM; r += 32) {
     int32_t e = -1;
     int64_t off = 0;
     if (r < it.nrows) {
@@ -129,10 +137,20 @@ __device__ __forceinline__ bool next_item(const Params& p, const KernelArgs& a, 
         off = t * p.sq_t + (row - t * p.Hq) * p.sq_h;
       }
     }
-    c.entry[r] = e;
-    c.qoff[r] = off;
+    c.entry[slot][r] = e;
+    c.qoff[slot][r] = off;
   }
-  __syncthreads();
+}
+
+// Common head of an item, executed by all 384 threads: take the prefetched item
+// of slot `slot` and gather its Q rows into the two swizzled Q tiles.  Returns
+// false when the queue is empty (or the kernel is aborting).
+__device__ __forceinline__ bool next_item(const KernelArgs& a, Ctrl& c, unsigned char* smem, int slot, Item& it) {
+  __syncthreads();                         // every role has finished the previous item; slot is filled
+  if (c.done[slot]) return false;
+  it = c.item[slot];
+  const int32_t* entry = c.entry[slot];
+  const int64_t* qoff = c.qoff[slot];
   // gather Q rows into two [2][128][64] blocks with the 128-byte swizzle TMA would produce
 #pragma unroll 1
   for (int i0 = threadIdx.x; i0 < 2 * kTileM * 16; i0 += 4 * kThreads) {
@@ -143,7 +161,7 @@ __device__ __forceinline__ bool next_item(const Params& p, const KernelArgs& a, 
       val[u] = make_uint4(0, 0, 0, 0);
       if (i < 2 * kTileM * 16) {
         const int r = i >> 4, ch = i & 15;
-        if (c.entry[r] >= 0) val[u] = __ldg(reinterpret_cast<const uint4*>(a.q + c.qoff[r] + ch * 8));
+        if (entry[r] >= 0) val[u] = __ldg(reinterpret_cast<const uint4*>(a.q + qoff[r] + ch * 8));
       }
     }
 #pragma unroll
@@ -296,7 +314,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
 
   if (warp < 4) {
     // =============================================== warps 0-3: TMA producer, MMA issuer, two spare warps
-    setmaxnreg_dec<64>();
+    setmaxnreg_dec<72>();
     uint32_t kc = 0, vc = 0;               // K / V tiles produced (warp 0) or consumed (warp 1) so far
     uint32_t pph0 = 0, pph1 = 0;           // p_full phases of tile A / B
     // warp-uniform copies of the TMEM base and of the low words of the shared-memory
@@ -307,7 +325,10 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     const uint32_t dk = __shfl_sync(0xffffffffu, desc_lo(sK, 16), 0);
     const uint32_t dv = __shfl_sync(0xffffffffu, desc_lo(sV, kHalfBytes), 0);
     const uint32_t el = elect_one();
-    while (next_item(p, a, c, smem, n_routed, n_items, it)) {
+    for (int n = 0;; ++n) {
+      // warp 2 runs one item ahead: it fills slot n & 1 while the others still work on item n - 1
+      if (warp == 2) prefetch_item(p, a, c, n & 1, n_routed, n_items);
+      if (!next_item(a, c, smem, n & 1, it)) break;
       const int ntiles = (it.kv_len + kBN - 1) / kBN;
       if (warp == 0 && lane == 0) {
         for (int j = 0; j < ntiles; ++j) {
@@ -422,10 +443,11 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     long long t_next = clock64();
     const long long t_kernel = t_next;
 #endif
-    while (next_item(p, a, c, smem, n_routed, n_items, it)) {
+    for (int n = 0; next_item(a, c, smem, n & 1, it); ++n) {
 #ifdef MOBA_TC5_TRACE
       if (threadIdx.x == 128) { TRACE_ADD(a, 8, t_next); atomicAdd(TRACE_BASE(a) + 9, 1ull); }
 #endif
+      const int32_t* entries = c.entry[n & 1];
       const int ntiles = (it.kv_len + kBN - 1) / kBN;
       const int qpos = it.tok0 + x * kTileM + row;
       const int lim = it.causal ? min(it.kv_len, qpos - it.kv_tok0 + 1) : it.kv_len;   // keys < lim are visible
@@ -454,7 +476,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
       if (ok) {
         oph ^= 1;
         tc_fence_after();
-        const int32_t e = c.entry[x * kTileM + row];
+        const int32_t e = entries[x * kTileM + row];
         const float inv = 1.f / l;
         float* dst = a.partial_out + (int64_t)(e >= 0 ? e : 0) * kHeadDim;
         uint32_t v[32];

@@ -114,10 +114,15 @@ int moba_forward_events(const moba_problem_t* p, const void* q, const void* k, c
                         const int32_t* cu_seqlens, void* out, float* lse_out, int32_t* selected_out,
                         void* workspace, size_t workspace_bytes, void* stream, void* const* events);
 
-/* Same call with HOST buffers (pinned memory recommended): copies q, k, v and
- * cu_seqlens to staging buffers inside `workspace`, runs moba_forward, copies
- * `out` (and lse_out / selected_out when given) back, all on `stream`.  The
- * caller synchronises the stream.  Use moba_workspace_size_host for sizing. */
+/* Same call with HOST buffers (pinned memory; cu_seqlens_host is also read by the
+ * CPU): copies q, k, v to staging buffers inside `workspace`, runs the operator
+ * and copies `out` back.  The caller synchronises `stream`, which completes after
+ * the last copy out.  Without the optional outputs the call is pipelined: every
+ * sequence is cut into chunk-aligned query windows (causality makes window w need
+ * K/V only up to its own end), and window w+1 is copied in and window w-1 copied
+ * out on two internal streams (created once per device) while window w computes;
+ * results are identical to moba_forward.  With lse_out / selected_out the whole
+ * batch runs as one call on `stream`.  Use moba_workspace_size_host for sizing. */
 int moba_workspace_size_host(const moba_problem_t* p, size_t* bytes);
 int moba_forward_host(const moba_problem_t* p, const void* q_host, const void* k_host,
                       const void* v_host, const int32_t* cu_seqlens_host, void* out_host,

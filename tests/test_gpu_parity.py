@@ -336,3 +336,32 @@ def test_query_window_equals_full_run(impl):
         assert torch.equal(sel, full_sel[:, :, lo:hi])
         assert torch.equal(out, full[lo:hi])
         assert torch.equal(lse, full_lse[:, lo:hi])
+
+
+def test_host_buffer_entry_point_matches_device_call():
+    """moba_forward_host (pinned host tensors, pipelined query windows) returns the bits of moba_forward."""
+    import ctypes as C
+    lens = (3000, 1100, 2048)
+    q, k, v, cu = _case_inputs(lens, 8, 2, 128, seed=33)
+    cud = torch.from_numpy(cu).cuda()
+    ref, ref_lse, ref_sel = parallel.moba_forward(*G.to_dev(q, k, v), cud, 3000, 128, 4, return_lse=True,
+                                                  return_selected=True)
+    hq, hk, hv = q.pin_memory(), k.pin_memory(), v.pin_memory()
+    hcu = torch.from_numpy(cu).pin_memory()
+    prob, _ = G.problem_for(q.cuda(), k.cuda(), v.cuda(), cud, 3000, 128, 4)
+    size = C.c_size_t(0)
+    _lib.check(_lib.lib().moba_workspace_size_host(C.byref(prob), C.byref(size)))
+    ws = torch.empty(size.value, dtype=torch.uint8, device="cuda")
+    for extra in (False, True):
+        hout = torch.zeros_like(q).pin_memory()
+        hlse = torch.zeros(8, sum(lens), dtype=torch.float32).pin_memory() if extra else None
+        hsel = torch.zeros(3, 8, sum(lens), dtype=torch.int32).pin_memory() if extra else None
+        for _ in range(2):                                   # back-to-back calls share the staging buffers
+            _lib.check(_lib.lib().moba_forward_host(
+                C.byref(prob), hq.data_ptr(), hk.data_ptr(), hv.data_ptr(), hcu.data_ptr(), hout.data_ptr(),
+                hlse.data_ptr() if extra else None, hsel.data_ptr() if extra else None,
+                ws.data_ptr(), ws.numel(), G.stream()))
+        torch.cuda.synchronize()
+        assert torch.equal(hout, ref.cpu())
+        if extra:
+            assert torch.equal(hlse, ref_lse.cpu()) and torch.equal(hsel, ref_sel.cpu())
