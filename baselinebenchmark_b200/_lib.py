@@ -21,7 +21,7 @@ SYMBOLS = (
     "moba_b200_abi_version", "moba_b200_strerror", "moba_problem_check", "moba_problem_dims",
     "moba_workspace_size", "moba_forward", "moba_forward_events", "moba_workspace_size_host", "moba_forward_host",
     "moba_chunk_metadata", "moba_chunk_means", "moba_gate_topk", "moba_compact_routes",
-    "moba_attend", "moba_merge", "moba_attend_tile_rows",
+    "moba_attend", "moba_merge", "moba_attend_tile_rows", "moba_route_static",
 )
 
 
@@ -83,6 +83,7 @@ def lib() -> C.CDLL:
         handle.moba_attend.argtypes = [pp, vp, vp, vp, i32p, i32p, i32p, i32p, i32p, vp, vp, i32p, vp]
         handle.moba_merge.argtypes = [pp, vp, vp, i32p, vp, vp, vp]
         handle.moba_attend_tile_rows.argtypes = [C.c_int]
+        handle.moba_route_static.argtypes = [pp, vp, vp, i32p, i32p, vp]
         _lib = handle
     return _lib
 

@@ -176,6 +176,7 @@ const char* moba_b200_strerror(int code) {
     case MOBA_E_TOPK: return "moba_topk must be in 1..64";
     case MOBA_E_ALIGN: return "pointers and strides must be multiples of 16 bytes";
     case MOBA_E_DEVICE: return "needs an sm_100 device and a driver that exports cuTensorMapEncodeTiled";
+    case MOBA_E_STATIC_LIMIT: return "problem exceeds the built-in scratch of moba_route_static (slots * kv heads * 128 <= 2 Mi)";
     default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
   }
 }

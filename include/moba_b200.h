@@ -37,7 +37,8 @@ enum {
   MOBA_E_NULL = -4,         /* a required pointer is null                        */
   MOBA_E_TOPK = -5,         /* moba_topk outside 1..64 (parallel.py:434-437)     */
   MOBA_E_ALIGN = -6,        /* base pointer or stride not 16-byte aligned        */
-  MOBA_E_DEVICE = -7        /* not an sm_100 device, or driver entry point missing */
+  MOBA_E_DEVICE = -7,       /* not an sm_100 device, or driver entry point missing */
+  MOBA_E_STATIC_LIMIT = -8  /* problem too large for the built-in scratch of moba_route_static */
 };
 
 /* Which implementation of the dense stage moba_attend/moba_forward run. */
@@ -185,6 +186,23 @@ int moba_attend(const moba_problem_t* p, const void* q, const void* k, const voi
  * when it is non-zero the output is filled with NaN instead of partial data. */
 int moba_merge(const moba_problem_t* p, const float* partial_out, const float* partial_lse,
                const int32_t* status, void* out, float* lse_out, void* stream);
+
+/* Routing without a workspace.  No counterpart in the reference, whose stages
+ * all allocate through torch; it exists for callers that cannot give the library
+ * device memory at call time (a server whose memory pool is fixed after start-up,
+ * a plugin called where allocation is not allowed, a client that owns nothing but
+ * its inputs and outputs).  Computes selected int32 [hist,Hq,T] from q and k like
+ * moba_chunk_means + moba_gate_topk, keeping the chunk means in a 4 MiB array that
+ * is part of the library image (held by every GPU that loads the library).
+ *   - limit: slots * num_kv_heads * 128 <= 2 Mi elements, otherwise
+ *     MOBA_E_STATIC_LIMIT;
+ *   - the first call on a device looks up the device address of that array; make
+ *     that first call outside any stream capture;
+ *   - all calls on a device share the array: calls whose kernels may overlap on the
+ *     GPU (unordered streams) race on it.  It needs no clearing between calls;
+ *   - performs no allocation and no host synchronisation. */
+int moba_route_static(const moba_problem_t* p, const void* q, const void* k, const int32_t* cu_seqlens,
+                      int32_t* selected, void* stream);
 
 /* Rows per routed work item that the selected attend implementation wants
  * (the tile_rows argument of moba_compact_routes). */
