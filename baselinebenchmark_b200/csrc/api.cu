@@ -102,7 +102,7 @@ Workspace carve(const Params& r, void* base) {
     return ptr;
   };
   const size_t lists = (size_t)r.lists;
-  w.zero_bytes = (lists + 64) * sizeof(int32_t);
+  w.zero_bytes = (lists + 512) * sizeof(int32_t);        // + work counter, status, debug counters
   w.list_counts = static_cast<int32_t*>(take(w.zero_bytes));
   w.work_counter = w.list_counts ? w.list_counts + lists : nullptr;
   w.status = w.list_counts ? w.list_counts + lists + 1 : nullptr;

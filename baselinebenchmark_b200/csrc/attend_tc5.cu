@@ -90,6 +90,18 @@ constexpr int kPolyPairs = MOBA_POLY_PAIRS;
 #define TRACE_ADD(args, slot, t0)
 #endif
 
+// Optional timeline (build with -DMOBA_TC5_TIMELINE): CTA 0 stores clock64 stamps of its
+// third item, tile steps 8-11, at status[64 + 16*j' + slot] (as 64-bit values).
+#ifdef MOBA_TC5_TIMELINE
+#define TL_STAMP(args, n, j, slot)                                                                          \
+  do {                                                                                                      \
+    if (blockIdx.x == 0 && (n) == 2 && (j) >= 8 && (j) < 12)                                                \
+      reinterpret_cast<long long*>(((uintptr_t)((args).status + 64) + 7) & ~(uintptr_t)7)[((j) - 8) * 16 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define TL_STAMP(args, n, j, slot)
+#endif
+
 struct KernelArgs {
   const __nv_bfloat16* q;
   const int32_t* cu;
@@ -184,10 +196,11 @@ __device__ __forceinline__ bool next_item(const KernelArgs& a, Ctrl& c, unsigned
 // -> P (bf16, written over the first 64 columns), running max / sum updated.
 template <bool kMasked>
 __device__ __forceinline__ void softmax_row(uint32_t tS, uint32_t tO, int j, int key0, int lim, float sl2,
-                                            float& m_ref, float& l) {
+                                            float& m_ref, float& l, const KernelArgs& a, int n) {
   uint32_t v[128];
   tmem_ld128(tS, v);
   tmem_wait_ld();
+  if (threadIdx.x == 128) TL_STAMP(a, n, j, 11);            // S loaded
   if (kMasked) {
 #pragma unroll
     for (int i = 0; i < 128; ++i) v[i] = (key0 + i < lim) ? v[i] : 0xff800000u;   // -inf
@@ -202,6 +215,7 @@ __device__ __forceinline__ void softmax_row(uint32_t tS, uint32_t tO, int j, int
   }
   const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
   const float m_new = fmaxf(m_ref, mx * sl2);
+  if (threadIdx.x == 128) TL_STAMP(a, n, j, 12);            // row max known
   if (__any_sync(0xffffffffu, m_new > m_ref + 8.f)) {
     const float alpha = (m_new == -INFINITY) ? 1.f : ex2_approx(m_ref - m_new);
     if (j > 0) {
@@ -228,6 +242,14 @@ __device__ __forceinline__ void softmax_row(uint32_t tS, uint32_t tO, int j, int
     for (int i = 0; i < 16; ++i) {
       const int e = ch * 32 + 2 * i;
       const uint64_t x = fma2(pack2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])), scale2, negm2);
+#ifdef MOBA_EXP_BF16X2
+      // both exponentials of the pair in one special-function op, in bf16 (the
+      // precision P is stored in anyway); the row sum adds the rounded values
+      const uint32_t pb = ex2_bf16x2(pack_bf16(lo2(x), hi2(x)));
+      const uint64_t pr = pack2(__uint_as_float(pb << 16), __uint_as_float(pb & 0xffff0000u));
+      if (i & 1) sum_b = add2(sum_b, pr); else sum_a = add2(sum_a, pr);
+      pk[i] = pb;
+#else
       uint64_t pr;
       if ((i & 7) < kPolyPairs) {
         pr = ex2_poly2(x);
@@ -236,12 +258,15 @@ __device__ __forceinline__ void softmax_row(uint32_t tS, uint32_t tO, int j, int
       }
       if (i & 1) sum_b = add2(sum_b, pr); else sum_a = add2(sum_a, pr);
       pk[i] = pack_bf16(lo2(pr), hi2(pr));
+#endif
     }
     tmem_st16(tS + ch * 16, pk);
   }
   const uint64_t sum = add2(sum_a, sum_b);
   l += lo2(sum) + hi2(sum);
+  if (threadIdx.x == 128) TL_STAMP(a, n, j, 13);            // exponentials done, stores issued
   tmem_wait_st();
+  if (threadIdx.x == 128) TL_STAMP(a, n, j, 14);            // stores complete
 }
 
 // Descriptor words.  Low word: start address >> 4 | (leading byte offset >> 4) << 16;
@@ -387,8 +412,10 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
           if (lane == 0) TRACE_ADD(a, 1, t_pa);
           pph0 ^= 1;
           tc_fence_after();
+          if (lane == 0) TL_STAMP(a, n, j, 0);               // P_A seen
           if (el) { if (vs) issue_pv<0, 1>(tm, dv, j == 0); else issue_pv<0, 0>(tm, dv, j == 0); }
           __syncwarp();
+          if (lane == 0) TL_STAMP(a, n, j, 1);               // PV_A issued
           if (more) {
             TRACE_T0(t_k);
             ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.k_full[ks]), (kc >> 1) & 1));
@@ -403,12 +430,14 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
             tc_commit(smem_u32(&c.o_full[0]));
           }
           __syncwarp();
+          if (lane == 0) TL_STAMP(a, n, j, 2);               // QK_A issued
           TRACE_T0(t_pb);
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.p_full[1]), pph1));
           if (!ok) break;
           if (lane == 0) TRACE_ADD(a, 3, t_pb);
           pph1 ^= 1;
           tc_fence_after();
+          if (lane == 0) TL_STAMP(a, n, j, 3);               // P_B seen
           if (el) {
             if (vs) issue_pv<1, 1>(tm, dv, j == 0); else issue_pv<1, 0>(tm, dv, j == 0);
             tc_commit(smem_u32(&c.v_empty[vs]));
@@ -421,6 +450,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
             }
           }
           __syncwarp();
+          if (lane == 0) TL_STAMP(a, n, j, 4);               // PV_B + QK_B issued
           ++vc;
           if (more) ++kc;
         }
@@ -461,13 +491,17 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         TRACE_T0(t_c);
         sph ^= 1;
         tc_fence_after();
+        if (threadIdx.x == 128) TL_STAMP(a, n, j, 5);        // S_A seen
+        if (threadIdx.x == 256) TL_STAMP(a, n, j, 9);        // S_B seen
         const int key0 = j * kBN;
         const bool masked = key0 + kBN > it.kv_len ||
                             (it.causal && it.kv_tok0 + key0 + kBN - 1 > it.tok0 + x * kTileM);
-        if (masked) softmax_row<true>(tS, tO, j, key0, lim, sl2, m_ref, l);
-        else softmax_row<false>(tS, tO, j, key0, lim, sl2, m_ref, l);
+        if (masked) softmax_row<true>(tS, tO, j, key0, lim, sl2, m_ref, l, a, n);
+        else softmax_row<false>(tS, tO, j, key0, lim, sl2, m_ref, l, a, n);
         tc_fence_before();
         mbar_arrive(smem_u32(&c.p_full[x]));
+        if (threadIdx.x == 128) TL_STAMP(a, n, j, 6);        // P_A arrived
+        if (threadIdx.x == 256) TL_STAMP(a, n, j, 10);       // P_B arrived
         if (threadIdx.x == 128) TRACE_ADD(a, 6, t_c);
       }
       TRACE_T0(t_e);
