@@ -129,12 +129,13 @@ def make_inputs_device(seq_lens, hq, hkv, d, chunk, seed, device):
 class Runner:
     """Holds problem, workspace and events for repeated calls through the C ABI."""
 
-    def __init__(self, q, k, v, cu, max_seqlen, chunk, topk):
+    def __init__(self, q, k, v, cu, max_seqlen, chunk, topk, q_token_begin=None):
         from baselinebenchmark_b200 import _lib, parallel
         self.lib, self._lib = _lib.lib(), _lib
         self.q, self.k, self.v, self.cu = q, k, v, cu
         self.out = torch.empty_like(q)
-        self.prob = parallel.make_problem(q, k, v, self.out, cu, max_seqlen, chunk, topk)
+        self.prob = parallel.make_problem(q, k, v, self.out, cu, max_seqlen, chunk, topk,
+                                          q_token_begin=q_token_begin)
         self.ws = torch.empty(parallel.workspace_bytes(self.prob), dtype=torch.uint8, device=q.device)
 
     def step(self, events=None):
@@ -239,6 +240,67 @@ def reference_arm(args, rank):
     emit(line)
 
 
+CP_TOKENS, CP_TOPK = 1048576, 16
+
+
+def run_context(args, rank, world, local, dev, dist, emit_fn):
+    """BASELINE.json configs[4]: one sequence of 1048576 tokens, 32/8 heads, chunk 4096,
+    top-k 16, split contiguously over the GPUs.  A step = all-gather of K and V over NCCL
+    into local memory + the operator on the rank's query window."""
+    from baselinebenchmark_b200 import build
+    build.build()
+    if world < 4:
+        raise SystemExit("--workload context needs at least 4 GPUs (per-GPU partial results of 1M tokens)")
+    tq = CP_TOKENS // world
+    q, k_loc, v_loc, _ = make_inputs_device([tq], HQ, HKV, D, CHUNK, 46000 + rank, dev)
+    k_full = torch.empty(CP_TOKENS, HKV, D, dtype=torch.bfloat16, device=dev)
+    v_full = torch.empty_like(k_full)
+    cu = torch.tensor([0, CP_TOKENS], dtype=torch.int32, device=dev)
+    runner = Runner(q, k_full, v_full, cu, CP_TOKENS, CHUNK, CP_TOPK, q_token_begin=rank * tq)
+
+    def step(evs=None):
+        dist.all_gather_into_tensor(k_full.view(-1), k_loc.view(-1))
+        dist.all_gather_into_tensor(v_full.view(-1), v_loc.view(-1))
+        runner.step(evs)
+
+    for _ in range(args.warmup):
+        step()
+    per_step = [new_events(6) for _ in range(args.steps)]
+    e0, e1 = new_events(2)
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    with ClockSampler(local) as clocks:
+        e0.record()
+        for evs in per_step:
+            step(evs)
+        e1.record()
+        torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1), float(np.mean([evs[3].elapsed_time(evs[4]) for evs in per_step])),
+                      float(np.mean([evs[0].elapsed_time(evs[5]) for evs in per_step]))], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, attend_ms, op_ms = (float(x) for x in t)
+    if rank == 0:
+        flops = attention_flops([CP_TOKENS], HQ, D, CHUNK, CP_TOPK)
+        pk = peaks()
+        emit_fn({
+            "metric": "MoBA prefill tokens/s", "value": CP_TOKENS * args.steps / (total_ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "BASELINE.json configs[4]: 1 sequence x 1048576 tokens split contiguously over "
+                                   f"{world} GPUs, 32 q / 8 kv heads, head_dim 128, chunk 4096, top-k 16, causal; "
+                                   "K and V all-gathered over NCCL inside the step",
+                       "tokens_per_gpu": tq, "parallelism": f"context x{world}",
+                       "l2": "inputs exceed the 126 MB L2"},
+            "tflops_effective": flops * args.steps / (total_ms * 1e-3) / 1e12,
+            "frac_of_bf16_peak": flops * args.steps / (total_ms * 1e-3) / 1e12 / (pk["sustained"] * world),
+            "exchange_ms_per_step": total_ms / args.steps - op_ms, "operator_ms_per_step": op_ms,
+            "dense_stage_ms": attend_ms, "gpu_launches": KERNELS_PER_STEP * args.steps, "clocks": clocks.summary(),
+        })
+    dist.destroy_process_group()
+
+
 def workload_config(n_gpus):
     return {"workload": "BASELINE.json configs[3] share: 16 (sequence, KV-head group) units per GPU = 2 sequences "
                         "x 131072 tokens, 32 q / 8 kv heads, head_dim 128, chunk 4096, top-k 8, causal "
@@ -270,6 +332,8 @@ def main():
     ap.add_argument("--no-also", action="store_true", help="skip the configs[2] extra measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--workload", default="units", choices=["units", "context"],
+                    help="units: config 3 share per GPU (default); context: config 4 over >= 4 GPUs")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -285,6 +349,12 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.workload == "context":
+        if dist is None:
+            raise SystemExit("--workload context runs under torchrun on >= 4 GPUs")
+        run_context(args, rank, world, local, dev, dist, emit)
+        return
 
     def barrier():
         if dist is not None:
