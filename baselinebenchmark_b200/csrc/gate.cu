@@ -114,8 +114,10 @@ cudaError_t launch_chunk_means(const Params& p, const __nv_bfloat16* k, const in
 //   groups of 4 lanes.  The CTA stages the means of its kv head for a tile of
 //   candidate chunks in shared memory as fp32; every row group then scores its
 //   rows against them and keeps the `hist` largest packed keys
-//   (order-preserving score bits << 32 | 0xFFFFFFFF - slot, routing.py:1151-1153)
-//   by repeated arg-max, which makes ties fall to the lower slot.
+//   (order-preserving score bits << 32 | 0xFFFFFFFF - slot, routing.py:1151-1153):
+//   a candidate replaces the smallest kept key when it beats it, and the kept keys
+//   are ordered once at the end.  Keys are unique, so ties in the score fall to
+//   the lower slot.
 //   Lane t of a group owns the 8-dim blocks t, t+4, t+8, t+12, so the first two
 //   levels of the halving tree (block l + block l+8, then l + l+4) stay inside
 //   the lane and only the last two cross lanes: same summation order as 16
@@ -146,16 +148,34 @@ __device__ __forceinline__ void unpack8(const uint4 x, float (&f)[8]) {
   f[4] = bf16_lo(x.z); f[5] = bf16_hi(x.z); f[6] = bf16_lo(x.w); f[7] = bf16_hi(x.w);
 }
 
-__global__ void __launch_bounds__(kGateThreads)
+// Smallest key of a row's list and its position (ties: lowest position), over the 4 lanes of a group.
+__device__ __forceinline__ void list_min(const unsigned long long* best, int hist, int t, unsigned gmask,
+                                         unsigned long long& tau, int& pos) {
+  unsigned long long mine = ~0ull;
+  int mine_i = hist;
+  for (int i = t; i < hist; i += 4) {
+    const unsigned long long kk = best[i];
+    if (kk < mine) { mine = kk; mine_i = i; }
+  }
+#pragma unroll
+  for (int o = 2; o > 0; o >>= 1) {
+    const unsigned long long ok = __shfl_xor_sync(gmask, mine, o);
+    const int oi = __shfl_xor_sync(gmask, mine_i, o);
+    if (ok < mine || (ok == mine && oi < mine_i)) { mine = ok; mine_i = oi; }
+  }
+  tau = mine;
+  pos = mine_i;
+}
+
+__global__ void __launch_bounds__(kGateThreads, 4)
 gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__ q,
                  const __nv_bfloat16* __restrict__ means, const int32_t* __restrict__ cu,
                  int32_t* __restrict__ selected, int32_t* __restrict__ list_counts) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int hist = p.hist;
-  // layout: means tile fp32 | cand[groups][kCandTile] | wins[groups][hist] | best[rows][hist] | counts[mc]
+  // layout: means tile fp32 | wins[groups][hist] | best[rows][hist] | counts[mc]
   float4* means_s = reinterpret_cast<float4*>(smem_raw);                            // kCandTile * 32 float4
-  unsigned long long* cand_s = reinterpret_cast<unsigned long long*>(means_s + kCandTile * 32);
-  unsigned long long* wins_s = cand_s + kGateGroups * kCandTile;
+  unsigned long long* wins_s = reinterpret_cast<unsigned long long*>(means_s + kCandTile * 32);
   unsigned long long* best_s = wins_s + kGateGroups * hist;
   int32_t* cnt_s = reinterpret_cast<int32_t*>(best_s + (size_t)kGateRows * hist);
 
@@ -175,8 +195,6 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
   // candidates of the last token of the tile bound the chunks to stage
   const int max_cand = (tok_lo + ntok - 1 - s0) / p.C;
   const int slot0 = b * p.mc;
-  unsigned long long* cand = cand_s + grp * kCandTile;
-  unsigned long long* wins = wins_s + grp * hist;
 
   for (int c0 = 0; c0 < max_cand; c0 += kCandTile) {
     const int ct = min(kCandTile, max_cand - c0);
@@ -203,6 +221,12 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
         for (int k = 0; k < 4; ++k)
           unpack8(__ldg(reinterpret_cast<const uint4*>(qrow + (t + 4 * k) * 8)), qf[k]);
       }
+      // The row keeps its `hist` largest keys so far (unordered) in shared memory; a new
+      // key replaces the smallest one if it is larger.  0 marks an empty place.
+      unsigned long long* best = best_s + (size_t)row * hist;
+      unsigned long long tau;
+      int pos;
+      list_min(best, hist, t, gmask, tau, pos);
       for (int c = 0; c < cend; ++c) {
         const float4* m = means_s + c * 32;
         float acc[4];
@@ -212,19 +236,29 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
         float s = __fadd_rn(__fadd_rn(acc[0], acc[2]), __fadd_rn(acc[1], acc[3]));
         s = __fadd_rn(s, __shfl_xor_sync(gmask, s, 2));
         s = __fadd_rn(s, __shfl_xor_sync(gmask, s, 1));
-        if (t == (c & 3))
-          cand[c] = ((unsigned long long)float_key(s) << 32) |
-                    (unsigned long long)(0xFFFFFFFFu - (uint32_t)(slot0 + c0 + c));
+        const unsigned long long key = ((unsigned long long)float_key(s) << 32) |
+                                       (unsigned long long)(0xFFFFFFFFu - (uint32_t)(slot0 + c0 + c));
+        if (key > tau) {                                      // same decision in the 4 lanes
+          if (t == 0) best[pos] = key;
+          __syncwarp(gmask);
+          list_min(best, hist, t, gmask, tau, pos);
+        }
       }
+    }
+  }
+  __syncthreads();
+  // order every row's list: rank 0 = largest key (repeated arg-max), into the same place
+  {
+    unsigned long long* wins = wins_s + grp * hist;
+    for (int row = grp; row < nrows; row += kGateGroups) {
       unsigned long long* best = best_s + (size_t)row * hist;
       for (int i = t; i < hist; i += 4) wins[i] = 0ull;
       __syncwarp(gmask);
-      // the `hist` largest of best[0..hist) U cand[0..cend), by repeated arg-max
       for (int r = 0; r < hist; ++r) {
         unsigned long long mine = 0ull;
         int mine_i = -1;
-        for (int i = t; i < hist + cend; i += 4) {
-          const unsigned long long kk = i < hist ? best[i] : cand[i - hist];
+        for (int i = t; i < hist; i += 4) {
+          const unsigned long long kk = best[i];
           if (kk > mine) { mine = kk; mine_i = i; }
         }
         unsigned long long top = mine;
@@ -235,7 +269,7 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
         }
         if (top == 0ull) break;                               // fewer than hist candidates
         if (mine == top) {                                    // keys are unique: exactly one owner
-          if (mine_i < hist) best[mine_i] = 0ull; else cand[mine_i - hist] = 0ull;
+          best[mine_i] = 0ull;
           wins[r] = top;
         }
         __syncwarp(gmask);
@@ -262,8 +296,8 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
 }
 
 static size_t gate_smem_bytes(const Params& p) {
-  return (size_t)kCandTile * 32 * sizeof(float4) + (size_t)kGateGroups * kCandTile * 8 +
-         (size_t)kGateGroups * p.hist * 8 + (size_t)kGateRows * p.hist * 8 + (size_t)p.mc * 4;
+  return (size_t)kCandTile * 32 * sizeof(float4) + (size_t)kGateGroups * p.hist * 8 +
+         (size_t)kGateRows * p.hist * 8 + (size_t)p.mc * 4;
 }
 
 cudaError_t launch_gate_topk(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* means,
