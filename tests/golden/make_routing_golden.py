@@ -85,7 +85,9 @@ def make_case(seq_lens, hq, hkv, d, chunk, kind, seed):
 
 
 def main():
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_routing_golden.py <path to the reference checkout>")
+    ref_root = Path(sys.argv[1])
     routing = load_routing(ref_root)
     out_dir = Path(__file__).resolve().parent
     for seed, (name, (lens, hq, hkv, d, chunk, topk, max_len, kind)) in enumerate(CASES.items()):

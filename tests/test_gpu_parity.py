@@ -365,3 +365,42 @@ def test_host_buffer_entry_point_matches_device_call():
         assert torch.equal(hout, ref.cpu())
         if extra:
             assert torch.equal(hlse, ref_lse.cpu()) and torch.equal(hsel, ref_sel.cpu())
+
+
+def test_config3_unit_sampled():
+    """BASELINE.json configs[3], one of its 128 (sequence, KV-head group) units at full size:
+    131072 tokens, 4 query heads sharing 1 KV head, chunk 4096, top-k 8."""
+    cfg = O.CONFIGS[3]
+    q, k, v, cu = O.make_inputs([131072], 4, 1, 128, cfg["chunk"], seed=45)
+    out, _, sel = parallel.moba_forward(*G.to_dev(q, k, v), torch.from_numpy(cu).cuda(), 131072, cfg["chunk"],
+                                        cfg["topk"], return_selected=True)
+    assert torch.isfinite(out.float()).all()
+    mx, mean = _sampled_check(q, k, v, cu, 131072, cfg["chunk"], cfg["topk"], out.cpu(), sel.cpu().numpy(), 64, 3)
+    assert mx < MAX_ABS and mean < MEAN_ABS, (mx, mean)
+
+
+def test_config4_window_sampled():
+    """BASELINE.json configs[4] as one of its 8 ranks sees it, for one KV-head group: K/V of
+    the whole 1048576-token sequence, queries of the window [5/8, 6/8), chunk 4096, top-k 16
+    (255 candidate chunks, 15 selected)."""
+    cfg = O.CONFIGS[4]
+    total, chunk, topk = 1048576, cfg["chunk"], cfg["topk"]
+    q, k, v, cu = O.make_inputs([total], 4, 1, 128, chunk, seed=46)
+    lo, hi = 5 * total // 8, 6 * total // 8
+    out, _, sel = parallel.moba_forward(q[lo:hi].cuda(), k.cuda(), v.cuda(), torch.from_numpy(cu).cuda(), total,
+                                        chunk, topk, return_selected=True, q_token_begin=lo)
+    assert torch.isfinite(out.float()).all()
+    out, sel = out.cpu(), sel.cpu().numpy()
+    rng = np.random.default_rng(4)
+    toks = sorted(set(rng.integers(lo, hi, 40).tolist()) | {lo, hi - 1, lo + chunk - 1, lo + chunk})
+    cu_chunk, _, valid, mc = O.chunk_slots(cu, total, chunk)
+    hist = O.historical_topk(topk, mc)
+    assert (mc, hist) == (256, 15)
+    means = O.chunk_means(k, cu_chunk, valid, chunk)
+    sel_o = O.select_chunks(q, means, cu, total, chunk, hist, rows=toks)
+    np.testing.assert_array_equal(sel[:, :, [t - lo for t in toks]], sel_o[:, :, toks])
+    rows = [(t, int(h)) for t in toks[::4] for h in rng.integers(0, 4, 2)]
+    ref, _ = O.attend_rows(q, k, v, cu, total, chunk, sel_o, rows)
+    got = torch.stack([out[t - lo, h] for t, h in rows]).double()
+    diff = (got - ref).abs()
+    assert diff.max().item() < MAX_ABS and diff.mean().item() < MEAN_ABS
