@@ -19,7 +19,7 @@ ATTEND_MMA_SYNC = 1
 #: every symbol include/moba_b200.h declares
 SYMBOLS = (
     "moba_b200_abi_version", "moba_b200_strerror", "moba_problem_check", "moba_problem_dims",
-    "moba_workspace_size", "moba_forward", "moba_forward_events", "moba_workspace_size_host", "moba_forward_host",
+    "moba_workspace_size", "moba_workspace_size_min", "moba_forward", "moba_forward_events", "moba_workspace_size_host", "moba_forward_host",
     "moba_chunk_metadata", "moba_chunk_means", "moba_gate_topk", "moba_compact_routes",
     "moba_attend", "moba_merge", "moba_attend_tile_rows", "moba_route_static",
 )
@@ -73,6 +73,7 @@ def lib() -> C.CDLL:
         handle.moba_problem_dims.argtypes = [pp, C.POINTER(Dims)]
         handle.moba_workspace_size.argtypes = [pp, C.POINTER(sz)]
         handle.moba_workspace_size_host.argtypes = [pp, C.POINTER(sz)]
+        handle.moba_workspace_size_min.argtypes = [pp, C.POINTER(sz)]
         handle.moba_forward.argtypes = [pp, vp, vp, vp, i32p, vp, vp, i32p, vp, sz, vp]
         handle.moba_forward_events.argtypes = [pp, vp, vp, vp, i32p, vp, vp, i32p, vp, sz, vp, C.POINTER(C.c_void_p)]
         handle.moba_forward_host.argtypes = [pp, vp, vp, vp, i32p, vp, vp, i32p, vp, sz, vp]

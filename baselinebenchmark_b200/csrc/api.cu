@@ -44,8 +44,9 @@ int check_problem(const moba_problem_t* p) {
   const int64_t hist = (p->topk - 1 < mc - 1) ? p->topk - 1 : mc - 1;
   const int64_t np = (hist > 0 ? hist : 0) + 1;
   // entry ids (row * partials + rank) are int32, like the reference's int32 offsets (routing.py:1094-1100)
+  // a pass covers at least one kv head with its query heads (forward_impl splits larger problems)
   const int64_t tq = p->q_tokens > 0 ? p->q_tokens : p->total_tokens;
-  if (tq * p->num_q_heads * np >= ((int64_t)1 << 31)) return MOBA_E_UNSUPPORTED;
+  if (tq * (p->num_q_heads / p->num_kv_heads) * np >= ((int64_t)1 << 31)) return MOBA_E_UNSUPPORTED;
   return MOBA_OK;
 }
 
@@ -68,6 +69,7 @@ Params make_params(const moba_problem_t* p) {
   if (r.hist < 0) r.hist = 0;
   r.NP = r.hist + 1;
   r.rows = r.Tq * r.Hq;
+  r.sel_rs = (int64_t)r.Hq * r.Tq;
   r.lists = (int64_t)r.slots * r.Hkv;
   r.sq_t = p->q_stride_token; r.sq_h = p->q_stride_head;
   r.sk_t = p->k_stride_token; r.sk_h = p->k_stride_head;
@@ -162,6 +164,15 @@ __global__ void set_pair_kernel(int32_t* dst, int32_t a, int32_t b) {
 
 }  // namespace
 
+// Workspace of the problem restricted to `kv_heads` kv heads (and their query heads).
+static size_t pass_bytes(const moba_problem_t* p, int kv_heads) {
+  moba_problem_t sub = *p;
+  sub.num_kv_heads = kv_heads;
+  sub.num_q_heads = kv_heads * (p->num_q_heads / p->num_kv_heads);
+  return carve(make_params(&sub), nullptr).total;
+}
+
+
 extern "C" {
 
 int moba_b200_abi_version(void) { return 2; }
@@ -203,7 +214,21 @@ int moba_workspace_size(const moba_problem_t* p, size_t* bytes) {
   const int rc = check_problem(p);
   if (rc != MOBA_OK) return rc;
   if (bytes == nullptr) return MOBA_E_NULL;
-  *bytes = carve(make_params(p), nullptr).total;
+  const Params r = make_params(p);
+  int per = r.Hkv;                                          // the largest pass whose entry ids fit int32
+  while (per > 1 && r.Tq * (int64_t)(per * r.G) * r.NP >= ((int64_t)1 << 31)) --per;
+  *bytes = pass_bytes(p, per);
+  return MOBA_OK;
+}
+
+int moba_workspace_size_min(const moba_problem_t* p, size_t* bytes) {
+  const int rc = check_problem(p);
+  if (rc != MOBA_OK) return rc;
+  if (bytes == nullptr) return MOBA_E_NULL;
+  moba_problem_t sub = *p;
+  sub.num_kv_heads = 1;
+  sub.num_q_heads = p->num_q_heads / p->num_kv_heads;
+  *bytes = carve(make_params(&sub), nullptr).total;
   return MOBA_OK;
 }
 
@@ -271,6 +296,49 @@ int moba_merge(const moba_problem_t* p, const float* partial_out, const float* p
                            lse_out, (cudaStream_t)stream);
 }
 
+// One pass over all query heads of `p` (the whole problem, or a group of kv heads
+// carved out of it by forward_impl).  `sel_rs`: rank stride of `selected_out`.
+static int forward_pass(const moba_problem_t* p, int64_t sel_rs, const void* q, const void* k, const void* v,
+                        const int32_t* cu, void* out, float* lse_out, int32_t* selected_out, void* workspace,
+                        cudaStream_t st, void* const* events, bool first, bool last) {
+  Params r = make_params(p);
+  if (selected_out) r.sel_rs = sel_rs;
+  const Workspace w = carve(r, workspace);
+  cudaError_t e;
+  auto mark = [&](int i) -> cudaError_t {
+    return (events && events[i]) ? cudaEventRecord((cudaEvent_t)events[i], st) : cudaSuccess;
+  };
+  if (first && (e = mark(0)) != cudaSuccess) return (int)e;
+  if ((e = cudaMemsetAsync(w.list_counts, 0, w.zero_bytes, st)) != cudaSuccess) return (int)e;
+  const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(q);
+  const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(k);
+  if (r.hist > 0) {
+    int32_t* sel = selected_out ? selected_out : w.selected;
+    if ((e = launch_chunk_means(r, kb, cu, w.means, st)) != cudaSuccess) return (int)e;
+    if (last && (e = mark(1)) != cudaSuccess) return (int)e;
+    if ((e = launch_gate_topk(r, qb, w.means, cu, sel, w.list_counts, st)) != cudaSuccess) return (int)e;
+    if (last && (e = mark(2)) != cudaSuccess) return (int)e;
+    if ((e = launch_compact(r, cu, sel, w.list_counts, w.list_offsets, w.tile_prefix, w.cursors, w.row_list,
+                            w.partial_lse, tile_rows_of(p->attend_impl), st)) != cudaSuccess)
+      return (int)e;
+  } else if (last) {
+    if ((e = mark(1)) != cudaSuccess || (e = mark(2)) != cudaSuccess) return (int)e;
+  }
+  if (last && (e = mark(3)) != cudaSuccess) return (int)e;
+  const int arc = attend_dispatch(p, r, q, k, v, cu, w.list_counts, w.list_offsets, w.tile_prefix, w.row_list,
+                                  w.partial_out, w.partial_lse, w.work_counter, w.status, st);
+  if (arc != 0) return arc;
+  if (last && (e = mark(4)) != cudaSuccess) return (int)e;
+  e = launch_merge(r, w.partial_out, w.partial_lse, w.status, static_cast<__nv_bfloat16*>(out), lse_out, st);
+  if (e != cudaSuccess) return (int)e;
+  return last ? (int)mark(5) : MOBA_OK;
+}
+
+// The operator.  With a workspace smaller than moba_workspace_size the kv heads are
+// processed in groups that fit (routing and attention never cross a kv-head group,
+// routing.py:1089, attention.py:649-650); the reference bounds its memory with rank
+// passes instead (parallel.py:322-373).  Events, when given, bracket the stages of the
+// last group ([0] is recorded before the first).
 static int forward_impl(const moba_problem_t* p, const void* q, const void* k, const void* v, const int32_t* cu,
                         void* out, float* lse_out, int32_t* selected_out, void* workspace, size_t workspace_bytes,
                         void* stream, void* const* events) {
@@ -280,39 +348,29 @@ static int forward_impl(const moba_problem_t* p, const void* q, const void* k, c
   const uintptr_t ptrs[5] = {(uintptr_t)q, (uintptr_t)k, (uintptr_t)v, (uintptr_t)out, (uintptr_t)workspace};
   for (int i = 0; i < 5; ++i)
     if (ptrs[i] % 16 != 0) return MOBA_E_ALIGN;
-  const Params r = make_params(p);
   if (workspace == nullptr) return MOBA_E_WORKSPACE;
-  const Workspace w = carve(r, workspace);
-  if (workspace_bytes < w.total) return MOBA_E_WORKSPACE;
+  const Params r = make_params(p);
   cudaStream_t st = (cudaStream_t)stream;
-  cudaError_t e;
-  auto mark = [&](int i) -> cudaError_t {
-    return (events && events[i]) ? cudaEventRecord((cudaEvent_t)events[i], st) : cudaSuccess;
-  };
-  if ((e = mark(0)) != cudaSuccess) return (int)e;
-  if ((e = cudaMemsetAsync(w.list_counts, 0, w.zero_bytes, st)) != cudaSuccess) return (int)e;
-  const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(q);
-  const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(k);
-  if (r.hist > 0) {
-    int32_t* sel = selected_out ? selected_out : w.selected;
-    if ((e = launch_chunk_means(r, kb, cu, w.means, st)) != cudaSuccess) return (int)e;
-    if ((e = mark(1)) != cudaSuccess) return (int)e;
-    if ((e = launch_gate_topk(r, qb, w.means, cu, sel, w.list_counts, st)) != cudaSuccess) return (int)e;
-    if ((e = mark(2)) != cudaSuccess) return (int)e;
-    if ((e = launch_compact(r, cu, sel, w.list_counts, w.list_offsets, w.tile_prefix, w.cursors, w.row_list,
-                            w.partial_lse, tile_rows_of(p->attend_impl), st)) != cudaSuccess)
-      return (int)e;
-  } else {
-    if ((e = mark(1)) != cudaSuccess || (e = mark(2)) != cudaSuccess) return (int)e;
+  int per = r.Hkv;                                          // kv heads per pass: the most that fit
+  while (per > 1 && (pass_bytes(p, per) > workspace_bytes ||
+                     r.Tq * (int64_t)(per * r.G) * r.NP >= ((int64_t)1 << 31)))
+    --per;
+  if (pass_bytes(p, per) > workspace_bytes) return MOBA_E_WORKSPACE;
+  for (int g0 = 0; g0 < r.Hkv; g0 += per) {
+    const int ng = g0 + per <= r.Hkv ? per : r.Hkv - g0;
+    moba_problem_t sub = *p;
+    sub.num_kv_heads = ng;
+    sub.num_q_heads = ng * r.G;
+    const int64_t h0 = (int64_t)g0 * r.G;
+    const int prc = forward_pass(
+        &sub, r.sel_rs, static_cast<const __nv_bfloat16*>(q) + h0 * r.sq_h,
+        static_cast<const __nv_bfloat16*>(k) + (int64_t)g0 * r.sk_h,
+        static_cast<const __nv_bfloat16*>(v) + (int64_t)g0 * r.sv_h, cu,
+        static_cast<__nv_bfloat16*>(out) + h0 * r.so_h, lse_out ? lse_out + h0 * r.Tq : nullptr,
+        selected_out ? selected_out + h0 * r.Tq : nullptr, workspace, st, events, g0 == 0, g0 + ng >= r.Hkv);
+    if (prc != MOBA_OK) return prc;
   }
-  if ((e = mark(3)) != cudaSuccess) return (int)e;
-  const int arc = attend_dispatch(p, r, q, k, v, cu, w.list_counts, w.list_offsets, w.tile_prefix, w.row_list,
-                                  w.partial_out, w.partial_lse, w.work_counter, w.status, st);
-  if (arc != 0) return arc;
-  if ((e = mark(4)) != cudaSuccess) return (int)e;
-  e = launch_merge(r, w.partial_out, w.partial_lse, w.status, static_cast<__nv_bfloat16*>(out), lse_out, st);
-  if (e != cudaSuccess) return (int)e;
-  return (int)mark(5);
+  return MOBA_OK;
 }
 
 int moba_forward(const moba_problem_t* p, const void* q, const void* k, const void* v, const int32_t* cu,

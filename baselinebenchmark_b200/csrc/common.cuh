@@ -22,6 +22,7 @@ struct Params {
   int max_seqlen, C, topk;
   int mc, slots, hist, NP;               // NP = partial results per row
   int64_t rows, lists;
+  int64_t sel_rs;                        // elements between two ranks of `selected` (heads of the full tensor * Tq)
   int64_t sq_t, sq_h, sk_t, sk_h, sv_t, sv_h, so_t, so_h;
 };
 

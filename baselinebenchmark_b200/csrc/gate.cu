@@ -286,7 +286,7 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
     const int hl = rem / ntok, tl = rem - hl * ntok;
     const unsigned long long w = best_s[(size_t)(tl * p.G + hl) * hist + r];
     const int slot = w ? (int)(0xFFFFFFFFu - (uint32_t)(w & 0xFFFFFFFFull)) : -1;
-    selected[((int64_t)r * p.Hq + (hk * p.G + hl)) * p.Tq + (tok_lo - p.win_lo) + tl] = slot;
+    selected[(int64_t)r * p.sel_rs + (int64_t)(hk * p.G + hl) * p.Tq + (tok_lo - p.win_lo) + tl] = slot;
     if (slot >= 0) atomicAdd(&cnt_s[slot - slot0], 1);
   }
   __syncthreads();

@@ -93,7 +93,7 @@ scatter_routes_kernel(Params p, const int32_t* __restrict__ cu, const int32_t* _
   for (int i = threadIdx.x; i < n; i += kScatterThreads) {
     const int tl = i % ntok, rh = i / ntok;
     const int hl = rh % p.G, r = rh / p.G;
-    const int slot = selected[((int64_t)r * p.Hq + hk * p.G + hl) * p.Tq + loc + tl];
+    const int slot = selected[(int64_t)r * p.sel_rs + (int64_t)(hk * p.G + hl) * p.Tq + loc + tl];
     if (slot >= 0) atomicAdd(&cnt_s[slot - slot0], 1);
   }
   __syncthreads();
@@ -107,7 +107,7 @@ scatter_routes_kernel(Params p, const int32_t* __restrict__ cu, const int32_t* _
     const int tl = i % ntok, rh = i / ntok;
     const int hl = rh % p.G, r = rh / p.G;
     const int head = hk * p.G + hl;
-    const int slot = selected[((int64_t)r * p.Hq + head) * p.Tq + loc + tl];
+    const int slot = selected[(int64_t)r * p.sel_rs + (int64_t)head * p.Tq + loc + tl];
     const int64_t entry = ((int64_t)(loc + tl) * p.Hq + head) * p.NP + r + 1;
     if (slot >= 0) {
       const int c = slot - slot0;

@@ -81,10 +81,16 @@ def make_problem(q, k, v, out, cu_seqlens, max_seqlen, chunk, topk, attend_impl=
         o_stride_token=out.stride(0), o_stride_head=out.stride(1))
 
 
-def workspace_bytes(problem) -> int:
+def workspace_bytes(problem, limit: Optional[int] = None) -> int:
+    """Workspace for one pass over all heads, or, with `limit`, the largest useful size not
+    above it (never below the one-kv-head minimum): the library then runs kv-head groups in turn."""
     size = C.c_size_t(0)
     _lib.check(_lib.lib().moba_workspace_size(C.byref(problem), C.byref(size)))
-    return int(size.value)
+    if limit is None or size.value <= limit:
+        return int(size.value)
+    least = C.c_size_t(0)
+    _lib.check(_lib.lib().moba_workspace_size_min(C.byref(problem), C.byref(least)))
+    return max(int(least.value), int(limit))
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
@@ -99,7 +105,7 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 def moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, *,
                  return_lse: bool = False, return_selected: bool = False,
                  attend_impl: int = _lib.ATTEND_TCGEN05, workspace: Optional[torch.Tensor] = None,
-                 q_token_begin: Optional[int] = None
+                 q_token_begin: Optional[int] = None, workspace_limit: Optional[int] = None
                  ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
     """Runs the operator and optionally returns the final LSE [Hq, T] (fp32) and
     the routing decision selected[hist, Hq, T] (int32, -1 padded).
@@ -107,17 +113,16 @@ def moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, *,
     `q_token_begin` (context parallelism): q holds only the packed tokens
     [q_token_begin, q_token_begin + q.shape[0]), a window that starts and ends on
     chunk boundaries, while k, v and cu_seqlens describe every token; outputs
-    cover the window."""
+    cover the window.  `workspace_limit` (bytes) bounds the scratch memory: the kv heads
+    are then processed in groups, with identical results."""
     _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, windowed=q_token_begin is not None)
     out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     prob = make_problem(q, k, v, out, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, attend_impl,
                         q_token_begin)
     dims = _lib.Dims()
     _lib.check(_lib.lib().moba_problem_dims(C.byref(prob), C.byref(dims)))
-    need = workspace_bytes(prob)
+    need = workspace_bytes(prob, workspace_limit)
     ws = workspace if workspace is not None else _workspace(q.device, need)
-    if ws.numel() * ws.element_size() < need:
-        raise ValueError(f"workspace too small: {ws.numel() * ws.element_size()} < {need} bytes")
     lse = torch.empty((q.shape[1], q.shape[0]), dtype=torch.float32, device=q.device) if return_lse else None
     sel = None
     if return_selected:

@@ -96,6 +96,13 @@ int moba_problem_dims(const moba_problem_t* p, moba_dims_t* dims);
  * routing.py:1653-1658, attention.py:418-419, :727-728). */
 int moba_workspace_size(const moba_problem_t* p, size_t* bytes);
 
+/* Smallest workspace moba_forward accepts for `p`: enough for one kv head and its
+ * query heads.  With anything between the two sizes moba_forward processes the kv
+ * heads in groups that fit, one after the other on the stream, with identical
+ * results; the reference bounds its scratch with a 512 MiB budget and a loop over
+ * rank passes instead (parallel.py:56, :322-373). */
+int moba_workspace_size_min(const moba_problem_t* p, size_t* bytes);
+
 /* The whole operator: replaces _moba_attn_varlen_inference (parallel.py:253-374).
  *   q [T,Hq,D], k,v [T,Hkv,D], out [T,Hq,D] bf16 on device; cu_seqlens int32[B+1] on device.
  *   lse_out       optional fp32 [Hq,T]   (natural log, layout of attention.py:419)

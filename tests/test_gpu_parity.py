@@ -404,3 +404,25 @@ def test_config4_window_sampled():
     got = torch.stack([out[t - lo, h] for t, h in rows]).double()
     diff = (got - ref).abs()
     assert diff.max().item() < MAX_ABS and diff.mean().item() < MEAN_ABS
+
+
+def test_bounded_workspace_runs_head_groups():
+    """A workspace below the one-pass size makes the library process kv-head groups in turn;
+    results, LSE and selection are the bits of the one-pass run."""
+    import ctypes as C
+    q, k, v, cu = _case_inputs((1536, 1000), 16, 4, 128, seed=41)
+    qd, kd, vd = G.to_dev(q, k, v)
+    cud = torch.from_numpy(cu).cuda()
+    ref, ref_lse, ref_sel = parallel.moba_forward(qd, kd, vd, cud, 1536, 128, 4, return_lse=True, return_selected=True)
+    prob, _ = G.problem_for(qd, kd, vd, cud, 1536, 128, 4)
+    full, least = C.c_size_t(0), C.c_size_t(0)
+    _lib.check(_lib.lib().moba_workspace_size(C.byref(prob), C.byref(full)))
+    _lib.check(_lib.lib().moba_workspace_size_min(C.byref(prob), C.byref(least)))
+    assert least.value * 3 < full.value
+    for limit in (least.value, least.value * 2 + 4096, (full.value * 3) // 4):
+        out, lse, sel = parallel.moba_forward(qd, kd, vd, cud, 1536, 128, 4, return_lse=True, return_selected=True,
+                                              workspace=torch.empty(limit, dtype=torch.uint8, device="cuda"))
+        assert torch.equal(out, ref) and torch.equal(lse, ref_lse) and torch.equal(sel, ref_sel)
+    with pytest.raises(_lib.MobaError):
+        parallel.moba_forward(qd, kd, vd, cud, 1536, 128, 4,
+                              workspace=torch.empty(least.value - 256, dtype=torch.uint8, device="cuda"))
