@@ -36,6 +36,7 @@ class Problem(C.Structure):
         ("v_stride_token", C.c_int64), ("v_stride_head", C.c_int64),
         ("o_stride_token", C.c_int64), ("o_stride_head", C.c_int64),
         ("q_token_begin", C.c_int64), ("q_tokens", C.c_int64),
+        ("dtype", C.c_int32), ("reserved", C.c_int32),
     ]
 
 

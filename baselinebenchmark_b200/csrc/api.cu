@@ -28,6 +28,7 @@ int check_problem(const moba_problem_t* p) {
   if (p->head_dim != kHeadDim) return MOBA_E_UNSUPPORTED;
   if (p->num_q_heads / p->num_kv_heads > 128) return MOBA_E_UNSUPPORTED;
   if (p->attend_impl != MOBA_ATTEND_TCGEN05 && p->attend_impl != MOBA_ATTEND_MMA_SYNC) return MOBA_E_UNSUPPORTED;
+  if ((p->dtype != MOBA_DTYPE_BF16 && p->dtype != MOBA_DTYPE_FP16) || p->reserved != 0) return MOBA_E_UNSUPPORTED;
   const int64_t strides[8] = {p->q_stride_token, p->q_stride_head, p->k_stride_token, p->k_stride_head,
                               p->v_stride_token, p->v_stride_head, p->o_stride_token, p->o_stride_head};
   for (int i = 0; i < 8; ++i) {
@@ -60,6 +61,7 @@ Params make_params(const moba_problem_t* p) {
   r.Hkv = p->num_kv_heads;
   r.G = r.Hq / r.Hkv;
   r.D = p->head_dim;
+  r.fp16 = p->dtype == MOBA_DTYPE_FP16;
   r.max_seqlen = p->max_seqlen;
   r.C = p->chunk_size;
   r.topk = p->topk;
@@ -175,13 +177,13 @@ static size_t pass_bytes(const moba_problem_t* p, int kv_heads) {
 
 extern "C" {
 
-int moba_b200_abi_version(void) { return 2; }
+int moba_b200_abi_version(void) { return 3; }
 
 const char* moba_b200_strerror(int code) {
   switch (code) {
     case MOBA_OK: return "ok";
     case MOBA_E_SHAPE: return "q, k, v, cu_seqlens or the integer arguments have an invalid shape or value";
-    case MOBA_E_UNSUPPORTED: return "configuration outside this build (bf16, head_dim 128, contiguous innermost dim)";
+    case MOBA_E_UNSUPPORTED: return "configuration outside this build (bf16 or fp16, head_dim 128, contiguous innermost dim)";
     case MOBA_E_WORKSPACE: return "workspace is null or too small";
     case MOBA_E_NULL: return "a required pointer is null";
     case MOBA_E_TOPK: return "moba_topk must be in 1..64";

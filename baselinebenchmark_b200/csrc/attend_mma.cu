@@ -47,15 +47,18 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& a, uint32_t& 
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr));
 }
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
+template <bool kHalf>
+__device__ __forceinline__ void mma_16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if (kHalf)
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  else
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
 struct Smem {
@@ -81,6 +84,7 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const Item& it, in
   }
 }
 
+template <bool kHalf>
 __global__ void __launch_bounds__(kThreads, 2)
 attend_mma_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                   const __nv_bfloat16* __restrict__ v, const int32_t* __restrict__ cu,
@@ -161,8 +165,8 @@ attend_mma_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bflo
           uint32_t b0, b1, b2, b3;
           const int r = np * 16 + (lane & 7) + ((lane >> 4) << 3);
           ldsm_x4(kb + swz(r, 2 * ks + ((lane >> 3) & 1)), b0, b1, b2, b3);
-          mma_bf16(sc[2 * np], qa, b0, b1);
-          mma_bf16(sc[2 * np + 1], qa, b2, b3);
+          mma_16<kHalf>(sc[2 * np], qa, b0, b1);
+          mma_16<kHalf>(sc[2 * np + 1], qa, b2, b3);
         }
       }
       // scale, mask, row maxima
@@ -201,8 +205,8 @@ attend_mma_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bflo
         const float p2 = exp2f(sc[nt][2] - mn1), p3 = exp2f(sc[nt][3] - mn1);
         ps0 += p0 + p1;
         ps1 += p2 + p3;
-        pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(p0, p1);
-        pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+        pa[nt >> 1][(nt & 1) * 2 + 0] = pack2_16<kHalf>(p0, p1);
+        pa[nt >> 1][(nt & 1) * 2 + 1] = pack2_16<kHalf>(p2, p3);
       }
       l0 = l0 * a0 + ps0;
       l1 = l1 * a1 + ps1;
@@ -215,8 +219,8 @@ attend_mma_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bflo
           uint32_t b0, b1, b2, b3;
           const int r = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
           ldsm_x4_t(vb + swz(r, 2 * dp + (lane >> 4)), b0, b1, b2, b3);
-          mma_bf16(o[2 * dp], pa[kk], b0, b1);
-          mma_bf16(o[2 * dp + 1], pa[kk], b2, b3);
+          mma_16<kHalf>(o[2 * dp], pa[kk], b0, b1);
+          mma_16<kHalf>(o[2 * dp + 1], pa[kk], b2, b3);
         }
       }
       __syncthreads();
@@ -254,12 +258,13 @@ cudaError_t launch_attend_mma(const Params& p, const __nv_bfloat16* q, const __n
                               const int32_t* row_list, float* partial_out, float* partial_lse,
                               int32_t* work_counter, cudaStream_t st) {
   const size_t smem = sizeof(Smem);
-  cudaError_t e = cudaFuncSetAttribute(attend_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  auto kernel = p.fp16 ? attend_mma_kernel<true> : attend_mma_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  attend_mma_kernel<<<sms * 2, kThreads, smem, st>>>(p, q, k, v, cu, list_counts, list_offsets, tile_prefix,
+  kernel<<<sms * 2, kThreads, smem, st>>>(p, q, k, v, cu, list_counts, list_offsets, tile_prefix,
                                                     row_list, partial_out, partial_lse, work_counter);
   return cudaGetLastError();
 }

@@ -45,8 +45,8 @@ constexpr int kHalfBytes = 128 * 64 * 2; // one [128][64] bf16 swizzled block
 constexpr int kTileBytes = 2 * kHalfBytes;
 constexpr uint32_t kTmemCols = 512;
 
-constexpr uint32_t kIdescQK = idesc_bf16_f32(128, kBN, 0, 0);
-constexpr uint32_t kIdescPV = idesc_bf16_f32(128, kHeadDim, 0, 1);
+template <bool kHalf> constexpr uint32_t kIdescQK = idesc_16_f32(kHalf, 128, kBN, 0, 0);
+template <bool kHalf> constexpr uint32_t kIdescPV = idesc_16_f32(kHalf, 128, kHeadDim, 0, 1);
 
 enum { ST_OK = 0, ST_PRODUCER = 1, ST_MMA = 2, ST_SOFTMAX = 3 };
 
@@ -194,7 +194,7 @@ __device__ __forceinline__ bool next_item(const KernelArgs& a, Ctrl& c, unsigned
 
 // One softmax step of one row: S (128 fp32 columns of this thread's TMEM lane)
 // -> P (bf16, written over the first 64 columns), running max / sum updated.
-template <bool kMasked>
+template <bool kMasked, bool kHalf>
 __device__ __forceinline__ void softmax_row(uint32_t tS, uint32_t tO, int j, int key0, int lim, float sl2,
                                             float& m_ref, float& l, const KernelArgs& a, int n) {
   uint32_t v[128];
@@ -257,7 +257,7 @@ __device__ __forceinline__ void softmax_row(uint32_t tS, uint32_t tO, int j, int
         pr = pack2(ex2_approx(lo2(x)), ex2_approx(hi2(x)));
       }
       if (i & 1) sum_b = add2(sum_b, pr); else sum_a = add2(sum_a, pr);
-      pk[i] = pack_bf16(lo2(pr), hi2(pr));
+      pk[i] = pack2_16<kHalf>(lo2(pr), hi2(pr));
 #endif
     }
     tmem_st16(tS + ch * 16, pk);
@@ -279,24 +279,25 @@ __device__ __forceinline__ uint64_t desc64(uint32_t lo) { return ((uint64_t)kDes
 
 // S_X = Q_X . K^T for one K tile: 8 k-steps of 16 dims; X and STAGE are compile-time
 // so every descriptor is the base word plus an immediate.
-template <int X, int STAGE>
+template <int X, int STAGE, bool kHalf>
 __device__ __forceinline__ void issue_qk(uint32_t tmem, uint32_t dq, uint32_t dk) {
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks) {
-    constexpr int kHalf = kHalfBytes >> 4, kTile = kTileBytes >> 4;
-    const uint32_t koff = (uint32_t)((ks >> 2) * kHalf + (ks & 3) * 2);
-    mma_ss(tmem + X * kBN, desc64(dq + X * kTile + koff), desc64(dk + STAGE * kTile + koff), kIdescQK, ks > 0);
+    constexpr int kBlock = kHalfBytes >> 4, kTile = kTileBytes >> 4;
+    const uint32_t koff = (uint32_t)((ks >> 2) * kBlock + (ks & 3) * 2);
+    mma_ss(tmem + X * kBN, desc64(dq + X * kTile + koff), desc64(dk + STAGE * kTile + koff), kIdescQK<kHalf>, ks > 0);
   }
 }
 // O_X (+)= P_X . V for one V tile: 8 k-steps of 16 keys, P read from tensor memory.
-template <int X, int STAGE>
+template <int X, int STAGE, bool kHalf>
 __device__ __forceinline__ void issue_pv(uint32_t tmem, uint32_t dv, bool first) {
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks)
     mma_ts(tmem + 256 + X * kHeadDim, tmem + X * kBN + ks * 8,
-           desc64(dv + STAGE * (kTileBytes >> 4) + ks * (2048 >> 4)), kIdescPV, (!first) || ks > 0);
+           desc64(dv + STAGE * (kTileBytes >> 4) + ks * (2048 >> 4)), kIdescPV<kHalf>, (!first) || ks > 0);
 }
 
+template <bool kHalf>
 __global__ void __launch_bounds__(kThreads, 1)
 attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
                   const __grid_constant__ CUtensorMap tmap_v, const KernelArgs a) {
@@ -390,8 +391,8 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         if (ok) {
           tc_fence_after();
           if (el) {
-            if (kc & 1) { issue_qk<0, 1>(tm, dq, dk); tc_commit(smem_u32(&c.s_full[0])); issue_qk<1, 1>(tm, dq, dk); }
-            else        { issue_qk<0, 0>(tm, dq, dk); tc_commit(smem_u32(&c.s_full[0])); issue_qk<1, 0>(tm, dq, dk); }
+            if (kc & 1) { issue_qk<0, 1, kHalf>(tm, dq, dk); tc_commit(smem_u32(&c.s_full[0])); issue_qk<1, 1, kHalf>(tm, dq, dk); }
+            else        { issue_qk<0, 0, kHalf>(tm, dq, dk); tc_commit(smem_u32(&c.s_full[0])); issue_qk<1, 0, kHalf>(tm, dq, dk); }
             tc_commit(smem_u32(&c.s_full[1]));
             tc_commit(smem_u32(&c.k_empty[kc & 1]));
           }
@@ -413,7 +414,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
           pph0 ^= 1;
           tc_fence_after();
           if (lane == 0) TL_STAMP(a, n, j, 0);               // P_A seen
-          if (el) { if (vs) issue_pv<0, 1>(tm, dv, j == 0); else issue_pv<0, 0>(tm, dv, j == 0); }
+          if (el) { if (vs) issue_pv<0, 1, kHalf>(tm, dv, j == 0); else issue_pv<0, 0, kHalf>(tm, dv, j == 0); }
           __syncwarp();
           if (lane == 0) TL_STAMP(a, n, j, 1);               // PV_A issued
           if (more) {
@@ -423,7 +424,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
             if (lane == 0) TRACE_ADD(a, 2, t_k);
             tc_fence_after();
             if (el) {
-              if (ks) issue_qk<0, 1>(tm, dq, dk); else issue_qk<0, 0>(tm, dq, dk);
+              if (ks) issue_qk<0, 1, kHalf>(tm, dq, dk); else issue_qk<0, 0, kHalf>(tm, dq, dk);
               tc_commit(smem_u32(&c.s_full[0]));
             }
           } else if (el) {
@@ -439,10 +440,10 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
           tc_fence_after();
           if (lane == 0) TL_STAMP(a, n, j, 3);               // P_B seen
           if (el) {
-            if (vs) issue_pv<1, 1>(tm, dv, j == 0); else issue_pv<1, 0>(tm, dv, j == 0);
+            if (vs) issue_pv<1, 1, kHalf>(tm, dv, j == 0); else issue_pv<1, 0, kHalf>(tm, dv, j == 0);
             tc_commit(smem_u32(&c.v_empty[vs]));
             if (more) {
-              if (ks) issue_qk<1, 1>(tm, dq, dk); else issue_qk<1, 0>(tm, dq, dk);
+              if (ks) issue_qk<1, 1, kHalf>(tm, dq, dk); else issue_qk<1, 0, kHalf>(tm, dq, dk);
               tc_commit(smem_u32(&c.s_full[1]));
               tc_commit(smem_u32(&c.k_empty[ks]));
             } else {
@@ -496,8 +497,8 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         const int key0 = j * kBN;
         const bool masked = key0 + kBN > it.kv_len ||
                             (it.causal && it.kv_tok0 + key0 + kBN - 1 > it.tok0 + x * kTileM);
-        if (masked) softmax_row<true>(tS, tO, j, key0, lim, sl2, m_ref, l, a, n);
-        else softmax_row<false>(tS, tO, j, key0, lim, sl2, m_ref, l, a, n);
+        if (masked) softmax_row<true, kHalf>(tS, tO, j, key0, lim, sl2, m_ref, l, a, n);
+        else softmax_row<false, kHalf>(tS, tO, j, key0, lim, sl2, m_ref, l, a, n);
         tc_fence_before();
         mbar_arrive(smem_u32(&c.p_full[x]));
         if (threadIdx.x == 128) TL_STAMP(a, n, j, 6);        // P_A arrived
@@ -572,14 +573,14 @@ EncodeTiledFn encode_fn() {
 }
 
 // [T, Hkv, D] bf16 with element strides (st, sh, 1): boxes of 128 tokens x 1 head x 64 dims
-bool make_kv_map(CUtensorMap* m, const __nv_bfloat16* base, int64_t T, int Hkv, int64_t st, int64_t sh) {
+bool make_kv_map(CUtensorMap* m, bool fp16, const __nv_bfloat16* base, int64_t T, int Hkv, int64_t st, int64_t sh) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return false;
   const cuuint64_t dims[3] = {(cuuint64_t)kHeadDim, (cuuint64_t)Hkv, (cuuint64_t)T};
   const cuuint64_t strides[2] = {(cuuint64_t)sh * 2, (cuuint64_t)st * 2};
   const cuuint32_t box[3] = {64, 1, (cuuint32_t)kBN};
   const cuuint32_t estr[3] = {1, 1, 1};
-  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<__nv_bfloat16*>(base), dims, strides, box, estr,
+  return fn(m, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<__nv_bfloat16*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -592,16 +593,17 @@ cudaError_t launch_attend_tc5(const Params& p, const __nv_bfloat16* q, const __n
                               const int32_t* row_list, float* partial_out, float* partial_lse,
                               int32_t* work_counter, int32_t* status, cudaStream_t st) {
   CUtensorMap mk, mv;
-  if (!make_kv_map(&mk, k, p.T, p.Hkv, p.sk_t, p.sk_h) || !make_kv_map(&mv, v, p.T, p.Hkv, p.sv_t, p.sv_h))
+  if (!make_kv_map(&mk, p.fp16 != 0, k, p.T, p.Hkv, p.sk_t, p.sk_h) || !make_kv_map(&mv, p.fp16 != 0, v, p.T, p.Hkv, p.sv_t, p.sv_h))
     return cudaErrorNotSupported;
-  cudaError_t e = cudaFuncSetAttribute(attend_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+  auto kernel = p.fp16 ? attend_tc5_kernel<true> : attend_tc5_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   if (e != cudaSuccess) return e;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const KernelArgs args{q, cu, list_counts, list_offsets, tile_prefix, row_list, partial_out, partial_lse,
                         work_counter, status};
-  attend_tc5_kernel<<<sms, kThreads, kSmemBytes, st>>>(p, mk, mv, args);
+  kernel<<<sms, kThreads, kSmemBytes, st>>>(p, mk, mv, args);
   return cudaGetLastError();
 }
 

@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -22,6 +23,7 @@ struct Params {
   int max_seqlen, C, topk;
   int mc, slots, hist, NP;               // NP = partial results per row
   int64_t rows, lists;
+  int fp16;                              // element type of q, k, v, out: 0 bf16, 1 fp16
   int64_t sel_rs;                        // elements between two ranks of `selected` (heads of the full tensor * Tq)
   int64_t sq_t, sq_h, sk_t, sk_h, sv_t, sv_h, so_t, so_h;
 };
@@ -30,6 +32,28 @@ __host__ inline int cdiv_i(int64_t a, int64_t b) { return (int)((a + b - 1) / b)
 
 __device__ __forceinline__ float bf16_lo(uint32_t x) { return __uint_as_float(x << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t x) { return __uint_as_float(x & 0xffff0000u); }
+
+// 16-bit element helpers; kHalf selects fp16, otherwise bf16.  Tensors are passed as
+// __nv_bfloat16* whatever their element type: only these helpers interpret the bits.
+template <bool kHalf>
+__device__ __forceinline__ float2 unpack2(uint32_t x) {
+  if (kHalf) return __half22float2(*reinterpret_cast<const __half2*>(&x));
+  return make_float2(bf16_lo(x), bf16_hi(x));
+}
+template <bool kHalf>
+__device__ __forceinline__ uint32_t pack2_16(float lo, float hi) {       // round to nearest even
+  if (kHalf) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <bool kHalf>
+__device__ __forceinline__ void unpack8(const uint4 x, float (&f)[8]) {
+  const float2 a = unpack2<kHalf>(x.x), b = unpack2<kHalf>(x.y), c = unpack2<kHalf>(x.z), d = unpack2<kHalf>(x.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
 
 // Chunk slot geometry (routing.py:565-579).
 struct Slot {

@@ -49,6 +49,7 @@ cudaError_t launch_chunk_metadata(const Params& p, const int32_t* cu, int32_t* c
 // ---------------------------------------------------------------------------
 constexpr int kMeanThreads = kMeanLanes * (kHeadDim / 8);   // 512
 
+template <bool kHalf>
 __global__ void __launch_bounds__(kMeanThreads)
 chunk_mean_kernel(Params p, const __nv_bfloat16* __restrict__ k, const int32_t* __restrict__ cu,
                   __nv_bfloat16* __restrict__ means) {
@@ -75,18 +76,18 @@ chunk_mean_kernel(Params p, const __nv_bfloat16* __restrict__ k, const int32_t* 
         x[u] = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)(r + u * kMeanLanes) * p.sk_t));
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        acc[0] += bf16_lo(x[u].x); acc[1] += bf16_hi(x[u].x);
-        acc[2] += bf16_lo(x[u].y); acc[3] += bf16_hi(x[u].y);
-        acc[4] += bf16_lo(x[u].z); acc[5] += bf16_hi(x[u].z);
-        acc[6] += bf16_lo(x[u].w); acc[7] += bf16_hi(x[u].w);
+        float f[8];
+        unpack8<kHalf>(x[u], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
       }
     }
     for (; r < p.C; r += kMeanLanes) {
       const uint4 x = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)r * p.sk_t));
-      acc[0] += bf16_lo(x.x); acc[1] += bf16_hi(x.x);
-      acc[2] += bf16_lo(x.y); acc[3] += bf16_hi(x.y);
-      acc[4] += bf16_lo(x.z); acc[5] += bf16_hi(x.z);
-      acc[6] += bf16_lo(x.w); acc[7] += bf16_hi(x.w);
+      float f[8];
+      unpack8<kHalf>(x, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
     }
   }
 #pragma unroll
@@ -97,14 +98,16 @@ chunk_mean_kernel(Params p, const __nv_bfloat16* __restrict__ k, const int32_t* 
 #pragma unroll
     for (int a = 1; a < kMeanLanes; ++a) tot += part[a][threadIdx.x];
     const float mean = sl.historical ? __fdiv_rn(tot, (float)p.C) : 0.f;
-    dst[threadIdx.x] = __float2bfloat16_rn(mean);
+    if (kHalf) reinterpret_cast<__half*>(dst)[threadIdx.x] = __float2half_rn(mean);
+    else dst[threadIdx.x] = __float2bfloat16_rn(mean);
   }
 }
 
 cudaError_t launch_chunk_means(const Params& p, const __nv_bfloat16* k, const int32_t* cu,
                                __nv_bfloat16* means, cudaStream_t st) {
   dim3 grid(p.slots, p.Hkv);
-  chunk_mean_kernel<<<grid, kMeanThreads, 0, st>>>(p, k, cu, means);
+  if (p.fp16) chunk_mean_kernel<true><<<grid, kMeanThreads, 0, st>>>(p, k, cu, means);
+  else chunk_mean_kernel<false><<<grid, kMeanThreads, 0, st>>>(p, k, cu, means);
   return cudaGetLastError();
 }
 
@@ -143,10 +146,6 @@ __device__ __forceinline__ float dot8(const float (&q)[8], const float4 a, const
   s = __fmaf_rn(q[7], b.w, s);
   return s;
 }
-__device__ __forceinline__ void unpack8(const uint4 x, float (&f)[8]) {
-  f[0] = bf16_lo(x.x); f[1] = bf16_hi(x.x); f[2] = bf16_lo(x.y); f[3] = bf16_hi(x.y);
-  f[4] = bf16_lo(x.z); f[5] = bf16_hi(x.z); f[6] = bf16_lo(x.w); f[7] = bf16_hi(x.w);
-}
 
 // Smallest key of a row's list and its position (ties: lowest position), over the 4 lanes of a group.
 __device__ __forceinline__ void list_min(const unsigned long long* best, int hist, int t, unsigned gmask,
@@ -167,6 +166,7 @@ __device__ __forceinline__ void list_min(const unsigned long long* best, int his
   pos = mine_i;
 }
 
+template <bool kHalf>
 __global__ void __launch_bounds__(kGateThreads, 4)
 gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__ q,
                  const __nv_bfloat16* __restrict__ means, const int32_t* __restrict__ cu,
@@ -204,7 +204,7 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
       const uint4 x = __ldg(reinterpret_cast<const uint4*>(
           means + ((int64_t)(slot0 + c0 + c) * p.Hkv + hk) * kHeadDim + part * 8));
       float f[8];
-      unpack8(x, f);
+      unpack8<kHalf>(x, f);
       means_s[c * 32 + part * 2] = make_float4(f[0], f[1], f[2], f[3]);
       means_s[c * 32 + part * 2 + 1] = make_float4(f[4], f[5], f[6], f[7]);
     }
@@ -219,7 +219,7 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
         const __nv_bfloat16* qrow = q + (int64_t)(tok - p.win_lo) * p.sq_t + (int64_t)(hk * p.G + hl) * p.sq_h;
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          unpack8(__ldg(reinterpret_cast<const uint4*>(qrow + (t + 4 * k) * 8)), qf[k]);
+          unpack8<kHalf>(__ldg(reinterpret_cast<const uint4*>(qrow + (t + 4 * k) * 8)), qf[k]);
       }
       // The row keeps its `hist` largest keys so far (unordered) in shared memory; a new
       // key replaces the smallest one if it is larger.  0 marks an empty place.
@@ -307,10 +307,11 @@ cudaError_t launch_gate_topk(const Params& p, const __nv_bfloat16* q, const __nv
   if (tokens_per_cta < 1) tokens_per_cta = 1;
   const size_t smem = gate_smem_bytes(p);
   if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
-  cudaError_t e = cudaFuncSetAttribute(gate_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  auto kernel = p.fp16 ? gate_topk_kernel<true> : gate_topk_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   dim3 grid(cdiv_i(p.max_seqlen, tokens_per_cta), p.Hkv, p.B);
-  gate_topk_kernel<<<grid, kGateThreads, smem, st>>>(p, tokens_per_cta, q, means, cu, selected, list_counts);
+  kernel<<<grid, kGateThreads, smem, st>>>(p, tokens_per_cta, q, means, cu, selected, list_counts);
   return cudaGetLastError();
 }
 

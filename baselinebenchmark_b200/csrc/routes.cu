@@ -141,6 +141,7 @@ cudaError_t launch_compact(const Params& p, const int32_t* cu, const int32_t* se
 // ---------------------------------------------------------------------------
 constexpr int kMergeThreads = 256;
 
+template <bool kHalf>
 __global__ void __launch_bounds__(kMergeThreads)
 merge_kernel(Params p, const float* __restrict__ partial_out, const float* __restrict__ partial_lse,
              const int32_t* __restrict__ status, __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out) {
@@ -170,11 +171,9 @@ merge_kernel(Params p, const float* __restrict__ partial_out, const float* __res
     }
     const int64_t t = row / p.Hq;
     const int h = (int)(row - t * p.Hq);
-    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
-    __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
     uint2 pk;
-    pk.x = *reinterpret_cast<uint32_t*>(&lo);
-    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    pk.x = pack2_16<kHalf>(acc.x, acc.y);
+    pk.y = pack2_16<kHalf>(acc.z, acc.w);
     *reinterpret_cast<uint2*>(out + t * p.so_t + (int64_t)h * p.so_h + lane * 4) = pk;
     if (lse_out != nullptr && lane == 0) lse_out[(int64_t)h * p.Tq + t] = logf(tot) + mx;
   }
@@ -184,7 +183,8 @@ cudaError_t launch_merge(const Params& p, const float* partial_out, const float*
                          const int32_t* status, __nv_bfloat16* out, float* lse_out, cudaStream_t st) {
   int64_t blocks = (p.rows + (kMergeThreads / 32) - 1) / (kMergeThreads / 32);
   if (blocks > 148 * 64) blocks = 148 * 64;
-  merge_kernel<<<(int)blocks, kMergeThreads, 0, st>>>(p, partial_out, partial_lse, status, out, lse_out);
+  if (p.fp16) merge_kernel<true><<<(int)blocks, kMergeThreads, 0, st>>>(p, partial_out, partial_lse, status, out, lse_out);
+  else merge_kernel<false><<<(int)blocks, kMergeThreads, 0, st>>>(p, partial_out, partial_lse, status, out, lse_out);
   return cudaGetLastError();
 }
 

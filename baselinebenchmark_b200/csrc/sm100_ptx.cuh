@@ -262,8 +262,9 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_
 // Instruction descriptor for kind::f16 with bf16 operands and fp32 accumulation:
 //   bits 4-5 D format (1 = f32), 7-9 A format (1 = bf16), 10-12 B format (1 = bf16),
 //   15 A major, 16 B major (0 = K-major, 1 = MN-major), 17-22 N >> 3, 24-28 M >> 4.
-__host__ __device__ constexpr uint32_t idesc_bf16_f32(int M, int N, int a_mn_major, int b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
+__host__ __device__ constexpr uint32_t idesc_16_f32(bool fp16, int M, int N, int a_mn_major, int b_mn_major) {
+  const uint32_t ab = fp16 ? 0u : 1u;    // operand format of A (bits 7-9) and B (bits 10-12): 0 f16, 1 bf16
+  return (1u << 4) | (ab << 7) | (ab << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 

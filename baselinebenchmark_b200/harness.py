@@ -104,12 +104,12 @@ def make_inputs(case: Case, device):
 
 
 def supported(case: Case) -> bool:
-    return case.dtype == "bfloat16" and case.head_dim == 128
+    return case.dtype in ("bfloat16", "float16") and case.head_dim == 128
 
 
 def run_case(case: Case, args, device):
     if not supported(case):
-        return {**asdict(case), "status": "skipped", "reason": "this build: bfloat16, head_dim 128"}
+        return {**asdict(case), "status": "skipped", "reason": "this build: head_dim 128"}
     q, k, v, cu = make_inputs(case, device)
     call = (q, k, v, cu, max(case.seq_lens), case.chunk_size, case.topk)
     with torch.inference_mode():

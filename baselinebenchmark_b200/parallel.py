@@ -59,8 +59,8 @@ def _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, windo
     if q.shape[2] > 256:
         raise ValueError(f"head_dim must be <= 256 to match FlashMoBA, got {q.shape[2]}")
     # limits of this build (no fallback by design)
-    if q.dtype != torch.bfloat16 or q.shape[2] != 128:
-        raise NotImplementedError("this build supports bfloat16 with head_dim 128 only")
+    if q.shape[2] != 128:
+        raise NotImplementedError("this build supports head_dim 128 only")
     for name, t in (("q", q), ("k", k), ("v", v)):
         if t.stride(2) != 1:
             raise NotImplementedError(f"{name} must be contiguous in its last dimension")
@@ -72,6 +72,7 @@ def make_problem(q, k, v, out, cu_seqlens, max_seqlen, chunk, topk, attend_impl=
     packed tokens [q_token_begin, q_token_begin + q.shape[0]) and k/v all of them."""
     return _lib.Problem(
         q_token_begin=q_token_begin or 0, q_tokens=q.shape[0] if q_token_begin is not None else 0,
+        dtype=1 if q.dtype == torch.float16 else 0,
         total_tokens=k.shape[0], batch=cu_seqlens.numel() - 1, num_q_heads=q.shape[1],
         num_kv_heads=k.shape[1], head_dim=q.shape[2], max_seqlen=max_seqlen, chunk_size=chunk,
         topk=topk, attend_impl=attend_impl,

@@ -47,6 +47,13 @@ enum {
   MOBA_ATTEND_MMA_SYNC = 1  /* legacy mma.sync tensor path, kept as cross-check  */
 };
 
+/* Element type of q, k, v and out (parallel.py:448-457 accepts both; the
+ * reference's suite runs bf16 and fp16, moba_compare.py:56, :69-71). */
+enum {
+  MOBA_DTYPE_BF16 = 0,
+  MOBA_DTYPE_FP16 = 1
+};
+
 /* Problem description.  Mirrors the arguments of parallel_moba
  * (parallel.py:377-385) plus the strides its kernels receive. */
 typedef struct moba_problem {
@@ -71,6 +78,8 @@ typedef struct moba_problem {
    * total_tokens.  The window must start and end on chunk boundaries of its
    * sequences (or at sequence ends).  q_tokens == 0: every token is a query. */
   int64_t q_token_begin, q_tokens;
+  int32_t dtype;            /* MOBA_DTYPE_*; 0 (bf16) in a zero-initialised struct */
+  int32_t reserved;         /* must be 0                                         */
 } moba_problem_t;
 
 /* Derived sizes: mc = ceil(max_seqlen / chunk), slots = B*mc,

@@ -38,7 +38,7 @@ def metadata(prob, cu):
 
 def means(prob, k, cu):
     d = dims_of(prob)
-    m = torch.empty(d.slots, prob.num_kv_heads, prob.head_dim, dtype=torch.bfloat16, device="cuda")
+    m = torch.empty(d.slots, prob.num_kv_heads, prob.head_dim, dtype=k.dtype, device="cuda")
     _lib.check(_lib.lib().moba_chunk_means(C.byref(prob), k.data_ptr(), cu.data_ptr(), m.data_ptr(), stream()))
     return m
 

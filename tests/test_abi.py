@@ -34,7 +34,7 @@ def test_header_symbols_are_exported(lib):
     assert declared == set(_lib.SYMBOLS)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.moba_b200_abi_version() == 2
+    assert lib.moba_b200_abi_version() == 3
 
 
 def test_problem_check_codes(lib):
@@ -128,8 +128,9 @@ def test_host_validation_value_checks(monkeypatch):
         parallel._validate(fq, fk, fv, fcu, 64, 32, 65)
     with pytest.raises(ValueError, match="divisible"):
         parallel._validate(T(q[:, :3]), fk, fv, fcu, 64, 32, 2)
+    parallel._validate(T(q.half()), T(k.half()), T(v.half()), fcu, 64, 32, 2)      # float16 is built
     with pytest.raises(NotImplementedError):
-        parallel._validate(T(q.half()), T(k.half()), T(v.half()), fcu, 64, 32, 2)
+        parallel._validate(T(q[..., :64]), T(k[..., :64]), T(v[..., :64]), fcu, 64, 32, 2)
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

@@ -21,6 +21,7 @@ pytestmark = pytest.mark.gpu
 
 MAX_ABS, MEAN_ABS = 2e-2, 2e-3
 IMPLS = [pytest.param(_lib.ATTEND_TCGEN05, id="tcgen05"), pytest.param(_lib.ATTEND_MMA_SYNC, id="mma_sync")]
+DTYPES = [pytest.param(torch.bfloat16, id="bf16"), pytest.param(torch.float16, id="fp16")]
 GOLDEN = sorted(glob.glob(str(Path(__file__).parent / "golden" / "routing_*.npz")))
 
 # (name, seq_lens, Hq, Hkv, chunk, topk, max_seqlen or None)
@@ -38,8 +39,8 @@ SMALL_CASES = [
 ]
 
 
-def _case_inputs(lens, hq, hkv, chunk, seed):
-    return O.make_inputs(list(lens), hq, hkv, 128, chunk, seed)
+def _case_inputs(lens, hq, hkv, chunk, seed, dtype=torch.bfloat16):
+    return O.make_inputs(list(lens), hq, hkv, 128, chunk, seed, dtype=dtype)
 
 
 @pytest.mark.parametrize("path", GOLDEN, ids=lambda p: p.split("routing_")[-1][:-4])
@@ -62,10 +63,31 @@ def test_golden_routing_through_cuda(path):
     np.testing.assert_array_equal(sel.cpu().numpy(), z["selected_ref"])
 
 
+@pytest.mark.parametrize("path", GOLDEN, ids=lambda p: p.split("routing_")[-1][:-4])
+def test_golden_routing_through_cuda_fp16(path):
+    """The same fixtures in float16, the dtype the reference kernels produced them in: the
+    float16 chunk means must equal the reference kernel's own output bit for bit, and the
+    selection from the means the reference's top-k kernel was given must equal its output."""
+    z = np.load(path)
+    if int(z["d"]) != 128:
+        pytest.skip("fixture has head_dim != 128")
+    q = torch.from_numpy(z["q_bits"]).view(torch.bfloat16).half().cuda()
+    k = torch.from_numpy(z["k_bits"]).view(torch.bfloat16).half().cuda()
+    cu = torch.from_numpy(z["cu_seqlens"]).cuda()
+    prob, _ = G.problem_for(q, k, k, cu, int(z["max_seqlen"]), int(z["chunk"]), int(z["topk"]))
+    assert prob.dtype == 1
+    m = G.means(prob, k, cu)
+    np.testing.assert_array_equal(m.cpu().numpy(), z["means_ref_f16"])
+    given = torch.from_numpy(z["means_rne_bits"]).view(torch.bfloat16).half().cuda()
+    sel, _ = G.gate(prob, q, given, cu)
+    np.testing.assert_array_equal(sel.cpu().numpy(), z["selected_ref"])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("case", SMALL_CASES, ids=lambda c: c[0])
-def test_routing_bit_exact(case):
+def test_routing_bit_exact(case, dtype):
     name, lens, hq, hkv, chunk, topk, max_len = case
-    q, k, v, cu = _case_inputs(lens, hq, hkv, chunk, seed=zlib.crc32(name.encode()) % 1000)
+    q, k, v, cu = _case_inputs(lens, hq, hkv, chunk, seed=zlib.crc32(name.encode()) % 1000, dtype=dtype)
     max_seqlen = max_len or max(lens)
     cu_chunk_o, chunk_end_o, valid_o, mc = O.chunk_slots(cu, max_seqlen, chunk)
     hist = O.historical_topk(topk, mc)
@@ -113,11 +135,12 @@ def test_routing_bit_exact(case):
         assert np.all(np.isneginf(plse[:, 1:][empty])) and np.all(plse[:, 1:][~empty] == 0)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("impl", IMPLS)
 @pytest.mark.parametrize("case", SMALL_CASES, ids=lambda c: c[0])
-def test_forward_matches_fp32_evaluation(case, impl):
+def test_forward_matches_fp32_evaluation(case, impl, dtype):
     name, lens, hq, hkv, chunk, topk, max_len = case
-    q, k, v, cu = _case_inputs(lens, hq, hkv, chunk, seed=zlib.crc32(name.encode()) % 1000)
+    q, k, v, cu = _case_inputs(lens, hq, hkv, chunk, seed=zlib.crc32(name.encode()) % 1000, dtype=dtype)
     max_seqlen = max_len or max(lens)
     ref, ref_lse, sel_o = O.moba_forward(q, k, v, cu, max_seqlen, chunk, topk, dtype=torch.float32)
     qd, kd, vd = G.to_dev(q, k, v)
@@ -199,12 +222,13 @@ def test_separated_scores_against_float64(lengths, topk, impl):
     assert diff.max().item() < 0.04 and diff.mean().item() < 4e-4
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("impl", IMPLS)
-def test_config0_full(impl):
+def test_config0_full(impl, dtype):
     """BASELINE.json configs[0]: 4096 tokens, 8/8 heads, chunk 512, top-k 3."""
     cfg = O.CONFIGS[0]
     lens = O.config_lengths(0)
-    q, k, v, cu = O.make_inputs(lens, cfg["hq"], cfg["hkv"], cfg["d"], cfg["chunk"], seed=42)
+    q, k, v, cu = O.make_inputs(lens, cfg["hq"], cfg["hkv"], cfg["d"], cfg["chunk"], seed=42, dtype=dtype)
     ref, ref_lse, sel_o = O.moba_forward(q, k, v, cu, max(lens), cfg["chunk"], cfg["topk"])
     out, lse, sel = parallel.moba_forward(*G.to_dev(q, k, v), torch.from_numpy(cu).cuda(), max(lens), cfg["chunk"],
                                           cfg["topk"], return_lse=True, return_selected=True, attend_impl=impl)
@@ -316,8 +340,10 @@ def test_public_operator_names():
         c = torch.ops.moba_b200.moba_attn_varlen(qd, kd, vd, cud, 512, 128, 3)
     assert torch.equal(a, b) and torch.equal(a, c)
     assert native_moba._supported(qd)
+    assert native_moba._supported(qd.half())
+    assert pkg.parallel_moba(qd.half(), kd.half(), vd.half(), cud, 512, 128, 3).dtype == torch.float16
     with pytest.raises(NotImplementedError):
-        pkg.parallel_moba(qd.half(), kd.half(), vd.half(), cud, 512, 128, 3)
+        pkg.parallel_moba(qd[..., :64], kd[..., :64], vd[..., :64], cud, 512, 128, 3)
 
 
 @pytest.mark.parametrize("impl", IMPLS)
