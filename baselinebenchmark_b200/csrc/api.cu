@@ -25,7 +25,9 @@ int check_problem(const moba_problem_t* p) {
   if (p->max_seqlen <= 0 || p->chunk_size <= 0) return MOBA_E_SHAPE;       // :428-431
   if (p->topk < 1 || p->topk > kMaxTopk) return MOBA_E_TOPK;               // :432-437
   if (p->head_dim > 256) return MOBA_E_SHAPE;                              // :445-446
-  if (p->head_dim != kHeadDim) return MOBA_E_UNSUPPORTED;
+  if (p->head_dim != 64 && p->head_dim != 96 && p->head_dim != 128 && p->head_dim != 256) return MOBA_E_UNSUPPORTED;
+  // the tcgen05 dense stage is built for head_dim 128; other sizes run the mma.sync one
+  if (p->attend_impl == MOBA_ATTEND_TCGEN05 && p->head_dim != kHeadDim) return MOBA_E_UNSUPPORTED;
   if (p->num_q_heads / p->num_kv_heads > 128) return MOBA_E_UNSUPPORTED;
   if (p->attend_impl != MOBA_ATTEND_TCGEN05 && p->attend_impl != MOBA_ATTEND_MMA_SYNC) return MOBA_E_UNSUPPORTED;
   if ((p->dtype != MOBA_DTYPE_BF16 && p->dtype != MOBA_DTYPE_FP16) || p->reserved != 0) return MOBA_E_UNSUPPORTED;
@@ -113,11 +115,11 @@ Workspace carve(const Params& r, void* base) {
   w.list_offsets = static_cast<int32_t*>(take((lists + 1) * sizeof(int32_t)));
   w.tile_prefix = static_cast<int32_t*>(take((lists + 1) * sizeof(int32_t)));
   w.cursors = static_cast<int32_t*>(take(lists * sizeof(int32_t)));
-  w.means = static_cast<__nv_bfloat16*>(take((size_t)r.slots * r.Hkv * kHeadDim * 2));
+  w.means = static_cast<__nv_bfloat16*>(take((size_t)r.slots * r.Hkv * r.D * 2));
   w.selected = static_cast<int32_t*>(take((size_t)r.hist * r.rows * sizeof(int32_t)));
   w.row_list = static_cast<int32_t*>(take((size_t)r.hist * r.rows * sizeof(int32_t)));
   w.partial_lse = static_cast<float*>(take((size_t)r.rows * r.NP * sizeof(float)));
-  w.partial_out = static_cast<float*>(take((size_t)r.rows * r.NP * kHeadDim * sizeof(float)));
+  w.partial_out = static_cast<float*>(take((size_t)r.rows * r.NP * r.D * sizeof(float)));
   w.total = off;
   return w;
 }
@@ -183,7 +185,7 @@ const char* moba_b200_strerror(int code) {
   switch (code) {
     case MOBA_OK: return "ok";
     case MOBA_E_SHAPE: return "q, k, v, cu_seqlens or the integer arguments have an invalid shape or value";
-    case MOBA_E_UNSUPPORTED: return "configuration outside this build (bf16 or fp16, head_dim 128, contiguous innermost dim)";
+    case MOBA_E_UNSUPPORTED: return "configuration outside this build (bf16 or fp16; head_dim 64, 96, 128 or 256, tcgen05 dense stage at 128 only)";
     case MOBA_E_WORKSPACE: return "workspace is null or too small";
     case MOBA_E_NULL: return "a required pointer is null";
     case MOBA_E_TOPK: return "moba_topk must be in 1..64";
@@ -393,8 +395,8 @@ int moba_workspace_size_host(const moba_problem_t* p, size_t* bytes) {
   if (rc != MOBA_OK) return rc;
   if (bytes == nullptr) return MOBA_E_NULL;
   const Params r = make_params(p);
-  size_t extra = align_up((size_t)r.T * r.Hq * kHeadDim * 2) * 2 +      // q, out
-                 align_up((size_t)r.T * r.Hkv * kHeadDim * 2) * 2 +     // k, v
+  size_t extra = align_up((size_t)r.T * r.Hq * r.D * 2) * 2 +      // q, out
+                 align_up((size_t)r.T * r.Hkv * r.D * 2) * 2 +     // k, v
                  align_up((size_t)(r.B + 1) * 4) +                      // cu_seqlens
                  align_up((size_t)kHostMaxUnits * 2 * 4) +              // [0, prefix] pairs of the windows
                  align_up((size_t)r.rows * 4);                          // lse
@@ -414,13 +416,13 @@ int moba_forward_host(const moba_problem_t* p, const void* q_host, const void* k
   const Params r = make_params(p);
   if (r.Tq != r.T) return MOBA_E_UNSUPPORTED;             // the host variant runs whole problems
   // host tensors are taken as contiguous [T, H, D]
-  if (r.sq_h != kHeadDim || r.sq_t != (int64_t)r.Hq * kHeadDim || r.sk_h != kHeadDim ||
-      r.sk_t != (int64_t)r.Hkv * kHeadDim || r.sv_h != kHeadDim || r.sv_t != (int64_t)r.Hkv * kHeadDim ||
-      r.so_h != kHeadDim || r.so_t != (int64_t)r.Hq * kHeadDim)
+  if (r.sq_h != r.D || r.sq_t != (int64_t)r.Hq * r.D || r.sk_h != r.D ||
+      r.sk_t != (int64_t)r.Hkv * r.D || r.sv_h != r.D || r.sv_t != (int64_t)r.Hkv * r.D ||
+      r.so_h != r.D || r.so_t != (int64_t)r.Hq * r.D)
     return MOBA_E_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
   char* base = static_cast<char*>(workspace) + core;
-  const size_t qrow = (size_t)r.Hq * kHeadDim * 2, krow = (size_t)r.Hkv * kHeadDim * 2;
+  const size_t qrow = (size_t)r.Hq * r.D * 2, krow = (size_t)r.Hkv * r.D * 2;
   const size_t qbytes = (size_t)r.T * qrow, kbytes = (size_t)r.T * krow;
   char* dq = base;               base += align_up(qbytes);
   char* dout = base;             base += align_up(qbytes);

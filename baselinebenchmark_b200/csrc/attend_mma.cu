@@ -22,14 +22,16 @@ namespace {
 constexpr int kRows = kMmaTileRows;   // 128
 constexpr int kBN = 64;
 constexpr int kThreads = 256;
-constexpr int kRowBytes = kHeadDim * 2;   // 256
+// Bytes of one tile row in shared memory: the head dim rounded up to 64, 128 or 256 elements.
+__host__ __device__ constexpr int row_bytes(int d) { return d <= 64 ? 128 : (d <= 128 ? 256 : 512); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
-// byte offset of 16-byte chunk `ch` (0..15) of row `r` in a [rows][128] bf16 tile
+// byte offset of 16-byte chunk `ch` of row `r` in a [rows][D] tile of 16-bit elements
+template <int D>
 __device__ __forceinline__ uint32_t swz(int r, int ch) {
-  return (uint32_t)(r * kRowBytes + (((ch & 8) | ((ch ^ r) & 7)) << 4));
+  return (uint32_t)(r * row_bytes(D) + (((ch & ~7) | ((ch ^ r) & 7)) << 4));
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
   const int n = pred ? 16 : 0;
@@ -61,31 +63,34 @@ __device__ __forceinline__ void mma_16(float (&c)[4], const uint32_t (&a)[4], ui
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+template <int D>
 struct Smem {
-  __nv_bfloat16 q[kRows * kHeadDim];
-  __nv_bfloat16 k[2][kBN * kHeadDim];
-  __nv_bfloat16 v[2][kBN * kHeadDim];
+  unsigned char q[kRows * row_bytes(D)];
+  unsigned char k[2][kBN * row_bytes(D)];
+  unsigned char v[2][kBN * row_bytes(D)];
   int64_t qoff[kRows];
   int32_t entry[kRows];
   int32_t item;
 };
 
-__device__ __forceinline__ void load_kv_tile(const Params& p, const Item& it, int tile, Smem& s, int buf,
+template <int D>
+__device__ __forceinline__ void load_kv_tile(const Params& p, const Item& it, int tile, Smem<D>& s, int buf,
                                              const __nv_bfloat16* __restrict__ k,
                                              const __nv_bfloat16* __restrict__ v) {
   const uint32_t kb = smem_u32(s.k[buf]), vb = smem_u32(s.v[buf]);
-  for (int i = threadIdx.x; i < kBN * 16; i += kThreads) {
-    const int r = i >> 4, ch = i & 15;
+  constexpr int kChunks = D / 8;
+  for (int i = threadIdx.x; i < kBN * kChunks; i += kThreads) {
+    const int r = i / kChunks, ch = i - r * kChunks;
     const int key = tile * kBN + r;
     const bool ok = key < it.kv_len;
     const int64_t tok = (int64_t)it.kv_tok0 + (ok ? key : 0);
-    cp_async16(kb + swz(r, ch), k + tok * p.sk_t + (int64_t)it.kv_head * p.sk_h + ch * 8, ok);
-    cp_async16(vb + swz(r, ch), v + tok * p.sv_t + (int64_t)it.kv_head * p.sv_h + ch * 8, ok);
+    cp_async16(kb + swz<D>(r, ch), k + tok * p.sk_t + (int64_t)it.kv_head * p.sk_h + ch * 8, ok);
+    cp_async16(vb + swz<D>(r, ch), v + tok * p.sv_t + (int64_t)it.kv_head * p.sv_h + ch * 8, ok);
   }
 }
 
-template <bool kHalf>
-__global__ void __launch_bounds__(kThreads, 2)
+template <bool kHalf, int D>
+__global__ void __launch_bounds__(kThreads, D > 128 ? 1 : 2)
 attend_mma_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                   const __nv_bfloat16* __restrict__ v, const int32_t* __restrict__ cu,
                   const int32_t* __restrict__ list_counts, const int32_t* __restrict__ list_offsets,
@@ -93,11 +98,12 @@ attend_mma_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bflo
                   float* __restrict__ partial_out, float* __restrict__ partial_lse,
                   int32_t* __restrict__ work_counter) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  Smem& s = *reinterpret_cast<Smem*>(smem_raw);
+  Smem<D>& s = *reinterpret_cast<Smem<D>*>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_routed = p.hist > 0 ? tile_prefix[p.lists] : 0;
   const int n_items = n_routed + own_item_count(p.slots, p.Hq, p.C, kRows);
-  const float sl2 = rsqrtf((float)kHeadDim) * 1.4426950408889634f;
+  const float sl2 = rsqrtf((float)D) * 1.4426950408889634f;
+  constexpr int kChunks = D / 8;
 
   for (;;) {
     __syncthreads();
@@ -129,24 +135,24 @@ attend_mma_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bflo
     __syncthreads();
     {
       const uint32_t qb = smem_u32(s.q);
-      for (int i = threadIdx.x; i < kRows * 16; i += kThreads) {
-        const int r = i >> 4, ch = i & 15;
-        cp_async16(qb + swz(r, ch), q + s.qoff[r] + ch * 8, s.entry[r] >= 0);
+      for (int i = threadIdx.x; i < kRows * kChunks; i += kThreads) {
+        const int r = i / kChunks, ch = i - r * kChunks;
+        cp_async16(qb + swz<D>(r, ch), q + s.qoff[r] + ch * 8, s.entry[r] >= 0);
       }
     }
     const int ntiles = (it.kv_len + kBN - 1) / kBN;
-    load_kv_tile(p, it, 0, s, 0, k, v);
+    load_kv_tile<D>(p, it, 0, s, 0, k, v);
     cp_async_commit();
 
-    float o[16][4];
+    float o[D / 8][4];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     const int row0 = warp * 16 + (lane >> 2);          // this thread's rows: row0 and row0 + 8
     const int qpos0 = it.tok0 + row0, qpos1 = qpos0 + 8;
 
     for (int j = 0; j < ntiles; ++j) {
-      if (j + 1 < ntiles) load_kv_tile(p, it, j + 1, s, (j + 1) & 1, k, v);
+      if (j + 1 < ntiles) load_kv_tile<D>(p, it, j + 1, s, (j + 1) & 1, k, v);
       cp_async_commit();
       cp_async_wait<1>();
       __syncthreads();
@@ -157,14 +163,14 @@ attend_mma_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bflo
 #pragma unroll
       for (int i = 0; i < 8; ++i) { sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f; }
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
+      for (int ks = 0; ks < D / 16; ++ks) {
         uint32_t qa[4];
-        ldsm_x4(qb + swz(qr, 2 * ks + (lane >> 4)), qa[0], qa[1], qa[2], qa[3]);
+        ldsm_x4(qb + swz<D>(qr, 2 * ks + (lane >> 4)), qa[0], qa[1], qa[2], qa[3]);
 #pragma unroll
         for (int np = 0; np < 4; ++np) {
           uint32_t b0, b1, b2, b3;
           const int r = np * 16 + (lane & 7) + ((lane >> 4) << 3);
-          ldsm_x4(kb + swz(r, 2 * ks + ((lane >> 3) & 1)), b0, b1, b2, b3);
+          ldsm_x4(kb + swz<D>(r, 2 * ks + ((lane >> 3) & 1)), b0, b1, b2, b3);
           mma_16<kHalf>(sc[2 * np], qa, b0, b1);
           mma_16<kHalf>(sc[2 * np + 1], qa, b2, b3);
         }
@@ -211,14 +217,14 @@ attend_mma_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bflo
       l0 = l0 * a0 + ps0;
       l1 = l1 * a1 + ps1;
 #pragma unroll
-      for (int dt = 0; dt < 16; ++dt) { o[dt][0] *= a0; o[dt][1] *= a0; o[dt][2] *= a1; o[dt][3] *= a1; }
+      for (int dt = 0; dt < D / 8; ++dt) { o[dt][0] *= a0; o[dt][1] *= a0; o[dt][2] *= a1; o[dt][3] *= a1; }
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
 #pragma unroll
-        for (int dp = 0; dp < 8; ++dp) {
+        for (int dp = 0; dp < D / 16; ++dp) {
           uint32_t b0, b1, b2, b3;
           const int r = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-          ldsm_x4_t(vb + swz(r, 2 * dp + (lane >> 4)), b0, b1, b2, b3);
+          ldsm_x4_t(vb + swz<D>(r, 2 * dp + (lane >> 4)), b0, b1, b2, b3);
           mma_16<kHalf>(o[2 * dp], pa[kk], b0, b1);
           mma_16<kHalf>(o[2 * dp + 1], pa[kk], b2, b3);
         }
@@ -234,16 +240,16 @@ attend_mma_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bflo
     const int e0 = s.entry[row0], e1 = s.entry[row0 + 8];
     const float i0 = 1.f / l0, i1 = 1.f / l1;
     if (e0 >= 0) {
-      float* dst = partial_out + (int64_t)e0 * kHeadDim + 2 * (lane & 3);
+      float* dst = partial_out + (int64_t)e0 * D + 2 * (lane & 3);
 #pragma unroll
-      for (int dt = 0; dt < 16; ++dt)
+      for (int dt = 0; dt < D / 8; ++dt)
         *reinterpret_cast<float2*>(dst + dt * 8) = make_float2(o[dt][0] * i0, o[dt][1] * i0);
       if ((lane & 3) == 0) partial_lse[e0] = (m0 + log2f(l0)) * 0.6931471805599453f;
     }
     if (e1 >= 0) {
-      float* dst = partial_out + (int64_t)e1 * kHeadDim + 2 * (lane & 3);
+      float* dst = partial_out + (int64_t)e1 * D + 2 * (lane & 3);
 #pragma unroll
-      for (int dt = 0; dt < 16; ++dt)
+      for (int dt = 0; dt < D / 8; ++dt)
         *reinterpret_cast<float2*>(dst + dt * 8) = make_float2(o[dt][2] * i1, o[dt][3] * i1);
       if ((lane & 3) == 0) partial_lse[e1] = (m1 + log2f(l1)) * 0.6931471805599453f;
     }
@@ -257,14 +263,22 @@ cudaError_t launch_attend_mma(const Params& p, const __nv_bfloat16* q, const __n
                               const int32_t* list_offsets, const int32_t* tile_prefix,
                               const int32_t* row_list, float* partial_out, float* partial_lse,
                               int32_t* work_counter, cudaStream_t st) {
-  const size_t smem = sizeof(Smem);
-  auto kernel = p.fp16 ? attend_mma_kernel<true> : attend_mma_kernel<false>;
+  void (*kernel)(Params, const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*, const int32_t*,
+                 const int32_t*, const int32_t*, const int32_t*, const int32_t*, float*, float*, int32_t*);
+  size_t smem;
+  switch (p.D) {
+    case 64:  kernel = p.fp16 ? attend_mma_kernel<true, 64>  : attend_mma_kernel<false, 64>;  smem = sizeof(Smem<64>);  break;
+    case 96:  kernel = p.fp16 ? attend_mma_kernel<true, 96>  : attend_mma_kernel<false, 96>;  smem = sizeof(Smem<96>);  break;
+    case 128: kernel = p.fp16 ? attend_mma_kernel<true, 128> : attend_mma_kernel<false, 128>; smem = sizeof(Smem<128>); break;
+    case 256: kernel = p.fp16 ? attend_mma_kernel<true, 256> : attend_mma_kernel<false, 256>; smem = sizeof(Smem<256>); break;
+    default: return cudaErrorInvalidValue;
+  }
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  kernel<<<sms * 2, kThreads, smem, st>>>(p, q, k, v, cu, list_counts, list_offsets, tile_prefix,
+  kernel<<<sms * (p.D > 128 ? 1 : 2), kThreads, smem, st>>>(p, q, k, v, cu, list_counts, list_offsets, tile_prefix,
                                                     row_list, partial_out, partial_lse, work_counter);
   return cudaGetLastError();
 }

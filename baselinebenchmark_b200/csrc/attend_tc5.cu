@@ -53,6 +53,7 @@ enum { ST_OK = 0, ST_PRODUCER = 1, ST_MMA = 2, ST_SOFTMAX = 3 };
 struct Ctrl {
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
   uint64_t s_full[2], p_full[2], o_full[2];
+  uint64_t item_ready[2];                  // slot filled by the prefetch warp (phase = fill count)
   uint32_t tmem_slot;
   volatile int32_t abort;
   // Work items are drawn and resolved one item ahead by a spare warp: slot (n & 1)
@@ -133,8 +134,7 @@ __device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs&
     if (it.valid) break;
   }
   if (lane == 0) { c.item[slot] = it; c.done[slot] = done; }
-  if (done) return;
-  for (int r = lane; r < 2 * kTileM; r += 32) {
+  for (int r = lane; !done && r < 2 * kTileM; r += 32) {
     int32_t e = -1;
     int64_t off = 0;
     if (r < it.nrows) {
@@ -151,40 +151,44 @@ __device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs&
     }
     c.entry[slot][r] = e;
     c.qoff[slot][r] = off;
+    if (e >= 0) {                                            // the gather of the next item then hits L2
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + off));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + off + 64));
+    }
   }
+  __syncwarp();
+  if (lane == 0) mbar_arrive(smem_u32(&c.item_ready[slot]));   // the producer may look at the slot now
 }
 
 // Common head of an item, executed by all 384 threads: take the prefetched item
-// of slot `slot` and gather its Q rows into the two swizzled Q tiles.  Returns
+// of slot `slot`; the softmax warps (kGather) gather its Q rows into the two swizzled Q tiles.  Returns
 // false when the queue is empty (or the kernel is aborting).
+template <bool kGather>
 __device__ __forceinline__ bool next_item(const KernelArgs& a, Ctrl& c, unsigned char* smem, int slot, Item& it) {
   __syncthreads();                         // every role has finished the previous item; slot is filled
   if (c.done[slot]) return false;
   it = c.item[slot];
   const int32_t* entry = c.entry[slot];
   const int64_t* qoff = c.qoff[slot];
-  // gather Q rows into two [2][128][64] blocks with the 128-byte swizzle TMA would produce
-#pragma unroll 1
-  for (int i0 = threadIdx.x; i0 < 2 * kTileM * 16; i0 += 4 * kThreads) {
-    uint4 val[4];
+  // gather Q rows into two [2][128][64] blocks with the 128-byte swizzle TMA would produce;
+  // the 256 softmax threads do it, each with its 16 loads in flight at once
+  if (kGather) {
+    const int t = threadIdx.x - 128;
+    uint4 val[16];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int i = i0 + u * kThreads;
+    for (int u = 0; u < 16; ++u) {
+      const int i = t + u * 256;
+      const int r = i >> 4, ch = i & 15;
       val[u] = make_uint4(0, 0, 0, 0);
-      if (i < 2 * kTileM * 16) {
-        const int r = i >> 4, ch = i & 15;
-        if (entry[r] >= 0) val[u] = __ldg(reinterpret_cast<const uint4*>(a.q + qoff[r] + ch * 8));
-      }
+      if (entry[r] >= 0) val[u] = __ldg(reinterpret_cast<const uint4*>(a.q + qoff[r] + ch * 8));
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int i = i0 + u * kThreads;
-      if (i < 2 * kTileM * 16) {
-        const int r = i >> 4, ch = i & 15;
-        const uint32_t dst = (uint32_t)((r >> 7) * kTileBytes + (ch >> 3) * kHalfBytes + (r & 127) * 128 +
-                                        (((ch & 7) ^ (r & 7)) << 4));
-        *reinterpret_cast<uint4*>(smem + dst) = val[u];
-      }
+    for (int u = 0; u < 16; ++u) {
+      const int i = t + u * 256;
+      const int r = i >> 4, ch = i & 15;
+      const uint32_t dst = (uint32_t)((r >> 7) * kTileBytes + (ch >> 3) * kHalfBytes + (r & 127) * 128 +
+                                      (((ch & 7) ^ (r & 7)) << 4));
+      *reinterpret_cast<uint4*>(smem + dst) = val[u];
     }
   }
   fence_proxy_async_smem();
@@ -319,6 +323,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
       mbar_init(smem_u32(&c.s_full[i]), 1);
       mbar_init(smem_u32(&c.p_full[i]), kTileM);
       mbar_init(smem_u32(&c.o_full[i]), 1);
+      mbar_init(smem_u32(&c.item_ready[i]), 1);
     }
     c.abort = 0;
     fence_barrier_init();
@@ -343,6 +348,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     setmaxnreg_dec<72>();
     uint32_t kc = 0, vc = 0;               // K / V tiles produced (warp 0) or consumed (warp 1) so far
     uint32_t pph0 = 0, pph1 = 0;           // p_full phases of tile A / B
+    int pre = 0;                           // producer: tiles of the coming item already requested
     // warp-uniform copies of the TMEM base and of the low words of the shared-memory
     // descriptors of the first Q / K / V block (every other block or k-step is a
     // compile-time offset from these), and the lane that issues
@@ -354,30 +360,47 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     for (int n = 0;; ++n) {
       // warp 2 runs one item ahead: it fills slot n & 1 while the others still work on item n - 1
       if (warp == 2) prefetch_item(p, a, c, n & 1, n_routed, n_items);
-      if (!next_item(a, c, smem, n & 1, it)) break;
+      if (!next_item<false>(a, c, smem, n & 1, it)) break;
       const int ntiles = (it.kv_len + kBN - 1) / kBN;
       if (warp == 0 && lane == 0) {
-        for (int j = 0; j < ntiles; ++j) {
-          const int tok = it.kv_tok0 + j * kBN;
+        // K and V tile `j` of item `w` into the next free stages; false after a timeout
+        auto load_tile = [&](const Item& w, int j) -> bool {
+          const int tok = w.kv_tok0 + j * kBN;
           {
             const uint32_t s = kc & 1;
-            if (!mbar_wait(smem_u32(&c.k_empty[s]), ((kc >> 1) & 1) ^ 1)) { atomicExch(a.status, ST_PRODUCER); c.abort = 1; break; }
+            if (!mbar_wait(smem_u32(&c.k_empty[s]), ((kc >> 1) & 1) ^ 1)) return false;
             const uint32_t bar = smem_u32(&c.k_full[s]);
             mbar_expect_tx(bar, kTileBytes);
-            tma_load_3d(sK + s * kTileBytes, &tmap_k, bar, 0, it.kv_head, tok);
-            tma_load_3d(sK + s * kTileBytes + kHalfBytes, &tmap_k, bar, 64, it.kv_head, tok);
+            tma_load_3d(sK + s * kTileBytes, &tmap_k, bar, 0, w.kv_head, tok);
+            tma_load_3d(sK + s * kTileBytes + kHalfBytes, &tmap_k, bar, 64, w.kv_head, tok);
             ++kc;
           }
           {
             const uint32_t s = vc & 1;
-            if (!mbar_wait(smem_u32(&c.v_empty[s]), ((vc >> 1) & 1) ^ 1)) { atomicExch(a.status, ST_PRODUCER); c.abort = 1; break; }
+            if (!mbar_wait(smem_u32(&c.v_empty[s]), ((vc >> 1) & 1) ^ 1)) return false;
             const uint32_t bar = smem_u32(&c.v_full[s]);
             mbar_expect_tx(bar, kTileBytes);
-            tma_load_3d(sV + s * kTileBytes, &tmap_v, bar, 0, it.kv_head, tok);
-            tma_load_3d(sV + s * kTileBytes + kHalfBytes, &tmap_v, bar, 64, it.kv_head, tok);
+            tma_load_3d(sV + s * kTileBytes, &tmap_v, bar, 0, w.kv_head, tok);
+            tma_load_3d(sV + s * kTileBytes + kHalfBytes, &tmap_v, bar, 64, w.kv_head, tok);
             ++vc;
           }
+          return true;
+        };
+        bool alive = true;
+        for (int j = pre; alive && j < ntiles; ++j) alive = load_tile(it, j);
+        pre = 0;
+        // The first tiles of the next item are requested as soon as stages free up, while the
+        // tail of this item still computes: the prefetch warp has the next item ready by then.
+        if (alive) {
+          const int s1 = (n + 1) & 1;
+          alive = mbar_wait(smem_u32(&c.item_ready[s1]), ((n + 1) >> 1) & 1);
+          if (alive && !c.done[s1]) {
+            const Item nx = c.item[s1];
+            const int nt = min(2, (nx.kv_len + kBN - 1) / kBN);
+            for (; alive && pre < nt; ++pre) alive = load_tile(nx, pre);
+          }
         }
+        if (!alive) { atomicExch(a.status, ST_PRODUCER); c.abort = 1; }
       } else if (warp == 1) {
         // MMA issuer.  The whole warp runs this code so that addresses and descriptors
         // stay warp-uniform (uniform registers); one elected lane executes the
@@ -474,7 +497,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     long long t_next = clock64();
     const long long t_kernel = t_next;
 #endif
-    for (int n = 0; next_item(a, c, smem, n & 1, it); ++n) {
+    for (int n = 0; next_item<true>(a, c, smem, n & 1, it); ++n) {
 #ifdef MOBA_TC5_TRACE
       if (threadIdx.x == 128) { TRACE_ADD(a, 8, t_next); atomicAdd(TRACE_BASE(a) + 9, 1ull); }
 #endif
@@ -513,19 +536,29 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         tc_fence_after();
         const int32_t e = entries[x * kTileM + row];
         const float inv = 1.f / l;
-        float* dst = a.partial_out + (int64_t)(e >= 0 ? e : 0) * kHeadDim;
+        // O rows go through this warp's 8 KB of the (now idle) Q tile so that every global
+        // store instruction writes whole 128-byte pieces of four rows: 32 columns at a
+        // time, rows 144 bytes apart in shared memory (conflict-free both ways).
+        unsigned char* stage = smem + x * kTileBytes + (warp & 3) * 8192;
         uint32_t v[32];
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
           tmem_ld32(tO + ch * 32, v);
           tmem_wait_ld();
-          if (e >= 0) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              reinterpret_cast<float4*>(dst + ch * 32)[i] =
-                  make_float4(__uint_as_float(v[4 * i]) * inv, __uint_as_float(v[4 * i + 1]) * inv,
-                              __uint_as_float(v[4 * i + 2]) * inv, __uint_as_float(v[4 * i + 3]) * inv);
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<float4*>(stage + lane * 144 + i * 16) =
+                make_float4(__uint_as_float(v[4 * i]) * inv, __uint_as_float(v[4 * i + 1]) * inv,
+                            __uint_as_float(v[4 * i + 2]) * inv, __uint_as_float(v[4 * i + 3]) * inv);
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rl = i * 4 + (lane >> 3), c16 = lane & 7;
+            const int32_t er = __shfl_sync(0xffffffffu, e, rl);
+            const float4 val = *reinterpret_cast<const float4*>(stage + rl * 144 + c16 * 16);
+            if (er >= 0) *reinterpret_cast<float4*>(a.partial_out + (int64_t)er * kHeadDim + ch * 32 + c16 * 4) = val;
           }
+          __syncwarp();
         }
         if (e >= 0) a.partial_lse[e] = (m_ref + log2f(l)) * 0.6931471805599453f;
         tc_fence_before();

@@ -10,7 +10,7 @@
 
 namespace moba {
 
-constexpr int kHeadDim = 128;            // the build is specialised for D = 128
+constexpr int kHeadDim = 128;            // head dim of the tcgen05 dense stage (others: mma.sync stage)
 constexpr int kMeanLanes = 32;           // row accumulators of a chunk mean
 constexpr int kMaxTopk = 64;             // parallel.py:436
 

@@ -12,9 +12,11 @@
 //   mean : row r of a chunk is added to accumulator r % 32 in increasing r, the
 //          32 accumulators are added in increasing index, the total is divided
 //          by C and rounded to bf16 (round to nearest even);
-//   score: bf16*bf16 products are exact in fp32; each of the 16 blocks of 8
-//          dims is added left to right, then a halving tree (block l + block
-//          l+8, then l + l+4, l + l+2, l + l+1) combines the block sums.
+//   score: products of two 16-bit values are exact in fp32; each block of 8
+//          dims is added left to right, then a halving tree combines the D/8
+//          block sums (for D = 128: block l + block l+8, then l + l+4, l + l+2,
+//          l + l+1); a block count that is no power of two (D = 96) is padded
+//          with blocks of +0.0 to the next one.
 #include "common.cuh"
 
 namespace moba {
@@ -44,23 +46,22 @@ cudaError_t launch_chunk_metadata(const Params& p, const int32_t* cu, int32_t* c
 }
 
 // ---------------------------------------------------------------------------
-// chunk means: one CTA per (slot, kv head), 32 row lanes x 16 dim lanes.
-// A warp covers two consecutive rows of one kv head with 16-byte loads.
+// chunk means: one CTA per (slot, kv head), 32 row lanes x D/8 dim lanes
+// (16-byte loads).
 // ---------------------------------------------------------------------------
-constexpr int kMeanThreads = kMeanLanes * (kHeadDim / 8);   // 512
-
-template <bool kHalf>
-__global__ void __launch_bounds__(kMeanThreads)
+template <bool kHalf, int D>
+__global__ void __launch_bounds__(kMeanLanes * (D / 8))
 chunk_mean_kernel(Params p, const __nv_bfloat16* __restrict__ k, const int32_t* __restrict__ cu,
                   __nv_bfloat16* __restrict__ means) {
   const int slot = blockIdx.x, hk = blockIdx.y;
   const int b = slot / p.mc, j = slot - b * p.mc;
   const Slot sl = slot_of(cu, b, j, p.C);
-  const int dl = threadIdx.x & 15;        // dims 8*dl .. 8*dl+7
-  const int rl = threadIdx.x >> 4;        // row lane 0..31
-  __nv_bfloat16* dst = means + ((int64_t)slot * p.Hkv + hk) * kHeadDim;
+  constexpr int kDimLanes = D / 8;
+  const int dl = threadIdx.x % kDimLanes;  // dims 8*dl .. 8*dl+7
+  const int rl = threadIdx.x / kDimLanes;  // row lane 0..31
+  __nv_bfloat16* dst = means + ((int64_t)slot * p.Hkv + hk) * D;
 
-  __shared__ float part[kMeanLanes][kHeadDim + 4];
+  __shared__ float part[kMeanLanes][D + 4];
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
@@ -93,7 +94,7 @@ chunk_mean_kernel(Params p, const __nv_bfloat16* __restrict__ k, const int32_t* 
 #pragma unroll
   for (int i = 0; i < 8; ++i) part[rl][dl * 8 + i] = acc[i];
   __syncthreads();
-  if (threadIdx.x < kHeadDim) {
+  if (threadIdx.x < D) {
     float tot = part[0][threadIdx.x];
 #pragma unroll
     for (int a = 1; a < kMeanLanes; ++a) tot += part[a][threadIdx.x];
@@ -106,8 +107,15 @@ chunk_mean_kernel(Params p, const __nv_bfloat16* __restrict__ k, const int32_t* 
 cudaError_t launch_chunk_means(const Params& p, const __nv_bfloat16* k, const int32_t* cu,
                                __nv_bfloat16* means, cudaStream_t st) {
   dim3 grid(p.slots, p.Hkv);
-  if (p.fp16) chunk_mean_kernel<true><<<grid, kMeanThreads, 0, st>>>(p, k, cu, means);
-  else chunk_mean_kernel<false><<<grid, kMeanThreads, 0, st>>>(p, k, cu, means);
+#define MOBA_MEANS(HALF, DIM) chunk_mean_kernel<HALF, DIM><<<grid, kMeanLanes * (DIM / 8), 0, st>>>(p, k, cu, means)
+  switch (p.D) {
+    case 64:  if (p.fp16) MOBA_MEANS(true, 64);  else MOBA_MEANS(false, 64);  break;
+    case 96:  if (p.fp16) MOBA_MEANS(true, 96);  else MOBA_MEANS(false, 96);  break;
+    case 128: if (p.fp16) MOBA_MEANS(true, 128); else MOBA_MEANS(false, 128); break;
+    case 256: if (p.fp16) MOBA_MEANS(true, 256); else MOBA_MEANS(false, 256); break;
+    default: return cudaErrorInvalidValue;
+  }
+#undef MOBA_MEANS
   return cudaGetLastError();
 }
 
@@ -121,10 +129,10 @@ cudaError_t launch_chunk_means(const Params& p, const __nv_bfloat16* k, const in
 //   a candidate replaces the smallest kept key when it beats it, and the kept keys
 //   are ordered once at the end.  Keys are unique, so ties in the score fall to
 //   the lower slot.
-//   Lane t of a group owns the 8-dim blocks t, t+4, t+8, t+12, so the first two
-//   levels of the halving tree (block l + block l+8, then l + l+4) stay inside
-//   the lane and only the last two cross lanes: same summation order as 16
-//   lanes with one block each, a quarter of the shuffles.
+//   Lane t of a group owns the 8-dim blocks t, t+4, t+8, ..., so all levels of
+//   the halving tree but the last two stay inside the lane and only those two
+//   cross lanes: same summation order as one lane per block, a fraction of the
+//   shuffles.
 // ---------------------------------------------------------------------------
 constexpr int kGateThreads = 256;
 constexpr int kGateGroups = kGateThreads / 4;
@@ -166,16 +174,19 @@ __device__ __forceinline__ void list_min(const unsigned long long* best, int his
   pos = mine_i;
 }
 
-template <bool kHalf>
-__global__ void __launch_bounds__(kGateThreads, 4)
+template <bool kHalf, int D>
+__global__ void __launch_bounds__(kGateThreads, D > 128 ? 2 : 4)
 gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__ q,
                  const __nv_bfloat16* __restrict__ means, const int32_t* __restrict__ cu,
                  int32_t* __restrict__ selected, int32_t* __restrict__ list_counts) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int hist = p.hist;
+  constexpr int kBlocks = D / 8;                       // 8-dim blocks per row
+  constexpr int kOwn = (kBlocks + 3) / 4;              // blocks owned by a lane: t, t+4, ...
+  constexpr int kOwnPad = kOwn <= 2 ? 2 : (kOwn <= 4 ? 4 : 8);   // padded to a power of two with +0.0
   // layout: means tile fp32 | wins[groups][hist] | best[rows][hist] | counts[mc]
-  float4* means_s = reinterpret_cast<float4*>(smem_raw);                            // kCandTile * 32 float4
-  unsigned long long* wins_s = reinterpret_cast<unsigned long long*>(means_s + kCandTile * 32);
+  float4* means_s = reinterpret_cast<float4*>(smem_raw);                            // kCandTile * D/4 float4
+  unsigned long long* wins_s = reinterpret_cast<unsigned long long*>(means_s + kCandTile * (D / 4));
   unsigned long long* best_s = wins_s + kGateGroups * hist;
   int32_t* cnt_s = reinterpret_cast<int32_t*>(best_s + (size_t)kGateRows * hist);
 
@@ -199,14 +210,14 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
   for (int c0 = 0; c0 < max_cand; c0 += kCandTile) {
     const int ct = min(kCandTile, max_cand - c0);
     __syncthreads();                                          // previous tile fully consumed
-    for (int i = threadIdx.x; i < ct * 16; i += kGateThreads) {
-      const int c = i >> 4, part = i & 15;
+    for (int i = threadIdx.x; i < ct * kBlocks; i += kGateThreads) {
+      const int c = i / kBlocks, part = i - c * kBlocks;
       const uint4 x = __ldg(reinterpret_cast<const uint4*>(
-          means + ((int64_t)(slot0 + c0 + c) * p.Hkv + hk) * kHeadDim + part * 8));
+          means + ((int64_t)(slot0 + c0 + c) * p.Hkv + hk) * D + part * 8));
       float f[8];
       unpack8<kHalf>(x, f);
-      means_s[c * 32 + part * 2] = make_float4(f[0], f[1], f[2], f[3]);
-      means_s[c * 32 + part * 2 + 1] = make_float4(f[4], f[5], f[6], f[7]);
+      means_s[c * (D / 4) + part * 2] = make_float4(f[0], f[1], f[2], f[3]);
+      means_s[c * (D / 4) + part * 2 + 1] = make_float4(f[4], f[5], f[6], f[7]);
     }
     __syncthreads();
     for (int row = grp; row < nrows; row += kGateGroups) {    // row = token-major, head-minor
@@ -214,11 +225,11 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
       const int tok = tok_lo + tl;
       const int cend = min(ct, (tok - s0) / p.C - c0);        // this row's candidates in the tile
       if (cend <= 0) continue;                                // uniform over the 4 lanes
-      float qf[4][8];
+      float qf[kOwn][8];
       {
         const __nv_bfloat16* qrow = q + (int64_t)(tok - p.win_lo) * p.sq_t + (int64_t)(hk * p.G + hl) * p.sq_h;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
+        for (int k = 0; k < kOwn; ++k)
           unpack8<kHalf>(__ldg(reinterpret_cast<const uint4*>(qrow + (t + 4 * k) * 8)), qf[k]);
       }
       // The row keeps its `hist` largest keys so far (unordered) in shared memory; a new
@@ -228,12 +239,18 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
       int pos;
       list_min(best, hist, t, gmask, tau, pos);
       for (int c = 0; c < cend; ++c) {
-        const float4* m = means_s + c * 32;
-        float acc[4];
+        const float4* m = means_s + c * (D / 4);
+        float acc[kOwnPad];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) acc[k] = dot8(qf[k], m[(t + 4 * k) * 2], m[(t + 4 * k) * 2 + 1]);
-        // halving tree over the 16 block sums: (l, l+8), (l, l+4) in-lane, (l, l+2), (l, l+1) across lanes
-        float s = __fadd_rn(__fadd_rn(acc[0], acc[2]), __fadd_rn(acc[1], acc[3]));
+        for (int k = 0; k < kOwnPad; ++k)
+          acc[k] = k < kOwn ? dot8(qf[k < kOwn ? k : 0], m[(t + 4 * k) * 2], m[(t + 4 * k) * 2 + 1]) : 0.f;
+        // halving tree over the block sums: every level but the last two pairs blocks of
+        // the same lane (block l with block l + half), the last two cross lanes
+#pragma unroll
+        for (int h = kOwnPad / 2; h >= 1; h >>= 1)
+#pragma unroll
+          for (int k = 0; k < h; ++k) acc[k] = __fadd_rn(acc[k], acc[k + h]);
+        float s = acc[0];
         s = __fadd_rn(s, __shfl_xor_sync(gmask, s, 2));
         s = __fadd_rn(s, __shfl_xor_sync(gmask, s, 1));
         const unsigned long long key = ((unsigned long long)float_key(s) << 32) |
@@ -296,7 +313,7 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
 }
 
 static size_t gate_smem_bytes(const Params& p) {
-  return (size_t)kCandTile * 32 * sizeof(float4) + (size_t)kGateGroups * p.hist * 8 +
+  return (size_t)kCandTile * (p.D / 4) * sizeof(float4) + (size_t)kGateGroups * p.hist * 8 +
          (size_t)kGateRows * p.hist * 8 + (size_t)p.mc * 4;
 }
 
@@ -307,7 +324,14 @@ cudaError_t launch_gate_topk(const Params& p, const __nv_bfloat16* q, const __nv
   if (tokens_per_cta < 1) tokens_per_cta = 1;
   const size_t smem = gate_smem_bytes(p);
   if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
-  auto kernel = p.fp16 ? gate_topk_kernel<true> : gate_topk_kernel<false>;
+  void (*kernel)(Params, int, const __nv_bfloat16*, const __nv_bfloat16*, const int32_t*, int32_t*, int32_t*);
+  switch (p.D) {
+    case 64:  kernel = p.fp16 ? gate_topk_kernel<true, 64>  : gate_topk_kernel<false, 64>;  break;
+    case 96:  kernel = p.fp16 ? gate_topk_kernel<true, 96>  : gate_topk_kernel<false, 96>;  break;
+    case 128: kernel = p.fp16 ? gate_topk_kernel<true, 128> : gate_topk_kernel<false, 128>; break;
+    case 256: kernel = p.fp16 ? gate_topk_kernel<true, 256> : gate_topk_kernel<false, 256>; break;
+    default: return cudaErrorInvalidValue;
+  }
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   dim3 grid(cdiv_i(p.max_seqlen, tokens_per_cta), p.Hkv, p.B);

@@ -60,7 +60,7 @@ extern "C" int moba_route_static(const moba_problem_t* p, const void* q, const v
   if (rc != MOBA_OK) return rc;
   if (!q || !k || !cu_seqlens || !selected) return MOBA_E_NULL;
   if (dims.hist <= 0) return MOBA_OK;                      // nothing to select: `selected` has no rows
-  if ((size_t)dims.slots * (size_t)p->num_kv_heads * kHeadDim > kStaticMeanElems) return MOBA_E_STATIC_LIMIT;
+  if ((size_t)dims.slots * (size_t)p->num_kv_heads * (size_t)p->head_dim > kStaticMeanElems) return MOBA_E_STATIC_LIMIT;
   __nv_bfloat16* means = nullptr;
   cudaError_t e = static_means_address(&means);
   if (e != cudaSuccess) return (int)e;

@@ -141,7 +141,8 @@ cudaError_t launch_compact(const Params& p, const int32_t* cu, const int32_t* se
 // ---------------------------------------------------------------------------
 constexpr int kMergeThreads = 256;
 
-template <bool kHalf>
+// kVecs = float4 pieces of a row per lane: 1 for D <= 128 (lanes beyond D/4 idle), 2 for D = 256.
+template <bool kHalf, int kVecs>
 __global__ void __launch_bounds__(kMergeThreads)
 merge_kernel(Params p, const float* __restrict__ partial_out, const float* __restrict__ partial_lse,
              const int32_t* __restrict__ status, __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out) {
@@ -160,21 +161,34 @@ merge_kernel(Params p, const float* __restrict__ partial_out, const float* __res
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
     const float inv = failed ? __int_as_float(0x7fc00000) : 1.f / tot;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4* src = reinterpret_cast<const float4*>(partial_out + row * p.NP * kHeadDim) + lane;
+    const int nvec = p.D / 4;
+    float4 acc[kVecs];
+#pragma unroll
+    for (int u = 0; u < kVecs; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4* src = reinterpret_cast<const float4*>(partial_out + row * p.NP * p.D) + lane;
     for (int j = 0; j < p.NP; ++j) {
       const float lj = lse[j];                                // same address for all lanes
       if (lj == -INFINITY) continue;
       const float w = expf(lj - mx) * inv;
-      const float4 o = __ldg(src + j * (kHeadDim / 4));
-      acc.x += w * o.x; acc.y += w * o.y; acc.z += w * o.z; acc.w += w * o.w;
+#pragma unroll
+      for (int u = 0; u < kVecs; ++u) {
+        if (lane + 32 * u < nvec) {
+          const float4 o = __ldg(src + j * nvec + 32 * u);
+          acc[u].x += w * o.x; acc[u].y += w * o.y; acc[u].z += w * o.z; acc[u].w += w * o.w;
+        }
+      }
     }
     const int64_t t = row / p.Hq;
     const int h = (int)(row - t * p.Hq);
-    uint2 pk;
-    pk.x = pack2_16<kHalf>(acc.x, acc.y);
-    pk.y = pack2_16<kHalf>(acc.z, acc.w);
-    *reinterpret_cast<uint2*>(out + t * p.so_t + (int64_t)h * p.so_h + lane * 4) = pk;
+#pragma unroll
+    for (int u = 0; u < kVecs; ++u) {
+      if (lane + 32 * u < nvec) {
+        uint2 pk;
+        pk.x = pack2_16<kHalf>(acc[u].x, acc[u].y);
+        pk.y = pack2_16<kHalf>(acc[u].z, acc[u].w);
+        *reinterpret_cast<uint2*>(out + t * p.so_t + (int64_t)h * p.so_h + (lane + 32 * u) * 4) = pk;
+      }
+    }
     if (lse_out != nullptr && lane == 0) lse_out[(int64_t)h * p.Tq + t] = logf(tot) + mx;
   }
 }
@@ -183,8 +197,11 @@ cudaError_t launch_merge(const Params& p, const float* partial_out, const float*
                          const int32_t* status, __nv_bfloat16* out, float* lse_out, cudaStream_t st) {
   int64_t blocks = (p.rows + (kMergeThreads / 32) - 1) / (kMergeThreads / 32);
   if (blocks > 148 * 64) blocks = 148 * 64;
-  if (p.fp16) merge_kernel<true><<<(int)blocks, kMergeThreads, 0, st>>>(p, partial_out, partial_lse, status, out, lse_out);
-  else merge_kernel<false><<<(int)blocks, kMergeThreads, 0, st>>>(p, partial_out, partial_lse, status, out, lse_out);
+#define MOBA_MERGE(HALF, VECS) \
+  merge_kernel<HALF, VECS><<<(int)blocks, kMergeThreads, 0, st>>>(p, partial_out, partial_lse, status, out, lse_out)
+  if (p.D > 128) { if (p.fp16) MOBA_MERGE(true, 2); else MOBA_MERGE(false, 2); }
+  else           { if (p.fp16) MOBA_MERGE(true, 1); else MOBA_MERGE(false, 1); }
+#undef MOBA_MERGE
   return cudaGetLastError();
 }
 

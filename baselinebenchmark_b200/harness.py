@@ -8,8 +8,9 @@ report (:39-44).  Like the original it performs no correctness check.
     python -m baselinebenchmark_b200.harness --case cfg2 --rounds 1 --iterations 3
     python -m baselinebenchmark_b200.harness --suite --output results.json
 
-`--suite` runs the reference's case list (moba_compare.py:59-99) restricted to
-what this build supports (bf16, head_dim 128); the rest is reported as skipped.
+`--suite` runs the reference's case list (moba_compare.py:59-99); a case outside
+what this build supports (bf16 or fp16; head_dim 64, 96, 128, 256) would be
+reported as skipped.
 """
 from __future__ import annotations
 
@@ -104,12 +105,12 @@ def make_inputs(case: Case, device):
 
 
 def supported(case: Case) -> bool:
-    return case.dtype in ("bfloat16", "float16") and case.head_dim == 128
+    return case.dtype in ("bfloat16", "float16") and case.head_dim in (64, 96, 128, 256)
 
 
 def run_case(case: Case, args, device):
     if not supported(case):
-        return {**asdict(case), "status": "skipped", "reason": "this build: head_dim 128"}
+        return {**asdict(case), "status": "skipped", "reason": "this build: head_dim 64, 96, 128, 256"}
     q, k, v, cu = make_inputs(case, device)
     call = (q, k, v, cu, max(case.seq_lens), case.chunk_size, case.topk)
     with torch.inference_mode():

@@ -21,6 +21,8 @@ from . import _lib
 
 __all__ = ["parallel_moba", "moba_attn_varlen", "moba_forward", "make_problem", "workspace_bytes"]
 
+#: head dims of the reference's benchmark suite (benchmarks/moba_compare.py:63, :70)
+HEAD_DIMS = (64, 96, 128, 256)
 _workspaces: dict = {}
 
 
@@ -59,14 +61,19 @@ def _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, windo
     if q.shape[2] > 256:
         raise ValueError(f"head_dim must be <= 256 to match FlashMoBA, got {q.shape[2]}")
     # limits of this build (no fallback by design)
-    if q.shape[2] != 128:
-        raise NotImplementedError("this build supports head_dim 128 only")
+    if q.shape[2] not in HEAD_DIMS:
+        raise NotImplementedError(f"this build supports head_dim {HEAD_DIMS} only")
     for name, t in (("q", q), ("k", k), ("v", v)):
         if t.stride(2) != 1:
             raise NotImplementedError(f"{name} must be contiguous in its last dimension")
 
 
-def make_problem(q, k, v, out, cu_seqlens, max_seqlen, chunk, topk, attend_impl=_lib.ATTEND_TCGEN05,
+def default_attend_impl(head_dim: int) -> int:
+    """The tcgen05 dense stage exists for head_dim 128; other head dims run the mma.sync stage."""
+    return _lib.ATTEND_TCGEN05 if head_dim == 128 else _lib.ATTEND_MMA_SYNC
+
+
+def make_problem(q, k, v, out, cu_seqlens, max_seqlen, chunk, topk, attend_impl=None,
                  q_token_begin=None):
     """struct moba_problem for these tensors.  With `q_token_begin` set, q/out hold the
     packed tokens [q_token_begin, q_token_begin + q.shape[0]) and k/v all of them."""
@@ -75,7 +82,7 @@ def make_problem(q, k, v, out, cu_seqlens, max_seqlen, chunk, topk, attend_impl=
         dtype=1 if q.dtype == torch.float16 else 0,
         total_tokens=k.shape[0], batch=cu_seqlens.numel() - 1, num_q_heads=q.shape[1],
         num_kv_heads=k.shape[1], head_dim=q.shape[2], max_seqlen=max_seqlen, chunk_size=chunk,
-        topk=topk, attend_impl=attend_impl,
+        topk=topk, attend_impl=default_attend_impl(q.shape[2]) if attend_impl is None else attend_impl,
         q_stride_token=q.stride(0), q_stride_head=q.stride(1),
         k_stride_token=k.stride(0), k_stride_head=k.stride(1),
         v_stride_token=v.stride(0), v_stride_head=v.stride(1),
@@ -105,7 +112,7 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 
 def moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, *,
                  return_lse: bool = False, return_selected: bool = False,
-                 attend_impl: int = _lib.ATTEND_TCGEN05, workspace: Optional[torch.Tensor] = None,
+                 attend_impl: Optional[int] = None, workspace: Optional[torch.Tensor] = None,
                  q_token_begin: Optional[int] = None, workspace_limit: Optional[int] = None
                  ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
     """Runs the operator and optionally returns the final LSE [Hq, T] (fp32) and

@@ -14,10 +14,13 @@
  *     (parallel.py:262-275);
  *   - return value: 0 success, < 0 invalid argument (MOBA_E_*), > 0 a
  *     cudaError_t raised by a launch or a copy.  Nothing throws or aborts;
- *   - tensors are bf16, head_dim 128, innermost dimension contiguous; token and
- *     head strides are given in elements (the reference kernels also take
- *     strides, attention.py:431-439).  Anything else returns
- *     MOBA_E_UNSUPPORTED: there is no fallback path.
+ *   - tensors are bf16 or fp16 (moba_problem.dtype), head_dim 64, 96, 128 or 256
+ *     (the head dims of the reference's benchmark suite, moba_compare.py:63, :70),
+ *     innermost dimension contiguous; token and head strides are given in
+ *     elements (the reference kernels also take strides, attention.py:431-439).
+ *     The tcgen05 dense stage exists for head_dim 128; the other head dims run
+ *     the mma.sync dense stage (attend_impl = MOBA_ATTEND_MMA_SYNC).  Anything
+ *     else returns MOBA_E_UNSUPPORTED: there is no fallback path.
  */
 #ifndef MOBA_B200_H_
 #define MOBA_B200_H_
@@ -43,7 +46,7 @@ enum {
 
 /* Which implementation of the dense stage moba_attend/moba_forward run. */
 enum {
-  MOBA_ATTEND_TCGEN05 = 0,  /* tcgen05.mma + TMEM accumulators + TMA K/V tiles   */
+  MOBA_ATTEND_TCGEN05 = 0,  /* tcgen05.mma + TMEM accumulators + TMA K/V tiles (head_dim 128) */
   MOBA_ATTEND_MMA_SYNC = 1  /* legacy mma.sync tensor path, kept as cross-check  */
 };
 
@@ -61,7 +64,7 @@ typedef struct moba_problem {
   int32_t batch;            /* B = len(cu_seqlens) - 1                           */
   int32_t num_q_heads;      /* Hq                                                */
   int32_t num_kv_heads;     /* Hkv, Hq % Hkv == 0                                */
-  int32_t head_dim;         /* D (128)                                           */
+  int32_t head_dim;         /* D: 64, 96, 128 or 256                             */
   int32_t max_seqlen;       /* >= the longest sequence                           */
   int32_t chunk_size;       /* moba_chunk_size                                   */
   int32_t topk;             /* moba_topk, counts the query's own chunk           */
@@ -210,7 +213,7 @@ int moba_merge(const moba_problem_t* p, const float* partial_out, const float* p
  * its inputs and outputs).  Computes selected int32 [hist,Hq,T] from q and k like
  * moba_chunk_means + moba_gate_topk, keeping the chunk means in a 4 MiB array that
  * is part of the library image (held by every GPU that loads the library).
- *   - limit: slots * num_kv_heads * 128 <= 2 Mi elements, otherwise
+ *   - limit: slots * num_kv_heads * head_dim <= 2 Mi elements, otherwise
  *     MOBA_E_STATIC_LIMIT;
  *   - the first call on a device looks up the device address of that array; make
  *     that first call outside any stream capture;

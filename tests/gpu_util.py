@@ -11,7 +11,7 @@ def to_dev(*tensors):
     return [t.cuda() for t in tensors]
 
 
-def problem_for(q, k, v, cu, max_seqlen, chunk, topk, impl=_lib.ATTEND_TCGEN05):
+def problem_for(q, k, v, cu, max_seqlen, chunk, topk, impl=None):
     out = torch.empty_like(q)
     return parallel.make_problem(q, k, v, out, cu, max_seqlen, chunk, topk, impl), out
 

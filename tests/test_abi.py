@@ -129,8 +129,9 @@ def test_host_validation_value_checks(monkeypatch):
     with pytest.raises(ValueError, match="divisible"):
         parallel._validate(T(q[:, :3]), fk, fv, fcu, 64, 32, 2)
     parallel._validate(T(q.half()), T(k.half()), T(v.half()), fcu, 64, 32, 2)      # float16 is built
+    parallel._validate(T(q[..., :64]), T(k[..., :64]), T(v[..., :64]), fcu, 64, 32, 2)   # head_dim 64 is built
     with pytest.raises(NotImplementedError):
-        parallel._validate(T(q[..., :64]), T(k[..., :64]), T(v[..., :64]), fcu, 64, 32, 2)
+        parallel._validate(T(q[..., :32]), T(k[..., :32]), T(v[..., :32]), fcu, 64, 32, 2)
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

@@ -39,16 +39,26 @@ SMALL_CASES = [
 ]
 
 
-def _case_inputs(lens, hq, hkv, chunk, seed, dtype=torch.bfloat16):
-    return O.make_inputs(list(lens), hq, hkv, 128, chunk, seed, dtype=dtype)
+def _case_inputs(lens, hq, hkv, chunk, seed, dtype=torch.bfloat16, d=128):
+    return O.make_inputs(list(lens), hq, hkv, d, chunk, seed, dtype=dtype)
+
+
+# the other head dims of the reference's suite (moba_compare.py:63, :70, :77):
+# (name, head_dim, seq_lens, Hq, Hkv, chunk, topk)
+HEAD_DIM_CASES = [
+    ("d64_gqa_varlen", 64, (700, 333, 1290), 8, 2, 128, 4),
+    ("d64_tail_k64", 64, (513, 2049), 4, 2, 32, 64),
+    ("d96_mha", 96, (1024, 300), 4, 4, 128, 3),
+    ("d96_gqa", 96, (127, 128, 129, 900), 8, 2, 64, 5),
+    ("d256_gqa", 256, (640, 257), 4, 2, 128, 3),
+    ("d256_mqa", 256, (900,), 4, 1, 64, 8),
+]
 
 
 @pytest.mark.parametrize("path", GOLDEN, ids=lambda p: p.split("routing_")[-1][:-4])
 def test_golden_routing_through_cuda(path):
-    """Reference-generated golden vectors (D = 128 cases) through the CUDA gating stage."""
+    """Reference-generated golden vectors (head_dim 64 and 128) through the CUDA gating stage."""
     z = np.load(path)
-    if int(z["d"]) != 128:
-        pytest.skip("fixture has head_dim != 128")
     q = torch.from_numpy(z["q_bits"]).view(torch.bfloat16).cuda()
     k = torch.from_numpy(z["k_bits"]).view(torch.bfloat16).cuda()
     cu = torch.from_numpy(z["cu_seqlens"]).cuda()
@@ -69,8 +79,6 @@ def test_golden_routing_through_cuda_fp16(path):
     float16 chunk means must equal the reference kernel's own output bit for bit, and the
     selection from the means the reference's top-k kernel was given must equal its output."""
     z = np.load(path)
-    if int(z["d"]) != 128:
-        pytest.skip("fixture has head_dim != 128")
     q = torch.from_numpy(z["q_bits"]).view(torch.bfloat16).half().cuda()
     k = torch.from_numpy(z["k_bits"]).view(torch.bfloat16).half().cuda()
     cu = torch.from_numpy(z["cu_seqlens"]).cuda()
@@ -133,6 +141,34 @@ def test_routing_bit_exact(case, dtype):
         plse = plse.cpu().numpy().reshape(-1, npart)
         empty = np.transpose(sel_o < 0, (2, 1, 0)).reshape(-1, hist)        # [row, rank]
         assert np.all(np.isneginf(plse[:, 1:][empty])) and np.all(plse[:, 1:][~empty] == 0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", HEAD_DIM_CASES, ids=lambda c: c[0])
+def test_other_head_dims(case, dtype):
+    """head_dim 64, 96 and 256: chunk means and selection bit-exact, output within tolerance
+    (these head dims run the mma.sync dense stage)."""
+    name, d, lens, hq, hkv, chunk, topk = case
+    q, k, v, cu = _case_inputs(lens, hq, hkv, chunk, zlib.crc32(name.encode()) % 1000, dtype=dtype, d=d)
+    max_seqlen = max(lens)
+    ref, ref_lse, sel_o = O.moba_forward(q, k, v, cu, max_seqlen, chunk, topk, dtype=torch.float32)
+    qd, kd, vd = G.to_dev(q, k, v)
+    cud = torch.from_numpy(cu).cuda()
+    prob, _ = G.problem_for(qd, kd, vd, cud, max_seqlen, chunk, topk)
+    assert prob.attend_impl == _lib.ATTEND_MMA_SYNC
+    cu_chunk_o, _, valid_o, _ = O.chunk_slots(cu, max_seqlen, chunk)
+    means_o = O.chunk_means(k, cu_chunk_o, valid_o, chunk)
+    m = G.means(prob, kd, cud)
+    assert torch.equal(m.cpu().view(torch.int16), means_o.view(torch.int16))
+    out, lse, sel = parallel.moba_forward(qd, kd, vd, cud, max_seqlen, chunk, topk, return_lse=True,
+                                          return_selected=True)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(sel.cpu().numpy(), sel_o)
+    mx, mean = G.rel_stats(out.cpu(), ref)
+    assert mx < MAX_ABS and mean < MEAN_ABS, (mx, mean)
+    assert (lse.cpu() - ref_lse).abs().max().item() < 2e-3
+    with pytest.raises(_lib.MobaError):                       # the tcgen05 stage is built for head_dim 128
+        parallel.moba_forward(qd, kd, vd, cud, max_seqlen, chunk, topk, attend_impl=_lib.ATTEND_TCGEN05)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -342,8 +378,10 @@ def test_public_operator_names():
     assert native_moba._supported(qd)
     assert native_moba._supported(qd.half())
     assert pkg.parallel_moba(qd.half(), kd.half(), vd.half(), cud, 512, 128, 3).dtype == torch.float16
+    assert not native_moba._supported(qd[..., :64])
+    assert pkg.parallel_moba(qd[..., :64], kd[..., :64], vd[..., :64], cud, 512, 128, 3).shape == qd[..., :64].shape
     with pytest.raises(NotImplementedError):
-        pkg.parallel_moba(qd[..., :64], kd[..., :64], vd[..., :64], cud, 512, 128, 3)
+        pkg.parallel_moba(qd[..., :32], kd[..., :32], vd[..., :32], cud, 512, 128, 3)
 
 
 @pytest.mark.parametrize("impl", IMPLS)
