@@ -174,8 +174,11 @@ __device__ __forceinline__ void list_min(const unsigned long long* best, int his
   pos = mine_i;
 }
 
+#ifndef MOBA_GATE_CTAS
+#define MOBA_GATE_CTAS 3             // resident CTAs per SM the register budget is set for (D <= 128)
+#endif
 template <bool kHalf, int D>
-__global__ void __launch_bounds__(kGateThreads, D > 128 ? 2 : 4)
+__global__ void __launch_bounds__(kGateThreads, D > 128 ? 2 : MOBA_GATE_CTAS)
 gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__ q,
                  const __nv_bfloat16* __restrict__ means, const int32_t* __restrict__ cu,
                  int32_t* __restrict__ selected, int32_t* __restrict__ list_counts) {
@@ -232,13 +235,8 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
         for (int k = 0; k < kOwn; ++k)
           unpack8<kHalf>(__ldg(reinterpret_cast<const uint4*>(qrow + (t + 4 * k) * 8)), qf[k]);
       }
-      // The row keeps its `hist` largest keys so far (unordered) in shared memory; a new
-      // key replaces the smallest one if it is larger.  0 marks an empty place.
-      unsigned long long* best = best_s + (size_t)row * hist;
-      unsigned long long tau;
-      int pos;
-      list_min(best, hist, t, gmask, tau, pos);
-      for (int c = 0; c < cend; ++c) {
+      // packed key of candidate c of this tile; the same value in the 4 lanes
+      auto score_key = [&](int c) -> unsigned long long {
         const float4* m = means_s + c * (D / 4);
         float acc[kOwnPad];
 #pragma unroll
@@ -253,8 +251,60 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
         float s = acc[0];
         s = __fadd_rn(s, __shfl_xor_sync(gmask, s, 2));
         s = __fadd_rn(s, __shfl_xor_sync(gmask, s, 1));
-        const unsigned long long key = ((unsigned long long)float_key(s) << 32) |
-                                       (unsigned long long)(0xFFFFFFFFu - (uint32_t)(slot0 + c0 + c));
+        return ((unsigned long long)float_key(s) << 32) |
+               (unsigned long long)(0xFFFFFFFFu - (uint32_t)(slot0 + c0 + c));
+      };
+      unsigned long long* best = best_s + (size_t)row * hist;
+      if (c0 == 0) {
+        // First tile: the list is empty.  Lane t keeps the keys of candidates c = 4e + t in
+        // registers and the group extracts the `hist` largest, best first: no shared-memory
+        // round trip per candidate, and the list comes out ordered.
+        unsigned long long mine[kCandTile / 4];
+#pragma unroll
+        for (int e = 0; e < kCandTile / 4; ++e) {
+          mine[e] = 0ull;
+          if (4 * e < cend) {
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+              const int c = 4 * e + cc;
+              const unsigned long long key = score_key(c < cend ? c : 0);
+              if (cc == t && c < cend) mine[e] = key;
+            }
+          }
+        }
+        for (int r = 0; r < hist; ++r) {
+          unsigned long long top = 0ull;
+          int top_e = 0;
+#pragma unroll
+          for (int e = 0; e < kCandTile / 4; ++e)
+            if (mine[e] > top) { top = mine[e]; top_e = e; }
+          unsigned long long all = top;
+#pragma unroll
+          for (int o = 2; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(gmask, all, o);
+            all = other > all ? other : all;
+          }
+          if (all == 0ull) break;                             // fewer than hist candidates
+          if (top == all) {                                   // keys are unique: exactly one owner
+#pragma unroll
+            for (int e = 0; e < kCandTile / 4; ++e)
+              if (e == top_e) mine[e] = 0ull;
+            best[r] = all;
+          }
+        }
+        continue;
+      }
+      // Later tiles: the row keeps its `hist` largest keys so far in shared memory (unordered
+      // from here on); a new key replaces the smallest one if it is larger.  0 marks an empty
+      // place.  (Extracting the keys of a later tile from registers like the first one and
+      // inserting only those that beat the list measured slower: 53 against 35 ms on a
+      // 255-candidate window.)
+      unsigned long long tau;
+      int pos;
+      __syncwarp(gmask);
+      list_min(best, hist, t, gmask, tau, pos);
+      for (int c = 0; c < cend; ++c) {
+        const unsigned long long key = score_key(c);
         if (key > tau) {                                      // same decision in the 4 lanes
           if (t == 0) best[pos] = key;
           __syncwarp(gmask);
@@ -264,8 +314,9 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
     }
   }
   __syncthreads();
-  // order every row's list: rank 0 = largest key (repeated arg-max), into the same place
-  {
+  // order every row's list: rank 0 = largest key (repeated arg-max), into the same place;
+  // a single candidate tile left the lists ordered already
+  if (max_cand > kCandTile) {
     unsigned long long* wins = wins_s + grp * hist;
     for (int row = grp; row < nrows; row += kGateGroups) {
       unsigned long long* best = best_s + (size_t)row * hist;
