@@ -66,11 +66,6 @@ struct Ctrl {
 
 constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + 6 * kTileBytes + sizeof(Ctrl);
 
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-
 // Pairs of score columns whose exponential is evaluated with the cubic on the
 // FMA pipe instead of the special-function unit: kPolyPairs out of every 8.
 // The special-function unit sustains 16 ex2 per clock and SM, which is exactly
@@ -246,14 +241,6 @@ __device__ __forceinline__ void softmax_row(uint32_t tS, uint32_t tO, int j, int
     for (int i = 0; i < 16; ++i) {
       const int e = ch * 32 + 2 * i;
       const uint64_t x = fma2(pack2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])), scale2, negm2);
-#ifdef MOBA_EXP_BF16X2
-      // both exponentials of the pair in one special-function op, in bf16 (the
-      // precision P is stored in anyway); the row sum adds the rounded values
-      const uint32_t pb = ex2_bf16x2(pack_bf16(lo2(x), hi2(x)));
-      const uint64_t pr = pack2(__uint_as_float(pb << 16), __uint_as_float(pb & 0xffff0000u));
-      if (i & 1) sum_b = add2(sum_b, pr); else sum_a = add2(sum_a, pr);
-      pk[i] = pb;
-#else
       uint64_t pr;
       if ((i & 7) < kPolyPairs) {
         pr = ex2_poly2(x);
@@ -262,7 +249,6 @@ __device__ __forceinline__ void softmax_row(uint32_t tS, uint32_t tO, int j, int
       }
       if (i & 1) sum_b = add2(sum_b, pr); else sum_a = add2(sum_a, pr);
       pk[i] = pack2_16<kHalf>(lo2(pr), hi2(pr));
-#endif
     }
     tmem_st16(tS + ch * 16, pk);
   }

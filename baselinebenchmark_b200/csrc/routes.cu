@@ -141,8 +141,8 @@ cudaError_t launch_compact(const Params& p, const int32_t* cu, const int32_t* se
 // ---------------------------------------------------------------------------
 constexpr int kMergeThreads = 256;
 
-// kVecs = float4 pieces of a row per lane: 1 for D <= 128 (lanes beyond D/4 idle), 2 for D = 256.
-template <bool kHalf, int kVecs>
+// A row has D/4 float4 pieces: one per lane for D <= 128 (lanes beyond D/4 idle), two for D = 256.
+template <bool kHalf, int D>
 __global__ void __launch_bounds__(kMergeThreads)
 merge_kernel(Params p, const float* __restrict__ partial_out, const float* __restrict__ partial_lse,
              const int32_t* __restrict__ status, __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out) {
@@ -161,18 +161,18 @@ merge_kernel(Params p, const float* __restrict__ partial_out, const float* __res
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
     const float inv = failed ? __int_as_float(0x7fc00000) : 1.f / tot;
-    const int nvec = p.D / 4;
+    constexpr int nvec = D / 4, kVecs = (nvec + 31) / 32;
     float4 acc[kVecs];
 #pragma unroll
     for (int u = 0; u < kVecs; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4* src = reinterpret_cast<const float4*>(partial_out + row * p.NP * p.D) + lane;
+    const float4* src = reinterpret_cast<const float4*>(partial_out + row * p.NP * D) + lane;
     for (int j = 0; j < p.NP; ++j) {
       const float lj = lse[j];                                // same address for all lanes
       if (lj == -INFINITY) continue;
       const float w = expf(lj - mx) * inv;
 #pragma unroll
       for (int u = 0; u < kVecs; ++u) {
-        if (lane + 32 * u < nvec) {
+        if (nvec % 32 == 0 || lane + 32 * u < nvec) {
           const float4 o = __ldg(src + j * nvec + 32 * u);
           acc[u].x += w * o.x; acc[u].y += w * o.y; acc[u].z += w * o.z; acc[u].w += w * o.w;
         }
@@ -182,7 +182,7 @@ merge_kernel(Params p, const float* __restrict__ partial_out, const float* __res
     const int h = (int)(row - t * p.Hq);
 #pragma unroll
     for (int u = 0; u < kVecs; ++u) {
-      if (lane + 32 * u < nvec) {
+      if (nvec % 32 == 0 || lane + 32 * u < nvec) {
         uint2 pk;
         pk.x = pack2_16<kHalf>(acc[u].x, acc[u].y);
         pk.y = pack2_16<kHalf>(acc[u].z, acc[u].w);
@@ -197,10 +197,15 @@ cudaError_t launch_merge(const Params& p, const float* partial_out, const float*
                          const int32_t* status, __nv_bfloat16* out, float* lse_out, cudaStream_t st) {
   int64_t blocks = (p.rows + (kMergeThreads / 32) - 1) / (kMergeThreads / 32);
   if (blocks > 148 * 64) blocks = 148 * 64;
-#define MOBA_MERGE(HALF, VECS) \
-  merge_kernel<HALF, VECS><<<(int)blocks, kMergeThreads, 0, st>>>(p, partial_out, partial_lse, status, out, lse_out)
-  if (p.D > 128) { if (p.fp16) MOBA_MERGE(true, 2); else MOBA_MERGE(false, 2); }
-  else           { if (p.fp16) MOBA_MERGE(true, 1); else MOBA_MERGE(false, 1); }
+#define MOBA_MERGE(HALF, DIM) \
+  merge_kernel<HALF, DIM><<<(int)blocks, kMergeThreads, 0, st>>>(p, partial_out, partial_lse, status, out, lse_out)
+  switch (p.D) {
+    case 64:  if (p.fp16) MOBA_MERGE(true, 64);  else MOBA_MERGE(false, 64);  break;
+    case 96:  if (p.fp16) MOBA_MERGE(true, 96);  else MOBA_MERGE(false, 96);  break;
+    case 128: if (p.fp16) MOBA_MERGE(true, 128); else MOBA_MERGE(false, 128); break;
+    case 256: if (p.fp16) MOBA_MERGE(true, 256); else MOBA_MERGE(false, 256); break;
+    default: return cudaErrorInvalidValue;
+  }
 #undef MOBA_MERGE
   return cudaGetLastError();
 }

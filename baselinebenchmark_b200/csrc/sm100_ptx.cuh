@@ -215,11 +215,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ uint32_t ex2_bf16x2(uint32_t x) {      // two bf16 lanes in, two out
-  uint32_t y;
-  asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
-}
 // 2^x (x <= 100; below -126 saturates to about 1e-38) on the FMA pipe: n = rint(x) through the 1.5*2^23 trick,
 // f = x - n in [-0.5, 0.5], cubic for 2^f (relative error 7.5e-5, far below the
 // bf16 rounding the result goes through), exponent patched with an integer add.

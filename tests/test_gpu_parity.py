@@ -190,6 +190,33 @@ def test_forward_matches_fp32_evaluation(case, impl, dtype):
     assert (lse.cpu() - ref_lse).abs().max().item() < 2e-3
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("jump", [4.0, 24.0, 140.0])
+def test_scores_rising_late_in_a_chunk(impl, dtype, jump):
+    """Keys whose scores lie far above everything seen earlier in the same chunk (by `jump`
+    in units of log2 after scaling): the running reference of the softmax has to follow,
+    whatever shortcut a kernel takes on tiles that look ordinary."""
+    t, hq, hkv, d, chunk, topk = 1536, 4, 2, 128, 512, 3
+    g = torch.Generator().manual_seed(int(jump))
+    q = torch.ones(t, hq, d) * 0.25
+    k = torch.randn(t, hkv, d, generator=g) * 0.05
+    v = torch.randn(t, hkv, d, generator=g)
+    amp = jump / (0.25 * d * d ** -0.5 * 1.4426950408889634)          # q.k * scale * log2(e) == jump
+    for start in (300, 700, 1400):                                     # late in chunk 0, 1 and 2
+        k[start:start + 3] = amp
+    q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+    cu = np.array([0, t], dtype=np.int32)
+    ref, ref_lse, sel_o = O.moba_forward(q, k, v, cu, t, chunk, topk, dtype=torch.float32)
+    out, lse, sel = parallel.moba_forward(*G.to_dev(q, k, v), torch.from_numpy(cu).cuda(), t, chunk, topk,
+                                          return_lse=True, return_selected=True, attend_impl=impl)
+    np.testing.assert_array_equal(sel.cpu().numpy(), sel_o)
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    mx, mean = G.rel_stats(out.cpu(), ref)
+    assert mx < MAX_ABS and mean < MEAN_ABS, (mx, mean)
+    assert (lse.cpu() - ref_lse).abs().max().item() < 2e-3 * max(1.0, jump / 8)
+
+
 @pytest.mark.parametrize("impl", IMPLS)
 def test_topk1_chunk_local_exact(impl):
     """test_moba_topk.py:30-57 with head_dim 128: exact equality required."""
