@@ -22,6 +22,7 @@ SYMBOLS = (
     "moba_workspace_size", "moba_workspace_size_min", "moba_forward", "moba_forward_events", "moba_workspace_size_host", "moba_forward_host",
     "moba_chunk_metadata", "moba_chunk_means", "moba_gate_topk", "moba_compact_routes",
     "moba_attend", "moba_merge", "moba_attend_tile_rows", "moba_route_static",
+    "moba_backward_workspace_size", "moba_backward",
 )
 
 
@@ -86,6 +87,8 @@ def lib() -> C.CDLL:
         handle.moba_merge.argtypes = [pp, vp, vp, i32p, vp, vp, vp]
         handle.moba_attend_tile_rows.argtypes = [C.c_int]
         handle.moba_route_static.argtypes = [pp, vp, vp, i32p, i32p, vp]
+        handle.moba_backward_workspace_size.argtypes = [pp, C.POINTER(sz)]
+        handle.moba_backward.argtypes = [pp, vp, vp, vp, i32p, vp, vp, i32p, vp, vp, vp, vp, vp, sz, vp]
         _lib = handle
     return _lib
 

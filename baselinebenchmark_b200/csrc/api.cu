@@ -389,6 +389,71 @@ int moba_forward_events(const moba_problem_t* p, const void* q, const void* k, c
   return forward_impl(p, q, k, v, cu, out, lse_out, selected_out, workspace, workspace_bytes, stream, events);
 }
 
+// ---------------------------------------------------------------------------
+// training path: backward of the operator
+// ---------------------------------------------------------------------------
+static int check_backward(const moba_problem_t* p) {
+  const int rc = check_problem(p);
+  if (rc != MOBA_OK) return rc;
+  if (p->q_tokens != 0) return MOBA_E_UNSUPPORTED;           // whole problems only
+  if (p->head_dim > 128) return MOBA_E_UNSUPPORTED;
+  const Params r = make_params(p);
+  if (r.rows * r.NP >= ((int64_t)1 << 31)) return MOBA_E_UNSUPPORTED;
+  return MOBA_OK;
+}
+
+int moba_backward_workspace_size(const moba_problem_t* p, size_t* bytes) {
+  const int rc = check_backward(p);
+  if (rc != MOBA_OK) return rc;
+  if (bytes == nullptr) return MOBA_E_NULL;
+  const Params r = make_params(p);
+  *bytes = carve(r, nullptr).total + 2 * align_up((size_t)r.rows * sizeof(float));
+  return MOBA_OK;
+}
+
+int moba_backward(const moba_problem_t* p, const void* q, const void* k, const void* v, const int32_t* cu,
+                  const void* out, const float* lse, const int32_t* selected, const void* dout, void* dq, void* dk,
+                  void* dv, void* workspace, size_t workspace_bytes, void* stream) {
+  size_t need = 0;
+  const int rc = moba_backward_workspace_size(p, &need);
+  if (rc != MOBA_OK) return rc;
+  if (!q || !k || !v || !cu || !out || !lse || !dout || !dq || !dk || !dv) return MOBA_E_NULL;
+  if (workspace == nullptr || workspace_bytes < need) return MOBA_E_WORKSPACE;
+  if (((uintptr_t)dout | (uintptr_t)dq | (uintptr_t)dk | (uintptr_t)dv | (uintptr_t)out) & 15) return MOBA_E_ALIGN;
+  const Params r = make_params(p);
+  if (r.hist > 0 && selected == nullptr) return MOBA_E_NULL;
+  cudaStream_t st = (cudaStream_t)stream;
+  const Workspace w = carve(r, workspace);
+  float* delta = reinterpret_cast<float*>(static_cast<char*>(workspace) + w.total);
+  float* lse2 = reinterpret_cast<float*>(reinterpret_cast<char*>(delta) + align_up((size_t)r.rows * sizeof(float)));
+  const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(q);
+  const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(k);
+  const __nv_bfloat16* vb = static_cast<const __nv_bfloat16*>(v);
+  const __nv_bfloat16* gb = static_cast<const __nv_bfloat16*>(dout);
+  // dout, dq: contiguous [T, Hq, D]; dk, dv: contiguous [T, Hkv, D]
+  const int64_t qt = (int64_t)r.Hq * r.D, kt = (int64_t)r.Hkv * r.D, hd = r.D;
+  cudaError_t e;
+  if ((e = cudaMemsetAsync(w.list_counts, 0, w.zero_bytes, st)) != cudaSuccess) return (int)e;
+  if (r.hist > 0) {
+    if ((e = launch_count_lists(r, selected, w.list_counts, st)) != cudaSuccess) return (int)e;
+    if ((e = launch_compact(r, cu, selected, w.list_counts, w.list_offsets, w.tile_prefix, w.cursors, w.row_list,
+                            w.partial_lse, kMmaTileRows, st)) != cudaSuccess)
+      return (int)e;
+  }
+  if ((e = launch_bwd_delta(r, static_cast<const __nv_bfloat16*>(out), gb, qt, hd, lse, delta, lse2, st)) != cudaSuccess)
+    return (int)e;
+  if ((e = launch_bwd_dq(r, qb, kb, vb, gb, qt, hd, cu, w.list_counts, w.list_offsets, w.tile_prefix, w.row_list, lse2,
+                         delta, w.partial_out, w.work_counter, st)) != cudaSuccess)
+    return (int)e;
+  if ((e = launch_bwd_sum_dq(r, w.partial_out, selected, static_cast<__nv_bfloat16*>(dq), qt, hd, st)) != cudaSuccess)
+    return (int)e;
+  if ((e = launch_bwd_dkdv(r, qb, kb, vb, gb, qt, hd, cu, w.list_counts, w.list_offsets, w.row_list, lse2, delta,
+                           static_cast<__nv_bfloat16*>(dk), kt, hd, static_cast<__nv_bfloat16*>(dv), kt, hd,
+                           w.work_counter + 8, st)) != cudaSuccess)
+    return (int)e;
+  return MOBA_OK;
+}
+
 int moba_workspace_size_host(const moba_problem_t* p, size_t* bytes) {
   size_t core = 0;
   const int rc = moba_workspace_size(p, &core);

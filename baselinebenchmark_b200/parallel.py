@@ -146,17 +146,64 @@ def moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, *,
     return out, lse, sel
 
 
+def moba_backward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, out, lse, selected, dout):
+    """Gradients (dq, dk, dv) of the operator for the output gradient `dout`, given what
+    `moba_forward(..., return_lse=True, return_selected=True)` returned
+    (MixedAttention.backward, parallel.py:149-250: merged LSE and output, constant selection)."""
+    _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)
+    if q.shape[2] > 128:
+        raise NotImplementedError("the backward is built for head_dim <= 128")
+    dout = dout.contiguous()
+    prob = make_problem(q, k, v, out, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, _lib.ATTEND_MMA_SYNC)
+    need = C.c_size_t(0)
+    _lib.check(_lib.lib().moba_backward_workspace_size(C.byref(prob), C.byref(need)))
+    ws = _workspace(q.device, need.value)
+    dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+    dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+        rc = _lib.lib().moba_backward(
+            C.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(),
+            lse.data_ptr(), selected.data_ptr() if selected is not None and selected.numel() else None,
+            dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+            ws.data_ptr(), ws.numel() * ws.element_size(), stream)
+    _lib.check(rc)
+    return dq, dk, dv
+
+
+class _MobaFunction(torch.autograd.Function):
+    """Training path: forward through the same kernels as inference, keeping the LSE and the
+    routing decision for the backward (the reference's MixedAttention, parallel.py:59-250)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk):
+        out, lse, sel = moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk,
+                                     return_lse=True, return_selected=True)
+        ctx.save_for_backward(q, k, v, cu_seqlens, out, lse, sel)
+        ctx.args = (max_seqlen, moba_chunk_size, moba_topk)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, cu_seqlens, out, lse, sel = ctx.saved_tensors
+        dq, dk, dv = moba_backward(q, k, v, cu_seqlens, *ctx.args, out, lse, sel, dout)
+        return dq, dk, dv, None, None, None, None
+
+
 def parallel_moba(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor,
                   max_seqlen: int, moba_chunk_size: int, moba_topk: int) -> torch.Tensor:
     """Causal variable-length MoBA forward, signature of parallel.py:377-385.
 
-    Only the inference path exists here: like the reference it is taken when
-    autograd is off (parallel.py:448); with autograd on this raises instead of
-    silently returning a tensor without a graph.
+    Like the reference (parallel.py:447-456) the inference dataflow is taken when autograd is
+    off; with autograd on and an input that requires grad the call goes through an
+    autograd.Function whose backward runs `moba_backward` (head_dim <= 128).
     """
     if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
-        raise NotImplementedError("the B200 build implements the inference forward only; "
-                                  "call under torch.no_grad() / torch.inference_mode()")
+        _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)
+        if q.shape[2] > 128:
+            raise NotImplementedError("the training path is built for head_dim <= 128")
+        return _MobaFunction.apply(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)
     return moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)[0]
 
 

@@ -223,6 +223,22 @@ int moba_merge(const moba_problem_t* p, const float* partial_out, const float* p
 int moba_route_static(const moba_problem_t* p, const void* q, const void* k, const int32_t* cu_seqlens,
                       int32_t* selected, void* stream);
 
+/* Training path: gradients of the operator (MixedAttention.backward, parallel.py:149-250;
+ * dq and dk/dv kernels attention.py:163-369).  Inputs are those of the forward plus what it
+ * returned: out [T,Hq,D], lse fp32 [Hq,T] and selected int32 [hist,Hq,T] (may be NULL when
+ * hist <= 0), and dout [T,Hq,D].  Writes dq [T,Hq,D], dk and dv [T,Hkv,D] in the input
+ * dtype; dout, dq, dk, dv are contiguous, q, k, v, out use the strides of the problem.  Like
+ * the reference, both branches are differentiated with the merged LSE and output, and the
+ * chunk selection is a constant.  No atomic accumulation: dq is bit-identical run to run,
+ * dk and dv up to the order in which the rows of a routed list are added.
+ * Whole problems only (q_tokens == 0), head_dim <= 128, T*Hq*(hist+1) < 2^31; otherwise
+ * MOBA_E_UNSUPPORTED.  The workspace holds, besides the route lists, one fp32 [D] slot per
+ * (row, partial) for dQ: about the size of the forward's. */
+int moba_backward_workspace_size(const moba_problem_t* p, size_t* bytes);
+int moba_backward(const moba_problem_t* p, const void* q, const void* k, const void* v, const int32_t* cu_seqlens,
+                  const void* out, const float* lse, const int32_t* selected, const void* dout, void* dq, void* dk,
+                  void* dv, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Rows per routed work item that the selected attend implementation wants
  * (the tile_rows argument of moba_compact_routes). */
 int moba_attend_tile_rows(int attend_impl);

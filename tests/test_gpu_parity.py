@@ -517,3 +517,91 @@ def test_bounded_workspace_runs_head_groups():
     with pytest.raises(_lib.MobaError):
         parallel.moba_forward(qd, kd, vd, cud, 1536, 128, 4,
                               workspace=torch.empty(least.value - 256, dtype=torch.uint8, device="cuda"))
+
+
+# --------------------------------------------------------------------------
+# training path (backward)
+# --------------------------------------------------------------------------
+BACKWARD_CASES = [
+    ("bwd_mha_c128", 128, (1024,), 4, 4, 128, 3),
+    ("bwd_gqa_varlen", 128, (700, 333, 1290), 8, 2, 128, 4),
+    ("bwd_tails", 128, (513, 257, 129), 4, 2, 64, 5),
+    ("bwd_k1_local", 128, (600, 300), 4, 2, 128, 1),
+    ("bwd_mqa_k8", 128, (900,), 8, 1, 64, 8),
+    ("bwd_d64", 64, (700, 333), 8, 2, 128, 4),
+    ("bwd_d96", 96, (640,), 4, 4, 64, 3),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", BACKWARD_CASES, ids=lambda c: c[0])
+def test_backward_matches_float64_autograd(case, dtype):
+    """dq, dk, dv against float64 autograd through the dense evaluation of the same selection.
+    Tolerance: the reference's forward bound scaled to the gradients (max-abs error below 4 %
+    of the largest gradient entry, mean-abs error below 0.4 % of it)."""
+    name, d, lens, hq, hkv, chunk, topk = case
+    q, k, v, cu = _case_inputs(lens, hq, hkv, chunk, zlib.crc32(name.encode()) % 1000, dtype=dtype, d=d)
+    g = torch.Generator().manual_seed(11)
+    dout = torch.randn(q.shape, generator=g).to(dtype)
+    max_seqlen = max(lens)
+    qd, kd, vd = (x.cuda().requires_grad_(True) for x in (q, k, v))
+    cud = torch.from_numpy(cu).cuda()
+    out = parallel.parallel_moba(qd, kd, vd, cud, max_seqlen, chunk, topk)
+    assert out.requires_grad
+    out.backward(dout.cuda())
+    torch.cuda.synchronize()
+    _, _, sel_o = O.moba_forward(q, k, v, cu, max_seqlen, chunk, topk)
+    rq, rk, rv = O.attend_grads(q, k, v, cu, max_seqlen, chunk, sel_o, dout)
+    for name_, got, ref in (("dq", qd.grad, rq), ("dk", kd.grad, rk), ("dv", vd.grad, rv)):
+        got = got.double().cpu()
+        assert torch.isfinite(got).all(), name_
+        ref_max = ref.abs().max().item()
+        err = (got - ref).abs()
+        assert err.max().item() < 0.04 * ref_max and err.mean().item() < 0.004 * ref_max, \
+            (name_, err.max().item(), err.mean().item(), ref_max)
+
+
+def test_backward_run_to_run_and_no_grad_for_inference():
+    """dq is bit-identical run to run (a row's keys are visited in a fixed order); dk and dv add
+    the rows of a routed list in the order the compaction's atomics produced, so they agree to
+    the last bits only (the reference's lists are unordered too, routing.py:1586-1591)."""
+    q, k, v, cu = _case_inputs((700, 333, 1290), 8, 2, 128, seed=3)
+    cud = torch.from_numpy(cu).cuda()
+    dout = torch.randn(q.shape, generator=torch.Generator().manual_seed(5)).bfloat16().cuda()
+    grads = []
+    for _ in range(2):
+        qd, kd, vd = (x.cuda().requires_grad_(True) for x in (q, k, v))
+        parallel.parallel_moba(qd, kd, vd, cud, 1290, 128, 4).backward(dout)
+        grads.append((qd.grad.clone(), kd.grad.clone(), vd.grad.clone()))
+    assert torch.equal(grads[0][0], grads[1][0])
+    for a, b in zip(grads[0][1:], grads[1][1:]):
+        assert (a.float() - b.float()).abs().max().item() <= 2.0 ** -7 * a.float().abs().max().item()
+    with torch.no_grad():
+        assert not parallel.parallel_moba(q.cuda(), k.cuda(), v.cuda(), cud, 1290, 128, 4).requires_grad
+
+
+def test_backward_config2_dq_sampled_and_dkdv_finite():
+    """BASELINE.json configs[2] at full size: dq of sampled rows against float64, dk / dv finite
+    and of the expected magnitude (their exact check runs on the small shapes above)."""
+    cfg = O.CONFIGS[2]
+    lens = O.config_lengths(2)
+    q, k, v, cu = O.make_inputs(lens, cfg["hq"], cfg["hkv"], cfg["d"], cfg["chunk"], seed=44)
+    dout = torch.randn(q.shape, generator=torch.Generator().manual_seed(7)).bfloat16()
+    qd, kd, vd = (x.cuda().requires_grad_(True) for x in (q, k, v))
+    cud = torch.from_numpy(cu).cuda()
+    out, lse, sel = parallel.moba_forward(qd.detach(), kd.detach(), vd.detach(), cud, max(lens), cfg["chunk"],
+                                          cfg["topk"], return_lse=True, return_selected=True)
+    dq, dk, dv = parallel.moba_backward(qd.detach(), kd.detach(), vd.detach(), cud, max(lens), cfg["chunk"],
+                                        cfg["topk"], out, lse, sel, dout.cuda())
+    torch.cuda.synchronize()
+    assert torch.isfinite(dq.float()).all() and torch.isfinite(dk.float()).all() and torch.isfinite(dv.float()).all()
+    rng = np.random.default_rng(3)
+    rows = [(int(rng.integers(0, q.shape[0])), int(rng.integers(0, q.shape[1]))) for _ in range(24)]
+    rows += [(0, 0), (q.shape[0] - 1, q.shape[1] - 1), (4095, 3), (4096, 5)]
+    ref = O.dq_rows(q, k, v, cu, max(lens), cfg["chunk"], sel.cpu().numpy(), dout, rows)
+    got = torch.stack([dq[t, h].double().cpu() for t, h in rows])
+    err = (got - ref).abs()
+    scale = ref.abs().max().item()
+    assert err.max().item() < 0.04 * scale and err.mean().item() < 0.004 * scale, (err.max().item(), err.mean().item(), scale)
+    # every key receives gradient from the later queries of its own chunk at least
+    assert dv.float().abs().sum(-1).min().item() > 0
