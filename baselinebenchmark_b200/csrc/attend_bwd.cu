@@ -131,7 +131,11 @@ __global__ void count_lists_kernel(Params p, const int32_t* __restrict__ selecte
     const int64_t rem = i - r * (p.Hq * p.Tq);
     const int h = (int)(rem / p.Tq);
     const int slot = selected[r * p.sel_rs + rem];
-    if (slot >= 0) atomicAdd(&list_counts[(int64_t)slot * p.Hkv + h / p.G], 1);
+    // lanes of a warp that hit the same list add once (neighbouring tokens mostly do)
+    const int list = slot >= 0 ? slot * p.Hkv + h / p.G : -1;
+    const unsigned active = __activemask();
+    const unsigned same = __match_any_sync(active, list);
+    if (list >= 0 && (int)(threadIdx.x & 31) == __ffs(same) - 1) atomicAdd(&list_counts[list], __popc(same));
   }
 }
 
@@ -330,15 +334,15 @@ template <int D>
 struct DkvSmem {
   unsigned char k[kBN * row_bytes(D)];
   unsigned char v[kBN * row_bytes(D)];
-  unsigned char q[kRows * row_bytes(D)];
-  unsigned char g[kRows * row_bytes(D)];
+  unsigned char q[2][kRows * row_bytes(D)];     // row tiles, double buffered
+  unsigned char g[2][kRows * row_bytes(D)];
   unsigned char ps[kRows * 128];                // P  [128 rows][64 keys], 16-bit, swizzled
   unsigned char ds[kRows * 128];                // dS
-  int64_t qoff[kRows];
-  int64_t goff[kRows];
-  float lse2[kRows];
-  float delta[kRows];
-  int32_t tok[kRows];                           // query token of the row, -1: no row
+  int64_t qoff[3][kRows];                       // row descriptions run two tiles ahead
+  int64_t goff[3][kRows];
+  float lse2[3][kRows];
+  float delta[3][kRows];
+  int32_t tok[3][kRows];                        // query token of the row, -1: no row
   int32_t unit;
 };
 
@@ -399,7 +403,9 @@ bwd_dkdv_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bfloat
     const int own_rows = sl.end - key0;                      // tokens key0 .. end see at least one key of the tile
     const int own_tiles = (own_rows + kRows - 1) / kRows;
     const int total_tiles = routed_tiles + own_tiles * p.G;
-    for (int rt = 0; rt < total_tiles; ++rt) {
+    // describes the rows of row tile `rt` into slot rt % 3
+    auto describe = [&](int rt) {
+      const int m = rt % 3;
       const bool routed = rt < routed_tiles;
       int hl = 0, ot = 0;
       if (!routed) { hl = (rt - routed_tiles) / own_tiles; ot = (rt - routed_tiles) - hl * own_tiles; }
@@ -426,29 +432,38 @@ bwd_dkdv_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bfloat
           l2 = lse2[row];
           dl = delta[row];
         }
-        s.qoff[r] = off; s.goff[r] = goff; s.lse2[r] = l2; s.delta[r] = dl; s.tok[r] = tokq;
+        s.qoff[m][r] = off; s.goff[m][r] = goff; s.lse2[m][r] = l2; s.delta[m][r] = dl; s.tok[m][r] = tokq;
       }
-      __syncthreads();
-      {
-        const uint32_t qb = smem_u32(s.q), gb = smem_u32(s.g);
-        for (int i = threadIdx.x; i < kRows * kChunks; i += kThreads) {
-          const int r = i / kChunks, ch = i - r * kChunks;
-          cp_async16(qb + swz<D>(r, ch), q + s.qoff[r] + ch * 8, s.tok[r] >= 0);
-          cp_async16(gb + swz<D>(r, ch), dout + s.goff[r] + ch * 8, s.tok[r] >= 0);
-        }
-        cp_async_commit();
-        cp_async_wait<0>();
+    };
+    // requests the Q and dO rows of row tile `rt` into buffer rt & 1
+    auto request = [&](int rt) {
+      const int m = rt % 3, bf = rt & 1;
+      const uint32_t qb = smem_u32(s.q[bf]), gb = smem_u32(s.g[bf]);
+      for (int i = threadIdx.x; i < kRows * kChunks; i += kThreads) {
+        const int r = i / kChunks, ch = i - r * kChunks;
+        cp_async16(qb + swz<D>(r, ch), q + s.qoff[m][r] + ch * 8, s.tok[m][r] >= 0);
+        cp_async16(gb + swz<D>(r, ch), dout + s.goff[m][r] + ch * 8, s.tok[m][r] >= 0);
       }
+      cp_async_commit();
+    };
+    describe(0);
+    __syncthreads();
+    request(0);
+    if (total_tiles > 1) describe(1);
+    __syncthreads();
+    for (int rt = 0; rt < total_tiles; ++rt) {
+      const int m = rt % 3, bf = rt & 1;
+      if (rt + 1 < total_tiles) { request(rt + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
       __syncthreads();
       // phase 1: this warp's 16 rows x 64 keys of P and dS
       {
         float sc[8][4], dp[8][4];
-        rows_times_keys<kHalf, D>(sc, smem_u32(s.q), smem_u32(s.k), warp, lane);
-        rows_times_keys<kHalf, D>(dp, smem_u32(s.g), smem_u32(s.v), warp, lane);
+        rows_times_keys<kHalf, D>(sc, smem_u32(s.q[bf]), smem_u32(s.k), warp, lane);
+        rows_times_keys<kHalf, D>(dp, smem_u32(s.g[bf]), smem_u32(s.v), warp, lane);
         const int row0 = warp * 16 + (lane >> 2);
-        const float l0 = s.lse2[row0], l1 = s.lse2[row0 + 8];
-        const float d0 = s.delta[row0], d1 = s.delta[row0 + 8];
-        const int t0 = s.tok[row0], t1 = s.tok[row0 + 8];
+        const float l0 = s.lse2[m][row0], l1 = s.lse2[m][row0 + 8];
+        const float d0 = s.delta[m][row0], d1 = s.delta[m][row0 + 8];
+        const int t0 = s.tok[m][row0], t1 = s.tok[m][row0 + 8];
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
           float pv[4], ds[4];
@@ -469,10 +484,11 @@ bwd_dkdv_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bfloat
           *reinterpret_cast<uint32_t*>(s.ds + (row0 + 8) * 128 + c1) = pack2_16<kHalf>(ds[2], ds[3]);
         }
       }
+      if (rt + 2 < total_tiles) describe(rt + 2);            // its loads overlap the other warps' MMAs
       __syncthreads();
       // phase 2: dV += P^T . dO,  dK += dS^T . Q  over the 128 rows of the tile
       {
-        const uint32_t pb = smem_u32(s.ps), sb = smem_u32(s.ds), qb = smem_u32(s.q), gb = smem_u32(s.g);
+        const uint32_t pb = smem_u32(s.ps), sb = smem_u32(s.ds), qb = smem_u32(s.q[bf]), gb = smem_u32(s.g[bf]);
 #pragma unroll
         for (int ks = 0; ks < kRows / 16; ++ks) {
           // A = transposed 16 keys x 16 rows: stored [row][key], loaded with .trans
