@@ -605,3 +605,34 @@ def test_backward_config2_dq_sampled_and_dkdv_finite():
     assert err.max().item() < 0.04 * scale and err.mean().item() < 0.004 * scale, (err.max().item(), err.mean().item(), scale)
     # every key receives gradient from the later queries of its own chunk at least
     assert dv.float().abs().sum(-1).min().item() > 0
+
+
+# --------------------------------------------------------------------------
+# CUDA path against outputs of the reference package itself (tests/golden/forward_*.npz)
+# --------------------------------------------------------------------------
+FORWARD_GOLDEN = sorted(glob.glob(str(Path(__file__).parent / "golden" / "forward_*.npz")))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("path", FORWARD_GOLDEN, ids=lambda p: p.split("forward_")[-1][:-4])
+def test_reference_outputs_and_gradients_through_cuda(path, dtype):
+    """Forward and backward on the fixture inputs (exact in bf16 and fp16) against what the
+    reference's own kernels returned for them: output within max-abs 2e-2 / mean-abs 2e-3
+    (BASELINE.json north_star), gradients within 4 % / 0.4 % of the largest entry."""
+    z = np.load(path)
+    lens = [int(x) for x in z["seq_lens"]]
+    q, k, v, dout = (torch.from_numpy(z[n]).to(dtype).cuda() for n in ("q", "k", "v", "dout"))
+    assert (q.float().cpu() == torch.from_numpy(z["q"]).float()).all()          # same numbers in both dtypes
+    cud = torch.from_numpy(z["cu_seqlens"]).cuda()
+    qd, kd, vd = (x.requires_grad_(True) for x in (q, k, v))
+    out = parallel.parallel_moba(qd, kd, vd, cud, max(lens), int(z["chunk"]), int(z["topk"]))
+    out.backward(dout)
+    torch.cuda.synchronize()
+    for name in ("out_ref", "out_train_ref"):
+        mx, mean = G.rel_stats(out.detach().cpu(), torch.from_numpy(z[name]).float())
+        assert mx < MAX_ABS and mean < MEAN_ABS, (name, mx, mean)
+    for name, got in (("dq_ref", qd.grad), ("dk_ref", kd.grad), ("dv_ref", vd.grad)):
+        ref = torch.from_numpy(z[name]).double()
+        err = (got.double().cpu() - ref).abs()
+        scale = ref.abs().max().item()
+        assert err.max().item() < 0.04 * scale and err.mean().item() < 0.004 * scale, (name, err.max().item(), scale)

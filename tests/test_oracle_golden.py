@@ -178,3 +178,48 @@ def test_reference_tile_numerics_agree_with_exact_evaluation():
         merged, mlse = O.merge_lse(outs, lses)
         assert np.abs(merged - out[t, h].numpy()).max() < 0.0063
         assert abs(float(mlse) - float(lse[h, t])) < 1e-3
+
+
+# --------------------------------------------------------------------------
+# the whole operator and its backward against the reference package run end to end
+# (tests/golden/forward_*.npz, produced by tests/golden/make_forward_golden.py)
+# --------------------------------------------------------------------------
+FORWARD_GOLDEN = sorted(glob.glob(str(__import__("pathlib").Path(__file__).parent / "golden" / "forward_*.npz")))
+
+
+def _load_forward(path):
+    z = np.load(path)
+    t = {n: torch.from_numpy(z[n]) for n in ("q", "k", "v", "dout", "out_ref", "out_train_ref", "dq_ref", "dk_ref", "dv_ref")}
+    return z, t
+
+
+def test_forward_golden_files_present():
+    assert len(FORWARD_GOLDEN) >= 4
+
+
+@pytest.mark.parametrize("path", FORWARD_GOLDEN, ids=lambda p: p.split("forward_")[-1][:-4])
+def test_oracle_forward_matches_reference_output(path):
+    """Oracle (contract routing + fp32 evaluation) against the output of the reference's
+    inference path and of its training forward, both float16: float16 rounding of the output
+    (2^-11 relative) plus the float16 rounding of P inside the reference kernels."""
+    z, t = _load_forward(path)
+    lens = [int(x) for x in z["seq_lens"]]
+    out, _, _ = O.moba_forward(t["q"], t["k"], t["v"], z["cu_seqlens"], max(lens), int(z["chunk"]), int(z["topk"]))
+    for name in ("out_ref", "out_train_ref"):
+        err = (out - t[name].float()).abs()
+        assert err.max().item() < 4e-3 and err.mean().item() < 2e-4, (name, err.max().item(), err.mean().item())
+
+
+@pytest.mark.parametrize("path", FORWARD_GOLDEN, ids=lambda p: p.split("forward_")[-1][:-4])
+def test_oracle_gradients_match_reference_backward(path):
+    """float64 autograd of the oracle's evaluation against the gradients the reference's
+    backward kernels produced (float16)."""
+    z, t = _load_forward(path)
+    lens = [int(x) for x in z["seq_lens"]]
+    _, _, sel = O.moba_forward(t["q"], t["k"], t["v"], z["cu_seqlens"], max(lens), int(z["chunk"]), int(z["topk"]))
+    dq, dk, dv = O.attend_grads(t["q"], t["k"], t["v"], z["cu_seqlens"], max(lens), int(z["chunk"]), sel, t["dout"])
+    for name, got in (("dq_ref", dq), ("dk_ref", dk), ("dv_ref", dv)):
+        ref = t[name].double()
+        err = (got - ref).abs()
+        scale = ref.abs().max().item()
+        assert err.max().item() < 4e-3 * scale and err.mean().item() < 2e-4 * scale, (name, err.max().item(), scale)
