@@ -42,6 +42,10 @@ SEQ_LEN = 131072
 SEQS_PER_GPU = 2
 HQ, HKV, D, CHUNK, TOPK = 32, 8, 128, 4096, 8
 KERNELS_PER_STEP = 6      # chunk_mean, gate_topk, scan_lists, scatter_routes, attend, merge
+# dram__bytes_read.sum + dram__bytes_write.sum of one attend_tc5_kernel launch on configs[2]
+# (32768 tokens x 32 heads, 8 partial results per row), from an ncu capture of that launch
+ATTEND_TRAFFIC_CFG2 = 2.713171e9 + 2.517811e9
+PARTIALS = min(TOPK - 1, SEQ_LEN // CHUNK - 1) + 1
 
 
 def cdiv(a, b):
@@ -438,7 +442,11 @@ def main():
                          "peak": pk["sustained"], "unit": "TFLOP/s", "frac": achieved / pk["sustained"],
                          "peak_kind": f"{pk['source']} cuBLAS bf16, sustained (kernel timed inside a long step); "
                                       f"burst {pk['burst']}", "frac_of_burst": achieved / pk["burst"],
-                         "flops_per_launch": flops, "ms_per_launch": attend_ms, "traffic": None},
+                         "flops_per_launch": flops, "ms_per_launch": attend_ms,
+                         "traffic": ATTEND_TRAFFIC_CFG2 * (SEQS_PER_GPU * SEQ_LEN * HQ * PARTIALS) / (32768 * 32 * 8),
+                         "traffic_unit": "bytes of DRAM read + write per launch, scaled from one ncu capture of "
+                                         "configs[2] (5.231e9 B for 32768 x 32 rows x 8 partial results) by "
+                                         "rows x partial results: the traffic is fp32 partial writes and Q gathers"},
             "stage_ms": {"means": float(stage_ms[0]), "gate_topk": float(stage_ms[1]), "compact": float(stage_ms[2]),
                          "attend": float(stage_ms[3]), "merge": float(stage_ms[4])},
             "cpu_baseline": cpu, "clocks": clocks.summary(), "also": also,
