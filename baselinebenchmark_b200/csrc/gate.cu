@@ -125,10 +125,10 @@ cudaError_t launch_chunk_means(const Params& p, const __nv_bfloat16* k, const in
 //   groups of 4 lanes.  The CTA stages the means of its kv head for a tile of
 //   candidate chunks in shared memory as fp32; every row group then scores its
 //   rows against them and keeps the `hist` largest packed keys
-//   (order-preserving score bits << 32 | 0xFFFFFFFF - slot, routing.py:1151-1153):
-//   a candidate replaces the smallest kept key when it beats it, and the kept keys
-//   are ordered once at the end.  Keys are unique, so ties in the score fall to
-//   the lower slot.
+//   (order-preserving score bits << 32 | 0xFFFFFFFF - slot, routing.py:1151-1153)
+//   in an ordered list: the keys of a candidate tile are held in registers,
+//   extracted largest first and merged with the list.  Keys are unique, so ties
+//   in the score fall to the lower slot.
 //   Lane t of a group owns the 8-dim blocks t, t+4, t+8, ..., so all levels of
 //   the halving tree but the last two stay inside the lane and only those two
 //   cross lanes: same summation order as one lane per block, a fraction of the
@@ -155,25 +155,6 @@ __device__ __forceinline__ float dot8(const float (&q)[8], const float4 a, const
   return s;
 }
 
-// Smallest key of a row's list and its position (ties: lowest position), over the 4 lanes of a group.
-__device__ __forceinline__ void list_min(const unsigned long long* best, int hist, int t, unsigned gmask,
-                                         unsigned long long& tau, int& pos) {
-  unsigned long long mine = ~0ull;
-  int mine_i = hist;
-  for (int i = t; i < hist; i += 4) {
-    const unsigned long long kk = best[i];
-    if (kk < mine) { mine = kk; mine_i = i; }
-  }
-#pragma unroll
-  for (int o = 2; o > 0; o >>= 1) {
-    const unsigned long long ok = __shfl_xor_sync(gmask, mine, o);
-    const int oi = __shfl_xor_sync(gmask, mine_i, o);
-    if (ok < mine || (ok == mine && oi < mine_i)) { mine = ok; mine_i = oi; }
-  }
-  tau = mine;
-  pos = mine_i;
-}
-
 #ifndef MOBA_GATE_CTAS
 #define MOBA_GATE_CTAS 3             // resident CTAs per SM the register budget is set for (D <= 128)
 #endif
@@ -187,10 +168,10 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
   constexpr int kBlocks = D / 8;                       // 8-dim blocks per row
   constexpr int kOwn = (kBlocks + 3) / 4;              // blocks owned by a lane: t, t+4, ...
   constexpr int kOwnPad = kOwn <= 2 ? 2 : (kOwn <= 4 ? 4 : 8);   // padded to a power of two with +0.0
-  // layout: means tile fp32 | wins[groups][hist] | best[rows][hist] | counts[mc]
+  // layout: means tile fp32 | scratch[groups][2 * hist] | best[rows][hist] | counts[mc]
   float4* means_s = reinterpret_cast<float4*>(smem_raw);                            // kCandTile * D/4 float4
   unsigned long long* wins_s = reinterpret_cast<unsigned long long*>(means_s + kCandTile * (D / 4));
-  unsigned long long* best_s = wins_s + kGateGroups * hist;
+  unsigned long long* best_s = wins_s + kGateGroups * 2 * hist;
   int32_t* cnt_s = reinterpret_cast<int32_t*>(best_s + (size_t)kGateRows * hist);
 
   const int b = blockIdx.z, hk = blockIdx.y;
@@ -254,97 +235,64 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
         return ((unsigned long long)float_key(s) << 32) |
                (unsigned long long)(0xFFFFFFFFu - (uint32_t)(slot0 + c0 + c));
       };
+      // The row's list best[0..hist) is kept ordered, largest key first, 0 = empty place.
+      // Lane t keeps the keys of candidates c = 4e + t of this tile in registers (only those
+      // that beat the smallest key of a full list) and the group extracts them largest first:
+      // no shared-memory round trip per candidate.  First tile: straight into the list.
+      // Later tiles: into a scratch list that is then merged with the old one.
       unsigned long long* best = best_s + (size_t)row * hist;
-      if (c0 == 0) {
-        // First tile: the list is empty.  Lane t keeps the keys of candidates c = 4e + t in
-        // registers and the group extracts the `hist` largest, best first: no shared-memory
-        // round trip per candidate, and the list comes out ordered.
-        unsigned long long mine[kCandTile / 4];
+      unsigned long long* fresh = wins_s + (size_t)grp * 2 * hist;       // [hist] new keys, [hist] merge output
+      const unsigned long long tau = c0 > 0 ? best[hist - 1] : 0ull;
+      unsigned long long mine[kCandTile / 4];
 #pragma unroll
-        for (int e = 0; e < kCandTile / 4; ++e) {
-          mine[e] = 0ull;
-          if (4 * e < cend) {
+      for (int e = 0; e < kCandTile / 4; ++e) {
+        mine[e] = 0ull;
+        if (4 * e < cend) {
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
-              const int c = 4 * e + cc;
-              const unsigned long long key = score_key(c < cend ? c : 0);
-              if (cc == t && c < cend) mine[e] = key;
-            }
+          for (int cc = 0; cc < 4; ++cc) {
+            const int c = 4 * e + cc;
+            const unsigned long long key = score_key(c < cend ? c : 0);
+            if (cc == t && c < cend && key > tau) mine[e] = key;
           }
-        }
-        for (int r = 0; r < hist; ++r) {
-          unsigned long long top = 0ull;
-          int top_e = 0;
-#pragma unroll
-          for (int e = 0; e < kCandTile / 4; ++e)
-            if (mine[e] > top) { top = mine[e]; top_e = e; }
-          unsigned long long all = top;
-#pragma unroll
-          for (int o = 2; o > 0; o >>= 1) {
-            const unsigned long long other = __shfl_xor_sync(gmask, all, o);
-            all = other > all ? other : all;
-          }
-          if (all == 0ull) break;                             // fewer than hist candidates
-          if (top == all) {                                   // keys are unique: exactly one owner
-#pragma unroll
-            for (int e = 0; e < kCandTile / 4; ++e)
-              if (e == top_e) mine[e] = 0ull;
-            best[r] = all;
-          }
-        }
-        continue;
-      }
-      // Later tiles: the row keeps its `hist` largest keys so far in shared memory (unordered
-      // from here on); a new key replaces the smallest one if it is larger.  0 marks an empty
-      // place.  (Extracting the keys of a later tile from registers like the first one and
-      // inserting only those that beat the list measured slower: 53 against 35 ms on a
-      // 255-candidate window.)
-      unsigned long long tau;
-      int pos;
-      __syncwarp(gmask);
-      list_min(best, hist, t, gmask, tau, pos);
-      for (int c = 0; c < cend; ++c) {
-        const unsigned long long key = score_key(c);
-        if (key > tau) {                                      // same decision in the 4 lanes
-          if (t == 0) best[pos] = key;
-          __syncwarp(gmask);
-          list_min(best, hist, t, gmask, tau, pos);
         }
       }
-    }
-  }
-  __syncthreads();
-  // order every row's list: rank 0 = largest key (repeated arg-max), into the same place;
-  // a single candidate tile left the lists ordered already
-  if (max_cand > kCandTile) {
-    unsigned long long* wins = wins_s + grp * hist;
-    for (int row = grp; row < nrows; row += kGateGroups) {
-      unsigned long long* best = best_s + (size_t)row * hist;
-      for (int i = t; i < hist; i += 4) wins[i] = 0ull;
-      __syncwarp(gmask);
-      for (int r = 0; r < hist; ++r) {
-        unsigned long long mine = 0ull;
-        int mine_i = -1;
-        for (int i = t; i < hist; i += 4) {
-          const unsigned long long kk = best[i];
-          if (kk > mine) { mine = kk; mine_i = i; }
-        }
-        unsigned long long top = mine;
+      unsigned long long* dst = c0 > 0 ? fresh : best;
+      int n_new = 0;
+      for (; n_new < hist; ++n_new) {
+        unsigned long long top = 0ull;
+        int top_e = 0;
+#pragma unroll
+        for (int e = 0; e < kCandTile / 4; ++e)
+          if (mine[e] > top) { top = mine[e]; top_e = e; }
+        unsigned long long all = top;
 #pragma unroll
         for (int o = 2; o > 0; o >>= 1) {
-          const unsigned long long other = __shfl_xor_sync(gmask, top, o);
-          top = other > top ? other : top;
+          const unsigned long long other = __shfl_xor_sync(gmask, all, o);
+          all = other > all ? other : all;
         }
-        if (top == 0ull) break;                               // fewer than hist candidates
-        if (mine == top) {                                    // keys are unique: exactly one owner
-          best[mine_i] = 0ull;
-          wins[r] = top;
+        if (all == 0ull) break;                               // nothing left
+        if (top == all) {                                     // keys are unique: exactly one owner
+#pragma unroll
+          for (int e = 0; e < kCandTile / 4; ++e)
+            if (e == top_e) mine[e] = 0ull;
+          dst[n_new] = all;
+        }
+      }
+      if (c0 > 0 && n_new > 0) {
+        // merge the two ordered lists (every lane follows the same steps, lane 0 writes)
+        __syncwarp(gmask);
+        unsigned long long a = best[0], b = fresh[0];
+        int ia = 0, ib = 0;
+        for (int o = 0; o < hist; ++o) {
+          const bool take = b > a;
+          if (t == 0) fresh[hist + o] = take ? b : a;
+          if (take) { ++ib; b = ib < n_new ? fresh[ib] : 0ull; }
+          else      { ++ia; a = ia < hist ? best[ia] : 0ull; }
         }
         __syncwarp(gmask);
+        for (int i = t; i < hist; i += 4) best[i] = fresh[hist + i];
+        __syncwarp(gmask);
       }
-      __syncwarp(gmask);
-      for (int i = t; i < hist; i += 4) best[i] = wins[i];
-      __syncwarp(gmask);
     }
   }
   __syncthreads();
@@ -364,7 +312,7 @@ gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__
 }
 
 static size_t gate_smem_bytes(const Params& p) {
-  return (size_t)kCandTile * (p.D / 4) * sizeof(float4) + (size_t)kGateGroups * p.hist * 8 +
+  return (size_t)kCandTile * (p.D / 4) * sizeof(float4) + (size_t)kGateGroups * 2 * p.hist * 8 +
          (size_t)kGateRows * p.hist * 8 + (size_t)p.mc * 4;
 }
 
