@@ -51,6 +51,31 @@ def test_problem_check_codes(lib):
     assert b"topk" in lib.moba_b200_strerror(-5)
 
 
+def test_head_dims_and_dtypes_accepted(lib):
+    for d in (64, 96, 256):                                   # the mma.sync dense stage
+        stride = dict(q_stride_token=8 * d, q_stride_head=d, k_stride_token=8 * d, k_stride_head=d,
+                      v_stride_token=8 * d, v_stride_head=d, o_stride_token=8 * d, o_stride_head=d)
+        assert lib.moba_problem_check(C.byref(_problem(head_dim=d, attend_impl=1, **stride))) == 0
+        assert lib.moba_problem_check(C.byref(_problem(head_dim=d, attend_impl=0, **stride))) == -2
+    assert lib.moba_problem_check(C.byref(_problem(head_dim=32, attend_impl=1))) == -2
+    assert lib.moba_problem_check(C.byref(_problem(dtype=1))) == 0                           # fp16
+    assert lib.moba_problem_check(C.byref(_problem(dtype=2))) == -2
+    assert lib.moba_problem_check(C.byref(_problem(reserved=1))) == -2
+
+
+def test_backward_argument_checks(lib):
+    need = C.c_size_t(0)
+    assert lib.moba_backward_workspace_size(C.byref(_problem(attend_impl=1)), C.byref(need)) == 0
+    fwd = C.c_size_t(0)
+    assert lib.moba_workspace_size(C.byref(_problem(attend_impl=1)), C.byref(fwd)) == 0
+    assert need.value == fwd.value + 2 * 4096 * 8 * 4                                        # + delta and lse per row
+    assert lib.moba_backward_workspace_size(C.byref(_problem(q_token_begin=0, q_tokens=512)), C.byref(need)) == -2
+    wide = dict(q_stride_token=2048, q_stride_head=256, k_stride_token=2048, k_stride_head=256,
+                v_stride_token=2048, v_stride_head=256, o_stride_token=2048, o_stride_head=256)
+    assert lib.moba_backward_workspace_size(C.byref(_problem(head_dim=256, attend_impl=1, **wide)), C.byref(need)) == -2
+    assert lib.moba_backward(C.byref(_problem()), *([None] * 12), 0, None) == -4             # null pointers
+
+
 def test_dims_follow_reference_formulas(lib):
     d = _lib.Dims()
     assert lib.moba_problem_dims(C.byref(_problem()), C.byref(d)) == 0
