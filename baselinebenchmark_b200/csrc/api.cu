@@ -26,8 +26,8 @@ int check_problem(const moba_problem_t* p) {
   if (p->topk < 1 || p->topk > kMaxTopk) return MOBA_E_TOPK;               // :432-437
   if (p->head_dim > 256) return MOBA_E_SHAPE;                              // :445-446
   if (p->head_dim != 64 && p->head_dim != 96 && p->head_dim != 128 && p->head_dim != 256) return MOBA_E_UNSUPPORTED;
-  // the tcgen05 dense stage is built for head_dim 128; other sizes run the mma.sync one
-  if (p->attend_impl == MOBA_ATTEND_TCGEN05 && p->head_dim != kHeadDim) return MOBA_E_UNSUPPORTED;
+  // the tcgen05 dense stage is built for head_dim 64 and 128; other sizes run the mma.sync one
+  if (p->attend_impl == MOBA_ATTEND_TCGEN05 && p->head_dim != 64 && p->head_dim != 128) return MOBA_E_UNSUPPORTED;
   if (p->num_q_heads / p->num_kv_heads > 128) return MOBA_E_UNSUPPORTED;
   if (p->attend_impl != MOBA_ATTEND_TCGEN05 && p->attend_impl != MOBA_ATTEND_MMA_SYNC) return MOBA_E_UNSUPPORTED;
   if ((p->dtype != MOBA_DTYPE_BF16 && p->dtype != MOBA_DTYPE_FP16) || p->reserved != 0) return MOBA_E_UNSUPPORTED;
@@ -185,7 +185,7 @@ const char* moba_b200_strerror(int code) {
   switch (code) {
     case MOBA_OK: return "ok";
     case MOBA_E_SHAPE: return "q, k, v, cu_seqlens or the integer arguments have an invalid shape or value";
-    case MOBA_E_UNSUPPORTED: return "configuration outside this build (bf16 or fp16; head_dim 64, 96, 128 or 256, tcgen05 dense stage at 128 only)";
+    case MOBA_E_UNSUPPORTED: return "configuration outside this build (bf16 or fp16; head_dim 64, 96, 128 or 256, tcgen05 dense stage at 64 and 128 only)";
     case MOBA_E_WORKSPACE: return "workspace is null or too small";
     case MOBA_E_NULL: return "a required pointer is null";
     case MOBA_E_TOPK: return "moba_topk must be in 1..64";

@@ -46,7 +46,7 @@ constexpr int kTileBytes = 2 * kHalfBytes;
 constexpr uint32_t kTmemCols = 512;
 
 template <bool kHalf> constexpr uint32_t kIdescQK = idesc_16_f32(kHalf, 128, kBN, 0, 0);
-template <bool kHalf> constexpr uint32_t kIdescPV = idesc_16_f32(kHalf, 128, kHeadDim, 0, 1);
+template <bool kHalf, int D> constexpr uint32_t kIdescPV = idesc_16_f32(kHalf, 128, D, 0, 1);
 
 enum { ST_OK = 0, ST_PRODUCER = 1, ST_MMA = 2, ST_SOFTMAX = 3 };
 
@@ -148,7 +148,7 @@ __device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs&
     c.qoff[slot][r] = off;
     if (e >= 0) {                                            // the gather of the next item then hits L2
       asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + off));
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + off + 64));
+      if (p.D > 64) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + off + 64));
     }
   }
   __syncwarp();
@@ -158,29 +158,30 @@ __device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs&
 // Common head of an item, executed by all 384 threads: take the prefetched item
 // of slot `slot`; the softmax warps (kGather) gather its Q rows into the two swizzled Q tiles.  Returns
 // false when the queue is empty (or the kernel is aborting).
-template <bool kGather>
+template <bool kGather, int D>
 __device__ __forceinline__ bool next_item(const KernelArgs& a, Ctrl& c, unsigned char* smem, int slot, Item& it) {
   __syncthreads();                         // every role has finished the previous item; slot is filled
   if (c.done[slot]) return false;
   it = c.item[slot];
   const int32_t* entry = c.entry[slot];
   const int64_t* qoff = c.qoff[slot];
-  // gather Q rows into two [2][128][64] blocks with the 128-byte swizzle TMA would produce;
-  // the 256 softmax threads do it, each with its 16 loads in flight at once
+  // gather Q rows into two tiles of D/64 [128][64] blocks with the 128-byte swizzle TMA would
+  // produce; the 256 softmax threads do it, each with its D/8 loads in flight at once
   if (kGather) {
+    constexpr int kChunks = D / 8;                  // 16-byte pieces of a row
     const int t = threadIdx.x - 128;
-    uint4 val[16];
+    uint4 val[kChunks];
 #pragma unroll
-    for (int u = 0; u < 16; ++u) {
+    for (int u = 0; u < kChunks; ++u) {
       const int i = t + u * 256;
-      const int r = i >> 4, ch = i & 15;
+      const int r = i / kChunks, ch = i % kChunks;
       val[u] = make_uint4(0, 0, 0, 0);
       if (entry[r] >= 0) val[u] = __ldg(reinterpret_cast<const uint4*>(a.q + qoff[r] + ch * 8));
     }
 #pragma unroll
-    for (int u = 0; u < 16; ++u) {
+    for (int u = 0; u < kChunks; ++u) {
       const int i = t + u * 256;
-      const int r = i >> 4, ch = i & 15;
+      const int r = i / kChunks, ch = i % kChunks;
       const uint32_t dst = (uint32_t)((r >> 7) * kTileBytes + (ch >> 3) * kHalfBytes + (r & 127) * 128 +
                                       (((ch & 7) ^ (r & 7)) << 4));
       *reinterpret_cast<uint4*>(smem + dst) = val[u];
@@ -193,7 +194,7 @@ __device__ __forceinline__ bool next_item(const KernelArgs& a, Ctrl& c, unsigned
 
 // One softmax step of one row: S (128 fp32 columns of this thread's TMEM lane)
 // -> P (bf16, written over the first 64 columns), running max / sum updated.
-template <bool kMasked, bool kHalf>
+template <bool kMasked, bool kHalf, int D>
 __device__ __forceinline__ void softmax_row(uint32_t tS, uint32_t tO, int j, int key0, int lim, float sl2,
                                             float& m_ref, float& l, const KernelArgs& a, int n) {
   uint32_t v[128];
@@ -220,7 +221,7 @@ __device__ __forceinline__ void softmax_row(uint32_t tS, uint32_t tO, int j, int
     if (j > 0) {
       uint32_t o[32];
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = 0; ch < D / 32; ++ch) {
         tmem_ld32(tO + ch * 32, o);
         tmem_wait_ld();
 #pragma unroll
@@ -269,25 +270,25 @@ __device__ __forceinline__ uint64_t desc64(uint32_t lo) { return ((uint64_t)kDes
 
 // S_X = Q_X . K^T for one K tile: 8 k-steps of 16 dims; X and STAGE are compile-time
 // so every descriptor is the base word plus an immediate.
-template <int X, int STAGE, bool kHalf>
+template <int X, int STAGE, bool kHalf, int D>
 __device__ __forceinline__ void issue_qk(uint32_t tmem, uint32_t dq, uint32_t dk) {
 #pragma unroll
-  for (int ks = 0; ks < 8; ++ks) {
+  for (int ks = 0; ks < D / 16; ++ks) {
     constexpr int kBlock = kHalfBytes >> 4, kTile = kTileBytes >> 4;
     const uint32_t koff = (uint32_t)((ks >> 2) * kBlock + (ks & 3) * 2);
     mma_ss(tmem + X * kBN, desc64(dq + X * kTile + koff), desc64(dk + STAGE * kTile + koff), kIdescQK<kHalf>, ks > 0);
   }
 }
 // O_X (+)= P_X . V for one V tile: 8 k-steps of 16 keys, P read from tensor memory.
-template <int X, int STAGE, bool kHalf>
+template <int X, int STAGE, bool kHalf, int D>
 __device__ __forceinline__ void issue_pv(uint32_t tmem, uint32_t dv, bool first) {
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks)
-    mma_ts(tmem + 256 + X * kHeadDim, tmem + X * kBN + ks * 8,
-           desc64(dv + STAGE * (kTileBytes >> 4) + ks * (2048 >> 4)), kIdescPV<kHalf>, (!first) || ks > 0);
+    mma_ts(tmem + 256 + X * 128, tmem + X * kBN + ks * 8,
+           desc64(dv + STAGE * (kTileBytes >> 4) + ks * (2048 >> 4)), kIdescPV<kHalf, D>, (!first) || ks > 0);
 }
 
-template <bool kHalf>
+template <bool kHalf, int D>
 __global__ void __launch_bounds__(kThreads, 1)
 attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
                   const __grid_constant__ CUtensorMap tmap_v, const KernelArgs a) {
@@ -346,7 +347,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     for (int n = 0;; ++n) {
       // warp 2 runs one item ahead: it fills slot n & 1 while the others still work on item n - 1
       if (warp == 2) prefetch_item(p, a, c, n & 1, n_routed, n_items);
-      if (!next_item<false>(a, c, smem, n & 1, it)) break;
+      if (!next_item<false, D>(a, c, smem, n & 1, it)) break;
       const int ntiles = (it.kv_len + kBN - 1) / kBN;
       if (warp == 0 && lane == 0) {
         // K and V tile `j` of item `w` into the next free stages; false after a timeout
@@ -356,18 +357,18 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
             const uint32_t s = kc & 1;
             if (!mbar_wait(smem_u32(&c.k_empty[s]), ((kc >> 1) & 1) ^ 1)) return false;
             const uint32_t bar = smem_u32(&c.k_full[s]);
-            mbar_expect_tx(bar, kTileBytes);
+            mbar_expect_tx(bar, (D / 64) * kHalfBytes);
             tma_load_3d(sK + s * kTileBytes, &tmap_k, bar, 0, w.kv_head, tok);
-            tma_load_3d(sK + s * kTileBytes + kHalfBytes, &tmap_k, bar, 64, w.kv_head, tok);
+            if (D > 64) tma_load_3d(sK + s * kTileBytes + kHalfBytes, &tmap_k, bar, 64, w.kv_head, tok);
             ++kc;
           }
           {
             const uint32_t s = vc & 1;
             if (!mbar_wait(smem_u32(&c.v_empty[s]), ((vc >> 1) & 1) ^ 1)) return false;
             const uint32_t bar = smem_u32(&c.v_full[s]);
-            mbar_expect_tx(bar, kTileBytes);
+            mbar_expect_tx(bar, (D / 64) * kHalfBytes);
             tma_load_3d(sV + s * kTileBytes, &tmap_v, bar, 0, w.kv_head, tok);
-            tma_load_3d(sV + s * kTileBytes + kHalfBytes, &tmap_v, bar, 64, w.kv_head, tok);
+            if (D > 64) tma_load_3d(sV + s * kTileBytes + kHalfBytes, &tmap_v, bar, 64, w.kv_head, tok);
             ++vc;
           }
           return true;
@@ -400,8 +401,8 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         if (ok) {
           tc_fence_after();
           if (el) {
-            if (kc & 1) { issue_qk<0, 1, kHalf>(tm, dq, dk); tc_commit(smem_u32(&c.s_full[0])); issue_qk<1, 1, kHalf>(tm, dq, dk); }
-            else        { issue_qk<0, 0, kHalf>(tm, dq, dk); tc_commit(smem_u32(&c.s_full[0])); issue_qk<1, 0, kHalf>(tm, dq, dk); }
+            if (kc & 1) { issue_qk<0, 1, kHalf, D>(tm, dq, dk); tc_commit(smem_u32(&c.s_full[0])); issue_qk<1, 1, kHalf, D>(tm, dq, dk); }
+            else        { issue_qk<0, 0, kHalf, D>(tm, dq, dk); tc_commit(smem_u32(&c.s_full[0])); issue_qk<1, 0, kHalf, D>(tm, dq, dk); }
             tc_commit(smem_u32(&c.s_full[1]));
             tc_commit(smem_u32(&c.k_empty[kc & 1]));
           }
@@ -423,7 +424,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
           pph0 ^= 1;
           tc_fence_after();
           if (lane == 0) TL_STAMP(a, n, j, 0);               // P_A seen
-          if (el) { if (vs) issue_pv<0, 1, kHalf>(tm, dv, j == 0); else issue_pv<0, 0, kHalf>(tm, dv, j == 0); }
+          if (el) { if (vs) issue_pv<0, 1, kHalf, D>(tm, dv, j == 0); else issue_pv<0, 0, kHalf, D>(tm, dv, j == 0); }
           __syncwarp();
           if (lane == 0) TL_STAMP(a, n, j, 1);               // PV_A issued
           if (more) {
@@ -433,7 +434,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
             if (lane == 0) TRACE_ADD(a, 2, t_k);
             tc_fence_after();
             if (el) {
-              if (ks) issue_qk<0, 1, kHalf>(tm, dq, dk); else issue_qk<0, 0, kHalf>(tm, dq, dk);
+              if (ks) issue_qk<0, 1, kHalf, D>(tm, dq, dk); else issue_qk<0, 0, kHalf, D>(tm, dq, dk);
               tc_commit(smem_u32(&c.s_full[0]));
             }
           } else if (el) {
@@ -449,10 +450,10 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
           tc_fence_after();
           if (lane == 0) TL_STAMP(a, n, j, 3);               // P_B seen
           if (el) {
-            if (vs) issue_pv<1, 1, kHalf>(tm, dv, j == 0); else issue_pv<1, 0, kHalf>(tm, dv, j == 0);
+            if (vs) issue_pv<1, 1, kHalf, D>(tm, dv, j == 0); else issue_pv<1, 0, kHalf, D>(tm, dv, j == 0);
             tc_commit(smem_u32(&c.v_empty[vs]));
             if (more) {
-              if (ks) issue_qk<1, 1, kHalf>(tm, dq, dk); else issue_qk<1, 0, kHalf>(tm, dq, dk);
+              if (ks) issue_qk<1, 1, kHalf, D>(tm, dq, dk); else issue_qk<1, 0, kHalf, D>(tm, dq, dk);
               tc_commit(smem_u32(&c.s_full[1]));
               tc_commit(smem_u32(&c.k_empty[ks]));
             } else {
@@ -476,14 +477,14 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     const int row = (warp & 3) * 32 + lane;              // row inside the tile = TMEM lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + lane_base + x * kBN;
-    const uint32_t tO = tmem + lane_base + 256 + x * kHeadDim;
-    const float sl2 = rsqrtf((float)kHeadDim) * 1.4426950408889634f;
+    const uint32_t tO = tmem + lane_base + 256 + x * 128;
+    const float sl2 = rsqrtf((float)D) * 1.4426950408889634f;
     uint32_t sph = 0, oph = 0;                           // s_full / o_full phases of this tile
 #ifdef MOBA_TC5_TRACE
     long long t_next = clock64();
     const long long t_kernel = t_next;
 #endif
-    for (int n = 0; next_item<true>(a, c, smem, n & 1, it); ++n) {
+    for (int n = 0; next_item<true, D>(a, c, smem, n & 1, it); ++n) {
 #ifdef MOBA_TC5_TRACE
       if (threadIdx.x == 128) { TRACE_ADD(a, 8, t_next); atomicAdd(TRACE_BASE(a) + 9, 1ull); }
 #endif
@@ -506,8 +507,8 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         const int key0 = j * kBN;
         const bool masked = key0 + kBN > it.kv_len ||
                             (it.causal && it.kv_tok0 + key0 + kBN - 1 > it.tok0 + x * kTileM);
-        if (masked) softmax_row<true, kHalf>(tS, tO, j, key0, lim, sl2, m_ref, l, a, n);
-        else softmax_row<false, kHalf>(tS, tO, j, key0, lim, sl2, m_ref, l, a, n);
+        if (masked) softmax_row<true, kHalf, D>(tS, tO, j, key0, lim, sl2, m_ref, l, a, n);
+        else softmax_row<false, kHalf, D>(tS, tO, j, key0, lim, sl2, m_ref, l, a, n);
         tc_fence_before();
         mbar_arrive(smem_u32(&c.p_full[x]));
         if (threadIdx.x == 128) TL_STAMP(a, n, j, 6);        // P_A arrived
@@ -528,7 +529,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         unsigned char* stage = smem + x * kTileBytes + (warp & 3) * 8192;
         uint32_t v[32];
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch = 0; ch < D / 32; ++ch) {
           tmem_ld32(tO + ch * 32, v);
           tmem_wait_ld();
 #pragma unroll
@@ -542,7 +543,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
             const int rl = i * 4 + (lane >> 3), c16 = lane & 7;
             const int32_t er = __shfl_sync(0xffffffffu, e, rl);
             const float4 val = *reinterpret_cast<const float4*>(stage + rl * 144 + c16 * 16);
-            if (er >= 0) *reinterpret_cast<float4*>(a.partial_out + (int64_t)er * kHeadDim + ch * 32 + c16 * 4) = val;
+            if (er >= 0) *reinterpret_cast<float4*>(a.partial_out + (int64_t)er * D + ch * 32 + c16 * 4) = val;
           }
           __syncwarp();
         }
@@ -592,10 +593,10 @@ EncodeTiledFn encode_fn() {
 }
 
 // [T, Hkv, D] bf16 with element strides (st, sh, 1): boxes of 128 tokens x 1 head x 64 dims
-bool make_kv_map(CUtensorMap* m, bool fp16, const __nv_bfloat16* base, int64_t T, int Hkv, int64_t st, int64_t sh) {
+bool make_kv_map(CUtensorMap* m, bool fp16, int D, const __nv_bfloat16* base, int64_t T, int Hkv, int64_t st, int64_t sh) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return false;
-  const cuuint64_t dims[3] = {(cuuint64_t)kHeadDim, (cuuint64_t)Hkv, (cuuint64_t)T};
+  const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)Hkv, (cuuint64_t)T};
   const cuuint64_t strides[2] = {(cuuint64_t)sh * 2, (cuuint64_t)st * 2};
   const cuuint32_t box[3] = {64, 1, (cuuint32_t)kBN};
   const cuuint32_t estr[3] = {1, 1, 1};
@@ -612,9 +613,11 @@ cudaError_t launch_attend_tc5(const Params& p, const __nv_bfloat16* q, const __n
                               const int32_t* row_list, float* partial_out, float* partial_lse,
                               int32_t* work_counter, int32_t* status, cudaStream_t st) {
   CUtensorMap mk, mv;
-  if (!make_kv_map(&mk, p.fp16 != 0, k, p.T, p.Hkv, p.sk_t, p.sk_h) || !make_kv_map(&mv, p.fp16 != 0, v, p.T, p.Hkv, p.sv_t, p.sv_h))
+  if (!make_kv_map(&mk, p.fp16 != 0, p.D, k, p.T, p.Hkv, p.sk_t, p.sk_h) || !make_kv_map(&mv, p.fp16 != 0, p.D, v, p.T, p.Hkv, p.sv_t, p.sv_h))
     return cudaErrorNotSupported;
-  auto kernel = p.fp16 ? attend_tc5_kernel<true> : attend_tc5_kernel<false>;
+  if (p.D != 64 && p.D != 128) return cudaErrorInvalidValue;
+  auto kernel = p.D == 128 ? (p.fp16 ? attend_tc5_kernel<true, 128> : attend_tc5_kernel<false, 128>)
+                           : (p.fp16 ? attend_tc5_kernel<true, 64> : attend_tc5_kernel<false, 64>);
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   if (e != cudaSuccess) return e;
   int dev = 0, sms = 148;

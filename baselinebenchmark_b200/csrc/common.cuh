@@ -10,7 +10,7 @@
 
 namespace moba {
 
-constexpr int kHeadDim = 128;            // head dim of the tcgen05 dense stage (others: mma.sync stage)
+constexpr int kHeadDim = 128;            // largest head dim of the tcgen05 dense stage (64 and 128; others: mma.sync stage)
 constexpr int kMeanLanes = 32;           // row accumulators of a chunk mean
 constexpr int kMaxTopk = 64;             // parallel.py:436
 

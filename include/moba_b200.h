@@ -18,7 +18,7 @@
  *     (the head dims of the reference's benchmark suite, moba_compare.py:63, :70),
  *     innermost dimension contiguous; token and head strides are given in
  *     elements (the reference kernels also take strides, attention.py:431-439).
- *     The tcgen05 dense stage exists for head_dim 128; the other head dims run
+ *     The tcgen05 dense stage exists for head_dim 64 and 128; 96 and 256 run
  *     the mma.sync dense stage (attend_impl = MOBA_ATTEND_MMA_SYNC).  Anything
  *     else returns MOBA_E_UNSUPPORTED: there is no fallback path.
  */
@@ -46,7 +46,7 @@ enum {
 
 /* Which implementation of the dense stage moba_attend/moba_forward run. */
 enum {
-  MOBA_ATTEND_TCGEN05 = 0,  /* tcgen05.mma + TMEM accumulators + TMA K/V tiles (head_dim 128) */
+  MOBA_ATTEND_TCGEN05 = 0,  /* tcgen05.mma + TMEM accumulators + TMA K/V tiles (head_dim 64, 128) */
   MOBA_ATTEND_MMA_SYNC = 1  /* legacy mma.sync tensor path, kept as cross-check  */
 };
 

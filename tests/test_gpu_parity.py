@@ -147,7 +147,7 @@ def test_routing_bit_exact(case, dtype):
 @pytest.mark.parametrize("case", HEAD_DIM_CASES, ids=lambda c: c[0])
 def test_other_head_dims(case, dtype):
     """head_dim 64, 96 and 256: chunk means and selection bit-exact, output within tolerance
-    (these head dims run the mma.sync dense stage)."""
+    (64 on both dense stages, 96 and 256 on the mma.sync one)."""
     name, d, lens, hq, hkv, chunk, topk = case
     q, k, v, cu = _case_inputs(lens, hq, hkv, chunk, zlib.crc32(name.encode()) % 1000, dtype=dtype, d=d)
     max_seqlen = max(lens)
@@ -155,20 +155,22 @@ def test_other_head_dims(case, dtype):
     qd, kd, vd = G.to_dev(q, k, v)
     cud = torch.from_numpy(cu).cuda()
     prob, _ = G.problem_for(qd, kd, vd, cud, max_seqlen, chunk, topk)
-    assert prob.attend_impl == _lib.ATTEND_MMA_SYNC
+    assert prob.attend_impl == (_lib.ATTEND_TCGEN05 if d == 64 else _lib.ATTEND_MMA_SYNC)
     cu_chunk_o, _, valid_o, _ = O.chunk_slots(cu, max_seqlen, chunk)
     means_o = O.chunk_means(k, cu_chunk_o, valid_o, chunk)
     m = G.means(prob, kd, cud)
     assert torch.equal(m.cpu().view(torch.int16), means_o.view(torch.int16))
-    out, lse, sel = parallel.moba_forward(qd, kd, vd, cud, max_seqlen, chunk, topk, return_lse=True,
-                                          return_selected=True)
-    torch.cuda.synchronize()
-    np.testing.assert_array_equal(sel.cpu().numpy(), sel_o)
-    mx, mean = G.rel_stats(out.cpu(), ref)
-    assert mx < MAX_ABS and mean < MEAN_ABS, (mx, mean)
-    assert (lse.cpu() - ref_lse).abs().max().item() < 2e-3
-    with pytest.raises(_lib.MobaError):                       # the tcgen05 stage is built for head_dim 128
-        parallel.moba_forward(qd, kd, vd, cud, max_seqlen, chunk, topk, attend_impl=_lib.ATTEND_TCGEN05)
+    for impl in ((_lib.ATTEND_TCGEN05, _lib.ATTEND_MMA_SYNC) if d == 64 else (_lib.ATTEND_MMA_SYNC,)):
+        out, lse, sel = parallel.moba_forward(qd, kd, vd, cud, max_seqlen, chunk, topk, return_lse=True,
+                                              return_selected=True, attend_impl=impl)
+        torch.cuda.synchronize()
+        np.testing.assert_array_equal(sel.cpu().numpy(), sel_o)
+        mx, mean = G.rel_stats(out.cpu(), ref)
+        assert mx < MAX_ABS and mean < MEAN_ABS, (impl, mx, mean)
+        assert (lse.cpu() - ref_lse).abs().max().item() < 2e-3
+    if d != 64:
+        with pytest.raises(_lib.MobaError):                   # the tcgen05 stage is built for head_dim 64 and 128
+            parallel.moba_forward(qd, kd, vd, cud, max_seqlen, chunk, topk, attend_impl=_lib.ATTEND_TCGEN05)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -405,7 +407,7 @@ def test_public_operator_names():
     assert native_moba._supported(qd)
     assert native_moba._supported(qd.half())
     assert pkg.parallel_moba(qd.half(), kd.half(), vd.half(), cud, 512, 128, 3).dtype == torch.float16
-    assert not native_moba._supported(qd[..., :64])
+    assert native_moba._supported(qd[..., :64]) and not native_moba._supported(qd[..., :96])
     assert pkg.parallel_moba(qd[..., :64], kd[..., :64], vd[..., :64], cud, 512, 128, 3).shape == qd[..., :64].shape
     with pytest.raises(NotImplementedError):
         pkg.parallel_moba(qd[..., :32], kd[..., :32], vd[..., :32], cud, 512, 128, 3)
