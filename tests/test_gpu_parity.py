@@ -638,3 +638,28 @@ def test_reference_outputs_and_gradients_through_cuda(path, dtype):
         err = (got.double().cpu() - ref).abs()
         scale = ref.abs().max().item()
         assert err.max().item() < 0.04 * scale and err.mean().item() < 0.004 * scale, (name, err.max().item(), scale)
+
+
+def test_forward_is_capturable_in_a_cuda_graph():
+    """The reference's inference path reads nothing back to the host so that it can be captured
+    (parallel.py:270-274); the same holds here: capture once, replay on new inputs."""
+    q, k, v, cu = _case_inputs((700, 333, 1290), 8, 2, 128, seed=21)
+    q2, k2, v2, _ = _case_inputs((700, 333, 1290), 8, 2, 128, seed=22)
+    cud = torch.from_numpy(cu).cuda()
+    sq, sk, sv = q.cuda(), k.cuda(), v.cuda()                 # static input buffers of the graph
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side), torch.no_grad():
+        for _ in range(2):                                      # warm-up: workspace, kernel attributes
+            parallel.parallel_moba(sq, sk, sv, cud, 1290, 128, 4)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph), torch.no_grad():
+        out = parallel.parallel_moba(sq, sk, sv, cud, 1290, 128, 4)
+    for a, b, c in ((q, k, v), (q2, k2, v2)):
+        sq.copy_(a); sk.copy_(b); sv.copy_(c)
+        graph.replay()
+        torch.cuda.synchronize()
+        with torch.no_grad():
+            eager = parallel.parallel_moba(sq, sk, sv, cud, 1290, 128, 4)
+        assert torch.equal(out, eager)
