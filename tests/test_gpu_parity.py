@@ -414,11 +414,12 @@ def test_public_operator_names():
 
 
 @pytest.mark.parametrize("impl", IMPLS)
-def test_query_window_equals_full_run(impl):
+@pytest.mark.parametrize("d,dtype", [(128, torch.bfloat16), (64, torch.float16)], ids=["d128_bf16", "d64_fp16"])
+def test_query_window_equals_full_run(impl, d, dtype):
     """Context-parallel building block: the operator run on a chunk-aligned query
     window, with K/V of the whole sequence, returns exactly the rows of the full run."""
     lens = (2048, 1280)
-    q, k, v, cu = _case_inputs(lens, 8, 2, 128, seed=21)
+    q, k, v, cu = _case_inputs(lens, 8, 2, 128, seed=21, dtype=dtype, d=d)
     qd, kd, vd = G.to_dev(q, k, v)
     cud = torch.from_numpy(cu).cuda()
     full, full_lse, full_sel = parallel.moba_forward(qd, kd, vd, cud, 2048, 128, 4, return_lse=True,
@@ -499,11 +500,13 @@ def test_config4_window_sampled():
     assert diff.max().item() < MAX_ABS and diff.mean().item() < MEAN_ABS
 
 
-def test_bounded_workspace_runs_head_groups():
+@pytest.mark.parametrize("d,dtype", [(128, torch.bfloat16), (64, torch.float16), (96, torch.bfloat16)],
+                         ids=["d128_bf16", "d64_fp16", "d96_bf16"])
+def test_bounded_workspace_runs_head_groups(d, dtype):
     """A workspace below the one-pass size makes the library process kv-head groups in turn;
     results, LSE and selection are the bits of the one-pass run."""
     import ctypes as C
-    q, k, v, cu = _case_inputs((1536, 1000), 16, 4, 128, seed=41)
+    q, k, v, cu = _case_inputs((1536, 1000), 16, 4, 128, seed=41, dtype=dtype, d=d)
     qd, kd, vd = G.to_dev(q, k, v)
     cud = torch.from_numpy(cu).cuda()
     ref, ref_lse, ref_sel = parallel.moba_forward(qd, kd, vd, cud, 1536, 128, 4, return_lse=True, return_selected=True)
