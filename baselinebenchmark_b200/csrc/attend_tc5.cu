@@ -48,6 +48,8 @@ constexpr uint32_t kTmemCols = 512;
 template <bool kHalf> constexpr uint32_t kIdescQK = idesc_16_f32(kHalf, 128, kBN, 0, 0);
 template <bool kHalf, int D> constexpr uint32_t kIdescPV = idesc_16_f32(kHalf, 128, D, 0, 1);
 
+constexpr int kPrefixCache = 6144;       // ints of tile_prefix kept in shared memory (24 KB)
+
 enum { ST_OK = 0, ST_PRODUCER = 1, ST_MMA = 2, ST_SOFTMAX = 3 };
 
 struct Ctrl {
@@ -62,6 +64,9 @@ struct Ctrl {
   int32_t done[2];
   int64_t qoff[2][2 * kTileM];
   int32_t entry[2][2 * kTileM];
+  // tile_prefix copied once per CTA when it fits: decoding an item searches it, and with
+  // short items (small chunks) eleven dependent global loads per item were the critical path
+  int32_t prefix_cache[kPrefixCache];
 };
 
 constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + 6 * kTileBytes + sizeof(Ctrl);
@@ -125,7 +130,8 @@ __device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs&
     if (lane == 0) idx = c.abort ? 0x7fffffff : atomicAdd(a.work_counter, 1);
     idx = __shfl_sync(0xffffffffu, idx, 0);
     if (idx >= n_items) { done = 1; break; }
-    it = decode_item(p, idx, n_routed, 2 * kTileM, a.cu, a.list_counts, a.list_offsets, a.tile_prefix);
+    it = decode_item(p, idx, n_routed, 2 * kTileM, a.cu, a.list_counts, a.list_offsets,
+                     p.lists < kPrefixCache ? c.prefix_cache : a.tile_prefix);
     if (it.valid) break;
   }
   if (lane == 0) { c.item[slot] = it; c.done[slot] = done; }
@@ -321,6 +327,8 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     tmem_alloc(smem_u32(&c.tmem_slot), kTmemCols);
     tmem_relinquish();
   }
+  if (p.hist > 0 && p.lists < kPrefixCache)
+    for (int i = threadIdx.x; i <= (int)p.lists; i += kThreads) c.prefix_cache[i] = a.tile_prefix[i];
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
