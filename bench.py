@@ -417,6 +417,20 @@ def main():
             "dense_stage_ms": float(st2[3]), "dense_stage_tflops": f2 / (float(st2[3]) * 1e-3) / 1e12,
             "stage_ms": {"means": float(st2[0]), "gate_topk": float(st2[1]), "compact": float(st2[2]),
                          "attend": float(st2[3]), "merge": float(st2[4])}}
+        # the training path on the same configuration: forward with LSE and selection, then moba_backward
+        from baselinebenchmark_b200 import parallel as _par
+        del r2
+        out2, lse2, sel2 = _par.moba_forward(q2, k2, v2, cu2, 32768, 4096, 12, return_lse=True, return_selected=True)
+        dout2 = torch.randn_like(q2)
+        for _ in range(2):
+            _par.moba_backward(q2, k2, v2, cu2, 32768, 4096, 12, out2, lse2, sel2, dout2)
+        b0, b1 = new_events(2)
+        b0.record()
+        for _ in range(3):
+            _par.moba_backward(q2, k2, v2, cu2, 32768, 4096, 12, out2, lse2, sel2, dout2)
+        b1.record()
+        torch.cuda.synchronize()
+        also["configs[2] backward (training path, mma.sync, first version)"] = {"ms_per_call": b0.elapsed_time(b1) / 3}
     barrier()
 
     cpu = None
