@@ -135,26 +135,34 @@ __device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs&
     if (it.valid) break;
   }
   if (lane == 0) { c.item[slot] = it; c.done[slot] = done; }
-  for (int r = lane; !done && r < 2 * kTileM; r += 32) {
-    int32_t e = -1;
-    int64_t off = 0;
-    if (r < it.nrows) {
-      if (it.causal) {
-        const int64_t tl = it.tok0 - p.win_lo + r;            // window-relative token
-        e = (int32_t)((tl * p.Hq + it.head) * p.NP);
-        off = tl * p.sq_t + (int64_t)it.head * p.sq_h;
-      } else {
-        e = a.row_list[it.row_start + r];
+  if (!done) {
+    // the 8 rows of a lane: all row_list loads in flight before any of them is used
+    int32_t ent[2 * kTileM / 32];
+#pragma unroll
+    for (int u = 0; u < 2 * kTileM / 32; ++u) {
+      const int r = lane + 32 * u;
+      ent[u] = -1;
+      if (r < it.nrows) {
+        if (it.causal) ent[u] = (int32_t)(((int64_t)(it.tok0 - p.win_lo + r) * p.Hq + it.head) * p.NP);
+        else ent[u] = __ldg(a.row_list + it.row_start + r);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2 * kTileM / 32; ++u) {
+      const int r = lane + 32 * u;
+      const int32_t e = ent[u];
+      int64_t off = 0;
+      if (e >= 0) {
         const int64_t row = e / p.NP;
         const int64_t t = row / p.Hq;
         off = t * p.sq_t + (row - t * p.Hq) * p.sq_h;
       }
-    }
-    c.entry[slot][r] = e;
-    c.qoff[slot][r] = off;
-    if (e >= 0) {                                            // the gather of the next item then hits L2
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + off));
-      if (p.D > 64) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + off + 64));
+      c.entry[slot][r] = e;
+      c.qoff[slot][r] = off;
+      if (e >= 0) {                                            // the gather of the next item then hits L2
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + off));
+        if (p.D > 64) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + off + 64));
+      }
     }
   }
   __syncwarp();
