@@ -1,5 +1,5 @@
-// C ABI of the MoBA forward (declared in include/moba_b200.h): argument
-// validation, workspace carving and the launch sequence.  Host-side only.
+// C ABI of the MoBA forward and backward (declared in include/moba_b200.h): argument
+// validation, workspace carving and the launch sequences.  Host-side only.
 //
 // Mirrors backends/_mthreads/ops/moba/parallel.py:253-457 of the reference:
 // the checks of parallel_moba (:410-443) and the dataflow of

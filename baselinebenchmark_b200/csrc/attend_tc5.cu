@@ -6,8 +6,10 @@
 //   _varlen_attn_fwd_kernel        backends/_mthreads/ops/moba/attention.py:53-160  (own chunk, causal)
 //   native_moba.routed / MATE FMHA backends/_mthreads/ops/moba/native_moba.py:120-135
 //   _routed_gqa_attn_fwd_kernel    attention.py:610-707                           (selected chunks)
+// Templated on the element type (bf16, fp16) and the head dim (64, 128); buffer
+// strides in shared memory and TMEM are those of head dim 128.
 // Numerics follow attention.py:116-155 (fp32 scores * D^-0.5 * log2 e, P rounded
-// to bf16 before P.V, fp32 accumulation, natural-log LSE); the running maximum is
+// to the input dtype before P.V, fp32 accumulation, natural-log LSE); the running maximum is
 // only refreshed when it grows by more than 8 (factor 256), which changes the
 // rounding pattern but not the value of the softmax.
 //
@@ -24,8 +26,8 @@
 //               warp runs convergent, one elected lane issues; owns the TMEM allocation
 //   warps 4-7   softmax of tile A: one thread per row (TMEM lane)
 //   warps 8-11  softmax of tile B
-//   all warps   gather of the Q rows into 128B-swizzled shared memory
-// TMEM columns: S_A 0-127, S_B 128-255, O_A 256-383, O_B 384-511; the bf16 P
+//   warps 4-11  also gather the Q rows into 128B-swizzled shared memory at the item start
+// TMEM columns: S_A 0-127, S_B 128-255, O_A 256-383, O_B 384-511; the 16-bit P
 // tile overwrites the first 64 columns of its S tile.
 // The tensor core alternates  QK_A(j+1) | PV_B(j) | QK_B(j+1) | PV_A(j+1) ...
 // so that the softmax of one tile runs while the MMAs of the other execute.
