@@ -61,6 +61,19 @@ def attention_flops(seq_lens, hq, d, chunk, topk):
     return 4.0 * d * hq * pairs
 
 
+def gating_roofline(ms, pk):
+    """Gating stage (chunk means + scores + top-k) against the HBM roofline: algorithmic bytes =
+    read Q and K once, write and re-read the chunk means, write the selection."""
+    tokens = SEQS_PER_GPU * SEQ_LEN
+    slots = SEQS_PER_GPU * (SEQ_LEN // CHUNK)
+    nbytes = 2 * tokens * HQ * D + 2 * tokens * HKV * D + 2 * 2 * slots * HKV * D + 4 * (PARTIALS - 1) * HQ * tokens
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"bound": "hbm", "algorithmic_bytes": nbytes, "ms": ms, "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s",
+            "frac": gbs / pk["hbm"],
+            "note": "not HBM bound: the scores run on CUDA cores in a fixed fp32 order so that the selection is "
+                    "reproducible bit for bit"}
+
+
 def peaks():
     f = ROOT / "MEASURED_PEAKS.json"
     if f.exists():
@@ -463,6 +476,7 @@ def main():
                                          "rows x partial results: the traffic is fp32 partial writes and Q gathers"},
             "stage_ms": {"means": float(stage_ms[0]), "gate_topk": float(stage_ms[1]), "compact": float(stage_ms[2]),
                          "attend": float(stage_ms[3]), "merge": float(stage_ms[4])},
+            "gating": gating_roofline(float(stage_ms[0]) + float(stage_ms[1]), pk),
             "cpu_baseline": cpu, "clocks": clocks.summary(), "also": also,
         }
         emit(line)
