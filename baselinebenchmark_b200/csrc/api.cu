@@ -432,20 +432,28 @@ int moba_backward(const moba_problem_t* p, const void* q, const void* k, const v
   const __nv_bfloat16* gb = static_cast<const __nv_bfloat16*>(dout);
   // dout, dq: contiguous [T, Hq, D]; dk, dv: contiguous [T, Hkv, D]
   const int64_t qt = (int64_t)r.Hq * r.D, kt = (int64_t)r.Hkv * r.D, hd = r.D;
+  // dq runs on the tcgen05 path where the forward's dense stage does (the mma.sync kernel
+  // otherwise); dk / dv are mma.sync kernels in both cases
+  const bool dq_tc5 = p->attend_impl == MOBA_ATTEND_TCGEN05 && (r.D == 64 || r.D == 128);
   cudaError_t e;
   if ((e = cudaMemsetAsync(w.list_counts, 0, w.zero_bytes, st)) != cudaSuccess) return (int)e;
   if (r.hist > 0) {
     if ((e = launch_count_lists(r, selected, w.list_counts, st)) != cudaSuccess) return (int)e;
     if ((e = launch_compact(r, cu, selected, w.list_counts, w.list_offsets, w.tile_prefix, w.cursors, w.row_list,
-                            w.partial_lse, kMmaTileRows, st)) != cudaSuccess)
+                            w.partial_lse, dq_tc5 ? kTc5TileRows : kMmaTileRows, st)) != cudaSuccess)
       return (int)e;
   }
   if ((e = launch_bwd_delta(r, static_cast<const __nv_bfloat16*>(out), gb, qt, hd, lse, delta, lse2, st)) != cudaSuccess)
     return (int)e;
-  if ((e = launch_bwd_dq(r, qb, kb, vb, gb, qt, hd, cu, w.list_counts, w.list_offsets, w.tile_prefix, w.row_list, lse2,
-                         delta, w.partial_out, w.work_counter, st)) != cudaSuccess)
-    return (int)e;
-  if ((e = launch_bwd_sum_dq(r, w.partial_out, selected, static_cast<__nv_bfloat16*>(dq), qt, hd, st)) != cudaSuccess)
+  if (dq_tc5)
+    e = launch_bwd_dq_tc5(r, qb, kb, vb, gb, cu, w.list_counts, w.list_offsets, w.tile_prefix, w.row_list, lse2, delta,
+                          w.partial_out, w.work_counter, w.status, st);
+  else
+    e = launch_bwd_dq(r, qb, kb, vb, gb, qt, hd, cu, w.list_counts, w.list_offsets, w.tile_prefix, w.row_list, lse2,
+                      delta, w.partial_out, w.work_counter, st);
+  if (e != cudaSuccess) return (int)e;
+  if ((e = launch_bwd_sum_dq(r, w.partial_out, selected, w.status, static_cast<__nv_bfloat16*>(dq), qt, hd, st)) !=
+      cudaSuccess)
     return (int)e;
   if ((e = launch_bwd_dkdv(r, qb, kb, vb, gb, qt, hd, cu, w.list_counts, w.list_offsets, w.row_list, lse2, delta,
                            static_cast<__nv_bfloat16*>(dk), kt, hd, static_cast<__nv_bfloat16*>(dv), kt, hd,

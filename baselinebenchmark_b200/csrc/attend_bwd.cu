@@ -305,8 +305,10 @@ bwd_dq_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 template <bool kHalf>
 __global__ void __launch_bounds__(256)
 sum_dq_kernel(Params p, const float* __restrict__ partial_dq, const int32_t* __restrict__ selected,
-              __nv_bfloat16* __restrict__ dq, int64_t dq_t, int64_t dq_h) {
+              const int32_t* __restrict__ status, __nv_bfloat16* __restrict__ dq, int64_t dq_t, int64_t dq_h) {
   const int lane = threadIdx.x & 31;
+  // a dq kernel that gave up on a wait leaves a non-zero status: poison the result
+  const bool failed = status != nullptr && *status != 0;
   const int nvec = p.D / 4;
   const int64_t warps = (int64_t)gridDim.x * 8;
   for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < p.rows; row += warps) {
@@ -319,6 +321,7 @@ sum_dq_kernel(Params p, const float* __restrict__ partial_dq, const int32_t* __r
         const float4 x = __ldg(reinterpret_cast<const float4*>(partial_dq + (row * p.NP + j) * p.D) + c);
         acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
       }
+      if (failed) acc.x = acc.y = acc.z = acc.w = __int_as_float(0x7fc00000);
       uint2 pk;
       pk.x = pack2_16<kHalf>(acc.x, acc.y);
       pk.y = pack2_16<kHalf>(acc.z, acc.w);
@@ -595,12 +598,12 @@ cudaError_t launch_bwd_dq(const Params& p, const __nv_bfloat16* q, const __nv_bf
 #undef MOBA_DQ
 }
 
-cudaError_t launch_bwd_sum_dq(const Params& p, const float* partial_dq, const int32_t* selected, __nv_bfloat16* dq,
-                              int64_t dq_t, int64_t dq_h, cudaStream_t st) {
+cudaError_t launch_bwd_sum_dq(const Params& p, const float* partial_dq, const int32_t* selected, const int32_t* status,
+                              __nv_bfloat16* dq, int64_t dq_t, int64_t dq_h, cudaStream_t st) {
   int64_t blocks = (p.rows + 7) / 8;
   if (blocks > 148 * 32) blocks = 148 * 32;
-  if (p.fp16) sum_dq_kernel<true><<<(int)blocks, 256, 0, st>>>(p, partial_dq, selected, dq, dq_t, dq_h);
-  else sum_dq_kernel<false><<<(int)blocks, 256, 0, st>>>(p, partial_dq, selected, dq, dq_t, dq_h);
+  if (p.fp16) sum_dq_kernel<true><<<(int)blocks, 256, 0, st>>>(p, partial_dq, selected, status, dq, dq_t, dq_h);
+  else sum_dq_kernel<false><<<(int)blocks, 256, 0, st>>>(p, partial_dq, selected, status, dq, dq_t, dq_h);
   return cudaGetLastError();
 }
 

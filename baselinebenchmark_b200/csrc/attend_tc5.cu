@@ -610,20 +610,21 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [T, Hkv, D] bf16 with element strides (st, sh, 1): boxes of 128 tokens x 1 head x 64 dims
-bool make_kv_map(CUtensorMap* m, bool fp16, int D, const __nv_bfloat16* base, int64_t T, int Hkv, int64_t st, int64_t sh) {
+}  // namespace
+
+// [T, Hkv, D] 16-bit tensor with element strides (st, sh, 1): boxes of `box_rows` tokens x 1 head x 64 dims
+bool make_kv_map(CUtensorMap* m, bool fp16, int D, const __nv_bfloat16* base, int64_t T, int Hkv, int64_t st, int64_t sh,
+                 int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return false;
   const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)Hkv, (cuuint64_t)T};
   const cuuint64_t strides[2] = {(cuuint64_t)sh * 2, (cuuint64_t)st * 2};
-  const cuuint32_t box[3] = {64, 1, (cuuint32_t)kBN};
+  const cuuint32_t box[3] = {64, 1, (cuuint32_t)box_rows};
   const cuuint32_t estr[3] = {1, 1, 1};
   return fn(m, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<__nv_bfloat16*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
-
-}  // namespace
 
 cudaError_t launch_attend_tc5(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* k,
                               const __nv_bfloat16* v, const int32_t* cu, const int32_t* list_counts,
@@ -631,7 +632,7 @@ cudaError_t launch_attend_tc5(const Params& p, const __nv_bfloat16* q, const __n
                               const int32_t* row_list, float* partial_out, float* partial_lse,
                               int32_t* work_counter, int32_t* status, cudaStream_t st) {
   CUtensorMap mk, mv;
-  if (!make_kv_map(&mk, p.fp16 != 0, p.D, k, p.T, p.Hkv, p.sk_t, p.sk_h) || !make_kv_map(&mv, p.fp16 != 0, p.D, v, p.T, p.Hkv, p.sv_t, p.sv_h))
+  if (!make_kv_map(&mk, p.fp16 != 0, p.D, k, p.T, p.Hkv, p.sk_t, p.sk_h, kBN) || !make_kv_map(&mv, p.fp16 != 0, p.D, v, p.T, p.Hkv, p.sv_t, p.sv_h, kBN))
     return cudaErrorNotSupported;
   if (p.D != 64 && p.D != 128) return cudaErrorInvalidValue;
   auto kernel = p.D == 128 ? (p.fp16 ? attend_tc5_kernel<true, 128> : attend_tc5_kernel<false, 128>)

@@ -146,15 +146,20 @@ def moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, *,
     return out, lse, sel
 
 
-def moba_backward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, out, lse, selected, dout):
+def moba_backward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, out, lse, selected, dout,
+                  attend_impl=None):
     """Gradients (dq, dk, dv) of the operator for the output gradient `dout`, given what
     `moba_forward(..., return_lse=True, return_selected=True)` returned
-    (MixedAttention.backward, parallel.py:149-250: merged LSE and output, constant selection)."""
+    (MixedAttention.backward, parallel.py:149-250: merged LSE and output, constant selection).
+    `attend_impl` picks the dq kernel (tcgen05 at head_dim 64 and 128 by default, else
+    mma.sync); dk and dv run on mma.sync either way."""
     _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)
     if q.shape[2] > 128:
         raise NotImplementedError("the backward is built for head_dim <= 128")
     dout = dout.contiguous()
-    prob = make_problem(q, k, v, out, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, _lib.ATTEND_MMA_SYNC)
+    if attend_impl is None:
+        attend_impl = default_attend_impl(q.shape[2])
+    prob = make_problem(q, k, v, out, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, attend_impl)
     need = C.c_size_t(0)
     _lib.check(_lib.lib().moba_backward_workspace_size(C.byref(prob), C.byref(need)))
     ws = _workspace(q.device, need.value)

@@ -612,6 +612,31 @@ def test_backward_config2_dq_sampled_and_dkdv_finite():
     assert dv.float().abs().sum(-1).min().item() > 0
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", [c for c in BACKWARD_CASES if c[1] in (64, 128)], ids=lambda c: c[0])
+def test_backward_dq_kernels_agree(case, dtype):
+    """The tcgen05 and the mma.sync dq kernels evaluate the same sums with the same roundings
+    of dS (64-key steps, fp32 accumulation): they agree to fp32 summation order, far inside
+    one rounding step of the 16-bit result for all but a few entries; dk / dv (one kernel)
+    are identical up to their run-to-run list order."""
+    name, d, lens, hq, hkv, chunk, topk = case
+    q, k, v, cu = _case_inputs(lens, hq, hkv, chunk, zlib.crc32(name.encode()) % 1000, dtype=dtype, d=d)
+    q, k, v = q.cuda(), k.cuda(), v.cuda()
+    cud = torch.from_numpy(cu).cuda()
+    dout = torch.randn(q.shape, generator=torch.Generator().manual_seed(13)).to(dtype).cuda()
+    out, lse, sel = parallel.moba_forward(q, k, v, cud, max(lens), chunk, topk, return_lse=True, return_selected=True)
+    res = [parallel.moba_backward(q, k, v, cud, max(lens), chunk, topk, out, lse, sel, dout, attend_impl=impl)
+           for impl in (_lib.ATTEND_TCGEN05, _lib.ATTEND_MMA_SYNC)]
+    torch.cuda.synchronize()
+    a, b = res[0][0].float(), res[1][0].float()
+    assert torch.isfinite(a).all()
+    scale = b.abs().max().item()
+    assert (a - b).abs().max().item() <= 0.01 * scale
+    assert (a != b).float().mean().item() < 0.5
+    for x, y in zip(res[0][1:], res[1][1:]):
+        assert (x.float() - y.float()).abs().max().item() <= 2.0 ** -6 * y.float().abs().max().item()
+
+
 # --------------------------------------------------------------------------
 # CUDA path against outputs of the reference package itself (tests/golden/forward_*.npz)
 # --------------------------------------------------------------------------
