@@ -8,7 +8,7 @@ from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
 ROOT = PKG.parent
-SOURCES = ["api.cu", "gate.cu", "routes.cu", "attend_mma.cu", "attend_tc5.cu", "attend_bwd.cu", "attend_bwd_tc5.cu", "route_static.cu"]
+SOURCES = ["api.cu", "gate.cu", "routes.cu", "attend_mma.cu", "attend_tc5.cu", "attend_bwd.cu", "attend_bwd_tc5.cu", "attend_bwd_dkdv_tc5.cu", "route_static.cu"]
 LIB = PKG / "libmoba_b200.so"
 
 

@@ -432,8 +432,8 @@ int moba_backward(const moba_problem_t* p, const void* q, const void* k, const v
   const __nv_bfloat16* gb = static_cast<const __nv_bfloat16*>(dout);
   // dout, dq: contiguous [T, Hq, D]; dk, dv: contiguous [T, Hkv, D]
   const int64_t qt = (int64_t)r.Hq * r.D, kt = (int64_t)r.Hkv * r.D, hd = r.D;
-  // dq runs on the tcgen05 path where the forward's dense stage does (the mma.sync kernel
-  // otherwise); dk / dv are mma.sync kernels in both cases
+  // the gradient kernels run on the tcgen05 path where the forward's dense stage does, on
+  // mma.sync otherwise
   const bool dq_tc5 = p->attend_impl == MOBA_ATTEND_TCGEN05 && (r.D == 64 || r.D == 128);
   cudaError_t e;
   if ((e = cudaMemsetAsync(w.list_counts, 0, w.zero_bytes, st)) != cudaSuccess) return (int)e;
@@ -455,10 +455,15 @@ int moba_backward(const moba_problem_t* p, const void* q, const void* k, const v
   if ((e = launch_bwd_sum_dq(r, w.partial_out, selected, w.status, static_cast<__nv_bfloat16*>(dq), qt, hd, st)) !=
       cudaSuccess)
     return (int)e;
-  if ((e = launch_bwd_dkdv(r, qb, kb, vb, gb, qt, hd, cu, w.list_counts, w.list_offsets, w.row_list, lse2, delta,
-                           static_cast<__nv_bfloat16*>(dk), kt, hd, static_cast<__nv_bfloat16*>(dv), kt, hd,
-                           w.work_counter + 8, st)) != cudaSuccess)
-    return (int)e;
+  if (dq_tc5)
+    e = launch_bwd_dkdv_tc5(r, qb, kb, vb, gb, cu, w.list_counts, w.list_offsets, w.row_list, lse2, delta,
+                            static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), w.work_counter + 8,
+                            w.status, st);
+  else
+    e = launch_bwd_dkdv(r, qb, kb, vb, gb, qt, hd, cu, w.list_counts, w.list_offsets, w.row_list, lse2, delta,
+                        static_cast<__nv_bfloat16*>(dk), kt, hd, static_cast<__nv_bfloat16*>(dv), kt, hd,
+                        w.work_counter + 8, st);
+  if (e != cudaSuccess) return (int)e;
   return MOBA_OK;
 }
 

@@ -1,0 +1,525 @@
+// dK and dV of the MoBA dense stage on the Blackwell tensor path (tcgen05.mma, accumulators
+// in tensor memory).
+//
+// Replaces, for the training path of the reference, the dk/dv kernel of
+//   _triton_varlen_backward   backends/_mthreads/ops/moba/attention.py:163-369
+// and the scatter of routed gradients (routing.py:1776-1896), as called for both branches by
+// MixedAttention.backward (parallel.py:171-236):
+//   p_ij = exp(s_ij * scale - lse_i),  dS_ij = p_ij (dO_i . V_j - delta_i),
+//   dV_j = sum_i p_ij dO_i,  dK_j = scale * sum_i dS_ij Q_i
+// over the (query, key) pairs the forward attends.
+//
+// Key-stationary: a unit is 128 keys of one (chunk, kv head); its K and V tiles stay in shared
+// memory (TMA) and dK, dV stay in tensor memory while the CTA visits every query row that
+// attends the keys - the routed list of the chunk, then the chunk's own rows of every query
+// head of the group - in steps of 64 rows gathered into a four-stage ring.  Per step
+//   S^T  = K . Q^T      (128 keys x 64 rows, operands in shared memory)
+//   dP^T = V . dO^T     (128 x 64)
+//   one thread per key turns them into P^T and dS^T (input dtype) in tensor memory
+//   dV  += P^T . dO     (128 x D, P^T read from tensor memory, dO as the MN-major operand)
+//   dK  += dS^T . Q     (128 x D)
+// No atomics: a key's gradient is written once.  The order of the rows of a routed list is
+// the compaction's (unspecified), so dK and dV vary in their last bits from run to run.
+//
+// Warp roles (384 threads): warp 0 lane 0 loads K/V by TMA, warp 1 issues the MMAs and owns
+// the TMEM allocation, warps 2-3 gather Q / dO rows with cp.async, warps 4-7 handle the even
+// steps (S buffer 0) and write dK, warps 8-11 the odd steps (S buffer 1) and write dV.
+// TMEM columns: buffer X: S^T 128X..+63 (P^T, 16-bit, over the first 32), dP^T 128X+64..+127
+// (dS^T over its first 32); dK 256.., dV 384...
+// Every wait is bounded; a wait that gives up sets a status word and the gradients of the
+// call are poisoned with NaN by the kernel's own epilogue of later units and by the caller's
+// status check.
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace moba {
+
+bool make_kv_map(CUtensorMap* m, bool fp16, int D, const __nv_bfloat16* base, int64_t T, int Hkv, int64_t st,
+                 int64_t sh, int box_rows);
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kThreads = 384;
+constexpr int kKeys = 128;                    // keys per unit
+constexpr int kStep = 64;                     // rows per step
+constexpr int kStages = 4;
+constexpr int kKvBlockBytes = kKeys * 64 * 2; // [128 keys][64 dims]
+constexpr int kKvTileBytes = 2 * kKvBlockBytes;
+constexpr int kRowBlockBytes = kStep * 64 * 2;  // [64 rows][64 dims]
+constexpr int kRowTileBytes = 2 * kRowBlockBytes;
+constexpr uint32_t kTmemCols = 512;
+
+template <bool kHalf> constexpr uint32_t kIdescST = idesc_16_f32(kHalf, 128, kStep, 0, 0);
+template <bool kHalf, int D> constexpr uint32_t kIdescAcc = idesc_16_f32(kHalf, 128, D, 0, 1);
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+
+enum { ST_PRODUCER = 21, ST_MMA = 22, ST_ROWS = 23, ST_GATHER = 24 };
+
+struct Ctrl {
+  uint64_t kv_full, acc_full;
+  uint64_t row_full[kStages], row_empty[kStages];
+  uint64_t s_full[2], p_full[2];
+  uint32_t tmem_slot;
+  volatile int32_t abort;
+  int32_t unit;
+  alignas(16) float2 meta[kStages][kStep];                 // {-lse * log2 e (or -inf: no row), delta}
+  alignas(16) int32_t tok[kStages][kStep];                 // query token of an own-chunk row (causal limit), else INT_MAX
+  int64_t qoff[kStages][kStep];                // element offset of the row in q, -1: no row
+  int32_t grow[kStages][kStep];                // row index t * Hq + h
+};
+
+constexpr size_t kSmemBytes = 1024 + 2 * kKvTileBytes + kStages * 2 * kRowTileBytes + sizeof(Ctrl);
+static_assert(kSmemBytes <= 232448, "shared memory of one CTA");
+
+struct KernelArgs {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* dout;                   // contiguous [T, Hq, D]
+  const int32_t* cu;
+  const int32_t* list_counts;
+  const int32_t* list_offsets;
+  const int32_t* row_list;
+  const float* lse2;
+  const float* delta;
+  __nv_bfloat16* dk;                           // contiguous [T, Hkv, D]
+  __nv_bfloat16* dv;
+  int32_t* work_counter;
+  int32_t* status;
+};
+
+// What every thread derives from the unit index.
+struct Unit {
+  int l, kvh, key0, nkeys, end;                // list, kv head, first key token, keys in the tile, chunk end
+  int n_routed, routed_steps, own_steps, steps;
+  int64_t list_off;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
+  const int n = pred ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// Row `r` of own-chunk step `i` of the unit: the global row index t * Hq + h (or -1) and its
+// token, which limits the keys it sees.
+__device__ __forceinline__ void own_row(const Params& p, const Unit& u, int i, int r, int& row, int& tokq) {
+  const int o = i - u.routed_steps;
+  const int hl = o / u.own_steps, ot = o - hl * u.own_steps;
+  const int tok = u.key0 + ot * kStep + r;
+  row = -1;
+  tokq = 0x7fffffff;
+  if (tok < u.end) { row = (tok - p.win_lo) * p.Hq + (u.kvh * p.G + hl); tokq = tok; }
+}
+
+#ifndef MOBA_BWD_POLY_PAIRS
+#define MOBA_BWD_POLY_PAIRS 2
+#endif
+constexpr int kPolyPairs = MOBA_BWD_POLY_PAIRS;
+
+// One step of one key: S^T and dP^T (64 fp32 columns each, one per query row of the step) ->
+// P^T over the first 32 columns of S^T, dS^T over the first 32 columns of dP^T (input dtype).
+//   p = 2^(s * scale * log2 e - lse_row * log2 e),  dS = p * (dP - delta_row)
+// `meta[row]` = {-lse * log2 e, delta}; rows that do not exist carry -inf (p = 0).  Masked
+// steps (own-chunk rows around the diagonal) also compare the key token with the row's token.
+template <bool kMasked, bool kHalf>
+__device__ __forceinline__ void ps_row(uint32_t tS, const float2* meta, const int32_t* tok, int key_tok, bool key_ok,
+                                       float sl2) {
+  uint32_t s[64], g[64];
+  tmem_ld64(tS, s);
+  tmem_ld64(tS + 64, g);
+  tmem_wait_ld();
+  const uint64_t scale2 = pack2(sl2, sl2);
+#pragma unroll
+  for (int ch = 0; ch < 2; ++ch) {
+    uint32_t pp[16], pd[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int e = ch * 32 + 2 * i;
+      const float4 m = *reinterpret_cast<const float4*>(meta + e);      // {-lse2, delta} of rows e, e + 1
+      uint64_t x = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, pack2(m.x, m.z));
+      uint64_t pr;
+      if (kMasked) {
+        const int2 t = *reinterpret_cast<const int2*>(tok + e);
+        const float x0 = key_tok <= t.x ? lo2(x) : -INFINITY, x1 = key_tok <= t.y ? hi2(x) : -INFINITY;
+        pr = pack2(ex2_approx(x0), ex2_approx(x1));
+      } else if ((i & 7) < kPolyPairs) {
+        pr = ex2_poly2(x);
+      } else {
+        pr = pack2(ex2_approx(lo2(x)), ex2_approx(hi2(x)));
+      }
+      const uint64_t d = mul2(pr, sub2(pack2(__uint_as_float(g[e]), __uint_as_float(g[e + 1])), pack2(m.y, m.w)));
+      pp[i] = key_ok ? pack2_16<kHalf>(lo2(pr), hi2(pr)) : 0u;
+      pd[i] = key_ok ? pack2_16<kHalf>(lo2(d), hi2(d)) : 0u;
+    }
+    tmem_st16(tS + ch * 16, pp);
+    tmem_st16(tS + 64 + ch * 16, pd);
+  }
+  tmem_wait_st();
+}
+
+// Low word of a shared-memory descriptor (128-byte swizzle): start address >> 4 | (leading
+// byte offset >> 4) << 16; the high word is kDescHi.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+  return ((addr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
+}
+
+// S^T = K . Q^T and dP^T = V . dO^T of one step into S buffer column `xcol`; `dqs`, `dgs`: the
+// stage's Q and dO tiles as K-major operands.
+template <bool kHalf, int D>
+__device__ __forceinline__ void issue_st(uint32_t tm, uint32_t xcol, uint32_t dk, uint32_t dv, uint32_t dqs,
+                                         uint32_t dgs) {
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    const uint32_t ao = (uint32_t)((ks >> 2) * (kKvBlockBytes >> 4) + (ks & 3) * 2);
+    const uint32_t bo = (uint32_t)((ks >> 2) * (kRowBlockBytes >> 4) + (ks & 3) * 2);
+    mma_ss_lo<kDescHi>(tm + xcol, dk + ao, dqs + bo, kIdescST<kHalf>, ks > 0);
+  }
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    const uint32_t ao = (uint32_t)((ks >> 2) * (kKvBlockBytes >> 4) + (ks & 3) * 2);
+    const uint32_t bo = (uint32_t)((ks >> 2) * (kRowBlockBytes >> 4) + (ks & 3) * 2);
+    mma_ss_lo<kDescHi>(tm + xcol + 64, dv + ao, dgs + bo, kIdescST<kHalf>, ks > 0);
+  }
+}
+// dV += P^T . dO and dK += dS^T . Q of one step; `dgt`, `dqt`: the stage's dO and Q tiles as
+// MN-major operands (64-dim blocks 8 KB apart, 16 rows per k-step).
+template <bool kHalf, int D>
+__device__ __forceinline__ void issue_acc(uint32_t tm, uint32_t xcol, uint32_t dgt, uint32_t dqt, bool first) {
+#pragma unroll
+  for (int ks = 0; ks < kStep / 16; ++ks) {
+    mma_ts_lo<kDescHi>(tm + 384, tm + xcol + ks * 8, dgt + ks * (2048 >> 4), kIdescAcc<kHalf, D>, (!first) || ks > 0);
+    mma_ts_lo<kDescHi>(tm + 256, tm + xcol + 64 + ks * 8, dqt + ks * (2048 >> 4), kIdescAcc<kHalf, D>,
+                       (!first) || ks > 0);
+  }
+}
+
+// Draws units until one has keys (all threads take part: two block barriers per draw).
+// Returns false when the queue is empty or the kernel is aborting.
+__device__ __forceinline__ bool next_unit(const Params& p, const KernelArgs& a, Ctrl& c, int key_tiles,
+                                          int64_t n_units, Unit& u) {
+  for (;;) {
+    __syncthreads();
+    if (threadIdx.x == 0) c.unit = c.abort ? 0x7fffffff : atomicAdd(a.work_counter, 1);
+    __syncthreads();
+    const int64_t idx = c.unit;
+    if (idx >= n_units) return false;
+    u.l = (int)(idx / key_tiles);
+    const int kt = (int)(idx - (int64_t)u.l * key_tiles);
+    const int slot = u.l / p.Hkv;
+    u.kvh = u.l - slot * p.Hkv;
+    const int b = slot / p.mc, jc = slot - b * p.mc;
+    const Slot sl = slot_of(a.cu, b, jc, p.C);
+    u.key0 = sl.start + kt * kKeys;
+    u.end = sl.end;
+    if (u.key0 >= sl.end) continue;
+    u.nkeys = min(kKeys, sl.end - u.key0);
+    u.n_routed = p.hist > 0 ? a.list_counts[u.l] : 0;
+    u.list_off = p.hist > 0 ? a.list_offsets[u.l] : 0;
+    u.routed_steps = (u.n_routed + kStep - 1) / kStep;
+    u.own_steps = (sl.end - u.key0 + kStep - 1) / kStep;       // tokens key0 .. end see at least one key
+    u.steps = u.routed_steps + u.own_steps * p.G;
+    return true;
+  }
+}
+
+template <bool kHalf, int D>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, const KernelArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sK = smem_u32(smem);
+  const uint32_t sV = sK + kKvTileBytes;
+  const uint32_t sRows = sV + kKvTileBytes;                 // stage s: Q tile, dO tile
+  Ctrl& c = *reinterpret_cast<Ctrl*>(smem + 2 * kKvTileBytes + kStages * 2 * kRowTileBytes);
+
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&c.kv_full), 1);
+    mbar_init(smem_u32(&c.acc_full), 1);
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(smem_u32(&c.row_full[i]), 64);
+      mbar_init(smem_u32(&c.row_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&c.s_full[i]), 1);
+      mbar_init(smem_u32(&c.p_full[i]), kKeys);
+    }
+    c.abort = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&c.tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = c.tmem_slot;
+
+  const int key_tiles = (p.C + kKeys - 1) / kKeys;
+  const int64_t n_units = p.lists * key_tiles;
+  const float scale = rsqrtf((float)D);
+  const float sl2 = scale * 1.4426950408889634f;
+  if (warp < 4) {
+    setmaxnreg_dec<72>();
+    uint32_t g0 = 0;                       // steps of the units this CTA has finished
+    uint32_t nu = 0;                       // units this CTA has finished
+    Unit u;
+    while (next_unit(p, a, c, key_tiles, n_units, u)) {
+    if (warp == 0) {
+      // ------------------------------------------------ K and V of the unit
+      if (lane == 0) {
+        const uint32_t bar = smem_u32(&c.kv_full);
+        mbar_expect_tx(bar, 2 * (D / 64) * kKvBlockBytes);
+        tma_load_3d(sK, &tmap_k, bar, 0, u.kvh, u.key0);
+        if (D > 64) tma_load_3d(sK + kKvBlockBytes, &tmap_k, bar, 64, u.kvh, u.key0);
+        tma_load_3d(sV, &tmap_v, bar, 0, u.kvh, u.key0);
+        if (D > 64) tma_load_3d(sV + kKvBlockBytes, &tmap_v, bar, 64, u.kvh, u.key0);
+      }
+    } else if (warp == 1) {
+      // ------------------------------------------------ MMA issuer (warp convergent, one lane issues)
+      const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+      const uint32_t dk = __shfl_sync(0xffffffffu, desc_lo(sK, 16), 0);
+      const uint32_t dv = __shfl_sync(0xffffffffu, desc_lo(sV, 16), 0);
+      const uint32_t dq = __shfl_sync(0xffffffffu, desc_lo(sRows, 16), 0);                      // K-major views
+      const uint32_t dg = __shfl_sync(0xffffffffu, desc_lo(sRows + kRowTileBytes, 16), 0);
+      const uint32_t dqt = __shfl_sync(0xffffffffu, desc_lo(sRows, kRowBlockBytes), 0);         // MN-major views
+      const uint32_t dgt = __shfl_sync(0xffffffffu, desc_lo(sRows + kRowTileBytes, kRowBlockBytes), 0);
+      const uint32_t el = elect_one();
+      constexpr uint32_t kStageDesc = (2 * kRowTileBytes) >> 4;
+      bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.kv_full), nu & 1));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.row_full[g0 & 3]), (g0 >> 2) & 1));
+      if (ok) {
+        tc_fence_after();
+        if (el) {
+          issue_st<kHalf, D>(tm, (g0 & 1) * 128, dk, dv, dq + (g0 & 3) * kStageDesc, dg + (g0 & 3) * kStageDesc);
+          tc_commit(smem_u32(&c.s_full[g0 & 1]));
+        }
+        __syncwarp();
+      }
+      for (int i = 0; ok && i < u.steps; ++i) {
+        const uint32_t gi = g0 + i, g1 = gi + 1;
+        if (i + 1 < u.steps) {
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.row_full[g1 & 3]), (g1 >> 2) & 1));
+          if (!ok) break;
+          tc_fence_after();
+          if (el) {
+            issue_st<kHalf, D>(tm, (g1 & 1) * 128, dk, dv, dq + (g1 & 3) * kStageDesc, dg + (g1 & 3) * kStageDesc);
+            tc_commit(smem_u32(&c.s_full[g1 & 1]));
+          }
+          __syncwarp();
+        }
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.p_full[gi & 1]), (gi >> 1) & 1));
+        if (!ok) break;
+        tc_fence_after();
+        if (el) {
+          issue_acc<kHalf, D>(tm, (gi & 1) * 128, dgt + (gi & 3) * kStageDesc, dqt + (gi & 3) * kStageDesc, i == 0);
+          tc_commit(smem_u32(&c.row_empty[gi & 3]));
+          if (i + 1 == u.steps) tc_commit(smem_u32(&c.acc_full));
+        }
+        __syncwarp();
+      }
+      if (!ok && lane == 0) { atomicExch(a.status, ST_MMA); c.abort = 1; }
+    } else {
+      // ------------------------------------------------ warps 2-3: gather Q and dO rows, 32 rows of a step each
+      const int w = warp - 2, r = w * 32 + lane;
+      constexpr int kChunks = D / 8;                 // 16-byte pieces of a row
+      constexpr int kRowsPerInstr = 32 / kChunks;
+      // entry of the routed list / own row of step i for this lane's row (raw; decoded later)
+      auto fetch = [&](int i, int& ent, int& tokq) {
+        ent = -1;
+        tokq = 0x7fffffff;
+        if (i >= u.steps) return;
+        if (i < u.routed_steps) {
+          const int j = i * kStep + r;
+          if (j < u.n_routed) ent = __ldg(a.row_list + u.list_off + j);
+        } else {
+          int row;
+          own_row(p, u, i, r, row, tokq);
+          ent = row >= 0 ? row * p.NP : -1;          // same encoding as a list entry
+        }
+      };
+      int entA, tokA, entB, tokB;
+      fetch(0, entA, tokA);
+      fetch(1, entB, tokB);
+      int rowA = entA >= 0 ? entA / p.NP : -1;
+      float l2A = rowA >= 0 ? __ldg(a.lse2 + rowA) : INFINITY;
+      float dlA = rowA >= 0 ? __ldg(a.delta + rowA) : 0.f;
+      bool ok = true;
+      for (int i = 0; i < u.steps; ++i) {
+        // loads for the next two steps go out before this step's copies are issued
+        int entC, tokC;
+        fetch(i + 2, entC, tokC);
+        const int rowB = entB >= 0 ? entB / p.NP : -1;
+        const float l2B = rowB >= 0 ? __ldg(a.lse2 + rowB) : INFINITY;
+        const float dlB = rowB >= 0 ? __ldg(a.delta + rowB) : 0.f;
+        const uint32_t gi = g0 + i, st = gi & 3;
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.row_empty[st]), ((gi >> 2) & 1) ^ 1));
+        if (!ok) break;
+        {
+          int64_t off = -1;
+          if (rowA >= 0) {
+            const int64_t t = rowA / p.Hq;
+            off = t * p.sq_t + (rowA - t * p.Hq) * p.sq_h;
+          }
+          c.meta[st][r] = make_float2(-l2A, dlA);
+          c.tok[st][r] = tokA;
+          c.qoff[st][r] = off;
+          c.grow[st][r] = rowA;
+        }
+        __syncwarp();
+        const uint32_t qb = sRows + st * 2 * kRowTileBytes, gb = qb + kRowTileBytes;
+#pragma unroll
+        for (int it = 0; it < kChunks; ++it) {
+          const int rr = w * 32 + it * kRowsPerInstr + lane / kChunks, ch = lane % kChunks;
+          const int64_t off = c.qoff[st][rr];
+          const bool valid = off >= 0;
+          const uint32_t dst = (uint32_t)((ch >> 3) * kRowBlockBytes + rr * 128 + (((ch & 7) ^ (rr & 7)) << 4));
+          cp_async16(qb + dst, a.q + (valid ? off : 0) + ch * 8, valid);
+          cp_async16(gb + dst, a.dout + (valid ? (int64_t)c.grow[st][rr] * D : 0) + ch * 8, valid);
+        }
+        cp_async_commit();
+        if (i >= 2) {
+          cp_async_wait<2>();
+          fence_proxy_async_smem();
+          mbar_arrive(smem_u32(&c.row_full[(gi - 2) & 3]));
+        }
+        entA = entB; tokA = tokB; rowA = rowB; l2A = l2B; dlA = dlB;
+        entB = entC; tokB = tokC;
+      }
+      if (ok) {
+        const uint32_t ge = g0 + u.steps;          // one past the last step
+        if (u.steps >= 2) {
+          cp_async_wait<1>();
+          fence_proxy_async_smem();
+          mbar_arrive(smem_u32(&c.row_full[(ge - 2) & 3]));
+        }
+        cp_async_wait<0>();
+        fence_proxy_async_smem();
+        mbar_arrive(smem_u32(&c.row_full[(ge - 1) & 3]));
+      } else {
+        cp_async_wait<0>();
+        if (lane == 0) { atomicExch(a.status, ST_GATHER); c.abort = 1; }
+      }
+    }
+      g0 += (uint32_t)u.steps;
+      ++nu;
+    }
+  } else {
+    setmaxnreg_inc<216>();
+    uint32_t g0 = 0, nu = 0;
+    Unit u;
+    while (next_unit(p, a, c, key_tiles, n_units, u)) {
+      // ------------------------------------------------ warps 4-11: one thread per key
+      const int x = (warp - 4) >> 2;                       // S buffer and parity of the steps handled
+      const int key = (warp & 3) * 32 + lane;              // key inside the tile = TMEM lane
+      const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+      const uint32_t tS = tmem + lane_base + x * 128;
+      const bool key_ok = key < u.nkeys;
+      const int key_tok = u.key0 + key;
+      bool ok = true;
+      for (int i = ((g0 & 1) == (uint32_t)x) ? 0 : 1; ok && i < u.steps; i += 2) {
+        const uint32_t gi = g0 + i, st = gi & 3;
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.row_full[st]), (gi >> 2) & 1));   // row data of the stage
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.s_full[x]), (gi >> 1) & 1));
+        if (!ok) break;
+        tc_fence_after();
+        bool masked = false;
+        if (i >= u.routed_steps) {
+          const int o = i - u.routed_steps;
+          const int ot = o - (o / u.own_steps) * u.own_steps;
+          masked = ot * kStep < kKeys - 1;                 // rows whose token lies inside the key tile
+        }
+        if (masked) ps_row<true, kHalf>(tS, c.meta[st], c.tok[st], key_tok, key_ok, sl2);
+        else ps_row<false, kHalf>(tS, c.meta[st], c.tok[st], key_tok, key_ok, sl2);
+        tc_fence_before();
+        mbar_arrive(smem_u32(&c.p_full[x]));
+      }
+      if (ok) ok = mbar_wait(smem_u32(&c.acc_full), nu & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tc_fence_after();
+        // warps 4-7 write dK (scaled), warps 8-11 dV: a thread owns the D values of its key
+        const uint32_t tA = tmem + lane_base + 256 + x * 128;
+        const float f = x == 0 ? scale : 1.f;
+        __nv_bfloat16* dst = (x == 0 ? a.dk : a.dv) + ((int64_t)key_tok * p.Hkv + u.kvh) * D;
+        uint32_t v[32];
+#pragma unroll
+        for (int ch = 0; ch < D / 32; ++ch) {
+          tmem_ld32(tA + ch * 32, v);
+          tmem_wait_ld();
+          if (key_ok) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 o;
+              o.x = pack2_16<kHalf>(__uint_as_float(v[8 * i]) * f, __uint_as_float(v[8 * i + 1]) * f);
+              o.y = pack2_16<kHalf>(__uint_as_float(v[8 * i + 2]) * f, __uint_as_float(v[8 * i + 3]) * f);
+              o.z = pack2_16<kHalf>(__uint_as_float(v[8 * i + 4]) * f, __uint_as_float(v[8 * i + 5]) * f);
+              o.w = pack2_16<kHalf>(__uint_as_float(v[8 * i + 6]) * f, __uint_as_float(v[8 * i + 7]) * f);
+              *reinterpret_cast<uint4*>(dst + ch * 32 + i * 8) = o;
+            }
+          }
+        }
+        tc_fence_before();
+      } else {
+        atomicExch(a.status, ST_ROWS);
+        c.abort = 1;
+      }
+      g0 += (uint32_t)u.steps;
+      ++nu;
+    }
+  }
+
+  if (c.abort) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+// dk, dv <- NaN when a kernel of the call gave up on a wait
+__global__ void poison_kernel(const int32_t* __restrict__ status, uint32_t* dk, uint32_t* dv, int64_t words) {
+  if (*status == 0) return;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += (int64_t)gridDim.x * blockDim.x) {
+    dk[i] = 0x7fc07fc0u;       // NaN in bf16; NaN in fp16 as well (exponent all ones, mantissa non-zero)
+    dv[i] = 0x7fc07fc0u;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_bwd_dkdv_tc5(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* k,
+                                const __nv_bfloat16* v, const __nv_bfloat16* dout, const int32_t* cu,
+                                const int32_t* list_counts, const int32_t* list_offsets, const int32_t* row_list,
+                                const float* lse2, const float* delta, __nv_bfloat16* dk, __nv_bfloat16* dv,
+                                int32_t* work_counter, int32_t* status, cudaStream_t st) {
+  if (p.D != 64 && p.D != 128) return cudaErrorInvalidValue;
+  CUtensorMap mk, mv;
+  if (!make_kv_map(&mk, p.fp16 != 0, p.D, k, p.T, p.Hkv, p.sk_t, p.sk_h, kKeys) ||
+      !make_kv_map(&mv, p.fp16 != 0, p.D, v, p.T, p.Hkv, p.sv_t, p.sv_h, kKeys))
+    return cudaErrorNotSupported;
+  auto kernel = p.D == 128 ? (p.fp16 ? bwd_dkdv_tc5_kernel<true, 128> : bwd_dkdv_tc5_kernel<false, 128>)
+                           : (p.fp16 ? bwd_dkdv_tc5_kernel<true, 64> : bwd_dkdv_tc5_kernel<false, 64>);
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+  if (e != cudaSuccess) return e;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const KernelArgs args{q, dout, cu, list_counts, list_offsets, row_list, lse2, delta, dk, dv, work_counter, status};
+  kernel<<<sms, kThreads, kSmemBytes, st>>>(p, mk, mv, args);
+  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  poison_kernel<<<sms, 256, 0, st>>>(status, reinterpret_cast<uint32_t*>(dk), reinterpret_cast<uint32_t*>(dv),
+                                     (int64_t)p.T * p.Hkv * p.D / 2);
+  return cudaGetLastError();
+}
+
+}  // namespace moba

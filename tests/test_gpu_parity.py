@@ -614,11 +614,10 @@ def test_backward_config2_dq_sampled_and_dkdv_finite():
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("case", [c for c in BACKWARD_CASES if c[1] in (64, 128)], ids=lambda c: c[0])
-def test_backward_dq_kernels_agree(case, dtype):
-    """The tcgen05 and the mma.sync dq kernels evaluate the same sums with the same roundings
-    of dS (64-key steps, fp32 accumulation): they agree to fp32 summation order, far inside
-    one rounding step of the 16-bit result for all but a few entries; dk / dv (one kernel)
-    are identical up to their run-to-run list order."""
+def test_backward_kernels_agree(case, dtype):
+    """The tcgen05 and the mma.sync gradient kernels evaluate the same sums with P and dS
+    rounded to the input dtype and fp32 accumulation: they agree up to the summation order
+    and the exponential's approximation, i.e. within a rounding step or two of the result."""
     name, d, lens, hq, hkv, chunk, topk = case
     q, k, v, cu = _case_inputs(lens, hq, hkv, chunk, zlib.crc32(name.encode()) % 1000, dtype=dtype, d=d)
     q, k, v = q.cuda(), k.cuda(), v.cuda()
@@ -634,7 +633,8 @@ def test_backward_dq_kernels_agree(case, dtype):
     assert (a - b).abs().max().item() <= 0.01 * scale
     assert (a != b).float().mean().item() < 0.5
     for x, y in zip(res[0][1:], res[1][1:]):
-        assert (x.float() - y.float()).abs().max().item() <= 2.0 ** -6 * y.float().abs().max().item()
+        assert torch.isfinite(x.float()).all()
+        assert (x.float() - y.float()).abs().max().item() <= 0.01 * y.float().abs().max().item()
 
 
 # --------------------------------------------------------------------------
