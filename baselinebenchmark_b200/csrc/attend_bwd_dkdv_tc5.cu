@@ -22,8 +22,9 @@
 // the compaction's (unspecified), so dK and dV vary in their last bits from run to run.
 //
 // Warp roles (384 threads): warp 0 lane 0 loads K/V by TMA, warp 1 issues the MMAs and owns
-// the TMEM allocation, warps 2-3 gather Q / dO rows with cp.async, warps 4-7 handle the even
-// steps (S buffer 0) and write dK, warps 8-11 the odd steps (S buffer 1) and write dV.
+// the TMEM allocation, warps 2-3 describe the rows of the coming steps, warps 4-7 handle the even
+// steps (S buffer 0) and write dK, warps 8-11 the odd steps (S buffer 1) and write dV; after a
+// step a group copies the Q / dO rows of the step three ahead with cp.async.
 // TMEM columns: buffer X: S^T 128X..+63 (P^T, 16-bit, over the first 32), dP^T 128X+64..+127
 // (dS^T over its first 32); dK 256.., dV 384...
 // Every wait is bounded; a wait that gives up sets a status word and the gradients of the
@@ -59,15 +60,16 @@ enum { ST_PRODUCER = 21, ST_MMA = 22, ST_ROWS = 23, ST_GATHER = 24 };
 
 struct Ctrl {
   uint64_t kv_full, acc_full;
-  uint64_t row_full[kStages], row_empty[kStages];
+  uint64_t row_full[kStages], row_empty[kStages], meta_full[kStages];
   uint64_t s_full[2], p_full[2];
   uint32_t tmem_slot;
   volatile int32_t abort;
   int32_t unit;
-  alignas(16) float2 meta[kStages][kStep];                 // {-lse * log2 e (or -inf: no row), delta}
+  alignas(16) float2 meta[kStages][kStep];     // {lse * log2 e, delta} of the row; {0, 0}: no row
   alignas(16) int32_t tok[kStages][kStep];                 // query token of an own-chunk row (causal limit), else INT_MAX
   int64_t qoff[kStages][kStep];                // element offset of the row in q, -1: no row
   int32_t grow[kStages][kStep];                // row index t * Hq + h
+  int32_t ent[4][kStep];                       // routed-list entries of the steps ahead (0: no row)
 };
 
 constexpr size_t kSmemBytes = 1024 + 2 * kKvTileBytes + kStages * 2 * kRowTileBytes + sizeof(Ctrl);
@@ -100,6 +102,15 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool p
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, bool pred) {
+  const int n = pred ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+// arrives on the mbarrier once every cp.async this thread has issued so far has landed
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
@@ -114,6 +125,19 @@ __device__ __forceinline__ void own_row(const Params& p, const Unit& u, int i, i
   if (tok < u.end) { row = (tok - p.win_lo) * p.Hq + (u.kvh * p.G + hl); tokq = tok; }
 }
 
+// Optional cycle accounting (build with -DMOBA_DKDV_TRACE): sums over all CTAs are added to
+// 64-bit counters at status + 64 ints; status must then be followed by zeroed memory.
+#ifdef MOBA_DKDV_TRACE
+#define TR_T0(var) const long long var = clock64()
+#define TR_BASE(args) reinterpret_cast<unsigned long long*>(((uintptr_t)((args).status + 64) + 7) & ~(uintptr_t)7)
+#define TR_ADD(args, slot, t0) atomicAdd(TR_BASE(args) + (slot), (unsigned long long)(clock64() - (t0)))
+#define TR_COUNT(args, slot, n) atomicAdd(TR_BASE(args) + (slot), (unsigned long long)(n))
+#else
+#define TR_T0(var)
+#define TR_ADD(args, slot, t0)
+#define TR_COUNT(args, slot, n)
+#endif
+
 #ifndef MOBA_BWD_POLY_PAIRS
 #define MOBA_BWD_POLY_PAIRS 2
 #endif
@@ -122,8 +146,9 @@ constexpr int kPolyPairs = MOBA_BWD_POLY_PAIRS;
 // One step of one key: S^T and dP^T (64 fp32 columns each, one per query row of the step) ->
 // P^T over the first 32 columns of S^T, dS^T over the first 32 columns of dP^T (input dtype).
 //   p = 2^(s * scale * log2 e - lse_row * log2 e),  dS = p * (dP - delta_row)
-// `meta[row]` = {-lse * log2 e, delta}; rows that do not exist carry -inf (p = 0).  Masked
-// steps (own-chunk rows around the diagonal) also compare the key token with the row's token.
+// `meta[row]` = {lse * log2 e, delta}.  Rows that do not exist carry {0, 0} and zero Q / dO rows:
+// their p is 1 but multiplies a zero dO row, their dS is 1 * (0 - 0).  Masked steps (own-chunk
+// rows around the diagonal) also compare the key token with the row's token.
 template <bool kMasked, bool kHalf>
 __device__ __forceinline__ void ps_row(uint32_t tS, const float2* meta, const int32_t* tok, int key_tok, bool key_ok,
                                        float sl2) {
@@ -139,7 +164,8 @@ __device__ __forceinline__ void ps_row(uint32_t tS, const float2* meta, const in
     for (int i = 0; i < 16; ++i) {
       const int e = ch * 32 + 2 * i;
       const float4 m = *reinterpret_cast<const float4*>(meta + e);      // {-lse2, delta} of rows e, e + 1
-      uint64_t x = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, pack2(m.x, m.z));
+      uint64_t x = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2,
+                        pack2(m.x, m.z) ^ 0x8000000080000000ull);
       uint64_t pr;
       if (kMasked) {
         const int2 t = *reinterpret_cast<const int2*>(tok + e);
@@ -242,8 +268,9 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     mbar_init(smem_u32(&c.kv_full), 1);
     mbar_init(smem_u32(&c.acc_full), 1);
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(smem_u32(&c.row_full[i]), 64);
+      mbar_init(smem_u32(&c.row_full[i]), 64 + kKeys);     // lse / delta of 64 rows + the copies of 128 threads
       mbar_init(smem_u32(&c.row_empty[i]), 1);
+      mbar_init(smem_u32(&c.meta_full[i]), 64);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&c.s_full[i]), 1);
@@ -267,6 +294,7 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
   const int64_t n_units = p.lists * key_tiles;
   const float scale = rsqrtf((float)D);
   const float sl2 = scale * 1.4426950408889634f;
+  TR_T0(t_kernel);
   if (warp < 4) {
     setmaxnreg_dec<72>();
     uint32_t g0 = 0;                       // steps of the units this CTA has finished
@@ -297,6 +325,7 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
       bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.kv_full), nu & 1));
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.row_full[g0 & 3]), (g0 >> 2) & 1));
       if (ok) {
+        fence_proxy_async_smem();
         tc_fence_after();
         if (el) {
           issue_st<kHalf, D>(tm, (g0 & 1) * 128, dk, dv, dq + (g0 & 3) * kStageDesc, dg + (g0 & 3) * kStageDesc);
@@ -307,8 +336,11 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
       for (int i = 0; ok && i < u.steps; ++i) {
         const uint32_t gi = g0 + i, g1 = gi + 1;
         if (i + 1 < u.steps) {
+          TR_T0(t_r);
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.row_full[g1 & 3]), (g1 >> 2) & 1));
           if (!ok) break;
+          if (lane == 0) TR_ADD(a, 0, t_r);
+          fence_proxy_async_smem();
           tc_fence_after();
           if (el) {
             issue_st<kHalf, D>(tm, (g1 & 1) * 128, dk, dv, dq + (g1 & 3) * kStageDesc, dg + (g1 & 3) * kStageDesc);
@@ -316,8 +348,10 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
           }
           __syncwarp();
         }
+        TR_T0(t_p);
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.p_full[gi & 1]), (gi >> 1) & 1));
         if (!ok) break;
+        if (lane == 0) TR_ADD(a, 1, t_p);
         tc_fence_after();
         if (el) {
           issue_acc<kHalf, D>(tm, (gi & 1) * 128, dgt + (gi & 3) * kStageDesc, dqt + (gi & 3) * kStageDesc, i == 0);
@@ -327,87 +361,67 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         __syncwarp();
       }
       if (!ok && lane == 0) { atomicExch(a.status, ST_MMA); c.abort = 1; }
+      if (lane == 0) TR_COUNT(a, 6, u.steps);
     } else {
-      // ------------------------------------------------ warps 2-3: gather Q and dO rows, 32 rows of a step each
+      // ------------------------------------------------ warps 2-3: describe the rows of each step (32 rows each)
       const int w = warp - 2, r = w * 32 + lane;
-      constexpr int kChunks = D / 8;                 // 16-byte pieces of a row
-      constexpr int kRowsPerInstr = 32 / kChunks;
-      // entry of the routed list / own row of step i for this lane's row (raw; decoded later)
-      auto fetch = [&](int i, int& ent, int& tokq) {
-        ent = -1;
-        tokq = 0x7fffffff;
-        if (i >= u.steps) return;
+      // Nothing in the loop waits for a global load: the list entries of step i + 3 travel into a
+      // small ring with the copies of step i (cp.async), the LSE and delta of a row go straight
+      // into the stage's meta array the same way.  A routed entry is row * NP + rank + 1, never 0:
+      // the zero a predicated-off copy leaves means "no row".
+      auto request_entries = [&](int i) {
         if (i < u.routed_steps) {
           const int j = i * kStep + r;
-          if (j < u.n_routed) ent = __ldg(a.row_list + u.list_off + j);
-        } else {
-          int row;
-          own_row(p, u, i, r, row, tokq);
-          ent = row >= 0 ? row * p.NP : -1;          // same encoding as a list entry
+          const bool in = j < u.n_routed;
+          cp_async4(smem_u32(&c.ent[i & 3][r]), a.row_list + u.list_off + (in ? j : 0), in);
         }
       };
-      int entA, tokA, entB, tokB;
-      fetch(0, entA, tokA);
-      fetch(1, entB, tokB);
-      int rowA = entA >= 0 ? entA / p.NP : -1;
-      float l2A = rowA >= 0 ? __ldg(a.lse2 + rowA) : INFINITY;
-      float dlA = rowA >= 0 ? __ldg(a.delta + rowA) : 0.f;
+      request_entries(0);
+      request_entries(1);
+      request_entries(2);
+      cp_async_commit();
+      cp_async_wait<0>();
       bool ok = true;
       for (int i = 0; i < u.steps; ++i) {
-        // loads for the next two steps go out before this step's copies are issued
-        int entC, tokC;
-        fetch(i + 2, entC, tokC);
-        const int rowB = entB >= 0 ? entB / p.NP : -1;
-        const float l2B = rowB >= 0 ? __ldg(a.lse2 + rowB) : INFINITY;
-        const float dlB = rowB >= 0 ? __ldg(a.delta + rowB) : 0.f;
+        TR_T0(t_c);
+        cp_async_wait<2>();                          // group i - 3 has landed: the entries of step i
+        if (threadIdx.x == 64) TR_ADD(a, 5, t_c);
+        int row = -1, tokq = 0x7fffffff;
+        if (i < u.routed_steps) {
+          const int ent = c.ent[i & 3][r];
+          if (ent > 0) row = ent / p.NP;
+        } else {
+          own_row(p, u, i, r, row, tokq);
+        }
         const uint32_t gi = g0 + i, st = gi & 3;
+        TR_T0(t_e);
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.row_empty[st]), ((gi >> 2) & 1) ^ 1));
         if (!ok) break;
+        if (threadIdx.x == 64) TR_ADD(a, 4, t_e);
+        TR_T0(t_i);
         {
           int64_t off = -1;
-          if (rowA >= 0) {
-            const int64_t t = rowA / p.Hq;
-            off = t * p.sq_t + (rowA - t * p.Hq) * p.sq_h;
+          if (row >= 0) {
+            const int t = row / p.Hq;
+            off = (int64_t)t * p.sq_t + (int64_t)(row - t * p.Hq) * p.sq_h;
           }
-          c.meta[st][r] = make_float2(-l2A, dlA);
-          c.tok[st][r] = tokA;
+          c.tok[st][r] = tokq;
           c.qoff[st][r] = off;
-          c.grow[st][r] = rowA;
+          c.grow[st][r] = row;
+          const int rs = row >= 0 ? row : 0;
+          cp_async4(smem_u32(&c.meta[st][r].x), a.lse2 + rs, row >= 0);      // absent rows: {0, 0}, their Q and
+          cp_async4(smem_u32(&c.meta[st][r].y), a.delta + rs, row >= 0);     // dO rows are zero as well
         }
-        __syncwarp();
-        const uint32_t qb = sRows + st * 2 * kRowTileBytes, gb = qb + kRowTileBytes;
-#pragma unroll
-        for (int it = 0; it < kChunks; ++it) {
-          const int rr = w * 32 + it * kRowsPerInstr + lane / kChunks, ch = lane % kChunks;
-          const int64_t off = c.qoff[st][rr];
-          const bool valid = off >= 0;
-          const uint32_t dst = (uint32_t)((ch >> 3) * kRowBlockBytes + rr * 128 + (((ch & 7) ^ (rr & 7)) << 4));
-          cp_async16(qb + dst, a.q + (valid ? off : 0) + ch * 8, valid);
-          cp_async16(gb + dst, a.dout + (valid ? (int64_t)c.grow[st][rr] * D : 0) + ch * 8, valid);
-        }
+        // lse and delta travel asynchronously and count on the stage's barrier when they land;
+        // the offsets are there now: the row threads may start copying the rows
+        mbar_arrive(smem_u32(&c.meta_full[st]));
+        cp_async_arrive(smem_u32(&c.row_full[st]));
+        request_entries(i + 3);
         cp_async_commit();
-        if (i >= 2) {
-          cp_async_wait<2>();
-          fence_proxy_async_smem();
-          mbar_arrive(smem_u32(&c.row_full[(gi - 2) & 3]));
-        }
-        entA = entB; tokA = tokB; rowA = rowB; l2A = l2B; dlA = dlB;
-        entB = entC; tokB = tokC;
+        if (threadIdx.x == 64) TR_ADD(a, 9, t_i);
       }
-      if (ok) {
-        const uint32_t ge = g0 + u.steps;          // one past the last step
-        if (u.steps >= 2) {
-          cp_async_wait<1>();
-          fence_proxy_async_smem();
-          mbar_arrive(smem_u32(&c.row_full[(ge - 2) & 3]));
-        }
-        cp_async_wait<0>();
-        fence_proxy_async_smem();
-        mbar_arrive(smem_u32(&c.row_full[(ge - 1) & 3]));
-      } else {
-        cp_async_wait<0>();
-        if (lane == 0) { atomicExch(a.status, ST_GATHER); c.abort = 1; }
-      }
+      cp_async_wait<0>();
+      if (!ok && lane == 0) { atomicExch(a.status, ST_GATHER); c.abort = 1; }
     }
       g0 += (uint32_t)u.steps;
       ++nu;
@@ -425,11 +439,39 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
       const bool key_ok = key < u.nkeys;
       const int key_tok = u.key0 + key;
       bool ok = true;
-      for (int i = ((g0 & 1) == (uint32_t)x) ? 0 : 1; ok && i < u.steps; i += 2) {
+      // The Q and dO rows of step j are copied by the 128 threads of one of the two groups in
+      // 16-byte pieces with the 128-byte swizzle of the tile.  Two dedicated warps issue such
+      // copies too slowly to feed the tensor core; the eight row warps keep up.
+      auto copy_rows = [&](int j) -> bool {
+        if (j >= u.steps) return true;
+        const uint32_t gj = g0 + j, sj = gj & 3;
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&c.meta_full[sj]), (gj >> 2) & 1))) return false;
+        const int rr = key & 63, which = key >> 6;
+        const int64_t off = c.qoff[sj][rr];
+        const bool valid = off >= 0;
+        const __nv_bfloat16* src = which ? a.dout + (valid ? (int64_t)c.grow[sj][rr] * D : 0) : a.q + (valid ? off : 0);
+        const uint32_t base = sRows + sj * 2 * kRowTileBytes + which * kRowTileBytes + rr * 128;
+#pragma unroll
+        for (int ch = 0; ch < D / 8; ++ch)
+          cp_async16(base + (ch >> 3) * kRowBlockBytes + (((ch & 7) ^ (rr & 7)) << 4), src + ch * 8, valid);
+        cp_async_arrive(smem_u32(&c.row_full[sj]));
+        return true;
+      };
+      const int first = ((g0 & 1) == (uint32_t)x) ? 0 : 1;
+      {
+        TR_T0(t_w);
+        ok = copy_rows(first);                     // steps 0, 1, 2 before the loop: 0 and 2 by the group of step 0
+        if (ok && first == 0) ok = copy_rows(2);
+        if (threadIdx.x == 128) TR_ADD(a, 10, t_w);
+      }
+      for (int i = first; ok && i < u.steps; i += 2) {
         const uint32_t gi = g0 + i, st = gi & 3;
+        TR_T0(t_s);
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.row_full[st]), (gi >> 2) & 1));   // row data of the stage
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.s_full[x]), (gi >> 1) & 1));
         if (!ok) break;
+        if (threadIdx.x == 128) TR_ADD(a, 2, t_s);
+        TR_T0(t_x);
         tc_fence_after();
         bool masked = false;
         if (i >= u.routed_steps) {
@@ -441,7 +483,13 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         else ps_row<false, kHalf>(tS, c.meta[st], c.tok[st], key_tok, key_ok, sl2);
         tc_fence_before();
         mbar_arrive(smem_u32(&c.p_full[x]));
+        if (threadIdx.x == 128) TR_ADD(a, 3, t_x);
+        TR_T0(t_w);
+        ok = copy_rows(i + 3);
+        if (threadIdx.x == 128) TR_ADD(a, 10, t_w);
       }
+      cp_async_wait_all();
+      TR_T0(t_a);
       if (ok) ok = mbar_wait(smem_u32(&c.acc_full), nu & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
@@ -468,6 +516,7 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
           }
         }
         tc_fence_before();
+        if (threadIdx.x == 128) TR_ADD(a, 8, t_a);
       } else {
         atomicExch(a.status, ST_ROWS);
         c.abort = 1;
@@ -477,6 +526,7 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     }
   }
 
+  if (threadIdx.x == 0) TR_ADD(a, 7, t_kernel);
   if (c.abort) {
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);

@@ -25,7 +25,7 @@ from itertools import accumulate
 import torch
 
 from . import native_moba
-from .parallel import parallel_moba
+from .parallel import moba_backward, moba_forward, parallel_moba
 
 
 @dataclass(frozen=True)
@@ -113,6 +113,8 @@ def run_case(case: Case, args, device):
         return {**asdict(case), "status": "skipped", "reason": "this build: head_dim 64, 96, 128, 256"}
     q, k, v, cu = make_inputs(case, device)
     call = (q, k, v, cu, max(case.seq_lens), case.chunk_size, case.topk)
+    if args.backward:
+        return run_backward_case(case, args, call)
     with torch.inference_mode():
         parallel_moba(*call)
         torch.cuda.synchronize()
@@ -135,6 +137,29 @@ def run_case(case: Case, args, device):
             "latency": stats, "tokens_per_s": tokens / (stats["median_ms"] * 1e-3)}
 
 
+def run_backward_case(case: Case, args, call):
+    """Latency of `moba_backward` alone (gradients of the training path, parallel.py:149-250)
+    on what one forward with LSE and selection returned; same timing protocol."""
+    if case.head_dim > 128:
+        return {**asdict(case), "status": "skipped", "reason": "backward: head_dim <= 128"}
+    q = call[0]
+    with torch.inference_mode():
+        out, lse, sel = moba_forward(*call, return_lse=True, return_selected=True)
+        dout = torch.randn_like(q)
+        samples = []
+        for _ in range(args.rounds):
+            for _ in range(max(args.warmup, 1)):
+                moba_backward(*call, out, lse, sel, dout)
+            torch.cuda.synchronize()
+            for _ in range(args.iterations):
+                t0 = time.perf_counter()
+                grads = moba_backward(*call, out, lse, sel, dout)
+                torch.cuda.synchronize()
+                samples.append((time.perf_counter() - t0) * 1e3)
+                del grads
+    return {**asdict(case), "status": "measured", "pass": "backward", "latency": summary(samples)}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--case", action="append", choices=sorted(BASELINE_CASES), help="BASELINE.json workload(s)")
@@ -142,6 +167,7 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--iterations", type=int, default=25)
     ap.add_argument("--rounds", type=int, default=4)
+    ap.add_argument("--backward", action="store_true", help="time moba_backward instead of the forward")
     ap.add_argument("--output")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():

@@ -443,7 +443,9 @@ def main():
             _par.moba_backward(q2, k2, v2, cu2, 32768, 4096, 12, out2, lse2, sel2, dout2)
         b1.record()
         torch.cuda.synchronize()
-        also["configs[2] backward (training path, mma.sync, first version)"] = {"ms_per_call": b0.elapsed_time(b1) / 3}
+        bwd_ms = b0.elapsed_time(b1) / 3
+        also["configs[2] backward (training path, dq and dk/dv kernels on tcgen05)"] = {
+            "ms_per_call": bwd_ms, "tflops_on_2.5x_forward_flops": 2.5 * f2 / bwd_ms / 1e9}
     barrier()
 
     cpu = None

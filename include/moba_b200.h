@@ -230,7 +230,9 @@ int moba_route_static(const moba_problem_t* p, const void* q, const void* k, con
  * dtype; dout, dq, dk, dv are contiguous, q, k, v, out use the strides of the problem.  Like
  * the reference, both branches are differentiated with the merged LSE and output, and the
  * chunk selection is a constant.  No atomic accumulation: dq is bit-identical run to run,
- * dk and dv up to the order in which the rows of a routed list are added.
+ * dk and dv up to the order in which the rows of a routed list are added.  With
+ * attend_impl = MOBA_ATTEND_TCGEN05 and head_dim 64 or 128 the dq and dk/dv kernels run on
+ * tcgen05 (accumulators in tensor memory), otherwise on mma.sync.
  * Whole problems only (q_tokens == 0), head_dim <= 128, T*Hq*(hist+1) < 2^31; otherwise
  * MOBA_E_UNSUPPORTED.  The workspace holds, besides the route lists, one fp32 [D] slot per
  * (row, partial) for dQ: about the size of the forward's. */
