@@ -446,14 +446,20 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         if (j >= u.steps) return true;
         const uint32_t gj = g0 + j, sj = gj & 3;
         if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&c.meta_full[sj]), (gj >> 2) & 1))) return false;
-        const int rr = key & 63, which = key >> 6;
-        const int64_t off = c.qoff[sj][rr];
-        const bool valid = off >= 0;
-        const __nv_bfloat16* src = which ? a.dout + (valid ? (int64_t)c.grow[sj][rr] * D : 0) : a.q + (valid ? off : 0);
-        const uint32_t base = sRows + sj * 2 * kRowTileBytes + which * kRowTileBytes + rr * 128;
+        // a warp takes 16 rows of Q and the same 16 rows of dO; an instruction covers whole rows
+        // (D / 8 lanes per row), so every 32-byte sector it asks for is used in full
+        constexpr int kChunks = D / 8, kRowsPerInstr = 32 / kChunks;
+        const int ch = lane % kChunks;
+        const uint32_t qb = sRows + sj * 2 * kRowTileBytes + (ch >> 3) * kRowBlockBytes, gb = qb + kRowTileBytes;
 #pragma unroll
-        for (int ch = 0; ch < D / 8; ++ch)
-          cp_async16(base + (ch >> 3) * kRowBlockBytes + (((ch & 7) ^ (rr & 7)) << 4), src + ch * 8, valid);
+        for (int it = 0; it < 16 / kRowsPerInstr; ++it) {
+          const int rr = (warp & 3) * 16 + it * kRowsPerInstr + lane / kChunks;
+          const int64_t off = c.qoff[sj][rr];
+          const bool valid = off >= 0;
+          const uint32_t dst = (uint32_t)(rr * 128 + (((ch & 7) ^ (rr & 7)) << 4));
+          cp_async16(qb + dst, a.q + (valid ? off : 0) + ch * 8, valid);
+          cp_async16(gb + dst, a.dout + (valid ? (int64_t)c.grow[sj][rr] * D : 0) + ch * 8, valid);
+        }
         cp_async_arrive(smem_u32(&c.row_full[sj]));
         return true;
       };
