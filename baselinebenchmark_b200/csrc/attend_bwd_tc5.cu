@@ -18,8 +18,8 @@
 // scale * dQ as an fp32 partial into the row's slot (own chunk = 0, rank r = r + 1); a later
 // kernel adds a row's slots.  No atomics: the result is bit-identical run to run.
 //
-// Warp roles (384 threads) as in the forward kernel: warp 0 TMA producer (K and V tiles,
-// two stages), warp 1 MMA issuer and owner of the TMEM allocation, warp 2 draws and resolves
+// Warp roles (384 threads) as in the forward kernel: warp 0 TMA producer (K tiles in three
+// stages, V tiles in two), warp 1 MMA issuer and owner of the TMEM allocation, warp 2 draws and resolves
 // the next item, warps 4-7 / 8-11 the rows of tile A / B.
 // TMEM columns of row tile X: S 128X..128X+63 (dS, 16-bit, overwrites the first 32),
 // dP 128X+64..128X+127, dQ 256+128X..; 512 columns in all, which is why a key step is 64 wide.
@@ -46,7 +46,8 @@ constexpr int kQTileBytes = 2 * kQBlockBytes;
 constexpr int kKvBlockBytes = kBN * 64 * 2; // one [64 keys][64 dims] swizzled block of K or V
 constexpr int kKvTileBytes = 2 * kKvBlockBytes;
 constexpr uint32_t kTmemCols = 512;
-constexpr int kPrefixCache = 6144;          // ints of tile_prefix kept in shared memory
+constexpr int kPrefixCache = 2048;          // ints of tile_prefix kept in shared memory
+constexpr int kKStages = 3;                 // K tiles serve S (early) and dQ (late): three stages give the next one a full step of lead
 
 template <bool kHalf> constexpr uint32_t kIdescS = idesc_16_f32(kHalf, 128, kBN, 0, 0);
 template <bool kHalf, int D> constexpr uint32_t kIdescDQ = idesc_16_f32(kHalf, 128, D, 0, 1);
@@ -54,7 +55,7 @@ template <bool kHalf, int D> constexpr uint32_t kIdescDQ = idesc_16_f32(kHalf, 1
 enum { ST_OK = 0, ST_PRODUCER = 11, ST_MMA = 12, ST_ROWS = 13 };
 
 struct Ctrl {
-  uint64_t kv_full[2], k_empty[2], v_empty[2];
+  uint64_t k_full[kKStages], k_empty[kKStages], v_full[2], v_empty[2];
   uint64_t s_full[2], ds_full[2], dq_full[2];
   uint64_t item_ready[2];
   uint32_t tmem_slot;
@@ -67,7 +68,7 @@ struct Ctrl {
   int32_t prefix_cache[kPrefixCache];
 };
 
-constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + 4 * kQTileBytes + 4 * kKvTileBytes + sizeof(Ctrl);
+constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + 4 * kQTileBytes + (kKStages + 2) * kKvTileBytes + sizeof(Ctrl);
 static_assert(kSmemBytes <= 232448, "shared memory of one CTA");
 
 struct KernelArgs {
@@ -236,33 +237,33 @@ __device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) {
 }
 constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
 
-// S_X = Q_X . K^T and dP_X = dO_X . V^T for one 64-key tile: D / 16 k-steps each.  X and
-// STAGE are compile-time so every descriptor is a base word plus an immediate.
-template <int X, int STAGE, bool kHalf, int D>
+// S_X = Q_X . K^T and dP_X = dO_X . V^T for one 64-key tile: D / 16 k-steps each; `dk`, `dv`:
+// descriptor words of the K and V stage.
+template <int X, bool kHalf, int D>
 __device__ __forceinline__ void issue_s_dp(uint32_t tmem, uint32_t dq, uint32_t dg, uint32_t dk, uint32_t dv) {
   constexpr int kQBlock = kQBlockBytes >> 4, kQTile = kQTileBytes >> 4;
-  constexpr int kKvBlock = kKvBlockBytes >> 4, kKvTile = kKvTileBytes >> 4;
+  constexpr int kKvBlock = kKvBlockBytes >> 4;
 #pragma unroll
   for (int ks = 0; ks < D / 16; ++ks) {
     const uint32_t qo = (uint32_t)(X * kQTile + (ks >> 2) * kQBlock + (ks & 3) * 2);
-    const uint32_t ko = (uint32_t)(STAGE * kKvTile + (ks >> 2) * kKvBlock + (ks & 3) * 2);
+    const uint32_t ko = (uint32_t)((ks >> 2) * kKvBlock + (ks & 3) * 2);
     mma_ss_lo<kDescHi>(tmem + X * 128, dq + qo, dk + ko, kIdescS<kHalf>, ks > 0);
   }
 #pragma unroll
   for (int ks = 0; ks < D / 16; ++ks) {
     const uint32_t qo = (uint32_t)(X * kQTile + (ks >> 2) * kQBlock + (ks & 3) * 2);
-    const uint32_t ko = (uint32_t)(STAGE * kKvTile + (ks >> 2) * kKvBlock + (ks & 3) * 2);
+    const uint32_t ko = (uint32_t)((ks >> 2) * kKvBlock + (ks & 3) * 2);
     mma_ss_lo<kDescHi>(tmem + X * 128 + 64, dg + qo, dv + ko, kIdescS<kHalf>, ks > 0);
   }
 }
 // dQ_X (+)= dS_X . K for one 64-key tile: 4 k-steps of 16 keys, dS read from tensor memory,
 // K read as the MN-major operand (`dkt`: descriptor word with the 64-dim block stride).
-template <int X, int STAGE, bool kHalf, int D>
+template <int X, bool kHalf, int D>
 __device__ __forceinline__ void issue_dq(uint32_t tmem, uint32_t dkt, bool first) {
 #pragma unroll
   for (int ks = 0; ks < kBN / 16; ++ks)
     mma_ts_lo<kDescHi>(tmem + 256 + X * 128, tmem + X * 128 + ks * 8,
-                       dkt + STAGE * (kKvTileBytes >> 4) + ks * (2048 >> 4), kIdescDQ<kHalf, D>, (!first) || ks > 0);
+                       dkt + ks * (2048 >> 4), kIdescDQ<kHalf, D>, (!first) || ks > 0);
 }
 
 template <bool kHalf, int D>
@@ -273,16 +274,19 @@ bwd_dq_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sQ = smem_u32(smem);                       // Q tile A, Q tile B
   const uint32_t sG = sQ + 2 * kQTileBytes;                 // dO tile A, dO tile B
-  const uint32_t sK = sG + 2 * kQTileBytes;                 // 2 stages
-  const uint32_t sV = sK + 2 * kKvTileBytes;                // 2 stages
-  Ctrl& c = *reinterpret_cast<Ctrl*>(smem + 4 * kQTileBytes + 4 * kKvTileBytes);
+  const uint32_t sK = sG + 2 * kQTileBytes;                 // 3 stages
+  const uint32_t sV = sK + kKStages * kKvTileBytes;         // 2 stages
+  Ctrl& c = *reinterpret_cast<Ctrl*>(smem + 4 * kQTileBytes + (kKStages + 2) * kKvTileBytes);
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&c.kv_full[i]), 1);
+    for (int i = 0; i < kKStages; ++i) {
+      mbar_init(smem_u32(&c.k_full[i]), 1);
       mbar_init(smem_u32(&c.k_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&c.v_full[i]), 1);
       mbar_init(smem_u32(&c.v_empty[i]), 1);
       mbar_init(smem_u32(&c.s_full[i]), 1);
       mbar_init(smem_u32(&c.ds_full[i]), kTileM);
@@ -330,15 +334,22 @@ bwd_dq_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         // K and V tile `j` of item `w` into the next stage; false after a timeout
         auto load_tile = [&](const Item& w, int j) -> bool {
           const int tok = w.kv_tok0 + j * kBN;
-          const uint32_t s = g & 1, par = ((g >> 1) & 1) ^ 1;
-          if (!mbar_wait(smem_u32(&c.k_empty[s]), par)) return false;
-          if (!mbar_wait(smem_u32(&c.v_empty[s]), par)) return false;
-          const uint32_t bar = smem_u32(&c.kv_full[s]);
-          mbar_expect_tx(bar, 2 * (D / 64) * kKvBlockBytes);
-          tma_load_3d(sK + s * kKvTileBytes, &tmap_k, bar, 0, w.kv_head, tok);
-          if (D > 64) tma_load_3d(sK + s * kKvTileBytes + kKvBlockBytes, &tmap_k, bar, 64, w.kv_head, tok);
-          tma_load_3d(sV + s * kKvTileBytes, &tmap_v, bar, 0, w.kv_head, tok);
-          if (D > 64) tma_load_3d(sV + s * kKvTileBytes + kKvBlockBytes, &tmap_v, bar, 64, w.kv_head, tok);
+          {
+            const uint32_t s = g % kKStages, par = ((g / kKStages) & 1) ^ 1;
+            if (!mbar_wait(smem_u32(&c.k_empty[s]), par)) return false;
+            const uint32_t bar = smem_u32(&c.k_full[s]);
+            mbar_expect_tx(bar, (D / 64) * kKvBlockBytes);
+            tma_load_3d(sK + s * kKvTileBytes, &tmap_k, bar, 0, w.kv_head, tok);
+            if (D > 64) tma_load_3d(sK + s * kKvTileBytes + kKvBlockBytes, &tmap_k, bar, 64, w.kv_head, tok);
+          }
+          {
+            const uint32_t s = g & 1, par = ((g >> 1) & 1) ^ 1;
+            if (!mbar_wait(smem_u32(&c.v_empty[s]), par)) return false;
+            const uint32_t bar = smem_u32(&c.v_full[s]);
+            mbar_expect_tx(bar, (D / 64) * kKvBlockBytes);
+            tma_load_3d(sV + s * kKvTileBytes, &tmap_v, bar, 0, w.kv_head, tok);
+            if (D > 64) tma_load_3d(sV + s * kKvTileBytes + kKvBlockBytes, &tmap_v, bar, 64, w.kv_head, tok);
+          }
           ++g;
           return true;
         };
@@ -359,18 +370,17 @@ bwd_dq_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
       } else if (warp == 1) {
         // MMA issuer: the whole warp runs convergent, one elected lane issues.
         bool ok = true;
+        constexpr uint32_t kStageDesc = kKvTileBytes >> 4;
         tc_fence_after();
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.kv_full[g & 1]), (g >> 1) & 1));
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.k_full[g % kKStages]), (g / kKStages) & 1));
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.v_full[g & 1]), (g >> 1) & 1));
         if (ok) {
           tc_fence_after();
           if (el) {
-            if (g & 1) {
-              issue_s_dp<0, 1, kHalf, D>(tm, dq, dg, dk, dv); tc_commit(smem_u32(&c.s_full[0]));
-              issue_s_dp<1, 1, kHalf, D>(tm, dq, dg, dk, dv);
-            } else {
-              issue_s_dp<0, 0, kHalf, D>(tm, dq, dg, dk, dv); tc_commit(smem_u32(&c.s_full[0]));
-              issue_s_dp<1, 0, kHalf, D>(tm, dq, dg, dk, dv);
-            }
+            const uint32_t ko = (g % kKStages) * kStageDesc, vo = (g & 1) * kStageDesc;
+            issue_s_dp<0, kHalf, D>(tm, dq, dg, dk + ko, dv + vo);
+            tc_commit(smem_u32(&c.s_full[0]));
+            issue_s_dp<1, kHalf, D>(tm, dq, dg, dk + ko, dv + vo);
             tc_commit(smem_u32(&c.s_full[1]));
             tc_commit(smem_u32(&c.v_empty[g & 1]));
           }
@@ -378,19 +388,20 @@ bwd_dq_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         }
         for (int j = 0; ok && j < ntiles; ++j) {
           const bool more = j + 1 < ntiles;
-          const uint32_t cur = g & 1, nxt = cur ^ 1;
+          const uint32_t kcur = g % kKStages, g1 = g + 1, knxt = g1 % kKStages, vnxt = g1 & 1;
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.ds_full[0]), pph0));
           if (!ok) break;
           pph0 ^= 1;
           tc_fence_after();
-          if (el) { if (cur) issue_dq<0, 1, kHalf, D>(tm, dkt, j == 0); else issue_dq<0, 0, kHalf, D>(tm, dkt, j == 0); }
+          if (el) issue_dq<0, kHalf, D>(tm, dkt + kcur * kStageDesc, j == 0);
           __syncwarp();
           if (more) {
-            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.kv_full[nxt]), ((g + 1) >> 1) & 1));
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.k_full[knxt]), (g1 / kKStages) & 1));
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.v_full[vnxt]), (g1 >> 1) & 1));
             if (!ok) break;
             tc_fence_after();
             if (el) {
-              if (nxt) issue_s_dp<0, 1, kHalf, D>(tm, dq, dg, dk, dv); else issue_s_dp<0, 0, kHalf, D>(tm, dq, dg, dk, dv);
+              issue_s_dp<0, kHalf, D>(tm, dq, dg, dk + knxt * kStageDesc, dv + vnxt * kStageDesc);
               tc_commit(smem_u32(&c.s_full[0]));
             }
           } else if (el) {
@@ -402,12 +413,12 @@ bwd_dq_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
           pph1 ^= 1;
           tc_fence_after();
           if (el) {
-            if (cur) issue_dq<1, 1, kHalf, D>(tm, dkt, j == 0); else issue_dq<1, 0, kHalf, D>(tm, dkt, j == 0);
-            tc_commit(smem_u32(&c.k_empty[cur]));
+            issue_dq<1, kHalf, D>(tm, dkt + kcur * kStageDesc, j == 0);
+            tc_commit(smem_u32(&c.k_empty[kcur]));
             if (more) {
-              if (nxt) issue_s_dp<1, 1, kHalf, D>(tm, dq, dg, dk, dv); else issue_s_dp<1, 0, kHalf, D>(tm, dq, dg, dk, dv);
+              issue_s_dp<1, kHalf, D>(tm, dq, dg, dk + knxt * kStageDesc, dv + vnxt * kStageDesc);
               tc_commit(smem_u32(&c.s_full[1]));
-              tc_commit(smem_u32(&c.v_empty[nxt]));
+              tc_commit(smem_u32(&c.v_empty[vnxt]));
             } else {
               tc_commit(smem_u32(&c.dq_full[1]));
             }
