@@ -1,6 +1,8 @@
-"""Host-side checks of the latency harness's workload list (no GPU): the list mirrors
-benchmarks/moba_compare.py:59-99, which yields 40 distinct shapes after its own
-de-duplication, and every one of them lies inside what the library accepts."""
+"""The latency harness: its workload list mirrors benchmarks/moba_compare.py:59-99, which
+yields 40 distinct shapes after its own de-duplication, every one of them inside what the
+library accepts (checked without a GPU); one small case measured end to end on the GPU."""
+import pytest
+
 from baselinebenchmark_b200 import harness
 from baselinebenchmark_b200.parallel import HEAD_DIMS
 
@@ -32,3 +34,17 @@ def test_summary_reports_p99_only_with_enough_samples():
     assert "p99_ms" not in few and few["median_ms"] == 2.0 and few["count"] == 3
     many = harness.summary([float(i) for i in range(200)])
     assert many["p99_ms"] == 197.0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("extra", [[], ["--backward"]], ids=["forward", "backward"])
+def test_harness_measures_a_baseline_case(extra, tmp_path):
+    """The harness end to end on BASELINE.json configs[0]: one measured case with a latency
+    summary, written as JSON (forward and --backward)."""
+    import json
+    out = tmp_path / "report.json"
+    report = harness.main(["--case", "cfg0", "--rounds", "1", "--iterations", "2", "--warmup", "1",
+                           "--output", str(out)] + extra)
+    (case,) = report["cases"]
+    assert case["status"] == "measured" and case["latency"]["count"] == 2 and case["latency"]["median_ms"] > 0
+    assert json.loads(out.read_text())["cases"][0]["name"] == "cfg0"
