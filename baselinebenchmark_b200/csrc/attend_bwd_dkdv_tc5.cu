@@ -27,9 +27,8 @@
 // step a group copies the Q / dO rows of the step three ahead with cp.async.
 // TMEM columns: buffer X: S^T 128X..+63 (P^T, 16-bit, over the first 32), dP^T 128X+64..+127
 // (dS^T over its first 32); dK 256.., dV 384...
-// Every wait is bounded; a wait that gives up sets a status word and the gradients of the
-// call are poisoned with NaN by the kernel's own epilogue of later units and by the caller's
-// status check.
+// Every wait is bounded; a wait that gives up sets a status word, the CTAs stop drawing units
+// and a small kernel launched behind this one overwrites dK and dV with NaN.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
