@@ -612,8 +612,12 @@ def test_backward_config2_dq_sampled_and_dkdv_finite():
     assert dv.float().abs().sum(-1).min().item() > 0
 
 
+# the last case has 2502 route lists: more than the dq kernel keeps of the tile prefix in shared memory
+AGREE_CASES = [c for c in BACKWARD_CASES if c[1] in (64, 128)] + [("bwd_many_lists", 64, (20010,), 2, 2, 16, 4)]
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", [c for c in BACKWARD_CASES if c[1] in (64, 128)], ids=lambda c: c[0])
+@pytest.mark.parametrize("case", AGREE_CASES, ids=lambda c: c[0])
 def test_backward_kernels_agree(case, dtype):
     """The tcgen05 and the mma.sync gradient kernels evaluate the same sums with P and dS
     rounded to the input dtype and fp32 accumulation: they agree up to the summation order
