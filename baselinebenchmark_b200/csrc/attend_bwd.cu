@@ -123,8 +123,18 @@ delta_kernel(Params p, const __nv_bfloat16* __restrict__ out, const __nv_bfloat1
   }
 }
 
-// list_counts[slot * Hkv + h / G] = rows that selected the slot
+// list_counts[slot * Hkv + h / G] = rows that selected the slot.  With up to kSmemLists lists a
+// block counts in shared memory and adds its totals once; the warp-aggregated global
+// atomics of the general path serialise on a few hundred hot counters.
+constexpr int kSmemLists = 8192;
+
 __global__ void count_lists_kernel(Params p, const int32_t* __restrict__ selected, int32_t* __restrict__ list_counts) {
+  __shared__ int32_t hist[kSmemLists];
+  const bool local = p.lists <= kSmemLists;
+  if (local) {
+    for (int i = threadIdx.x; i < (int)p.lists; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+  }
   const int64_t n = (int64_t)p.hist * p.Hq * p.Tq;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / (p.Hq * p.Tq);
@@ -135,7 +145,15 @@ __global__ void count_lists_kernel(Params p, const int32_t* __restrict__ selecte
     const int list = slot >= 0 ? slot * p.Hkv + h / p.G : -1;
     const unsigned active = __activemask();
     const unsigned same = __match_any_sync(active, list);
-    if (list >= 0 && (int)(threadIdx.x & 31) == __ffs(same) - 1) atomicAdd(&list_counts[list], __popc(same));
+    if (list >= 0 && (int)(threadIdx.x & 31) == __ffs(same) - 1) {
+      if (local) atomicAdd(&hist[list], __popc(same));
+      else atomicAdd(&list_counts[list], __popc(same));
+    }
+  }
+  if (local) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < (int)p.lists; i += blockDim.x)
+      if (hist[i] != 0) atomicAdd(&list_counts[i], hist[i]);
   }
 }
 
@@ -555,7 +573,7 @@ int sm_count() {
 
 cudaError_t launch_count_lists(const Params& p, const int32_t* selected, int32_t* list_counts, cudaStream_t st) {
   if (p.hist <= 0) return cudaSuccess;
-  count_lists_kernel<<<sm_count() * 8, 256, 0, st>>>(p, selected, list_counts);
+  count_lists_kernel<<<sm_count() * (p.lists <= kSmemLists ? 2 : 8), 512, 0, st>>>(p, selected, list_counts);
   return cudaGetLastError();
 }
 
