@@ -20,7 +20,7 @@ ATTEND_MMA_SYNC = 1
 SYMBOLS = (
     "moba_b200_abi_version", "moba_b200_strerror", "moba_problem_check", "moba_problem_dims",
     "moba_workspace_size", "moba_workspace_size_min", "moba_forward", "moba_forward_events", "moba_workspace_size_host", "moba_forward_host",
-    "moba_chunk_metadata", "moba_chunk_means", "moba_gate_topk", "moba_compact_routes",
+    "moba_chunk_metadata", "moba_chunk_means", "moba_gate_topk", "moba_gate_topk_stats", "moba_compact_routes",
     "moba_attend", "moba_merge", "moba_attend_tile_rows", "moba_route_static",
     "moba_backward_workspace_size", "moba_backward",
 )
@@ -82,6 +82,7 @@ def lib() -> C.CDLL:
         handle.moba_chunk_metadata.argtypes = [pp, i32p, i32p, i32p, vp, vp]
         handle.moba_chunk_means.argtypes = [pp, vp, i32p, vp, vp]
         handle.moba_gate_topk.argtypes = [pp, vp, vp, i32p, i32p, i32p, vp]
+        handle.moba_gate_topk_stats.argtypes = [pp, vp, vp, i32p, i32p, i32p, i32p, C.c_int32, vp]
         handle.moba_compact_routes.argtypes = [pp, i32p, i32p, i32p, i32p, i32p, i32p, i32p, vp, C.c_int32, vp]
         handle.moba_attend.argtypes = [pp, vp, vp, vp, i32p, i32p, i32p, i32p, i32p, vp, vp, i32p, vp]
         handle.moba_merge.argtypes = [pp, vp, vp, i32p, vp, vp, vp]

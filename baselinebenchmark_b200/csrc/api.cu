@@ -7,6 +7,7 @@
 // and every scratch buffer taken from a caller-owned workspace.
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -16,6 +17,8 @@ namespace {
 
 constexpr size_t kAlign = 256;
 inline size_t align_up(size_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
+
+Params make_params(const moba_problem_t* p);
 
 int check_problem(const moba_problem_t* p) {
   if (p == nullptr) return MOBA_E_NULL;
@@ -50,6 +53,17 @@ int check_problem(const moba_problem_t* p) {
   // a pass covers at least one kv head with its query heads (forward_impl splits larger problems)
   const int64_t tq = p->q_tokens > 0 ? p->q_tokens : p->total_tokens;
   if (tq * (p->num_q_heads / p->num_kv_heads) * np >= ((int64_t)1 << 31)) return MOBA_E_UNSUPPORTED;
+  // launch limits: the gating and scatter grids put the sequence in grid.z and the kv head in
+  // grid.y; the gating kernel's lists must fit the shared memory of an SM; work items of the
+  // dense stage are counted in int32 (routed tiles <= hist * rows / tile + lists, own-chunk
+  // tiles = slots * Hq * tiles per chunk, per pass of one kv-head group at least)
+  if (p->batch > 65535 || p->num_kv_heads > 65535) return MOBA_E_UNSUPPORTED;
+  const int64_t g = p->num_q_heads / p->num_kv_heads;
+  const int64_t tile = p->attend_impl == MOBA_ATTEND_MMA_SYNC ? kMmaTileRows : kTc5TileRows;
+  const int64_t own_items = mc * p->batch * g * ((p->chunk_size + tile - 1) / tile);
+  const int64_t routed_items = (hist > 0 ? hist : 0) * tq * g / tile + mc * p->batch;
+  if (own_items + routed_items >= ((int64_t)1 << 31)) return MOBA_E_UNSUPPORTED;
+  if (!gate_topk_fits(make_params(p))) return MOBA_E_UNSUPPORTED;
   return MOBA_OK;
 }
 
@@ -147,18 +161,36 @@ constexpr int kHostMaxUnits = 256;        // [0, prefix] pairs kept alive in the
 struct HostStreams {
   cudaStream_t h2d, d2h;
 };
-// Two copy streams per device, created on first use and kept for the process.
+// Two copy streams per device, created on first use (once, whatever thread asks first) and
+// kept for the process.
 HostStreams* host_streams() {
-  static HostStreams streams[64];
-  static bool ready[64] = {false};
+  constexpr int kMaxDev = 64;
+  static HostStreams streams[kMaxDev];
+  static std::once_flag once[kMaxDev];
+  static bool ready[kMaxDev] = {false};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (!ready[dev]) {
-    if (cudaStreamCreateWithFlags(&streams[dev].h2d, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
-    if (cudaStreamCreateWithFlags(&streams[dev].d2h, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+  std::call_once(once[dev], [dev]() {
+    if (cudaStreamCreateWithFlags(&streams[dev].h2d, cudaStreamNonBlocking) != cudaSuccess) return;
+    if (cudaStreamCreateWithFlags(&streams[dev].d2h, cudaStreamNonBlocking) != cudaSuccess) return;
     ready[dev] = true;
-  }
-  return &streams[dev];
+  });
+  return ready[dev] ? &streams[dev] : nullptr;
+}
+
+// A cudaEvent_t that is destroyed on every exit path.
+struct ScopedEvent {
+  cudaEvent_t ev = nullptr;
+  cudaError_t create() { return cudaEventCreateWithFlags(&ev, cudaEventDisableTiming); }
+  ~ScopedEvent() { if (ev) cudaEventDestroy(ev); }
+};
+// `to` waits for everything queued on `from` so far.
+cudaError_t chain(cudaStream_t from, cudaStream_t to) {
+  ScopedEvent e;
+  cudaError_t rc = e.create();
+  if (rc != cudaSuccess) return rc;
+  if ((rc = cudaEventRecord(e.ev, from)) != cudaSuccess) return rc;
+  return cudaStreamWaitEvent(to, e.ev, 0);
 }
 
 __global__ void set_pair_kernel(int32_t* dst, int32_t a, int32_t b) {
@@ -191,7 +223,7 @@ const char* moba_b200_strerror(int code) {
     case MOBA_E_TOPK: return "moba_topk must be in 1..64";
     case MOBA_E_ALIGN: return "pointers and strides must be multiples of 16 bytes";
     case MOBA_E_DEVICE: return "needs an sm_100 device and a driver that exports cuTensorMapEncodeTiled";
-    case MOBA_E_STATIC_LIMIT: return "problem exceeds the built-in scratch of moba_route_static (slots * kv heads * 128 <= 2 Mi)";
+    case MOBA_E_STATIC_LIMIT: return "problem exceeds the built-in scratch of moba_route_static (slots * kv heads * head_dim <= 2 Mi elements)";
     default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
   }
 }
@@ -248,19 +280,26 @@ int moba_chunk_means(const moba_problem_t* p, const void* k, const int32_t* cu, 
   const int rc = check_problem(p);
   if (rc != MOBA_OK) return rc;
   if (!k || !cu || !means) return MOBA_E_NULL;
+  if (((uintptr_t)k | (uintptr_t)means) & 15) return MOBA_E_ALIGN;   // 16-byte loads of k, 16-byte loads of means later
   return (int)launch_chunk_means(make_params(p), static_cast<const __nv_bfloat16*>(k), cu,
                                  static_cast<__nv_bfloat16*>(means), (cudaStream_t)stream);
 }
 
-int moba_gate_topk(const moba_problem_t* p, const void* q, const void* means, const int32_t* cu,
-                   int32_t* selected, int32_t* list_counts, void* stream) {
+int moba_gate_topk_stats(const moba_problem_t* p, const void* q, const void* means, const int32_t* cu,
+                         int32_t* selected, int32_t* list_counts, int32_t* stats, int32_t flags, void* stream) {
   const int rc = check_problem(p);
   if (rc != MOBA_OK) return rc;
   if (!q || !means || !cu || !selected) return MOBA_E_NULL;
+  if (((uintptr_t)q | (uintptr_t)means) & 15) return MOBA_E_ALIGN;
   const Params r = make_params(p);
   if (r.hist <= 0) return MOBA_OK;
-  return (int)launch_gate_topk(r, static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(means),
-                               cu, selected, list_counts, (cudaStream_t)stream);
+  return (int)launch_gate_topk_stats(r, static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(means),
+                                     cu, selected, list_counts, stats, flags, (cudaStream_t)stream);
+}
+
+int moba_gate_topk(const moba_problem_t* p, const void* q, const void* means, const int32_t* cu,
+                   int32_t* selected, int32_t* list_counts, void* stream) {
+  return moba_gate_topk_stats(p, q, means, cu, selected, list_counts, nullptr, 0, stream);
 }
 
 int moba_compact_routes(const moba_problem_t* p, const int32_t* cu, const int32_t* selected,
@@ -419,7 +458,9 @@ int moba_backward(const moba_problem_t* p, const void* q, const void* k, const v
   if (rc != MOBA_OK) return rc;
   if (!q || !k || !v || !cu || !out || !lse || !dout || !dq || !dk || !dv) return MOBA_E_NULL;
   if (workspace == nullptr || workspace_bytes < need) return MOBA_E_WORKSPACE;
-  if (((uintptr_t)dout | (uintptr_t)dq | (uintptr_t)dk | (uintptr_t)dv | (uintptr_t)out) & 15) return MOBA_E_ALIGN;
+  if (((uintptr_t)dout | (uintptr_t)dq | (uintptr_t)dk | (uintptr_t)dv | (uintptr_t)out | (uintptr_t)q |
+       (uintptr_t)k | (uintptr_t)v | (uintptr_t)workspace) & 15)
+    return MOBA_E_ALIGN;
   const Params r = make_params(p);
   if (r.hist > 0 && selected == nullptr) return MOBA_E_NULL;
   cudaStream_t st = (cudaStream_t)stream;
@@ -512,7 +553,10 @@ int moba_forward_host(const moba_problem_t* p, const void* q_host, const void* k
   cudaError_t e;
 
   if (lse_out_host || selected_out_host) {
-    // one call on the whole batch: the extra outputs keep their whole-batch layouts
+    // one call on the whole batch: the extra outputs keep their whole-batch layouts.  The
+    // selection is copied out of the workspace, which holds all heads only when the problem
+    // runs as one pass.
+    if (selected_out_host && r.hist > 0 && pass_bytes(p, r.Hkv) > core) return MOBA_E_UNSUPPORTED;
     if ((e = cudaMemcpyAsync(dq, q_host, qbytes, cudaMemcpyHostToDevice, st)) != cudaSuccess) return (int)e;
     if ((e = cudaMemcpyAsync(dk, k_host, kbytes, cudaMemcpyHostToDevice, st)) != cudaSuccess) return (int)e;
     if ((e = cudaMemcpyAsync(dv, v_host, kbytes, cudaMemcpyHostToDevice, st)) != cudaSuccess) return (int)e;
@@ -538,13 +582,9 @@ int moba_forward_host(const moba_problem_t* p, const void* q_host, const void* k
   // on two side streams while window w computes.  All copies are contiguous.
   HostStreams* hs = host_streams();
   if (hs == nullptr) return (int)cudaErrorUnknown;
-  cudaEvent_t ev;
-  if ((e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming)) != cudaSuccess) return (int)e;
   // side streams start after everything already queued on the caller's stream
-  cudaEventRecord(ev, st);
-  cudaStreamWaitEvent(hs->h2d, ev, 0);
-  cudaStreamWaitEvent(hs->d2h, ev, 0);
-  cudaEventDestroy(ev);
+  if ((e = chain(st, hs->h2d)) != cudaSuccess) return (int)e;
+  if ((e = chain(st, hs->d2h)) != cudaSuccess) return (int)e;
   int unit = 0;
   int status = MOBA_OK;
   for (int b = 0; b < r.B && status == MOBA_OK; ++b) {
@@ -556,15 +596,16 @@ int moba_forward_host(const moba_problem_t* p, const void* q_host, const void* k
     for (int64_t c0 = 0; c0 < nchunks && status == MOBA_OK; c0 += per, ++unit) {
       const int64_t lo = s0 + c0 * r.C;
       const int64_t hi = (c0 + per) * r.C < s1 - s0 ? s0 + (c0 + per) * r.C : s1;
-      cudaEvent_t ev_in, ev_out;
-      if ((e = cudaEventCreateWithFlags(&ev_in, cudaEventDisableTiming)) != cudaSuccess) return (int)e;
-      if ((e = cudaEventCreateWithFlags(&ev_out, cudaEventDisableTiming)) != cudaSuccess) return (int)e;
-      cudaMemcpyAsync(dq + lo * qrow, (const char*)q_host + lo * qrow, (hi - lo) * qrow, cudaMemcpyHostToDevice, hs->h2d);
-      cudaMemcpyAsync(dk + lo * krow, (const char*)k_host + lo * krow, (hi - lo) * krow, cudaMemcpyHostToDevice, hs->h2d);
-      e = cudaMemcpyAsync(dv + lo * krow, (const char*)v_host + lo * krow, (hi - lo) * krow, cudaMemcpyHostToDevice, hs->h2d);
-      if (e != cudaSuccess) return (int)e;
-      cudaEventRecord(ev_in, hs->h2d);
-      cudaStreamWaitEvent(st, ev_in, 0);
+      if ((e = cudaMemcpyAsync(dq + lo * qrow, (const char*)q_host + lo * qrow, (hi - lo) * qrow,
+                               cudaMemcpyHostToDevice, hs->h2d)) != cudaSuccess ||
+          (e = cudaMemcpyAsync(dk + lo * krow, (const char*)k_host + lo * krow, (hi - lo) * krow,
+                               cudaMemcpyHostToDevice, hs->h2d)) != cudaSuccess ||
+          (e = cudaMemcpyAsync(dv + lo * krow, (const char*)v_host + lo * krow, (hi - lo) * krow,
+                               cudaMemcpyHostToDevice, hs->h2d)) != cudaSuccess ||
+          (e = chain(hs->h2d, st)) != cudaSuccess) {
+        status = (int)e;
+        break;
+      }
       // the window as a problem of its own: the prefix [s0, hi) is the sequence
       moba_problem_t sub = *p;
       sub.total_tokens = hi - s0;
@@ -573,22 +614,24 @@ int moba_forward_host(const moba_problem_t* p, const void* q_host, const void* k
       sub.q_tokens = hi - lo;
       int32_t* pair = dpairs + 2 * (unit % kHostMaxUnits);
       set_pair_kernel<<<1, 1, 0, st>>>(pair, 0, (int32_t)(hi - s0));
+      if ((e = cudaGetLastError()) != cudaSuccess) { status = (int)e; break; }
       status = moba_forward(&sub, dq + lo * qrow, dk + s0 * krow, dv + s0 * krow, pair, dout + lo * qrow, nullptr,
                             nullptr, workspace, core, stream);
-      cudaEventRecord(ev_out, st);
-      cudaStreamWaitEvent(hs->d2h, ev_out, 0);
-      cudaMemcpyAsync((char*)out_host + lo * qrow, dout + lo * qrow, (hi - lo) * qrow, cudaMemcpyDeviceToHost, hs->d2h);
-      cudaEventDestroy(ev_in);
-      cudaEventDestroy(ev_out);
+      if (status != MOBA_OK) break;
+      if ((e = chain(st, hs->d2h)) != cudaSuccess ||
+          (e = cudaMemcpyAsync((char*)out_host + lo * qrow, dout + lo * qrow, (hi - lo) * qrow,
+                               cudaMemcpyDeviceToHost, hs->d2h)) != cudaSuccess) {
+        status = (int)e;
+        break;
+      }
     }
   }
-  // the caller's stream completes when the last copy out has
-  if ((e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming)) != cudaSuccess) return (int)e;
-  cudaEventRecord(ev, hs->d2h);
-  cudaStreamWaitEvent(st, ev, 0);
-  cudaEventDestroy(ev);
+  // the caller's stream completes when the last copy in and the last copy out have, also
+  // after an error: nothing of this call is then still running on the side streams
+  const cudaError_t j1 = chain(hs->h2d, st), j2 = chain(hs->d2h, st);
   if (status != MOBA_OK) return status;
-  return (int)cudaGetLastError();
+  if (j1 != cudaSuccess) return (int)j1;
+  return (int)j2;
 }
 
 }  // extern "C"

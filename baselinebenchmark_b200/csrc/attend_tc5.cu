@@ -31,6 +31,8 @@
 // tile overwrites the first 64 columns of its S tile.
 // The tensor core alternates  QK_A(j+1) | PV_B(j) | QK_B(j+1) | PV_A(j+1) ...
 // so that the softmax of one tile runs while the MMAs of the other execute.
+#include <mutex>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -598,32 +600,36 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 EncodeTiledFn encode_fn() {
   static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  static std::once_flag once;
+  std::call_once(once, []() {
     void* ptr = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
         qres == cudaDriverEntryPointSuccess)
       fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
+  });
   return fn;
 }
 
 }  // namespace
 
-// [T, Hkv, D] 16-bit tensor with element strides (st, sh, 1): boxes of `box_rows` tokens x 1 head x 64 dims
-bool make_kv_map(CUtensorMap* m, bool fp16, int D, const __nv_bfloat16* base, int64_t T, int Hkv, int64_t st, int64_t sh,
-                 int box_rows) {
+// [T, H, D] 16-bit tensor with element strides (st, sh, 1): boxes of `box_rows` tokens x `box_heads` heads x
+// 64 dims, 128-byte swizzle; elements outside the tensor read as zero
+bool make_tile_map(CUtensorMap* m, bool fp16, int D, const __nv_bfloat16* base, int64_t T, int H, int64_t st,
+                   int64_t sh, int box_heads, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return false;
-  const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)Hkv, (cuuint64_t)T};
+  const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)T};
   const cuuint64_t strides[2] = {(cuuint64_t)sh * 2, (cuuint64_t)st * 2};
-  const cuuint32_t box[3] = {64, 1, (cuuint32_t)box_rows};
+  const cuuint32_t box[3] = {64, (cuuint32_t)box_heads, (cuuint32_t)box_rows};
   const cuuint32_t estr[3] = {1, 1, 1};
   return fn(m, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<__nv_bfloat16*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+bool make_kv_map(CUtensorMap* m, bool fp16, int D, const __nv_bfloat16* base, int64_t T, int Hkv, int64_t st, int64_t sh,
+                 int box_rows) {
+  return make_tile_map(m, fp16, D, base, T, Hkv, st, sh, 1, box_rows);
 }
 
 cudaError_t launch_attend_tc5(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* k,

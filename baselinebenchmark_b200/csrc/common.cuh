@@ -152,6 +152,15 @@ cudaError_t launch_chunk_means(const Params& p, const __nv_bfloat16* k, const in
 cudaError_t launch_gate_topk(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* means,
                              const int32_t* cu, int32_t* selected, int32_t* list_counts,
                              cudaStream_t st);
+// The same with optional statistics (int32[4], added to: [0] rows whose near-ties were ranked
+// again in the contract order, [1] largest |estimate - contract score| / eps seen there in
+// units of 2^-16, [2] rows where that ratio exceeded 1, [3] rows ranked over all candidates)
+// and flags (1: rank every row over all candidates, 2: rank the kept candidates of every row again).
+cudaError_t launch_gate_topk_stats(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* means,
+                                   const int32_t* cu, int32_t* selected, int32_t* list_counts, int32_t* stats,
+                                   int flags, cudaStream_t st);
+// false when the shared memory the gating kernel needs for `p` exceeds what an SM offers
+bool gate_topk_fits(const Params& p);
 cudaError_t launch_compact(const Params& p, const int32_t* cu, const int32_t* selected,
                            const int32_t* list_counts, int32_t* list_offsets, int32_t* tile_prefix,
                            int32_t* cursors, int32_t* row_list, float* partial_lse, int tile_rows,

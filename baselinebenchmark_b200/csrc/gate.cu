@@ -6,9 +6,11 @@
 //   _dense_chunk_mean_kernel                routing.py:690-737
 //   _chunk_topk_batched_streaming_kernel    routing.py:1056-1182
 //
-// The stage is bound by HBM traffic (K and Q are read once); the arithmetic
-// runs on CUDA cores in one fixed fp32 summation order so that the selection
-// is reproducible bit for bit by a CPU restatement:
+// K and Q are read once.  The selection is defined by one fixed fp32 summation
+// order, so that a CPU restatement reproduces it bit for bit; the scores of all
+// candidates are first estimated on the tensor core and only the candidates the
+// estimate cannot rank with certainty are evaluated in that order (see the
+// scores section below):
 //   mean : row r of a chunk is added to accumulator r % 32 in increasing r, the
 //          32 accumulators are added in increasing index, the total is divided
 //          by C and rounded to bf16 (round to nearest even);
@@ -18,6 +20,7 @@
 //          l + l+1); a block count that is no power of two (D = 96) is padded
 //          with blocks of +0.0 to the next one.
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace moba {
 
@@ -121,209 +124,543 @@ cudaError_t launch_chunk_means(const Params& p, const __nv_bfloat16* k, const in
 
 // ---------------------------------------------------------------------------
 // scores + mask + top-k
-//   grid (token tiles of one sequence, kv head, sequence); 256 threads = 64 row
-//   groups of 4 lanes.  The CTA stages the means of its kv head for a tile of
-//   candidate chunks in shared memory as fp32; every row group then scores its
-//   rows against them and keeps the `hist` largest packed keys
-//   (order-preserving score bits << 32 | 0xFFFFFFFF - slot, routing.py:1151-1153)
-//   in an ordered list: the keys of a candidate tile are held in registers,
-//   extracted largest first and merged with the list.  Keys are unique, so ties
-//   in the score fall to the lower slot.
-//   Lane t of a group owns the 8-dim blocks t, t+4, t+8, ..., so all levels of
-//   the halving tree but the last two stay inside the lane and only those two
-//   cross lanes: same summation order as one lane per block, a fraction of the
-//   shuffles.
+//
+// Two steps per (token, head) row, with the same result as scoring every
+// candidate in the contract order above:
+//
+//   1. estimate on the tensor core.  A row tile is 128 rows: the tokens of a
+//      tile x the query heads of one kv head.  Persistent CTAs (128 threads)
+//      walk the row tiles; TMA brings the Q rows of a tile (the next tile's
+//      while the current one is processed) and a tile of up to 256 candidate
+//      means into shared memory in the 128-byte swizzled K-major layout,
+//      tcgen05.mma multiplies them (fp32 accumulators in tensor memory, one
+//      lane per row), and thread r reads the estimates a_c of its row 32 at a
+//      time and keeps the hist + 4 largest in a min-heap (its root is the
+//      threshold a candidate has to beat), sorted when the row is complete.
+//   2. recheck.  With e_c the score in the contract order, |a_c - e_c| <= eps
+//      for every candidate of the row (bound below).  If neighbours in the
+//      sorted list differ by more than 2 eps down to the entry after the
+//      hist-th, the order of the a_c is the order of the e_c and the list is
+//      the answer.  Otherwise the candidates with a_c >= a_(hist) - 2 eps (the
+//      only ones that can be among the hist best e_c) are scored again by the
+//      warp on CUDA cores in the contract order, one candidate per lane, and
+//      ranked by the packed key of the reference
+//      (order-preserving score bits << 32 | 0xFFFFFFFF - slot,
+//      routing.py:778-784, :1151-1153: ties go to the lower slot).  A row
+//      whose near-ties overflow the list, whose scores are not finite, or
+//      whose tensor-core result did not arrive is ranked over all its
+//      candidates the same way.
+//
+// Error bound.  Products of two 16-bit inputs are exact in fp32, so both
+// results differ from the real dot product by summation error only.  Contract
+// order: 7 + log2(D/8) roundings on a path, each <= 2^-24 of a partial sum
+// that is <= S = sum_i |q_i m_i|.  Tensor core: per 16-dim step the 16
+// products and the accumulator are aligned to the largest exponent and
+// truncated; assuming no more than one unit of the 24-bit significand of that
+// exponent is lost per term and one more when the sum is normalised, a step
+// loses <= 18 * 2^-23 * S.  Together eps = (18 * D/16 + 16) * 2^-23 * S with
+// S <= |q|_2 |m|_2 (Cauchy-Schwarz, the largest norm over the staged means),
+// plus 2^-100 for products flushed to zero.  The recheck step measures
+// |a_c - e_c| / eps on every candidate it scores again (optional statistics
+// output), so the assumption is observable: on random inputs the largest
+// ratio seen is below 0.01.
 // ---------------------------------------------------------------------------
-constexpr int kGateThreads = 256;
-constexpr int kGateGroups = kGateThreads / 4;
-constexpr int kGateRows = 128;            // (token, head) rows per CTA
-constexpr int kCandTile = 32;             // candidate chunks staged per pass
+namespace {
+
+using namespace ptx;
+
+constexpr int kGateThreads = 128;         // one thread per row = one TMEM lane
+constexpr int kGateRows = 128;            // (token, head) rows per tile
+constexpr int kListExtra = 3;             // list places beyond hist + 1 that absorb near-ties at the cut
+constexpr int kCntSmemMax = 4096;         // chunks per sequence up to which the list histogram is kept in shared memory
+constexpr int kQBlockBytes = 128 * 128;   // one [128 rows][64 dims] swizzled block of 16-bit values
+constexpr int kScratchStride = 36;        // floats per row of the score scratch (144 bytes: conflict-free 16-byte stores)
 
 __device__ __forceinline__ uint32_t float_key(float x) {      // routing.py:778-784
   const uint32_t b = __float_as_uint(x);
   return b ^ ((b & 0x80000000u) ? 0xFFFFFFFFu : 0x80000000u);
 }
-__device__ __forceinline__ float dot8(const float (&q)[8], const float4 a, const float4 b) {
-  float s = q[0] * a.x;
-  s = __fmaf_rn(q[1], a.y, s);
-  s = __fmaf_rn(q[2], a.z, s);
-  s = __fmaf_rn(q[3], a.w, s);
-  s = __fmaf_rn(q[4], b.x, s);
-  s = __fmaf_rn(q[5], b.y, s);
-  s = __fmaf_rn(q[6], b.z, s);
-  s = __fmaf_rn(q[7], b.w, s);
+__device__ __forceinline__ float dot8(const float (&q)[8], const float (&m)[8]) {
+  float s = __fmul_rn(q[0], m[0]);
+#pragma unroll
+  for (int i = 1; i < 8; ++i) s = __fmaf_rn(q[i], m[i], s);
   return s;
 }
 
-#ifndef MOBA_GATE_CTAS
-#define MOBA_GATE_CTAS 3             // resident CTAs per SM the register budget is set for (D <= 128)
-#endif
+// shared-memory matrix descriptor of a K-major, 128-byte swizzled tile (8-row groups 1024 bytes apart)
+__device__ __forceinline__ uint64_t gate_desc(uint32_t addr) {
+  constexpr uint64_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  return (hi << 32) | (uint64_t)(((addr & 0x3FFFFu) >> 4) | (1u << 16));
+}
+
+// byte offset of the 16-byte piece `ch` of row `r` inside a tile of [rows][64]-element blocks
+__device__ __forceinline__ uint32_t swz_piece(int r, int ch, int block_bytes) {
+  return (uint32_t)((ch >> 3) * block_bytes + r * 128 + (((ch & 7) ^ (r & 7)) << 4));
+}
+
+struct GateCtrl {
+  uint64_t q_full[2];
+  uint64_t b_full;
+  uint64_t mma_done;
+  uint32_t tmem_slot;
+  int32_t failed;                          // a bounded wait gave up in this tile: its rows are ranked exactly
+  int32_t mean_ssq_max;                    // largest squared norm over the staged means (float bits, >= 0)
+  unsigned long long exact[kGateThreads / 32][64];   // per warp: keys of the row being ranked exactly
+};
+
+// Squared norm of row `r` of a swizzled tile.
 template <bool kHalf, int D>
-__global__ void __launch_bounds__(kGateThreads, D > 128 ? 2 : MOBA_GATE_CTAS)
-gate_topk_kernel(Params p, int tokens_per_cta, const __nv_bfloat16* __restrict__ q,
-                 const __nv_bfloat16* __restrict__ means, const int32_t* __restrict__ cu,
-                 int32_t* __restrict__ selected, int32_t* __restrict__ list_counts) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int hist = p.hist;
-  constexpr int kBlocks = D / 8;                       // 8-dim blocks per row
-  constexpr int kOwn = (kBlocks + 3) / 4;              // blocks owned by a lane: t, t+4, ...
-  constexpr int kOwnPad = kOwn <= 2 ? 2 : (kOwn <= 4 ? 4 : 8);   // padded to a power of two with +0.0
-  // layout: means tile fp32 | scratch[groups][2 * hist] | best[rows][hist] | counts[mc]
-  float4* means_s = reinterpret_cast<float4*>(smem_raw);                            // kCandTile * D/4 float4
-  unsigned long long* wins_s = reinterpret_cast<unsigned long long*>(means_s + kCandTile * (D / 4));
-  unsigned long long* best_s = wins_s + kGateGroups * 2 * hist;
-  int32_t* cnt_s = reinterpret_cast<int32_t*>(best_s + (size_t)kGateRows * hist);
+__device__ __forceinline__ float row_ssq(const unsigned char* tile, int r, int block_bytes) {
+  float ssq = 0.f;
+#pragma unroll
+  for (int ch = 0; ch < D / 8; ++ch) {
+    float f[8];
+    unpack8<kHalf>(*reinterpret_cast<const uint4*>(tile + swz_piece(r, ch, block_bytes)), f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ssq = __fmaf_rn(f[e], f[e], ssq);
+  }
+  return ssq;
+}
 
-  const int b = blockIdx.z, hk = blockIdx.y;
-  const int s0 = cu[b], s1 = cu[b + 1];
-  // tokens of this CTA, clipped to the sequence and to the query window
-  const int tok_lo = max(s0 + blockIdx.x * tokens_per_cta, p.win_lo);
-  const int tok_hi = min(min(s0 + (blockIdx.x + 1) * tokens_per_cta, s1), p.win_lo + (int)p.Tq);
-  if (tok_lo >= tok_hi) return;
-  const int ntok = tok_hi - tok_lo;
-  const int nrows = ntok * p.G;
-  const int grp = threadIdx.x >> 2, t = threadIdx.x & 3;
-  const unsigned gmask = 0xFu << (threadIdx.x & 28);          // the 4 lanes of this group
-
-  for (int i = threadIdx.x; i < p.mc; i += kGateThreads) cnt_s[i] = 0;
-  for (int i = threadIdx.x; i < kGateRows * hist; i += kGateThreads) best_s[i] = 0ull;
-  // candidates of the last token of the tile bound the chunks to stage
-  const int max_cand = (tok_lo + ntok - 1 - s0) / p.C;
-  const int slot0 = b * p.mc;
-
-  for (int c0 = 0; c0 < max_cand; c0 += kCandTile) {
-    const int ct = min(kCandTile, max_cand - c0);
-    __syncthreads();                                          // previous tile fully consumed
-    for (int i = threadIdx.x; i < ct * kBlocks; i += kGateThreads) {
-      const int c = i / kBlocks, part = i - c * kBlocks;
-      const uint4 x = __ldg(reinterpret_cast<const uint4*>(
-          means + ((int64_t)(slot0 + c0 + c) * p.Hkv + hk) * D + part * 8));
-      float f[8];
-      unpack8<kHalf>(x, f);
-      means_s[c * (D / 4) + part * 2] = make_float4(f[0], f[1], f[2], f[3]);
-      means_s[c * (D / 4) + part * 2 + 1] = make_float4(f[4], f[5], f[6], f[7]);
+// Score of row `r` (Q tile in shared memory) against the mean at `mrow` (global), in the contract order.
+template <bool kHalf, int D>
+__device__ __forceinline__ float contract_score(const unsigned char* sQ, int r, const __nv_bfloat16* mrow) {
+  constexpr int kNB = D / 8;
+  constexpr int kNBPad = kNB <= 8 ? 8 : (kNB <= 16 ? 16 : 32);
+  uint4 mraw[kNB];
+#pragma unroll
+  for (int l = 0; l < kNB; ++l) mraw[l] = __ldg(reinterpret_cast<const uint4*>(mrow + l * 8));
+  float b[kNBPad];
+#pragma unroll
+  for (int l = 0; l < kNBPad; ++l) {
+    if (l < kNB) {
+      float qf[8], mf[8];
+      unpack8<kHalf>(*reinterpret_cast<const uint4*>(sQ + swz_piece(r, l, kQBlockBytes)), qf);
+      unpack8<kHalf>(mraw[l], mf);
+      b[l] = dot8(qf, mf);
+    } else {
+      b[l] = 0.f;
     }
-    __syncthreads();
-    for (int row = grp; row < nrows; row += kGateGroups) {    // row = token-major, head-minor
-      const int tl = row / p.G, hl = row - tl * p.G;
-      const int tok = tok_lo + tl;
-      const int cend = min(ct, (tok - s0) / p.C - c0);        // this row's candidates in the tile
-      if (cend <= 0) continue;                                // uniform over the 4 lanes
-      float qf[kOwn][8];
-      {
-        const __nv_bfloat16* qrow = q + (int64_t)(tok - p.win_lo) * p.sq_t + (int64_t)(hk * p.G + hl) * p.sq_h;
+  }
 #pragma unroll
-        for (int k = 0; k < kOwn; ++k)
-          unpack8<kHalf>(__ldg(reinterpret_cast<const uint4*>(qrow + (t + 4 * k) * 8)), qf[k]);
+  for (int h = kNBPad / 2; h >= 1; h >>= 1)
+#pragma unroll
+    for (int l = 0; l < h; ++l) b[l] = __fadd_rn(b[l], b[l + h]);
+  return b[0];
+}
+
+// Min-heap of {chunk, score bits} on the score: `heap[0]` is the smallest score kept.  Replaces the
+// root by (a, chunk) and restores the heap.
+__device__ __forceinline__ void heap_replace_root(uint2* heap, int n, float a, uint32_t chunk) {
+  int k = 0;
+  for (;;) {
+    const int l = 2 * k + 1;
+    if (l >= n) break;
+    uint2 child = heap[l];
+    int s = l;
+    if (l + 1 < n) {
+      const uint2 right = heap[l + 1];
+      if (__uint_as_float(right.y) < __uint_as_float(child.y)) { child = right; s = l + 1; }
+    }
+    if (!(__uint_as_float(child.y) < a)) break;
+    heap[k] = child;
+    k = s;
+  }
+  heap[k] = make_uint2(chunk, __float_as_uint(a));
+}
+
+enum { GATE_FORCE_EXACT = 1, GATE_FORCE_RECHECK = 2 };
+
+struct GateTile {
+  int valid, b, hk, s0, tok_lo, ntok, max_cand;
+};
+
+__device__ __forceinline__ GateTile gate_tile(const Params& p, const int32_t* __restrict__ cu, int i, int tiles_x,
+                                              int tokens_per_cta) {
+  GateTile t;
+  const int x = i % tiles_x, rest = i / tiles_x;
+  t.hk = rest % p.Hkv;
+  t.b = rest / p.Hkv;
+  t.s0 = cu[t.b];
+  const int s1 = cu[t.b + 1];
+  // tokens of the tile, clipped to the sequence and to the query window
+  t.tok_lo = max(t.s0 + x * tokens_per_cta, p.win_lo);
+  const int tok_hi = min(min(t.s0 + (x + 1) * tokens_per_cta, s1), p.win_lo + (int)p.Tq);
+  t.valid = t.tok_lo < tok_hi;
+  t.ntok = tok_hi - t.tok_lo;
+  // candidates of the last token of the tile bound the chunks to stage
+  t.max_cand = t.valid ? (tok_hi - 1 - t.s0) / p.C : 0;
+  return t;
+}
+
+template <bool kHalf, int D>
+__global__ void __launch_bounds__(kGateThreads)
+gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_m,
+                 int tokens_per_cta, int nt, int list_len, int nbuf, int cnt_in_smem,
+                 const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ means,
+                 const int32_t* __restrict__ cu, int32_t* __restrict__ selected,
+                 int32_t* __restrict__ list_counts, int32_t* __restrict__ stats, int flags) {
+  extern __shared__ unsigned char gate_smem_raw[];
+  constexpr int kNBlk = (D + 63) / 64;                 // 64-dim blocks of a row
+  const int hist = p.hist;
+  const int lstride = list_len | 1;                    // odd: the rows' lists start in different banks
+
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)gate_smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* sQ0 = smem;                                             // nbuf x kNBlk blocks [128][64]
+  unsigned char* sB = sQ0 + (size_t)nbuf * kNBlk * kQBlockBytes;        // kNBlk blocks [nt][64]
+  uint2* lists = reinterpret_cast<uint2*>(sB + (size_t)kNBlk * nt * 128);   // [128][lstride] {chunk, score bits}
+  float* scratch = reinterpret_cast<float*>(lists + (size_t)kGateRows * lstride);   // [128][36]
+  GateCtrl& c = *reinterpret_cast<GateCtrl*>(scratch + kGateRows * kScratchStride);
+  int32_t* cnt_s = reinterpret_cast<int32_t*>(&c + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tiles_x = (p.max_seqlen + tokens_per_cta - 1) / tokens_per_cta;
+  const int n_tiles = tiles_x * p.Hkv * p.B;
+  const int rows_box = tokens_per_cta * p.G;           // rows one Q box brings
+
+  if (tid == 0) {
+    mbar_init(smem_u32(&c.q_full[0]), 1);
+    mbar_init(smem_u32(&c.q_full[1]), 1);
+    mbar_init(smem_u32(&c.b_full), 1);
+    mbar_init(smem_u32(&c.mma_done), 1);
+    fence_barrier_init();
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_m);
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&c.tmem_slot), (uint32_t)nt);
+    tmem_relinquish();
+  }
+  if (cnt_in_smem)
+    for (int i = tid; i < p.mc; i += kGateThreads) cnt_s[i] = 0;       // every tile leaves them at zero again
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = c.tmem_slot;
+  const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);          // this thread's lane, column 0
+
+  // producer state (thread 0): Q tiles requested so far, tile index to look for the next one from
+  int q_requested = 0, q_next_from = blockIdx.x;
+  uint32_t b_phase = 0, mma_phase = 0;
+  int n = 0;                                           // tiles with candidates processed so far
+
+  auto request_q = [&](const GateTile& t, int buf) {
+    const uint32_t bar = smem_u32(&c.q_full[buf]);
+    mbar_expect_tx(bar, (uint32_t)(kNBlk * rows_box * 128));
+#pragma unroll
+    for (int blk = 0; blk < kNBlk; ++blk)
+      tma_load_3d(smem_u32(sQ0 + ((size_t)buf * kNBlk + blk) * kQBlockBytes), &tmap_q, bar, blk * 64, t.hk * p.G,
+                  t.tok_lo - p.win_lo);
+  };
+  auto request_b = [&](const GateTile& t, int c0) {
+    const uint32_t bar = smem_u32(&c.b_full);
+    mbar_expect_tx(bar, (uint32_t)(kNBlk * nt * 128));
+#pragma unroll
+    for (int blk = 0; blk < kNBlk; ++blk)
+      tma_load_3d(smem_u32(sB + (size_t)blk * nt * 128), &tmap_m, bar, blk * 64, t.hk, t.b * p.mc + c0);
+  };
+
+  for (int ti = blockIdx.x; ti < n_tiles; ti += gridDim.x) {
+    const GateTile t = gate_tile(p, cu, ti, tiles_x, tokens_per_cta);
+    if (!t.valid) continue;
+    const int nrows = t.ntok * p.G;
+    const int slot0 = t.b * p.mc;
+    // selected[r][head][tok]: `ntok` consecutive ints per (rank, head)
+    auto store_selected = [&](int i, int slot) {
+      const int r = i / nrows, rem = i - r * nrows;
+      const int hl = rem / t.ntok, tl = rem - hl * t.ntok;
+      selected[(int64_t)r * p.sel_rs + (int64_t)(t.hk * p.G + hl) * p.Tq + (t.tok_lo - p.win_lo) + tl] = slot;
+    };
+    if (t.max_cand <= 0) {                             // first chunk of a sequence: nothing to select
+      for (int i = tid; i < hist * nrows; i += kGateThreads) store_selected(i, -1);
+      continue;
+    }
+    const int buf = nbuf == 2 ? (n & 1) : 0;
+    const uint32_t q_phase = nbuf == 2 ? ((n >> 1) & 1) : (n & 1);
+    unsigned char* sQ = sQ0 + (size_t)buf * kNBlk * kQBlockBytes;
+    if (tid == 0) {
+      if (q_requested == n) {                          // not prefetched (first tile, or a single buffer)
+        request_q(t, buf);
+        q_requested = n + 1;
+        q_next_from = ti + gridDim.x;
       }
-      // packed key of candidate c of this tile; the same value in the 4 lanes
-      auto score_key = [&](int c) -> unsigned long long {
-        const float4* m = means_s + c * (D / 4);
-        float acc[kOwnPad];
-#pragma unroll
-        for (int k = 0; k < kOwnPad; ++k)
-          acc[k] = k < kOwn ? dot8(qf[k < kOwn ? k : 0], m[(t + 4 * k) * 2], m[(t + 4 * k) * 2 + 1]) : 0.f;
-        // halving tree over the block sums: every level but the last two pairs blocks of
-        // the same lane (block l with block l + half), the last two cross lanes
-#pragma unroll
-        for (int h = kOwnPad / 2; h >= 1; h >>= 1)
-#pragma unroll
-          for (int k = 0; k < h; ++k) acc[k] = __fadd_rn(acc[k], acc[k + h]);
-        float s = acc[0];
-        s = __fadd_rn(s, __shfl_xor_sync(gmask, s, 2));
-        s = __fadd_rn(s, __shfl_xor_sync(gmask, s, 1));
-        return ((unsigned long long)float_key(s) << 32) |
-               (unsigned long long)(0xFFFFFFFFu - (uint32_t)(slot0 + c0 + c));
-      };
-      // The row's list best[0..hist) is kept ordered, largest key first, 0 = empty place.
-      // Lane t keeps the keys of candidates c = 4e + t of this tile in registers (only those
-      // that beat the smallest key of a full list) and the group extracts them largest first:
-      // no shared-memory round trip per candidate.  First tile: straight into the list.
-      // Later tiles: into a scratch list that is then merged with the old one.
-      unsigned long long* best = best_s + (size_t)row * hist;
-      unsigned long long* fresh = wins_s + (size_t)grp * 2 * hist;       // [hist] new keys, [hist] merge output
-      const unsigned long long tau = c0 > 0 ? best[hist - 1] : 0ull;
-      unsigned long long mine[kCandTile / 4];
-#pragma unroll
-      for (int e = 0; e < kCandTile / 4; ++e) {
-        mine[e] = 0ull;
-        if (4 * e < cend) {
-#pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {
-            const int c = 4 * e + cc;
-            const unsigned long long key = score_key(c < cend ? c : 0);
-            if (cc == t && c < cend && key > tau) mine[e] = key;
+      request_b(t, 0);
+      if (nbuf == 2 && q_requested == n + 1) {         // the next tile with candidates, into the other buffer
+        for (; q_next_from < n_tiles; q_next_from += gridDim.x) {
+          const GateTile nx = gate_tile(p, cu, q_next_from, tiles_x, tokens_per_cta);
+          if (nx.valid && nx.max_cand > 0) {
+            request_q(nx, buf ^ 1);
+            q_requested = n + 2;
+            q_next_from += gridDim.x;
+            break;
           }
         }
       }
-      unsigned long long* dst = c0 > 0 ? fresh : best;
-      int n_new = 0;
-      for (; n_new < hist; ++n_new) {
-        unsigned long long top = 0ull;
-        int top_e = 0;
-#pragma unroll
-        for (int e = 0; e < kCandTile / 4; ++e)
-          if (mine[e] > top) { top = mine[e]; top_e = e; }
-        unsigned long long all = top;
-#pragma unroll
-        for (int o = 2; o > 0; o >>= 1) {
-          const unsigned long long other = __shfl_xor_sync(gmask, all, o);
-          all = other > all ? other : all;
+      c.failed = 0;
+      c.mean_ssq_max = 0;
+    }
+
+    // this thread's row
+    const int row = tid;
+    const int ncand = row < nrows ? (t.tok_lo + row / p.G - t.s0) / p.C : 0;     // chunks before the row's own chunk
+    uint2* mylist = lists + (size_t)row * lstride;
+    for (int i = 0; i < list_len; ++i) mylist[i] = make_uint2(0xFFFFFFFFu, 0xFF800000u);   // chunk -1, score -inf
+    float tau = -INFINITY;                                               // smallest score kept: the heap's root
+    float* myscratch = scratch + row * kScratchStride;
+
+    bool q_ok = mbar_wait(smem_u32(&c.q_full[buf]), q_phase);
+    if (!__syncthreads_and(q_ok)) {
+      // the Q tile did not arrive: fetch it with plain loads so that the exact ranking has its rows
+      for (int i = tid; i < kGateRows * (D / 8); i += kGateThreads) {
+        const int r = i / (D / 8), ch = i % (D / 8);
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (r < nrows) {
+          const int tl = r / p.G, hl = r - tl * p.G;
+          val = __ldg(reinterpret_cast<const uint4*>(q + (int64_t)(t.tok_lo + tl - p.win_lo) * p.sq_t +
+                                                     (int64_t)(t.hk * p.G + hl) * p.sq_h + ch * 8));
         }
-        if (all == 0ull) break;                               // nothing left
-        if (top == all) {                                     // keys are unique: exactly one owner
+        *reinterpret_cast<uint4*>(sQ + swz_piece(r, ch, kQBlockBytes)) = val;
+      }
+      if (tid == 0) c.failed = 1;
+      fence_proxy_async_smem();
+      __syncthreads();
+    }
+    const float q_ssq = row_ssq<kHalf, D>(sQ, row, kQBlockBytes);
+
+    for (int c0 = 0; c0 < t.max_cand; c0 += nt) {
+      const int ct = min(nt, t.max_cand - c0);
+      if (!mbar_wait(smem_u32(&c.b_full), b_phase)) c.failed = 1;
+      b_phase ^= 1;
+      if (tid == 0) {
+        tc_fence_after();
+        const uint32_t idesc = idesc_16_f32(kHalf, 128, nt, 0, 0);
+        const uint32_t aQ = smem_u32(sQ), aB = smem_u32(sB);
 #pragma unroll
-          for (int e = 0; e < kCandTile / 4; ++e)
-            if (e == top_e) mine[e] = 0ull;
-          dst[n_new] = all;
+        for (int ks = 0; ks < D / 16; ++ks)
+          mma_ss(tmem, gate_desc(aQ + (ks >> 2) * kQBlockBytes + (ks & 3) * 32),
+                 gate_desc(aB + (ks >> 2) * nt * 128 + (ks & 3) * 32), idesc, ks > 0);
+        tc_commit(smem_u32(&c.mma_done));
+      }
+      // while the tensor core works: largest squared norm over the means of this tile
+      {
+        int ssq_max = 0;
+        for (int cc = tid; cc < ct; cc += kGateThreads)
+          // floats >= 0 order like their bit patterns; +inf and NaN have the largest patterns
+          ssq_max = max(ssq_max, __float_as_int(row_ssq<kHalf, D>(sB, cc, nt * 128)) & 0x7FFFFFFF);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ssq_max = max(ssq_max, __shfl_xor_sync(0xffffffffu, ssq_max, o));
+        if (lane == 0 && ssq_max > 0) atomicMax(&c.mean_ssq_max, ssq_max);
+      }
+      if (!mbar_wait(smem_u32(&c.mma_done), mma_phase)) c.failed = 1;
+      mma_phase ^= 1;
+      tc_fence_after();
+      // ---- estimates of this row: keep the largest in the heap -------------------------------
+      const int cend = min(ct, ncand - c0);                   // this row's candidates in the tile
+      int wend = cend;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) wend = max(wend, __shfl_xor_sync(0xffffffffu, wend, o));
+      for (int col = 0; col < wend; col += 32) {
+        uint32_t v[32];
+        __syncwarp();
+        tmem_ld32(trow + col, v);
+        tmem_wait_ld();
+        uint32_t hits = 0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) hits |= (col + i < cend && __uint_as_float(v[i]) > tau) ? (1u << i) : 0u;
+        if (__any_sync(0xffffffffu, hits != 0)) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<uint4*>(myscratch + i) = make_uint4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+          // every lane walks its own hits; tau rises as it goes
+          while (hits) {
+            const int i = __ffs(hits) - 1;
+            hits &= hits - 1;
+            const float a = myscratch[i];
+            if (a > tau) {
+              heap_replace_root(mylist, list_len, a, (uint32_t)(c0 + col + i));
+              tau = __uint_as_float(mylist[0].y);
+            }
+          }
         }
       }
-      if (c0 > 0 && n_new > 0) {
-        // merge the two ordered lists (every lane follows the same steps, lane 0 writes)
-        __syncwarp(gmask);
-        unsigned long long a = best[0], b = fresh[0];
-        int ia = 0, ib = 0;
-        for (int o = 0; o < hist; ++o) {
-          const bool take = b > a;
-          if (t == 0) fresh[hist + o] = take ? b : a;
-          if (take) { ++ib; b = ib < n_new ? fresh[ib] : 0ull; }
-          else      { ++ia; a = ia < hist ? best[ia] : 0ull; }
+      tc_fence_before();
+      __syncthreads();                                        // the tile and its estimates are consumed
+      if (tid == 0 && c0 + nt < t.max_cand) request_b(t, c0 + nt);
+    }
+
+    // ---- sort the heap: largest score first (equal scores in any order: they are rechecked) ------
+    for (int m = list_len - 1; m > 0; --m) {
+      const uint2 last = mylist[m];
+      mylist[m] = mylist[0];
+      heap_replace_root(mylist, m, __uint_as_float(last.y), last.x);
+    }
+
+    // ---- recheck ------------------------------------------------------------------------------
+    // eps of this row (see the head of this section); inf or NaN sends the row to the exact ranking
+    constexpr float kKappa = (18.f * (D / 16) + 16.f) / 8388608.f;
+    const float eps = kKappa * 1.001f * sqrtf(q_ssq) * sqrtf(__int_as_float(c.mean_ssq_max)) + 7.9e-31f;
+    const int n_keep = min(hist, ncand);
+    int mode = 0, n_surv = 0;                                 // 0: list is exact, 1: rank survivors, 2: rank all candidates
+    if (ncand > 0) {
+      int n_real = 0;
+      for (int i = 0; i < list_len; ++i) n_real += (int32_t)mylist[i].x >= 0;
+      if ((flags & GATE_FORCE_EXACT) || c.failed || n_real < min(ncand, list_len)) {
+        mode = 2;
+      } else {
+        const float eps2 = 2.f * eps;
+        bool amb = (flags & GATE_FORCE_RECHECK) != 0;
+        for (int i = 0; i < n_keep && i + 1 < n_real; ++i)
+          if (!(__uint_as_float(mylist[i].y) - __uint_as_float(mylist[i + 1].y) > eps2)) amb = true;
+        if (amb) {
+          const float theta = __uint_as_float(mylist[n_keep - 1].y) - eps2;
+          while (n_surv < n_real && __uint_as_float(mylist[n_surv].y) >= theta) ++n_surv;
+          // the last place also survives and more candidates exist: the near-ties may go on below the list
+          mode = (n_surv == list_len && ncand > list_len) || !(eps2 < INFINITY) || n_surv < n_keep ? 2 : 1;
         }
-        __syncwarp(gmask);
-        for (int i = t; i < hist; i += 4) best[i] = fresh[hist + i];
-        __syncwarp(gmask);
       }
     }
+    unsigned need = __ballot_sync(0xffffffffu, mode != 0);
+    unsigned long long* lx = c.exact[warp];
+    while (need) {
+      const int src = __ffs(need) - 1;
+      need &= need - 1;
+      const int r = warp * 32 + src;
+      const int r_mode = __shfl_sync(0xffffffffu, mode, src);
+      const int r_total = r_mode == 2 ? __shfl_sync(0xffffffffu, ncand, src) : __shfl_sync(0xffffffffu, n_surv, src);
+      const int r_keep = __shfl_sync(0xffffffffu, n_keep, src);
+      const float r_eps = __shfl_sync(0xffffffffu, eps, src);
+      uint2* rlist = lists + (size_t)r * lstride;
+      lx[lane] = 0ull;
+      lx[lane + 32] = 0ull;
+      __syncwarp();
+      int viol = 0, ratio = 0;
+      for (int base = 0; base < r_total; base += 32) {
+        const int idx = base + lane;
+        unsigned long long key = 0ull;
+        if (idx < r_total) {
+          const int cc = r_mode == 2 ? idx : (int)rlist[idx].x;
+          const float e = contract_score<kHalf, D>(sQ, r, means + ((int64_t)(slot0 + cc) * p.Hkv + t.hk) * D);
+          key = ((unsigned long long)float_key(e) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)(slot0 + cc));
+          if (r_mode == 1 && stats != nullptr) {
+            const float diff = fabsf(__uint_as_float(rlist[idx].y) - e);
+            if (!(diff <= r_eps)) viol = 1;
+            ratio = (int)fminf(diff / r_eps * 65536.f, 1.0e9f);
+          }
+        }
+        // the keys of this batch, in lane order, into the ordered list lx[0, r_keep)
+        unsigned hits = __ballot_sync(0xffffffffu, key > lx[r_keep - 1]);
+        while (hits) {
+          const int l = __ffs(hits) - 1;
+          hits &= hits - 1;
+          const unsigned long long kk = __shfl_sync(0xffffffffu, key, l);
+          const unsigned long long k0 = lane < r_keep ? lx[lane] : 0ull;
+          const unsigned long long k1 = lane + 32 < r_keep ? lx[lane + 32] : 0ull;
+          const int pos = __popc(__ballot_sync(0xffffffffu, k0 > kk)) + __popc(__ballot_sync(0xffffffffu, k1 > kk));
+          if (pos < r_keep) {                                  // uniform; false when the list filled up meanwhile
+            if (lane >= pos && lane + 1 < r_keep) lx[lane + 1] = k0;
+            if (lane + 32 >= pos && lane + 33 < r_keep) lx[lane + 33] = k1;
+            if (lane == 0) lx[pos] = kk;
+          }
+          __syncwarp();
+        }
+      }
+      // the exact ranking replaces the chunk ids of the row's list
+      for (int i = lane; i < hist; i += 32) {
+        const unsigned long long key = i < r_keep ? lx[i] : 0ull;
+        rlist[i].x = key ? (0xFFFFFFFFu - (uint32_t)(key & 0xFFFFFFFFull)) - (uint32_t)slot0 : 0xFFFFFFFFu;
+      }
+      __syncwarp();
+      if (stats != nullptr) {
+        viol = __any_sync(0xffffffffu, viol);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ratio = max(ratio, __shfl_xor_sync(0xffffffffu, ratio, o));
+        if (lane == 0) {
+          atomicAdd(&stats[r_mode == 2 ? 3 : 0], 1);
+          if (r_mode == 1) atomicMax(&stats[1], ratio);
+          if (viol) atomicAdd(&stats[2], 1);
+        }
+      }
+    }
+    __syncthreads();
+
+    for (int i = tid; i < hist * nrows; i += kGateThreads) {
+      const int r = i / nrows, rem = i - r * nrows;
+      const int hl = rem / t.ntok, tl = rem - hl * t.ntok;
+      const int cc = (int32_t)lists[(size_t)(tl * p.G + hl) * lstride + r].x;
+      store_selected(i, cc >= 0 ? slot0 + cc : -1);
+      if (cc >= 0 && list_counts != nullptr) {
+        if (cnt_in_smem) atomicAdd(&cnt_s[cc], 1);
+        else atomicAdd(&list_counts[(int64_t)(slot0 + cc) * p.Hkv + t.hk], 1);
+      }
+    }
+    __syncthreads();                                          // lists, scratch and the Q buffer are free again
+    if (cnt_in_smem && list_counts != nullptr)
+      for (int cc = tid; cc < t.max_cand; cc += kGateThreads) {        // flush and clear this thread's counters
+        const int m = cnt_s[cc];
+        if (m > 0) {
+          atomicAdd(&list_counts[(int64_t)(slot0 + cc) * p.Hkv + t.hk], m);
+          cnt_s[cc] = 0;
+        }
+      }
+    ++n;
   }
+
+  tc_fence_before();
   __syncthreads();
-  // selected[r][head][tok]: `ntok` consecutive ints per (rank, head)
-  for (int i = threadIdx.x; i < hist * nrows; i += kGateThreads) {
-    const int r = i / nrows, rem = i - r * nrows;
-    const int hl = rem / ntok, tl = rem - hl * ntok;
-    const unsigned long long w = best_s[(size_t)(tl * p.G + hl) * hist + r];
-    const int slot = w ? (int)(0xFFFFFFFFu - (uint32_t)(w & 0xFFFFFFFFull)) : -1;
-    selected[(int64_t)r * p.sel_rs + (int64_t)(hk * p.G + hl) * p.Tq + (tok_lo - p.win_lo) + tl] = slot;
-    if (slot >= 0) atomicAdd(&cnt_s[slot - slot0], 1);
-  }
-  __syncthreads();
-  if (list_counts != nullptr)
-    for (int c = threadIdx.x; c < p.mc; c += kGateThreads)
-      if (cnt_s[c] > 0) atomicAdd(&list_counts[(int64_t)(slot0 + c) * p.Hkv + hk], cnt_s[c]);
+  if (warp == 0) tmem_dealloc(tmem, (uint32_t)nt);
 }
 
-static size_t gate_smem_bytes(const Params& p) {
-  return (size_t)kCandTile * (p.D / 4) * sizeof(float4) + (size_t)kGateGroups * 2 * p.hist * 8 +
-         (size_t)kGateRows * p.hist * 8 + (size_t)p.mc * 4;
+struct GateLaunch {
+  int nt, list_len, nbuf, cnt_in_smem, ctas_per_sm;
+  size_t smem;
+};
+
+// Candidate tile, Q buffers, list length and shared memory of a launch: the combination that puts
+// the most CTAs on an SM (more warps hide the latency of the heap updates), then two Q buffers,
+// then the wider candidate tile.  smem == 0: nothing fits.
+GateLaunch gate_launch_config(const Params& p) {
+  GateLaunch best{};
+  const int nblk = (p.D + 63) / 64;
+  const int list_len = p.hist + 1 + kListExtra;
+  const int cnt_in_smem = p.mc <= kCntSmemMax;
+  int want = 32;
+  while (want < p.mc - 1 && want < 256) want *= 2;            // a row has at most mc - 1 candidates
+  for (int nbuf = 2; nbuf >= 1; --nbuf)
+    for (int nt = want; nt >= 32; nt /= 2) {
+      const size_t smem = 1024 + (size_t)nbuf * nblk * kQBlockBytes + (size_t)nblk * nt * 128 +
+                          (size_t)kGateRows * (list_len | 1) * sizeof(uint2) +
+                          (size_t)kGateRows * kScratchStride * sizeof(float) + sizeof(GateCtrl) +
+                          (cnt_in_smem ? (size_t)p.mc * sizeof(int32_t) : 0);
+      if (smem > 227 * 1024) continue;
+      int ctas = (int)((228 * 1024) / (smem + 1024));         // 1 KB per CTA is reserved by the system
+      if (ctas > 512 / nt) ctas = 512 / nt;                   // tensor memory columns
+      if (ctas > 4) ctas = 4;
+      if (ctas < 1) continue;
+      if (ctas > best.ctas_per_sm) best = GateLaunch{nt, list_len, nbuf, cnt_in_smem, ctas, smem};
+    }
+  return best;
 }
 
-cudaError_t launch_gate_topk(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* means,
-                             const int32_t* cu, int32_t* selected, int32_t* list_counts,
-                             cudaStream_t st) {
+}  // namespace
+
+bool make_tile_map(CUtensorMap* m, bool fp16, int D, const __nv_bfloat16* base, int64_t T, int H, int64_t st,
+                   int64_t sh, int box_heads, int box_rows);
+
+bool gate_topk_fits(const Params& p) { return p.hist <= 0 || gate_launch_config(p).smem != 0; }
+
+cudaError_t launch_gate_topk_stats(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* means,
+                                   const int32_t* cu, int32_t* selected, int32_t* list_counts, int32_t* stats,
+                                   int flags, cudaStream_t st) {
   int tokens_per_cta = kGateRows / p.G;
-  if (tokens_per_cta < 1) tokens_per_cta = 1;
-  const size_t smem = gate_smem_bytes(p);
-  if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
-  void (*kernel)(Params, int, const __nv_bfloat16*, const __nv_bfloat16*, const int32_t*, int32_t*, int32_t*);
+  if (tokens_per_cta < 1) return cudaErrorInvalidConfiguration;
+  const GateLaunch g = gate_launch_config(p);
+  if (g.smem == 0) return cudaErrorInvalidConfiguration;
+  CUtensorMap mq, mm;
+  if (!make_tile_map(&mq, p.fp16 != 0, p.D, q, p.Tq, p.Hq, p.sq_t, p.sq_h, p.G, tokens_per_cta) ||
+      !make_tile_map(&mm, p.fp16 != 0, p.D, means, p.slots, p.Hkv, (int64_t)p.Hkv * p.D, p.D, 1, g.nt))
+    return cudaErrorNotSupported;
+  void (*kernel)(Params, CUtensorMap, CUtensorMap, int, int, int, int, int, const __nv_bfloat16*, const __nv_bfloat16*,
+                 const int32_t*, int32_t*, int32_t*, int32_t*, int);
   switch (p.D) {
     case 64:  kernel = p.fp16 ? gate_topk_kernel<true, 64>  : gate_topk_kernel<false, 64>;  break;
     case 96:  kernel = p.fp16 ? gate_topk_kernel<true, 96>  : gate_topk_kernel<false, 96>;  break;
@@ -331,11 +668,24 @@ cudaError_t launch_gate_topk(const Params& p, const __nv_bfloat16* q, const __nv
     case 256: kernel = p.fp16 ? gate_topk_kernel<true, 256> : gate_topk_kernel<false, 256>; break;
     default: return cudaErrorInvalidValue;
   }
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
   if (e != cudaSuccess) return e;
-  dim3 grid(cdiv_i(p.max_seqlen, tokens_per_cta), p.Hkv, p.B);
-  kernel<<<grid, kGateThreads, smem, st>>>(p, tokens_per_cta, q, means, cu, selected, list_counts);
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t n_tiles = (int64_t)cdiv_i(p.max_seqlen, tokens_per_cta) * p.Hkv * p.B;
+  if (n_tiles >= ((int64_t)1 << 31)) return cudaErrorInvalidConfiguration;
+  int64_t grid = (int64_t)sms * g.ctas_per_sm;
+  if (grid > n_tiles) grid = n_tiles;
+  kernel<<<(int)grid, kGateThreads, g.smem, st>>>(p, mq, mm, tokens_per_cta, g.nt, g.list_len, g.nbuf, g.cnt_in_smem, q,
+                                                  means, cu, selected, list_counts, stats, flags);
   return cudaGetLastError();
+}
+
+cudaError_t launch_gate_topk(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* means,
+                             const int32_t* cu, int32_t* selected, int32_t* list_counts,
+                             cudaStream_t st) {
+  return launch_gate_topk_stats(p, q, means, cu, selected, list_counts, nullptr, 0, st);
 }
 
 }  // namespace moba

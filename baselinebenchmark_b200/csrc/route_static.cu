@@ -22,7 +22,7 @@
 namespace moba {
 namespace {
 
-constexpr size_t kStaticMeanElems = (size_t)2 << 20;     // bf16 elements: slots * kv heads * 128 <= 2 Mi (4 MiB)
+constexpr size_t kStaticMeanElems = (size_t)2 << 20;     // 16-bit elements: slots * kv heads * head_dim <= 2 Mi (4 MiB)
 
 static __device__ __align__(256) __nv_bfloat16 g_static_means[kStaticMeanElems];
 
@@ -32,7 +32,10 @@ __nv_bfloat16* g_means_addr[kMaxDevices] = {nullptr};
 
 // In host code `g_static_means` is only a handle for the symbol, not a device
 // address.  The address on the current device is asked for once per device and
-// remembered; the kernels receive that pointer.
+// remembered; the kernels receive that pointer.  cudaDeviceReset unloads the
+// module and with it the array: a process that resets a device must not call
+// this entry point on that device afterwards (the remembered address would be
+// stale).
 cudaError_t static_means_address(__nv_bfloat16** out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
@@ -59,6 +62,7 @@ extern "C" int moba_route_static(const moba_problem_t* p, const void* q, const v
   const int rc = moba_problem_dims(p, &dims);
   if (rc != MOBA_OK) return rc;
   if (!q || !k || !cu_seqlens || !selected) return MOBA_E_NULL;
+  if (((uintptr_t)q | (uintptr_t)k) & 15) return MOBA_E_ALIGN;     // both are read with 16-byte loads
   if (dims.hist <= 0) return MOBA_OK;                      // nothing to select: `selected` has no rows
   if ((size_t)dims.slots * (size_t)p->num_kv_heads * (size_t)p->head_dim > kStaticMeanElems) return MOBA_E_STATIC_LIMIT;
   __nv_bfloat16* means = nullptr;

@@ -23,7 +23,6 @@ __all__ = ["parallel_moba", "moba_attn_varlen", "moba_forward", "make_problem", 
 
 #: head dims of the reference's benchmark suite (benchmarks/moba_compare.py:63, :70)
 HEAD_DIMS = (64, 96, 128, 256)
-_workspaces: dict = {}
 
 
 def _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, windowed: bool = False) -> None:
@@ -102,12 +101,11 @@ def workspace_bytes(problem, limit: Optional[int] = None) -> int:
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """One grow-only scratch buffer per device, reused stream-ordered across calls."""
-    ws = _workspaces.get(device)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
-        _workspaces[device] = ws
-    return ws
+    """Scratch for one call, taken from torch's caching allocator like the reference's own
+    per-call buffers (parallel.py:283-374): the allocator orders reuse by stream, so calls on
+    unordered streams never share a buffer, and a buffer allocated while a CUDA graph is
+    being captured belongs to that graph's memory pool and stays valid for its replays."""
+    return torch.empty(nbytes, dtype=torch.uint8, device=device)
 
 
 def moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, *,
@@ -122,7 +120,9 @@ def moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, *,
     [q_token_begin, q_token_begin + q.shape[0]), a window that starts and ends on
     chunk boundaries, while k, v and cu_seqlens describe every token; outputs
     cover the window.  `workspace_limit` (bytes) bounds the scratch memory: the kv heads
-    are then processed in groups, with identical results."""
+    are then processed in groups, with identical results.  Scratch memory is allocated per
+    call through torch's caching allocator unless `workspace` (a uint8 tensor the caller
+    keeps alive and does not share between unordered streams) is given."""
     _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, windowed=q_token_begin is not None)
     out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     prob = make_problem(q, k, v, out, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, attend_impl,
@@ -151,8 +151,8 @@ def moba_backward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, o
     """Gradients (dq, dk, dv) of the operator for the output gradient `dout`, given what
     `moba_forward(..., return_lse=True, return_selected=True)` returned
     (MixedAttention.backward, parallel.py:149-250: merged LSE and output, constant selection).
-    `attend_impl` picks the dq kernel (tcgen05 at head_dim 64 and 128 by default, else
-    mma.sync); dk and dv run on mma.sync either way."""
+    `attend_impl` picks the dq and dk/dv kernels: tcgen05 at head_dim 64 and 128 by default,
+    mma.sync otherwise (head_dim 96, or when asked for)."""
     _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)
     if q.shape[2] > 128:
         raise NotImplementedError("the backward is built for head_dim <= 128")

@@ -11,7 +11,9 @@
  *   - every entry point is stream ordered on `stream` (a cudaStream_t passed as
  *     void*), performs no device-to-host read and no allocation, so a caller
  *     may capture it in a CUDA graph, exactly like the reference path
- *     (parallel.py:262-275);
+ *     (parallel.py:262-275).  The one exception is moba_forward_host, which
+ *     creates two copy streams per device on first use and short-lived events
+ *     on every call: it is not meant to be captured;
  *   - return value: 0 success, < 0 invalid argument (MOBA_E_*), > 0 a
  *     cudaError_t raised by a launch or a copy.  Nothing throws or aborts;
  *   - tensors are bf16 or fp16 (moba_problem.dtype), head_dim 64, 96, 128 or 256
@@ -171,6 +173,21 @@ int moba_chunk_means(const moba_problem_t* p, const void* k, const int32_t* cu_s
 int moba_gate_topk(const moba_problem_t* p, const void* q, const void* means,
                    const int32_t* cu_seqlens, int32_t* selected, int32_t* list_counts,
                    void* stream);
+
+/* moba_gate_topk with its decision path observable and steerable, for tests and profiling
+ * (the reference kernel has one path only, routing.py:1056-1182).  The kernel estimates all
+ * scores of a row on the tensor core and evaluates in the reference-compatible fp32 order
+ * only the candidates the estimate cannot rank with certainty; `selected` is the same
+ * whatever path a row takes.
+ *   stats  optional int32[4], added to (zero it first):
+ *          [0] rows whose near-ties were scored again, [1] largest |estimate - exact| / bound
+ *          seen while doing so, in units of 2^-16, [2] rows where that ratio exceeded 1 (never
+ *          expected), [3] rows ranked over all their candidates
+ *   flags  0 normal; 1 rank every row over all candidates in the exact order (no estimate
+ *          used); 2 score the kept candidates of every row again. */
+int moba_gate_topk_stats(const moba_problem_t* p, const void* q, const void* means,
+                         const int32_t* cu_seqlens, int32_t* selected, int32_t* list_counts,
+                         int32_t* stats, int32_t flags, void* stream);
 
 /* Grouping of the routed rows: replaces _build_sparse_routes_device_triton
  * (routing.py:1642-1718), grouped by (slot, kv head) instead of (slot, q head)

@@ -53,6 +53,21 @@ def gate(prob, q, m, cu):
     return sel, counts
 
 
+def gate_stats(prob, q, m, cu, flags=0):
+    """moba_gate_topk_stats: (selected, list counts, stats int32[4] as numpy)."""
+    d = dims_of(prob)
+    tq = prob.q_tokens if prob.q_tokens > 0 else prob.total_tokens
+    sel = torch.full((max(d.hist, 0), prob.num_q_heads, tq), -9, dtype=torch.int32, device="cuda")
+    counts = torch.zeros(d.lists, dtype=torch.int32, device="cuda")
+    stats = torch.zeros(4, dtype=torch.int32, device="cuda")
+    if d.hist > 0:
+        _lib.check(_lib.lib().moba_gate_topk_stats(C.byref(prob), q.data_ptr(), m.data_ptr(), cu.data_ptr(),
+                                                   sel.data_ptr(), counts.data_ptr(), stats.data_ptr(), flags,
+                                                   stream()))
+    torch.cuda.synchronize()
+    return sel, counts, stats.cpu().numpy()
+
+
 def compact(prob, cu, sel, counts, tile_rows):
     d = dims_of(prob)
     offsets = torch.empty(d.lists + 1, dtype=torch.int32, device="cuda")

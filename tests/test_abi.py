@@ -76,6 +76,44 @@ def test_backward_argument_checks(lib):
     assert lib.moba_backward(C.byref(_problem()), *([None] * 12), 0, None) == -4             # null pointers
 
 
+def test_misaligned_pointers_are_refused_before_any_launch(lib):
+    """q, k, v and the means are read with 16-byte loads (and K/V through TMA descriptors): a
+    base pointer that is not 16-byte aligned returns MOBA_E_ALIGN from every entry point that
+    would dereference it.  The check comes before anything touches a device, so fake addresses do."""
+    ok, off = 0x10000, 0x10002
+    prob = C.byref(_problem())
+    assert lib.moba_forward(prob, off, ok, ok, ok, ok, None, None, ok, 1 << 40, None) == -6
+    assert lib.moba_forward(prob, ok, ok, off, ok, ok, None, None, ok, 1 << 40, None) == -6
+    assert lib.moba_chunk_means(prob, off, ok, ok, None) == -6
+    assert lib.moba_chunk_means(prob, ok, ok, off, None) == -6
+    assert lib.moba_gate_topk(prob, off, ok, ok, ok, None, None) == -6
+    assert lib.moba_gate_topk(prob, ok, off, ok, ok, None, None) == -6
+    assert lib.moba_gate_topk_stats(prob, off, ok, ok, ok, None, None, 0, None) == -6
+    assert lib.moba_route_static(prob, off, ok, ok, ok, None) == -6
+    assert lib.moba_route_static(prob, ok, off, ok, ok, None) == -6
+    need = C.c_size_t(0)
+    assert lib.moba_backward_workspace_size(prob, C.byref(need)) == 0
+    for bad in range(3):                                                 # q, k, v in turn
+        ptrs = [ok, ok, ok]
+        ptrs[bad] = off
+        assert lib.moba_backward(prob, *ptrs, ok, ok, ok, ok, ok, ok, ok, ok, ok, need.value, None) == -6
+
+
+def test_launch_limits_are_refused_by_the_problem_check(lib):
+    """Shapes the launchers could not run are refused up front instead of failing at launch:
+    more sequences than a grid dimension holds, and dense-stage work items beyond int32."""
+    assert lib.moba_problem_check(C.byref(_problem(batch=65536, total_tokens=65536 * 16, max_seqlen=16, chunk_size=8))) == -2
+    assert lib.moba_problem_check(C.byref(_problem(batch=65535, total_tokens=65535 * 16, max_seqlen=16, chunk_size=8))) == 0
+    # max_seqlen far above the real lengths: slots * heads * tiles overflows the item counter
+    big = _problem(batch=4096, total_tokens=1 << 20, max_seqlen=1 << 22, chunk_size=256, num_q_heads=128, num_kv_heads=1)
+    assert lib.moba_problem_check(C.byref(big)) == -2
+    # the largest chunk table (16384 chunks per sequence) with top-k 64 still fits the gating kernel
+    stride = dict(q_stride_token=2048, q_stride_head=256, k_stride_token=2048, k_stride_head=256,
+                  v_stride_token=2048, v_stride_head=256, o_stride_token=2048, o_stride_head=256)
+    wide = _problem(total_tokens=16384 * 16, max_seqlen=16384 * 16, chunk_size=16, topk=64, head_dim=256, attend_impl=1, **stride)
+    assert lib.moba_problem_check(C.byref(wide)) == 0
+
+
 def test_dims_follow_reference_formulas(lib):
     d = _lib.Dims()
     assert lib.moba_problem_dims(C.byref(_problem()), C.byref(d)) == 0
