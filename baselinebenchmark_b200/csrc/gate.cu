@@ -21,6 +21,7 @@
 //          with blocks of +0.0 to the next one.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+#include "topk_network.cuh"
 
 namespace moba {
 
@@ -130,13 +131,17 @@ cudaError_t launch_chunk_means(const Params& p, const __nv_bfloat16* k, const in
 //
 //   1. estimate on the tensor core.  A row tile is 128 rows: the tokens of a
 //      tile x the query heads of one kv head.  Persistent CTAs (128 threads)
-//      walk the row tiles; TMA brings the Q rows of a tile (the next tile's
-//      while the current one is processed) and a tile of up to 256 candidate
-//      means into shared memory in the 128-byte swizzled K-major layout,
-//      tcgen05.mma multiplies them (fp32 accumulators in tensor memory, one
-//      lane per row), and thread r reads the estimates a_c of its row 32 at a
-//      time and keeps the hist + 4 largest in a min-heap (its root is the
-//      threshold a candidate has to beat), sorted when the row is complete.
+//      walk the row tiles; TMA brings the Q rows of a tile and a tile of up to
+//      256 candidate means into shared memory in the 128-byte swizzled K-major
+//      layout, tcgen05.mma multiplies them (fp32 accumulators in tensor
+//      memory, one lane per row), and thread r reads the estimates a_c of its
+//      row 32 at a time and keeps the L = hist + 1 (+ 3 when a row can have
+//      more than 32 candidates) largest, sorted, in shared memory.  For
+//      L <= 32 the 32 estimates become order-preserving integer keys whose
+//      five lowest bits hold the position (a change of less than 2^-18 of
+//      the score, counted in eps), a compare-exchange network over the 32
+//      registers brings the largest 8, 16 or 32 keys to the front, and they
+//      are merged with the list; longer lists are kept as a min-heap.
 //   2. recheck.  With e_c the score in the contract order, |a_c - e_c| <= eps
 //      for every candidate of the row (bound below).  If neighbours in the
 //      sorted list differ by more than 2 eps down to the entry after the
@@ -158,8 +163,8 @@ cudaError_t launch_chunk_means(const Params& p, const __nv_bfloat16* k, const in
 // products and the accumulator are aligned to the largest exponent and
 // truncated; assuming no more than one unit of the 24-bit significand of that
 // exponent is lost per term and one more when the sum is normalised, a step
-// loses <= 18 * 2^-23 * S.  Together eps = (18 * D/16 + 16) * 2^-23 * S with
-// S <= |q|_2 |m|_2 (Cauchy-Schwarz, the largest norm over the staged means),
+// loses <= 18 * 2^-23 * S.  Together eps = ((18 * D/16 + 16) * 2^-23 + 2^-18) * S
+// with S <= |q|_2 |m|_2 (Cauchy-Schwarz, the largest norm over the staged means),
 // plus 2^-100 for products flushed to zero.  The recheck step measures
 // |a_c - e_c| / eps on every candidate it scores again (optional statistics
 // output), so the assumption is observable: on random inputs the largest
@@ -179,6 +184,9 @@ constexpr int kScratchStride = 36;        // floats per row of the score scratch
 __device__ __forceinline__ uint32_t float_key(float x) {      // routing.py:778-784
   const uint32_t b = __float_as_uint(x);
   return b ^ ((b & 0x80000000u) ? 0xFFFFFFFFu : 0x80000000u);
+}
+__device__ __forceinline__ float key_float(uint32_t k) {      // inverse of float_key
+  return __uint_as_float(k ^ ((k & 0x80000000u) ? 0x80000000u : 0xFFFFFFFFu));
 }
 __device__ __forceinline__ float dot8(const float (&q)[8], const float (&m)[8]) {
   float s = __fmul_rn(q[0], m[0]);
@@ -203,8 +211,7 @@ struct GateCtrl {
   uint64_t b_full;
   uint64_t mma_done;
   uint32_t tmem_slot;
-  int32_t failed;                          // a bounded wait gave up in this tile: its rows are ranked exactly
-  int32_t mean_ssq_max;                    // largest squared norm over the staged means (float bits, >= 0)
+  int32_t mean_ssq_max;                    // largest squared norm over the means seen so far of this (sequence, kv head)
   unsigned long long exact[kGateThreads / 32][64];   // per warp: keys of the row being ranked exactly
 };
 
@@ -212,10 +219,23 @@ struct GateCtrl {
 template <bool kHalf, int D>
 __device__ __forceinline__ float row_ssq(const unsigned char* tile, int r, int block_bytes) {
   float ssq = 0.f;
-#pragma unroll
+#pragma unroll 4
   for (int ch = 0; ch < D / 8; ++ch) {
     float f[8];
     unpack8<kHalf>(*reinterpret_cast<const uint4*>(tile + swz_piece(r, ch, block_bytes)), f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ssq = __fmaf_rn(f[e], f[e], ssq);
+  }
+  return ssq;
+}
+// Squared norm of the D values at `row` (global memory).
+template <bool kHalf, int D>
+__device__ __forceinline__ float global_ssq(const __nv_bfloat16* row) {
+  float ssq = 0.f;
+#pragma unroll 4
+  for (int ch = 0; ch < D / 8; ++ch) {
+    float f[8];
+    unpack8<kHalf>(__ldg(reinterpret_cast<const uint4*>(row + ch * 8)), f);
 #pragma unroll
     for (int e = 0; e < 8; ++e) ssq = __fmaf_rn(f[e], f[e], ssq);
   }
@@ -249,9 +269,9 @@ __device__ __forceinline__ float contract_score(const unsigned char* sQ, int r, 
   return b[0];
 }
 
-// Min-heap of {chunk, score bits} on the score: `heap[0]` is the smallest score kept.  Replaces the
-// root by (a, chunk) and restores the heap.
-__device__ __forceinline__ void heap_replace_root(uint2* heap, int n, float a, uint32_t chunk) {
+// Min-heap of {chunk, key} on the key: `heap[0]` is the smallest key kept.  Replaces the
+// root by (key, chunk) and restores the heap.
+__device__ __forceinline__ void heap_replace_root(uint2* heap, int n, uint32_t key, uint32_t chunk) {
   int k = 0;
   for (;;) {
     const int l = 2 * k + 1;
@@ -260,16 +280,21 @@ __device__ __forceinline__ void heap_replace_root(uint2* heap, int n, float a, u
     int s = l;
     if (l + 1 < n) {
       const uint2 right = heap[l + 1];
-      if (__uint_as_float(right.y) < __uint_as_float(child.y)) { child = right; s = l + 1; }
+      if (right.y < child.y) { child = right; s = l + 1; }
     }
-    if (!(__uint_as_float(child.y) < a)) break;
+    if (!(child.y < key)) break;
     heap[k] = child;
     k = s;
   }
-  heap[k] = make_uint2(chunk, __float_as_uint(a));
+  heap[k] = make_uint2(chunk, key);
 }
 
 enum { GATE_FORCE_EXACT = 1, GATE_FORCE_RECHECK = 2 };
+
+// Resident CTAs per SM the register budget is set for: four with the narrow network (its
+// working set is small and the kernel is bound by the latency of dependent instructions, which
+// more warps hide), three otherwise (a fourth would spill the 32 keys of the wide network).
+template <int kW> constexpr int kGateMinCtas = kW == 8 ? 4 : 3;
 
 struct GateTile {
   int valid, b, hk, s0, tok_lo, ntok, max_cand;
@@ -293,8 +318,9 @@ __device__ __forceinline__ GateTile gate_tile(const Params& p, const int32_t* __
   return t;
 }
 
-template <bool kHalf, int D>
-__global__ void __launch_bounds__(kGateThreads)
+// kW: width of the compare-exchange network (8, 16 or 32 >= list_len), 0: lists longer than 32 (min-heap)
+template <bool kHalf, int D, int kW>
+__global__ void __launch_bounds__(kGateThreads, kGateMinCtas<kW>)
 gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_m,
                  int tokens_per_cta, int nt, int list_len, int nbuf, int cnt_in_smem,
                  const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ means,
@@ -309,8 +335,9 @@ gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, con
   unsigned char* sQ0 = smem;                                             // nbuf x kNBlk blocks [128][64]
   unsigned char* sB = sQ0 + (size_t)nbuf * kNBlk * kQBlockBytes;        // kNBlk blocks [nt][64]
   uint2* lists = reinterpret_cast<uint2*>(sB + (size_t)kNBlk * nt * 128);   // [128][lstride] {chunk, score bits}
-  float* scratch = reinterpret_cast<float*>(lists + (size_t)kGateRows * lstride);   // [128][36]
-  GateCtrl& c = *reinterpret_cast<GateCtrl*>(scratch + kGateRows * kScratchStride);
+  float* scratch = reinterpret_cast<float*>(lists + (size_t)kGateRows * lstride);   // [128][36], absent when unused
+  const bool has_scratch = kW == 0 || p.mc - 1 > 32;   // one 32-candidate step per row needs no merge
+  GateCtrl& c = *reinterpret_cast<GateCtrl*>(scratch + (has_scratch ? kGateRows * kScratchStride : 0));
   int32_t* cnt_s = reinterpret_cast<int32_t*>(&c + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -323,6 +350,7 @@ gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, con
     mbar_init(smem_u32(&c.q_full[1]), 1);
     mbar_init(smem_u32(&c.b_full), 1);
     mbar_init(smem_u32(&c.mma_done), 1);
+    c.mean_ssq_max = 0;
     fence_barrier_init();
     prefetch_tmap(&tmap_q);
     prefetch_tmap(&tmap_m);
@@ -343,6 +371,8 @@ gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, con
   int q_requested = 0, q_next_from = blockIdx.x;
   uint32_t b_phase = 0, mma_phase = 0;
   int n = 0;                                           // tiles with candidates processed so far
+  // mean norms: the (sequence, kv head) the running maximum belongs to and the candidates it covers
+  int norm_b = -1, norm_hk = -1, norm_covered = 0;
 
   auto request_q = [&](const GateTile& t, int buf) {
     const uint32_t bar = smem_u32(&c.q_full[buf]);
@@ -396,40 +426,47 @@ gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, con
           }
         }
       }
-      c.failed = 0;
-      c.mean_ssq_max = 0;
+    }
+
+    // Largest squared norm over the means this tile's rows can meet: kept per (sequence, kv head)
+    // and extended when a tile reaches further than the ones before it (a CTA walks the tiles
+    // of a sequence in order, so every mean is read once per CTA).
+    if (t.b != norm_b || t.hk != norm_hk || t.max_cand > norm_covered) {
+      const bool fresh = t.b != norm_b || t.hk != norm_hk;
+      if (fresh) {                                   // every thread is past its last read of the old maximum
+        if (tid == 0) c.mean_ssq_max = 0;
+        __syncthreads();
+      }
+      int ssq_max = 0;
+      for (int cc = (fresh ? 0 : norm_covered) + tid; cc < t.max_cand; cc += kGateThreads)
+        // floats >= 0 order like their bit patterns; +inf and NaN have the largest patterns
+        ssq_max = max(ssq_max, __float_as_int(global_ssq<kHalf, D>(means + ((int64_t)(slot0 + cc) * p.Hkv + t.hk) * D)) &
+                                   0x7FFFFFFF);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ssq_max = max(ssq_max, __shfl_xor_sync(0xffffffffu, ssq_max, o));
+      if (lane == 0 && ssq_max > 0) atomicMax(&c.mean_ssq_max, ssq_max);
+      __syncthreads();
+      norm_b = t.b;
+      norm_hk = t.hk;
+      norm_covered = t.max_cand;
     }
 
     // this thread's row
     const int row = tid;
     const int ncand = row < nrows ? (t.tok_lo + row / p.G - t.s0) / p.C : 0;     // chunks before the row's own chunk
     uint2* mylist = lists + (size_t)row * lstride;
-    for (int i = 0; i < list_len; ++i) mylist[i] = make_uint2(0xFFFFFFFFu, 0xFF800000u);   // chunk -1, score -inf
-    float tau = -INFINITY;                                               // smallest score kept: the heap's root
-    float* myscratch = scratch + row * kScratchStride;
+    for (int i = 0; i < list_len; ++i) mylist[i] = make_uint2(0xFFFFFFFFu, 0u);   // chunk -1, key 0: empty place
+    uint32_t tau = 0;                                  // smallest key kept (heap root / last place); 0 while places are free
+    uint32_t* myscratch = reinterpret_cast<uint32_t*>(scratch + row * kScratchStride);
 
-    bool q_ok = mbar_wait(smem_u32(&c.q_full[buf]), q_phase);
-    if (!__syncthreads_and(q_ok)) {
-      // the Q tile did not arrive: fetch it with plain loads so that the exact ranking has its rows
-      for (int i = tid; i < kGateRows * (D / 8); i += kGateThreads) {
-        const int r = i / (D / 8), ch = i % (D / 8);
-        uint4 val = make_uint4(0, 0, 0, 0);
-        if (r < nrows) {
-          const int tl = r / p.G, hl = r - tl * p.G;
-          val = __ldg(reinterpret_cast<const uint4*>(q + (int64_t)(t.tok_lo + tl - p.win_lo) * p.sq_t +
-                                                     (int64_t)(t.hk * p.G + hl) * p.sq_h + ch * 8));
-        }
-        *reinterpret_cast<uint4*>(sQ + swz_piece(r, ch, kQBlockBytes)) = val;
-      }
-      if (tid == 0) c.failed = 1;
-      fence_proxy_async_smem();
-      __syncthreads();
-    }
-    const float q_ssq = row_ssq<kHalf, D>(sQ, row, kQBlockBytes);
+    // A wait that gives up is remembered by the thread: its row is then ranked exactly, from Q rows
+    // read with plain loads (see the recheck).
+    bool failed = !mbar_wait(smem_u32(&c.q_full[buf]), q_phase);
+    const float q_ssq = failed ? 0.f : row_ssq<kHalf, D>(sQ, row, kQBlockBytes);
 
     for (int c0 = 0; c0 < t.max_cand; c0 += nt) {
       const int ct = min(nt, t.max_cand - c0);
-      if (!mbar_wait(smem_u32(&c.b_full), b_phase)) c.failed = 1;
+      if (!mbar_wait(smem_u32(&c.b_full), b_phase)) failed = true;
       b_phase ^= 1;
       if (tid == 0) {
         tc_fence_after();
@@ -441,17 +478,7 @@ gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, con
                  gate_desc(aB + (ks >> 2) * nt * 128 + (ks & 3) * 32), idesc, ks > 0);
         tc_commit(smem_u32(&c.mma_done));
       }
-      // while the tensor core works: largest squared norm over the means of this tile
-      {
-        int ssq_max = 0;
-        for (int cc = tid; cc < ct; cc += kGateThreads)
-          // floats >= 0 order like their bit patterns; +inf and NaN have the largest patterns
-          ssq_max = max(ssq_max, __float_as_int(row_ssq<kHalf, D>(sB, cc, nt * 128)) & 0x7FFFFFFF);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ssq_max = max(ssq_max, __shfl_xor_sync(0xffffffffu, ssq_max, o));
-        if (lane == 0 && ssq_max > 0) atomicMax(&c.mean_ssq_max, ssq_max);
-      }
-      if (!mbar_wait(smem_u32(&c.mma_done), mma_phase)) c.failed = 1;
+      if (!mbar_wait(smem_u32(&c.mma_done), mma_phase)) failed = true;
       mma_phase ^= 1;
       tc_fence_after();
       // ---- estimates of this row: keep the largest in the heap -------------------------------
@@ -464,10 +491,55 @@ gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, con
         __syncwarp();
         tmem_ld32(trow + col, v);
         tmem_wait_ld();
-        uint32_t hits = 0;
+        // estimates -> order-preserving keys; places past the row's candidates get key 0
+        const int rem = cend - col;
+        uint32_t vmax = 0;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) hits |= (col + i < cend && __uint_as_float(v[i]) > tau) ? (1u << i) : 0u;
-        if (__any_sync(0xffffffffu, hits != 0)) {
+        for (int i = 0; i < 32; ++i) {
+          uint32_t key = float_key(__uint_as_float(v[i]));
+          if (kW > 0) key = (key & ~31u) | (uint32_t)(31 - i);         // position in the low bits: earlier wins ties
+          v[i] = i < rem ? key : 0u;
+          vmax = max(vmax, v[i]);
+        }
+        if (!__any_sync(0xffffffffu, vmax > tau)) continue;             // nothing here enters any list of the warp
+        const uint32_t chunk0 = (uint32_t)(c0 + col);
+        if (kW > 0) {
+          topk::top_of_32<(kW > 0 ? kW : 32)>(v);
+          if (c0 == 0 && col == 0) {
+            // first candidates of the row: the list is the head of the sorted keys
+#pragma unroll
+            for (int i = 0; i < kW; ++i)
+              if (i < list_len) mylist[i] = make_uint2(v[i] ? chunk0 + 31u - (v[i] & 31u) : 0xFFFFFFFFu, v[i]);
+          } else {
+            // s_t enters the list iff it beats the entry t places from the end (both are sorted)
+            int j = 0;
+#pragma unroll
+            for (int t2 = 0; t2 < kW; ++t2)
+              if (t2 < list_len) j += v[t2] > mylist[list_len - 1 - t2].y;
+            if (j > 0) {
+#pragma unroll
+              for (int i = 0; i < kW; i += 4)
+                *reinterpret_cast<uint4*>(myscratch + i) = make_uint4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+              // in-place merge from the bottom: the smaller of the two tails goes to `pos`; equal keys
+              // keep the list's entry (an earlier chunk) above
+              int i = list_len - j - 1, jj = j - 1;
+              for (int pos = list_len - 1; jj >= 0; --pos) {
+                const uint32_t sk = myscratch[jj];
+                if (i >= 0 && mylist[i].y < sk) {
+                  mylist[pos] = mylist[i];
+                  --i;
+                } else {
+                  mylist[pos] = make_uint2(chunk0 + 31u - (sk & 31u), sk);
+                  --jj;
+                }
+              }
+            }
+          }
+          tau = mylist[list_len - 1].y;
+        } else {
+          uint32_t hits = 0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) hits |= v[i] > tau ? (1u << i) : 0u;
 #pragma unroll
           for (int i = 0; i < 32; i += 4)
             *reinterpret_cast<uint4*>(myscratch + i) = make_uint4(v[i], v[i + 1], v[i + 2], v[i + 3]);
@@ -475,45 +547,48 @@ gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, con
           while (hits) {
             const int i = __ffs(hits) - 1;
             hits &= hits - 1;
-            const float a = myscratch[i];
-            if (a > tau) {
-              heap_replace_root(mylist, list_len, a, (uint32_t)(c0 + col + i));
-              tau = __uint_as_float(mylist[0].y);
+            const uint32_t key = myscratch[i];
+            if (key > tau) {
+              heap_replace_root(mylist, list_len, key, chunk0 + (uint32_t)i);
+              tau = mylist[0].y;
             }
           }
         }
       }
       tc_fence_before();
-      __syncthreads();                                        // the tile and its estimates are consumed
-      if (tid == 0 && c0 + nt < t.max_cand) request_b(t, c0 + nt);
+      if (c0 + nt < t.max_cand) {
+        __syncthreads();                                      // the means and their estimates are consumed
+        if (tid == 0) request_b(t, c0 + nt);
+      }
     }
 
-    // ---- sort the heap: largest score first (equal scores in any order: they are rechecked) ------
-    for (int m = list_len - 1; m > 0; --m) {
-      const uint2 last = mylist[m];
-      mylist[m] = mylist[0];
-      heap_replace_root(mylist, m, __uint_as_float(last.y), last.x);
-    }
+    // ---- a heap is sorted now: largest key first (equal scores in any order: they are rechecked) ----
+    if (kW == 0)
+      for (int m = list_len - 1; m > 0; --m) {
+        const uint2 last = mylist[m];
+        mylist[m] = mylist[0];
+        heap_replace_root(mylist, m, last.y, last.x);
+      }
 
     // ---- recheck ------------------------------------------------------------------------------
     // eps of this row (see the head of this section); inf or NaN sends the row to the exact ranking
-    constexpr float kKappa = (18.f * (D / 16) + 16.f) / 8388608.f;
+    constexpr float kKappa = (18.f * (D / 16) + 16.f) / 8388608.f + (kW > 0 ? 1.f / 262144.f : 0.f);
     const float eps = kKappa * 1.001f * sqrtf(q_ssq) * sqrtf(__int_as_float(c.mean_ssq_max)) + 7.9e-31f;
     const int n_keep = min(hist, ncand);
     int mode = 0, n_surv = 0;                                 // 0: list is exact, 1: rank survivors, 2: rank all candidates
     if (ncand > 0) {
       int n_real = 0;
       for (int i = 0; i < list_len; ++i) n_real += (int32_t)mylist[i].x >= 0;
-      if ((flags & GATE_FORCE_EXACT) || c.failed || n_real < min(ncand, list_len)) {
+      if ((flags & GATE_FORCE_EXACT) || failed || n_real < min(ncand, list_len)) {
         mode = 2;
       } else {
         const float eps2 = 2.f * eps;
         bool amb = (flags & GATE_FORCE_RECHECK) != 0;
         for (int i = 0; i < n_keep && i + 1 < n_real; ++i)
-          if (!(__uint_as_float(mylist[i].y) - __uint_as_float(mylist[i + 1].y) > eps2)) amb = true;
+          if (!(key_float(mylist[i].y) - key_float(mylist[i + 1].y) > eps2)) amb = true;
         if (amb) {
-          const float theta = __uint_as_float(mylist[n_keep - 1].y) - eps2;
-          while (n_surv < n_real && __uint_as_float(mylist[n_surv].y) >= theta) ++n_surv;
+          const float theta = key_float(mylist[n_keep - 1].y) - eps2;
+          while (n_surv < n_real && key_float(mylist[n_surv].y) >= theta) ++n_surv;
           // the last place also survives and more candidates exist: the near-ties may go on below the list
           mode = (n_surv == list_len && ncand > list_len) || !(eps2 < INFINITY) || n_surv < n_keep ? 2 : 1;
         }
@@ -532,6 +607,15 @@ gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, con
       uint2* rlist = lists + (size_t)r * lstride;
       lx[lane] = 0ull;
       lx[lane + 32] = 0ull;
+      if (__shfl_sync(0xffffffffu, (int)failed, src)) {
+        // the row's thread gave up waiting for the Q tile: fetch the row with plain loads into its place
+        if (lane < D / 8) {
+          const int tl = r / p.G, hl = r - tl * p.G;
+          const uint4 val = __ldg(reinterpret_cast<const uint4*>(
+              q + (int64_t)(t.tok_lo + tl - p.win_lo) * p.sq_t + (int64_t)(t.hk * p.G + hl) * p.sq_h + lane * 8));
+          *reinterpret_cast<uint4*>(sQ + swz_piece(r, lane, kQBlockBytes)) = val;
+        }
+      }
       __syncwarp();
       int viol = 0, ratio = 0;
       for (int base = 0; base < r_total; base += 32) {
@@ -542,7 +626,7 @@ gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, con
           const float e = contract_score<kHalf, D>(sQ, r, means + ((int64_t)(slot0 + cc) * p.Hkv + t.hk) * D);
           key = ((unsigned long long)float_key(e) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)(slot0 + cc));
           if (r_mode == 1 && stats != nullptr) {
-            const float diff = fabsf(__uint_as_float(rlist[idx].y) - e);
+            const float diff = fabsf(key_float(rlist[idx].y) - e);
             if (!(diff <= r_eps)) viol = 1;
             ratio = (int)fminf(diff / r_eps * 65536.f, 1.0e9f);
           }
@@ -581,16 +665,18 @@ gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, con
         }
       }
     }
-    __syncthreads();
-
-    for (int i = tid; i < hist * nrows; i += kGateThreads) {
-      const int r = i / nrows, rem = i - r * nrows;
-      const int hl = rem / t.ntok, tl = rem - hl * t.ntok;
-      const int cc = (int32_t)lists[(size_t)(tl * p.G + hl) * lstride + r].x;
-      store_selected(i, cc >= 0 ? slot0 + cc : -1);
-      if (cc >= 0 && list_counts != nullptr) {
-        if (cnt_in_smem) atomicAdd(&cnt_s[cc], 1);
-        else atomicAdd(&list_counts[(int64_t)(slot0 + cc) * p.Hkv + t.hk], 1);
+    // selected[rank][head][token]: every thread stores the chunks of its own row (its list was
+    // written by its own warp); neighbouring lanes are neighbouring heads, then tokens
+    if (row < nrows) {
+      const int tl = row / p.G, hl = row - tl * p.G;
+      int32_t* dst = selected + (int64_t)(t.hk * p.G + hl) * p.Tq + (t.tok_lo - p.win_lo) + tl;
+      for (int r = 0; r < hist; ++r) {
+        const int cc = (int32_t)mylist[r].x;
+        dst[(int64_t)r * p.sel_rs] = cc >= 0 ? slot0 + cc : -1;
+        if (cc >= 0 && list_counts != nullptr) {
+          if (cnt_in_smem) atomicAdd(&cnt_s[cc], 1);
+          else atomicAdd(&list_counts[(int64_t)(slot0 + cc) * p.Hkv + t.hk], 1);
+        }
       }
     }
     __syncthreads();                                          // lists, scratch and the Q buffer are free again
@@ -621,15 +707,18 @@ struct GateLaunch {
 GateLaunch gate_launch_config(const Params& p) {
   GateLaunch best{};
   const int nblk = (p.D + 63) / 64;
-  const int list_len = p.hist + 1 + kListExtra;
+  // hist + 1 places settle the cut; more only help rows with more than 32 candidates (a row with
+  // fewer is ranked over all of them in one round of the exact path anyway)
+  const int list_len = p.hist + 1 + (p.mc - 1 > 32 ? kListExtra : 0);
   const int cnt_in_smem = p.mc <= kCntSmemMax;
   int want = 32;
   while (want < p.mc - 1 && want < 256) want *= 2;            // a row has at most mc - 1 candidates
   for (int nbuf = 2; nbuf >= 1; --nbuf)
     for (int nt = want; nt >= 32; nt /= 2) {
+      const bool has_scratch = list_len > 32 || p.mc - 1 > 32;
       const size_t smem = 1024 + (size_t)nbuf * nblk * kQBlockBytes + (size_t)nblk * nt * 128 +
                           (size_t)kGateRows * (list_len | 1) * sizeof(uint2) +
-                          (size_t)kGateRows * kScratchStride * sizeof(float) + sizeof(GateCtrl) +
+                          (has_scratch ? (size_t)kGateRows * kScratchStride * sizeof(float) : 0) + sizeof(GateCtrl) +
                           (cnt_in_smem ? (size_t)p.mc * sizeof(int32_t) : 0);
       if (smem > 227 * 1024) continue;
       int ctas = (int)((228 * 1024) / (smem + 1024));         // 1 KB per CTA is reserved by the system
@@ -659,15 +748,21 @@ cudaError_t launch_gate_topk_stats(const Params& p, const __nv_bfloat16* q, cons
   if (!make_tile_map(&mq, p.fp16 != 0, p.D, q, p.Tq, p.Hq, p.sq_t, p.sq_h, p.G, tokens_per_cta) ||
       !make_tile_map(&mm, p.fp16 != 0, p.D, means, p.slots, p.Hkv, (int64_t)p.Hkv * p.D, p.D, 1, g.nt))
     return cudaErrorNotSupported;
-  void (*kernel)(Params, CUtensorMap, CUtensorMap, int, int, int, int, int, const __nv_bfloat16*, const __nv_bfloat16*,
-                 const int32_t*, int32_t*, int32_t*, int32_t*, int);
+  typedef void (*Kernel)(Params, CUtensorMap, CUtensorMap, int, int, int, int, int, const __nv_bfloat16*,
+                         const __nv_bfloat16*, const int32_t*, int32_t*, int32_t*, int32_t*, int);
+  Kernel kernel = nullptr;
+  const int w = g.list_len <= 8 ? 8 : (g.list_len <= 16 ? 16 : (g.list_len <= 32 ? 32 : 0));
+#define MOBA_GATE_W(HALF, DIM)                                                                       \
+  kernel = w == 8 ? (Kernel)gate_topk_kernel<HALF, DIM, 8> : w == 16 ? (Kernel)gate_topk_kernel<HALF, DIM, 16> \
+         : w == 32 ? (Kernel)gate_topk_kernel<HALF, DIM, 32> : (Kernel)gate_topk_kernel<HALF, DIM, 0>
   switch (p.D) {
-    case 64:  kernel = p.fp16 ? gate_topk_kernel<true, 64>  : gate_topk_kernel<false, 64>;  break;
-    case 96:  kernel = p.fp16 ? gate_topk_kernel<true, 96>  : gate_topk_kernel<false, 96>;  break;
-    case 128: kernel = p.fp16 ? gate_topk_kernel<true, 128> : gate_topk_kernel<false, 128>; break;
-    case 256: kernel = p.fp16 ? gate_topk_kernel<true, 256> : gate_topk_kernel<false, 256>; break;
+    case 64:  if (p.fp16) MOBA_GATE_W(true, 64);  else MOBA_GATE_W(false, 64);  break;
+    case 96:  if (p.fp16) MOBA_GATE_W(true, 96);  else MOBA_GATE_W(false, 96);  break;
+    case 128: if (p.fp16) MOBA_GATE_W(true, 128); else MOBA_GATE_W(false, 128); break;
+    case 256: if (p.fp16) MOBA_GATE_W(true, 256); else MOBA_GATE_W(false, 256); break;
     default: return cudaErrorInvalidValue;
   }
+#undef MOBA_GATE_W
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
   if (e != cudaSuccess) return e;
   int dev = 0, sms = 148;
@@ -675,7 +770,20 @@ cudaError_t launch_gate_topk_stats(const Params& p, const __nv_bfloat16* q, cons
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int64_t n_tiles = (int64_t)cdiv_i(p.max_seqlen, tokens_per_cta) * p.Hkv * p.B;
   if (n_tiles >= ((int64_t)1 << 31)) return cudaErrorInvalidConfiguration;
-  int64_t grid = (int64_t)sms * g.ctas_per_sm;
+  // persistent CTAs: as many as are resident at once, by shared memory (1 KB per CTA is reserved),
+  // registers (allocated in units of 8 per thread) and tensor memory (512 columns per SM)
+  cudaFuncAttributes attr;
+  if ((e = cudaFuncGetAttributes(&attr, kernel)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100)) != cudaSuccess) return e;
+  int smem_per_sm = 0, regs_per_sm = 0;
+  cudaDeviceGetAttribute(&smem_per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+  cudaDeviceGetAttribute(&regs_per_sm, cudaDevAttrMaxRegistersPerMultiprocessor, dev);
+  int resident = (int)(smem_per_sm / (g.smem + 1024));
+  const int regs_per_cta = ((attr.numRegs + 7) / 8 * 8) * kGateThreads;
+  if (regs_per_cta > 0 && resident > regs_per_sm / regs_per_cta) resident = regs_per_sm / regs_per_cta;
+  if (resident > 512 / g.nt) resident = 512 / g.nt;
+  if (resident < 1) resident = 1;
+  int64_t grid = (int64_t)sms * resident;
   if (grid > n_tiles) grid = n_tiles;
   kernel<<<(int)grid, kGateThreads, g.smem, st>>>(p, mq, mm, tokens_per_cta, g.nt, g.list_len, g.nbuf, g.cnt_in_smem, q,
                                                   means, cu, selected, list_counts, stats, flags);

@@ -22,8 +22,11 @@ namespace topk {
 
 // after the call: hi = max, lo = min
 MOBA_TOPK_FN void ce(uint32_t& hi, uint32_t& lo) {
-  const uint32_t a = hi > lo ? hi : lo;
-  const uint32_t b = hi > lo ? lo : hi;
+#if defined(__CUDA_ARCH__)
+  const uint32_t a = max(hi, lo), b = min(hi, lo);       // two integer min/max instructions
+#else
+  const uint32_t a = hi > lo ? hi : lo, b = hi > lo ? lo : hi;
+#endif
   hi = a;
   lo = b;
 }
@@ -73,7 +76,11 @@ MOBA_TOPK_FN void top_of_32(uint32_t (&v)[32]) {
 #pragma unroll
         for (int i = 0; i < W; ++i) {
           const uint32_t x = v[a + i], y = v[b + i];
+#if defined(__CUDA_ARCH__)
+          v[dst + i] = max(x, y);
+#else
           v[dst + i] = x > y ? x : y;
+#endif
         }
         if (k % 2 == 0) bitonic_merge<W, true>(v, dst);
         else bitonic_merge<W, false>(v, dst);
