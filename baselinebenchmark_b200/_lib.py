@@ -23,6 +23,7 @@ SYMBOLS = (
     "moba_chunk_metadata", "moba_chunk_means", "moba_gate_topk", "moba_gate_topk_stats", "moba_compact_routes",
     "moba_attend", "moba_merge", "moba_attend_tile_rows", "moba_route_static",
     "moba_backward_workspace_size", "moba_backward",
+    "moba_cp_workspace_size", "moba_cp_forward", "moba_cp_poll", "moba_cp_abort",
 )
 
 
@@ -90,6 +91,11 @@ def lib() -> C.CDLL:
         handle.moba_route_static.argtypes = [pp, vp, vp, i32p, i32p, vp]
         handle.moba_backward_workspace_size.argtypes = [pp, C.POINTER(sz)]
         handle.moba_backward.argtypes = [pp, vp, vp, vp, i32p, vp, vp, i32p, vp, vp, vp, vp, vp, sz, vp]
+        handle.moba_cp_workspace_size.argtypes = [pp, C.POINTER(sz)]
+        handle.moba_cp_forward.argtypes = [pp, vp, C.c_int32, C.c_int32, C.POINTER(C.c_int64), vp, vp, vp, i32p, vp, vp,
+                                           i32p, vp, sz, vp, vp, C.POINTER(C.c_void_p)]
+        handle.moba_cp_poll.argtypes = [vp, C.POINTER(C.c_int32)]
+        handle.moba_cp_abort.argtypes = [vp]
         _lib = handle
     return _lib
 

@@ -8,7 +8,7 @@ from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
 ROOT = PKG.parent
-SOURCES = ["api.cu", "gate.cu", "routes.cu", "attend_mma.cu", "attend_tc5.cu", "attend_bwd.cu", "attend_bwd_tc5.cu", "attend_bwd_dkdv_tc5.cu", "route_static.cu"]
+SOURCES = ["api.cu", "gate.cu", "routes.cu", "attend_mma.cu", "attend_tc5.cu", "attend_bwd.cu", "attend_bwd_tc5.cu", "attend_bwd_dkdv_tc5.cu", "route_static.cu", "nccl_dl.cu"]
 LIB = PKG / "libmoba_b200.so"
 
 
@@ -25,7 +25,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     cmd = [nvcc(), "-shared", "-Xcompiler", "-fPIC", "-O3", "-std=c++17", "-lineinfo",
            "-gencode", "arch=compute_100a,code=sm_100a",
            "-I", str(ROOT / "include"), "-I", str(PKG / "csrc"),
-           "-o", str(LIB)] + [str(s) for s in srcs]
+           "-o", str(LIB)] + [str(s) for s in srcs] + ["-ldl"]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

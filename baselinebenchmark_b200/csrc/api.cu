@@ -10,6 +10,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "nccl_dl.cuh"
 
 using namespace moba;
 
@@ -223,6 +224,7 @@ const char* moba_b200_strerror(int code) {
     case MOBA_E_TOPK: return "moba_topk must be in 1..64";
     case MOBA_E_ALIGN: return "pointers and strides must be multiples of 16 bytes";
     case MOBA_E_DEVICE: return "needs an sm_100 device and a driver that exports cuTensorMapEncodeTiled";
+    case MOBA_E_NCCL: return "an NCCL call failed, or no NCCL library with the needed entry points could be loaded";
     case MOBA_E_STATIC_LIMIT: return "problem exceeds the built-in scratch of moba_route_static (slots * kv heads * head_dim <= 2 Mi elements)";
     default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
   }
@@ -341,9 +343,12 @@ int moba_merge(const moba_problem_t* p, const float* partial_out, const float* p
 
 // One pass over all query heads of `p` (the whole problem, or a group of kv heads
 // carved out of it by forward_impl).  `sel_rs`: rank stride of `selected_out`.
+// `means_ready`: the chunk means already are in the workspace (context-parallel callers gather
+// them); `kv_ready`: an event the dense stage waits for (K and V still arriving), or null.
 static int forward_pass(const moba_problem_t* p, int64_t sel_rs, const void* q, const void* k, const void* v,
                         const int32_t* cu, void* out, float* lse_out, int32_t* selected_out, void* workspace,
-                        cudaStream_t st, void* const* events, bool first, bool last) {
+                        cudaStream_t st, void* const* events, bool first, bool last, bool means_ready = false,
+                        cudaEvent_t kv_ready = nullptr) {
   Params r = make_params(p);
   if (selected_out) r.sel_rs = sel_rs;
   const Workspace w = carve(r, workspace);
@@ -357,7 +362,7 @@ static int forward_pass(const moba_problem_t* p, int64_t sel_rs, const void* q, 
   const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(k);
   if (r.hist > 0) {
     int32_t* sel = selected_out ? selected_out : w.selected;
-    if ((e = launch_chunk_means(r, kb, cu, w.means, st)) != cudaSuccess) return (int)e;
+    if (!means_ready && (e = launch_chunk_means(r, kb, cu, w.means, st)) != cudaSuccess) return (int)e;
     if (last && (e = mark(1)) != cudaSuccess) return (int)e;
     if ((e = launch_gate_topk(r, qb, w.means, cu, sel, w.list_counts, st)) != cudaSuccess) return (int)e;
     if (last && (e = mark(2)) != cudaSuccess) return (int)e;
@@ -367,6 +372,7 @@ static int forward_pass(const moba_problem_t* p, int64_t sel_rs, const void* q, 
   } else if (last) {
     if ((e = mark(1)) != cudaSuccess || (e = mark(2)) != cudaSuccess) return (int)e;
   }
+  if (kv_ready != nullptr && (e = cudaStreamWaitEvent(st, kv_ready, 0)) != cudaSuccess) return (int)e;
   if (last && (e = mark(3)) != cudaSuccess) return (int)e;
   const int arc = attend_dispatch(p, r, q, k, v, cu, w.list_counts, w.list_offsets, w.tile_prefix, w.row_list,
                                   w.partial_out, w.partial_lse, w.work_counter, w.status, st);
@@ -632,6 +638,113 @@ int moba_forward_host(const moba_problem_t* p, const void* q_host, const void* k
   if (status != MOBA_OK) return status;
   if (j1 != cudaSuccess) return (int)j1;
   return (int)j2;
+}
+
+// ---------------------------------------------------------------------------
+// context parallelism: one sequence split contiguously over the ranks of an NCCL communicator
+// ---------------------------------------------------------------------------
+int moba_cp_workspace_size(const moba_problem_t* p, size_t* bytes) {
+  const int rc = check_problem(p);
+  if (rc != MOBA_OK) return rc;
+  if (bytes == nullptr) return MOBA_E_NULL;
+  if (p->batch != 1 || p->q_tokens <= 0) return MOBA_E_SHAPE;
+  *bytes = pass_bytes(p, p->num_kv_heads);                  // one pass: the gathered means cover all kv heads
+  return MOBA_OK;
+}
+
+int moba_cp_forward(const moba_problem_t* p, void* nccl_comm, int32_t rank, int32_t world, const int64_t* bounds,
+                    const void* q_local, void* k_full, void* v_full, const int32_t* cu, void* out_local,
+                    float* lse_out, int32_t* selected_out, void* workspace, size_t workspace_bytes, void* stream,
+                    void* comm_stream, void* const* events) {
+  size_t need = 0;
+  const int rc = moba_cp_workspace_size(p, &need);
+  if (rc != MOBA_OK) return rc;
+  if (!nccl_comm || !bounds || !q_local || !k_full || !v_full || !cu || !out_local) return MOBA_E_NULL;
+  if (workspace == nullptr || workspace_bytes < need) return MOBA_E_WORKSPACE;
+  if (world < 1 || rank < 0 || rank >= world) return MOBA_E_SHAPE;
+  const Params r = make_params(p);
+  if (r.rows * (int64_t)r.NP >= ((int64_t)1 << 31)) return MOBA_E_UNSUPPORTED;   // one pass over all heads
+  // windows: increasing, chunk aligned, covering the sequence; this rank's is the query window of `p`
+  if (bounds[0] != 0 || bounds[world] != p->total_tokens) return MOBA_E_SHAPE;
+  for (int i = 0; i < world; ++i)
+    if (bounds[i + 1] < bounds[i] || (bounds[i + 1] % r.C != 0 && bounds[i + 1] != p->total_tokens)) return MOBA_E_SHAPE;
+  if (bounds[rank] != p->q_token_begin || bounds[rank + 1] - bounds[rank] != p->q_tokens) return MOBA_E_SHAPE;
+  // K and V are taken as contiguous [T, Hkv, D] buffers that every rank lays out alike
+  if (r.sk_h != r.D || r.sk_t != (int64_t)r.Hkv * r.D || r.sv_h != r.D || r.sv_t != (int64_t)r.Hkv * r.D)
+    return MOBA_E_UNSUPPORTED;
+  const uintptr_t ptrs[5] = {(uintptr_t)q_local, (uintptr_t)k_full, (uintptr_t)v_full, (uintptr_t)out_local,
+                             (uintptr_t)workspace};
+  for (int i = 0; i < 5; ++i)
+    if (ptrs[i] % 16 != 0) return MOBA_E_ALIGN;
+  const NcclApi* nc = nccl_api();
+  if (nc == nullptr) return MOBA_E_NCCL;
+  ncclComm_t comm = static_cast<ncclComm_t>(nccl_comm);
+  cudaStream_t st = (cudaStream_t)stream, cs = (cudaStream_t)comm_stream;
+  const Workspace w = carve(r, workspace);
+  cudaError_t e;
+
+  // 1. means of this rank's own chunks, from its own K rows (already in place inside k_full)
+  const int slot_lo = (int)(bounds[rank] / r.C), slot_hi = (int)((bounds[rank + 1] + r.C - 1) / r.C);
+  if (events && events[0] && (e = cudaEventRecord((cudaEvent_t)events[0], st)) != cudaSuccess) return (int)e;
+  if (r.hist > 0 &&
+      (e = launch_chunk_means_range(r, slot_lo, slot_hi, static_cast<const __nv_bfloat16*>(k_full), cu, w.means, st)) !=
+          cudaSuccess)
+    return (int)e;
+  // 2. on the communication stream: every rank's means to every rank (a few hundred KB), then the K
+  //    and V rows of the earlier ranks to the later ones (rank r receives tokens [0, bounds[r]) only).
+  //    The gating of step 3 runs while the rows travel.
+  if ((e = chain(st, cs)) != cudaSuccess) return (int)e;
+  const size_t mean_row = (size_t)r.Hkv * r.D * 2, kv_row = (size_t)r.Hkv * r.D * 2;
+  ncclResult_t nrc = ncclSuccess;
+  auto ok = [&](ncclResult_t x) { if (x != ncclSuccess && nrc == ncclSuccess) nrc = x; };
+  if (r.hist > 0 && world > 1) {
+    ok(nc->GroupStart());
+    for (int s = 0; s < world; ++s) {
+      const int64_t lo = bounds[s] / r.C, hi = (bounds[s + 1] + r.C - 1) / r.C;
+      char* buf = reinterpret_cast<char*>(w.means) + lo * mean_row;
+      if (hi > lo) ok(nc->Broadcast(buf, buf, (size_t)(hi - lo) * mean_row, ncclChar, s, comm, cs));
+    }
+    ok(nc->GroupEnd());
+  }
+  ScopedEvent means_ready, kv_ready;
+  if ((e = means_ready.create()) != cudaSuccess || (e = kv_ready.create()) != cudaSuccess) return (int)e;
+  if ((e = cudaEventRecord(means_ready.ev, cs)) != cudaSuccess) return (int)e;
+  if (world > 1) {
+    ok(nc->GroupStart());
+    for (int pass = 0; pass < 2; ++pass) {
+      char* base = static_cast<char*>(pass == 0 ? k_full : v_full);
+      for (int s = 0; s < rank; ++s)                          // rows of the earlier ranks
+        if (bounds[s + 1] > bounds[s])
+          ok(nc->Recv(base + bounds[s] * kv_row, (size_t)(bounds[s + 1] - bounds[s]) * kv_row, ncclChar, s, comm, cs));
+      for (int d = rank + 1; d < world; ++d)                  // this rank's rows to the later ranks
+        if (bounds[rank + 1] > bounds[rank] && bounds[d + 1] > bounds[d])
+          ok(nc->Send(base + bounds[rank] * kv_row, (size_t)(bounds[rank + 1] - bounds[rank]) * kv_row, ncclChar, d, comm, cs));
+    }
+    ok(nc->GroupEnd());
+  }
+  if ((e = cudaEventRecord(kv_ready.ev, cs)) != cudaSuccess) return (int)e;
+  if (nrc != ncclSuccess) return MOBA_E_NCCL;
+  // 3. gating and compaction once the means are complete, dense stage and merge once K and V are
+  if ((e = cudaStreamWaitEvent(st, means_ready.ev, 0)) != cudaSuccess) return (int)e;
+  return forward_pass(p, r.sel_rs, q_local, k_full, v_full, cu, out_local, lse_out, selected_out, workspace, st, events,
+                      false, true, true, kv_ready.ev);
+}
+
+int moba_cp_poll(void* nccl_comm, int32_t* async_error) {
+  if (!nccl_comm || !async_error) return MOBA_E_NULL;
+  const NcclApi* nc = nccl_api();
+  if (nc == nullptr) return MOBA_E_NCCL;
+  ncclResult_t state = ncclSuccess;
+  if (nc->CommGetAsyncError(static_cast<ncclComm_t>(nccl_comm), &state) != ncclSuccess) return MOBA_E_NCCL;
+  *async_error = (int32_t)state;
+  return MOBA_OK;
+}
+
+int moba_cp_abort(void* nccl_comm) {
+  if (!nccl_comm) return MOBA_E_NULL;
+  const NcclApi* nc = nccl_api();
+  if (nc == nullptr) return MOBA_E_NCCL;
+  return nc->CommAbort(static_cast<ncclComm_t>(nccl_comm)) == ncclSuccess ? MOBA_OK : MOBA_E_NCCL;
 }
 
 }  // extern "C"

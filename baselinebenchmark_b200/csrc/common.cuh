@@ -149,6 +149,8 @@ cudaError_t launch_chunk_metadata(const Params& p, const int32_t* cu, int32_t* c
                                   int32_t* chunk_end, int8_t* valid, cudaStream_t st);
 cudaError_t launch_chunk_means(const Params& p, const __nv_bfloat16* k, const int32_t* cu,
                                __nv_bfloat16* means, cudaStream_t st);
+cudaError_t launch_chunk_means_range(const Params& p, int slot_begin, int slot_end, const __nv_bfloat16* k,
+                                     const int32_t* cu, __nv_bfloat16* means, cudaStream_t st);
 cudaError_t launch_gate_topk(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* means,
                              const int32_t* cu, int32_t* selected, int32_t* list_counts,
                              cudaStream_t st);

@@ -55,9 +55,9 @@ cudaError_t launch_chunk_metadata(const Params& p, const int32_t* cu, int32_t* c
 // ---------------------------------------------------------------------------
 template <bool kHalf, int D>
 __global__ void __launch_bounds__(kMeanLanes * (D / 8))
-chunk_mean_kernel(Params p, const __nv_bfloat16* __restrict__ k, const int32_t* __restrict__ cu,
+chunk_mean_kernel(Params p, int slot_begin, const __nv_bfloat16* __restrict__ k, const int32_t* __restrict__ cu,
                   __nv_bfloat16* __restrict__ means) {
-  const int slot = blockIdx.x, hk = blockIdx.y;
+  const int slot = slot_begin + blockIdx.x, hk = blockIdx.y;
   const int b = slot / p.mc, j = slot - b * p.mc;
   const Slot sl = slot_of(cu, b, j, p.C);
   constexpr int kDimLanes = D / 8;
@@ -108,10 +108,13 @@ chunk_mean_kernel(Params p, const __nv_bfloat16* __restrict__ k, const int32_t* 
   }
 }
 
-cudaError_t launch_chunk_means(const Params& p, const __nv_bfloat16* k, const int32_t* cu,
-                               __nv_bfloat16* means, cudaStream_t st) {
-  dim3 grid(p.slots, p.Hkv);
-#define MOBA_MEANS(HALF, DIM) chunk_mean_kernel<HALF, DIM><<<grid, kMeanLanes * (DIM / 8), 0, st>>>(p, k, cu, means)
+// Means of the slots [slot_begin, slot_end) only (context-parallel ranks compute those of their own chunks).
+cudaError_t launch_chunk_means_range(const Params& p, int slot_begin, int slot_end, const __nv_bfloat16* k,
+                                     const int32_t* cu, __nv_bfloat16* means, cudaStream_t st) {
+  if (slot_end <= slot_begin) return cudaSuccess;
+  dim3 grid(slot_end - slot_begin, p.Hkv);
+#define MOBA_MEANS(HALF, DIM) \
+  chunk_mean_kernel<HALF, DIM><<<grid, kMeanLanes * (DIM / 8), 0, st>>>(p, slot_begin, k, cu, means)
   switch (p.D) {
     case 64:  if (p.fp16) MOBA_MEANS(true, 64);  else MOBA_MEANS(false, 64);  break;
     case 96:  if (p.fp16) MOBA_MEANS(true, 96);  else MOBA_MEANS(false, 96);  break;
@@ -121,6 +124,11 @@ cudaError_t launch_chunk_means(const Params& p, const __nv_bfloat16* k, const in
   }
 #undef MOBA_MEANS
   return cudaGetLastError();
+}
+
+cudaError_t launch_chunk_means(const Params& p, const __nv_bfloat16* k, const int32_t* cu,
+                               __nv_bfloat16* means, cudaStream_t st) {
+  return launch_chunk_means_range(p, 0, p.slots, k, cu, means, st);
 }
 
 // ---------------------------------------------------------------------------

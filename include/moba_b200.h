@@ -43,7 +43,8 @@ enum {
   MOBA_E_TOPK = -5,         /* moba_topk outside 1..64 (parallel.py:434-437)     */
   MOBA_E_ALIGN = -6,        /* base pointer or stride not 16-byte aligned        */
   MOBA_E_DEVICE = -7,       /* not an sm_100 device, or driver entry point missing */
-  MOBA_E_STATIC_LIMIT = -8  /* problem too large for the built-in scratch of moba_route_static */
+  MOBA_E_STATIC_LIMIT = -8, /* problem too large for the built-in scratch of moba_route_static */
+  MOBA_E_NCCL = -9          /* an NCCL call failed or no NCCL library could be loaded */
 };
 
 /* Which implementation of the dense stage moba_attend/moba_forward run. */
@@ -257,6 +258,39 @@ int moba_backward_workspace_size(const moba_problem_t* p, size_t* bytes);
 int moba_backward(const moba_problem_t* p, const void* q, const void* k, const void* v, const int32_t* cu_seqlens,
                   const void* out, const float* lse, const int32_t* selected, const void* dout, void* dq, void* dk,
                   void* dv, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- context parallelism: one long sequence split over the GPUs of a communicator ----------
+ *
+ * The reference has no multi-device path (its native kernel is rendered with enable_cp=False,
+ * native_moba.py:69); this is the partition BASELINE.json's million-token configuration asks
+ * for.  Rank i owns the tokens [bounds[i], bounds[i+1]) of ONE sequence (bounds[0] = 0,
+ * bounds[world] = total_tokens, inner bounds on chunk boundaries): its queries, its output rows
+ * and its K/V rows.  `p` describes the whole sequence (batch 1, cu_seqlens = {0, total_tokens} on
+ * the device) with the query window q_token_begin / q_tokens equal to this rank's range.
+ *   k_full, v_full  contiguous [total_tokens, Hkv, D] buffers in this GPU's memory; on entry the
+ *                   rank's own rows are in place at their token positions, on return (stream
+ *                   order) the rows of all earlier ranks are too.  Later ranks' rows are not
+ *                   needed (causal) and not transferred: rank i receives bounds[i] rows, not all.
+ *   nccl_comm       an ncclComm_t of `world` ranks (the host framework's, or the caller's own),
+ *                   used on `comm_stream` only.  NCCL is bound at run time from the library
+ *                   already in the process.
+ *   Schedule: the means of the rank's own chunks are computed from its own K rows, all ranks'
+ *   means are exchanged (a few hundred KB), gating and compaction run on `stream` while K and V
+ *   rows travel on `comm_stream`; the dense stage waits for them.  Every kernel reads local
+ *   memory only.  Results are bit-identical to a single-device moba_forward on the same window.
+ *   events          optional, as for moba_forward_events.
+ * The call creates two short-lived events and is not meant to be captured in a CUDA graph.
+ * All ranks must call with the same bounds; a rank that does not leaves the others waiting in
+ * NCCL, which is what moba_cp_poll / moba_cp_abort are for: poll returns the communicator's
+ * asynchronous error state (ncclCommGetAsyncError: 0 ok, 7 still in progress), abort tears the
+ * communicator down (ncclCommAbort) so that a host that gave up waiting gets its stream back. */
+int moba_cp_workspace_size(const moba_problem_t* p, size_t* bytes);
+int moba_cp_forward(const moba_problem_t* p, void* nccl_comm, int32_t rank, int32_t world, const int64_t* bounds,
+                    const void* q_local, void* k_full, void* v_full, const int32_t* cu_seqlens, void* out_local,
+                    float* lse_out, int32_t* selected_out, void* workspace, size_t workspace_bytes, void* stream,
+                    void* comm_stream, void* const* events);
+int moba_cp_poll(void* nccl_comm, int32_t* async_error);
+int moba_cp_abort(void* nccl_comm);
 
 /* Rows per routed work item that the selected attend implementation wants
  * (the tile_rows argument of moba_compact_routes). */

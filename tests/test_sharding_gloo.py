@@ -107,3 +107,65 @@ def test_unit_sharding_needs_no_exchange():
         # a unit evaluated alone equals its slice of the whole-batch evaluation
         assert max(r[0] for r in result.values()) == 0.0
         assert all(r[2] == 3.0 for r in result.values())
+
+
+def _bad_shape_worker(rank, world, port, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        total, chunk = 640, 64
+        q, k, v, _ = O.make_inputs([total], 4, 2, 128, chunk, seed=3)
+        lo, hi = sharding.context_window(total, chunk, world, rank)
+        if rank == 1:
+            hi -= 5                                  # this rank passes too few rows
+        try:
+            sharding.moba_context_parallel(q[lo:hi], k[lo:hi], v[lo:hi], total, chunk, 3, forward=_oracle_forward)
+            result[rank] = "returned"
+        except ValueError as exc:
+            result[rank] = str(exc)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_a_rank_with_a_bad_shape_makes_every_rank_raise():
+    """Failure made on the host: rank 1 passes the wrong number of rows.  Every rank gets a
+    ValueError from the agreement step instead of waiting in the exchange for a peer that
+    never joins."""
+    world = 2
+    with mp.Manager() as mgr:
+        result = mgr.dict()
+        mp.spawn(_bad_shape_worker, args=(world, _free_port(), result), nprocs=world, join=True)
+        assert sorted(result.keys()) == [0, 1]
+        assert "invalid" in result[0] and "this rank" not in result[0]
+        assert "invalid" in result[1] and "this rank" in result[1]
+
+
+def _absent_rank_worker(rank, world, port, result):
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    try:
+        if rank == 1:
+            result[rank] = "left between steps"      # returns early: never enters the collective
+            return
+        try:
+            sharding.agree(True, None)
+            result[rank] = "returned"
+        except Exception as exc:                     # noqa: BLE001  (gloo raises RuntimeError / DistBackendError)
+            result[rank] = f"error: {type(exc).__name__}"
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:                            # noqa: BLE001
+            pass
+
+
+def test_a_rank_that_never_joins_ends_the_collective_with_an_error():
+    """Rank 1 leaves before the step; rank 0's agreement collective ends with an error after the
+    process group's (short) timeout instead of blocking."""
+    world = 2
+    with mp.Manager() as mgr:
+        result = mgr.dict()
+        mp.spawn(_absent_rank_worker, args=(world, _free_port(), result), nprocs=world, join=True)
+        assert result[1] == "left between steps"
+        assert result[0].startswith("error")
