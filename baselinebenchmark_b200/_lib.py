@@ -19,11 +19,11 @@ ATTEND_MMA_SYNC = 1
 #: every symbol include/moba_b200.h declares
 SYMBOLS = (
     "moba_b200_abi_version", "moba_b200_strerror", "moba_problem_check", "moba_problem_dims",
-    "moba_workspace_size", "moba_workspace_size_min", "moba_forward", "moba_forward_events", "moba_workspace_size_host", "moba_forward_host",
+    "moba_workspace_size", "moba_workspace_size_min", "moba_forward", "moba_forward_events", "moba_forward_cached", "moba_workspace_size_host", "moba_forward_host",
     "moba_chunk_metadata", "moba_chunk_means", "moba_gate_topk", "moba_gate_topk_stats", "moba_compact_routes",
     "moba_attend", "moba_merge", "moba_attend_tile_rows", "moba_route_static",
     "moba_backward_workspace_size", "moba_backward",
-    "moba_cp_workspace_size", "moba_cp_forward", "moba_cp_poll", "moba_cp_abort",
+    "moba_cp_workspace_size", "moba_cp_forward", "moba_cp_poll", "moba_cp_abort", "moba_selftest_bounded_wait",
 )
 
 
@@ -79,6 +79,7 @@ def lib() -> C.CDLL:
         handle.moba_workspace_size_min.argtypes = [pp, C.POINTER(sz)]
         handle.moba_forward.argtypes = [pp, vp, vp, vp, i32p, vp, vp, i32p, vp, sz, vp]
         handle.moba_forward_events.argtypes = [pp, vp, vp, vp, i32p, vp, vp, i32p, vp, sz, vp, C.POINTER(C.c_void_p)]
+        handle.moba_forward_cached.argtypes = [pp, vp, vp, vp, i32p, vp, vp, i32p, vp, C.c_int32, vp, sz, vp]
         handle.moba_forward_host.argtypes = [pp, vp, vp, vp, i32p, vp, vp, i32p, vp, sz, vp]
         handle.moba_chunk_metadata.argtypes = [pp, i32p, i32p, i32p, vp, vp]
         handle.moba_chunk_means.argtypes = [pp, vp, i32p, vp, vp]
@@ -96,6 +97,7 @@ def lib() -> C.CDLL:
                                            i32p, vp, sz, vp, vp, C.POINTER(C.c_void_p)]
         handle.moba_cp_poll.argtypes = [vp, C.POINTER(C.c_int32)]
         handle.moba_cp_abort.argtypes = [vp]
+        handle.moba_selftest_bounded_wait.argtypes = [i32p, C.c_uint32, vp]
         _lib = handle
     return _lib
 

@@ -30,8 +30,8 @@ int check_problem(const moba_problem_t* p) {
   if (p->topk < 1 || p->topk > kMaxTopk) return MOBA_E_TOPK;               // :432-437
   if (p->head_dim > 256) return MOBA_E_SHAPE;                              // :445-446
   if (p->head_dim != 64 && p->head_dim != 96 && p->head_dim != 128 && p->head_dim != 256) return MOBA_E_UNSUPPORTED;
-  // the tcgen05 dense stage is built for head_dim 64 and 128; other sizes run the mma.sync one
-  if (p->attend_impl == MOBA_ATTEND_TCGEN05 && p->head_dim != 64 && p->head_dim != 128) return MOBA_E_UNSUPPORTED;
+  // the tcgen05 dense stage is built for head_dim 64, 96 and 128; 256 runs the mma.sync one
+  if (p->attend_impl == MOBA_ATTEND_TCGEN05 && p->head_dim == 256) return MOBA_E_UNSUPPORTED;
   if (p->num_q_heads / p->num_kv_heads > 128) return MOBA_E_UNSUPPORTED;
   if (p->attend_impl != MOBA_ATTEND_TCGEN05 && p->attend_impl != MOBA_ATTEND_MMA_SYNC) return MOBA_E_UNSUPPORTED;
   if ((p->dtype != MOBA_DTYPE_BF16 && p->dtype != MOBA_DTYPE_FP16) || p->reserved != 0) return MOBA_E_UNSUPPORTED;
@@ -218,7 +218,7 @@ const char* moba_b200_strerror(int code) {
   switch (code) {
     case MOBA_OK: return "ok";
     case MOBA_E_SHAPE: return "q, k, v, cu_seqlens or the integer arguments have an invalid shape or value";
-    case MOBA_E_UNSUPPORTED: return "configuration outside this build (bf16 or fp16; head_dim 64, 96, 128 or 256, tcgen05 dense stage at 64 and 128 only)";
+    case MOBA_E_UNSUPPORTED: return "configuration outside this build (bf16 or fp16; head_dim 64, 96, 128 or 256, tcgen05 dense stage up to 128 only)";
     case MOBA_E_WORKSPACE: return "workspace is null or too small";
     case MOBA_E_NULL: return "a required pointer is null";
     case MOBA_E_TOPK: return "moba_topk must be in 1..64";
@@ -343,12 +343,20 @@ int moba_merge(const moba_problem_t* p, const float* partial_out, const float* p
 
 // One pass over all query heads of `p` (the whole problem, or a group of kv heads
 // carved out of it by forward_impl).  `sel_rs`: rank stride of `selected_out`.
-// `means_ready`: the chunk means already are in the workspace (context-parallel callers gather
-// them); `kv_ready`: an event the dense stage waits for (K and V still arriving), or null.
+// Variations of a pass:
+//   means_ready  the chunk means already are in the workspace (context-parallel callers gather them)
+//   kv_ready     an event the dense stage waits for (K and V rows still arriving), or null
+//   means_ext    a caller-held means array [slots, Hkv, D] used instead of the workspace's, of which
+//                the slots below means_from are valid already and the rest is computed here
+struct PassOptions {
+  bool means_ready = false;
+  cudaEvent_t kv_ready = nullptr;
+  __nv_bfloat16* means_ext = nullptr;
+  int means_from = 0;
+};
 static int forward_pass(const moba_problem_t* p, int64_t sel_rs, const void* q, const void* k, const void* v,
                         const int32_t* cu, void* out, float* lse_out, int32_t* selected_out, void* workspace,
-                        cudaStream_t st, void* const* events, bool first, bool last, bool means_ready = false,
-                        cudaEvent_t kv_ready = nullptr) {
+                        cudaStream_t st, void* const* events, bool first, bool last, const PassOptions& opt = {}) {
   Params r = make_params(p);
   if (selected_out) r.sel_rs = sel_rs;
   const Workspace w = carve(r, workspace);
@@ -362,9 +370,12 @@ static int forward_pass(const moba_problem_t* p, int64_t sel_rs, const void* q, 
   const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(k);
   if (r.hist > 0) {
     int32_t* sel = selected_out ? selected_out : w.selected;
-    if (!means_ready && (e = launch_chunk_means(r, kb, cu, w.means, st)) != cudaSuccess) return (int)e;
+    __nv_bfloat16* means = opt.means_ext ? opt.means_ext : w.means;
+    if (!opt.means_ready &&
+        (e = launch_chunk_means_range(r, opt.means_ext ? opt.means_from : 0, r.slots, kb, cu, means, st)) != cudaSuccess)
+      return (int)e;
     if (last && (e = mark(1)) != cudaSuccess) return (int)e;
-    if ((e = launch_gate_topk(r, qb, w.means, cu, sel, w.list_counts, st)) != cudaSuccess) return (int)e;
+    if ((e = launch_gate_topk(r, qb, means, cu, sel, w.list_counts, st)) != cudaSuccess) return (int)e;
     if (last && (e = mark(2)) != cudaSuccess) return (int)e;
     if ((e = launch_compact(r, cu, sel, w.list_counts, w.list_offsets, w.tile_prefix, w.cursors, w.row_list,
                             w.partial_lse, tile_rows_of(p->attend_impl), st)) != cudaSuccess)
@@ -372,7 +383,7 @@ static int forward_pass(const moba_problem_t* p, int64_t sel_rs, const void* q, 
   } else if (last) {
     if ((e = mark(1)) != cudaSuccess || (e = mark(2)) != cudaSuccess) return (int)e;
   }
-  if (kv_ready != nullptr && (e = cudaStreamWaitEvent(st, kv_ready, 0)) != cudaSuccess) return (int)e;
+  if (opt.kv_ready != nullptr && (e = cudaStreamWaitEvent(st, opt.kv_ready, 0)) != cudaSuccess) return (int)e;
   if (last && (e = mark(3)) != cudaSuccess) return (int)e;
   const int arc = attend_dispatch(p, r, q, k, v, cu, w.list_counts, w.list_offsets, w.tile_prefix, w.row_list,
                                   w.partial_out, w.partial_lse, w.work_counter, w.status, st);
@@ -432,6 +443,33 @@ int moba_forward_events(const moba_problem_t* p, const void* q, const void* k, c
                         void* out, float* lse_out, int32_t* selected_out, void* workspace,
                         size_t workspace_bytes, void* stream, void* const* events) {
   return forward_impl(p, q, k, v, cu, out, lse_out, selected_out, workspace, workspace_bytes, stream, events);
+}
+
+int moba_selftest_bounded_wait(int32_t* status, uint32_t limit_us, void* stream) {
+  if (status == nullptr) return MOBA_E_NULL;
+  if (limit_us == 0 || limit_us > 100000) return MOBA_E_SHAPE;            // at most 0.1 s
+  return (int)launch_bounded_wait_probe(status, (unsigned long long)limit_us * 1000ull, (cudaStream_t)stream);
+}
+
+int moba_forward_cached(const moba_problem_t* p, const void* q, const void* k, const void* v, const int32_t* cu,
+                        void* out, float* lse_out, int32_t* selected_out, void* means_cache, int32_t cached_slots,
+                        void* workspace, size_t workspace_bytes, void* stream) {
+  const int rc = check_problem(p);
+  if (rc != MOBA_OK) return rc;
+  if (!q || !k || !v || !cu || !out || !means_cache) return MOBA_E_NULL;
+  const uintptr_t ptrs[6] = {(uintptr_t)q, (uintptr_t)k, (uintptr_t)v, (uintptr_t)out, (uintptr_t)workspace,
+                             (uintptr_t)means_cache};
+  for (int i = 0; i < 6; ++i)
+    if (ptrs[i] % 16 != 0) return MOBA_E_ALIGN;
+  const Params r = make_params(p);
+  if (cached_slots < 0 || cached_slots > r.slots) return MOBA_E_SHAPE;
+  if (r.rows * (int64_t)r.NP >= ((int64_t)1 << 31)) return MOBA_E_UNSUPPORTED;   // the cache covers all kv heads: one pass
+  if (workspace == nullptr || workspace_bytes < pass_bytes(p, r.Hkv)) return MOBA_E_WORKSPACE;
+  PassOptions opt;
+  opt.means_ext = static_cast<__nv_bfloat16*>(means_cache);
+  opt.means_from = cached_slots;
+  return forward_pass(p, r.sel_rs, q, k, v, cu, out, lse_out, selected_out, workspace, (cudaStream_t)stream, nullptr, true,
+                      true, opt);
 }
 
 // ---------------------------------------------------------------------------
@@ -726,8 +764,11 @@ int moba_cp_forward(const moba_problem_t* p, void* nccl_comm, int32_t rank, int3
   if (nrc != ncclSuccess) return MOBA_E_NCCL;
   // 3. gating and compaction once the means are complete, dense stage and merge once K and V are
   if ((e = cudaStreamWaitEvent(st, means_ready.ev, 0)) != cudaSuccess) return (int)e;
+  PassOptions opt;
+  opt.means_ready = true;
+  opt.kv_ready = kv_ready.ev;
   return forward_pass(p, r.sel_rs, q_local, k_full, v_full, cu, out_local, lse_out, selected_out, workspace, st, events,
-                      false, true, true, kv_ready.ev);
+                      false, true, opt);
 }
 
 int moba_cp_poll(void* nccl_comm, int32_t* async_error) {

@@ -6,8 +6,10 @@
 //   _varlen_attn_fwd_kernel        backends/_mthreads/ops/moba/attention.py:53-160  (own chunk, causal)
 //   native_moba.routed / MATE FMHA backends/_mthreads/ops/moba/native_moba.py:120-135
 //   _routed_gqa_attn_fwd_kernel    attention.py:610-707                           (selected chunks)
-// Templated on the element type (bf16, fp16) and the head dim (64, 128); buffer
-// strides in shared memory and TMEM are those of head dim 128.
+// Templated on the element type (bf16, fp16) and the head dim (64, 96, 128); buffer
+// strides in shared memory and TMEM are those of head dim 128.  At head dim 96 the second
+// 64-dim block of a K / V tile is half filled (TMA fills dims 96-127 with zeros), Q.K^T runs
+// six 16-dim steps and P.V writes 96 accumulator columns.
 // Numerics follow attention.py:116-155 (fp32 scores * D^-0.5 * log2 e, P rounded
 // to the input dtype before P.V, fp32 accumulation, natural-log LSE); the running maximum is
 // only refreshed when it grows by more than 8 (factor 256), which changes the
@@ -377,7 +379,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
             const uint32_t s = kc & 1;
             if (!mbar_wait(smem_u32(&c.k_empty[s]), ((kc >> 1) & 1) ^ 1)) return false;
             const uint32_t bar = smem_u32(&c.k_full[s]);
-            mbar_expect_tx(bar, (D / 64) * kHalfBytes);
+            mbar_expect_tx(bar, ((D + 63) / 64) * kHalfBytes);
             tma_load_3d(sK + s * kTileBytes, &tmap_k, bar, 0, w.kv_head, tok);
             if (D > 64) tma_load_3d(sK + s * kTileBytes + kHalfBytes, &tmap_k, bar, 64, w.kv_head, tok);
             ++kc;
@@ -386,7 +388,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
             const uint32_t s = vc & 1;
             if (!mbar_wait(smem_u32(&c.v_empty[s]), ((vc >> 1) & 1) ^ 1)) return false;
             const uint32_t bar = smem_u32(&c.v_full[s]);
-            mbar_expect_tx(bar, (D / 64) * kHalfBytes);
+            mbar_expect_tx(bar, ((D + 63) / 64) * kHalfBytes);
             tma_load_3d(sV + s * kTileBytes, &tmap_v, bar, 0, w.kv_head, tok);
             if (D > 64) tma_load_3d(sV + s * kTileBytes + kHalfBytes, &tmap_v, bar, 64, w.kv_head, tok);
             ++vc;
@@ -594,6 +596,19 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
   if (warp == 1) tmem_dealloc(tmem, kTmemCols);
 }
 
+// One warp waits, with the same bounded wait every role of the dense stage uses, on a barrier
+// nobody ever arrives on: the wait gives up after `limit_ns`, the status word is set like the
+// kernel would set it, and the warp returns.  Lets a test see the give-up path without a fault.
+__global__ void bounded_wait_probe_kernel(int32_t* status, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (!mbar_wait(smem_u32(&bar), 0, limit_ns) && threadIdx.x == 0) atomicExch(status, ST_SOFTMAX);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -632,6 +647,11 @@ bool make_kv_map(CUtensorMap* m, bool fp16, int D, const __nv_bfloat16* base, in
   return make_tile_map(m, fp16, D, base, T, Hkv, st, sh, 1, box_rows);
 }
 
+cudaError_t launch_bounded_wait_probe(int32_t* status, unsigned long long limit_ns, cudaStream_t st) {
+  bounded_wait_probe_kernel<<<1, 32, 0, st>>>(status, limit_ns);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_attend_tc5(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* k,
                               const __nv_bfloat16* v, const int32_t* cu, const int32_t* list_counts,
                               const int32_t* list_offsets, const int32_t* tile_prefix,
@@ -640,8 +660,9 @@ cudaError_t launch_attend_tc5(const Params& p, const __nv_bfloat16* q, const __n
   CUtensorMap mk, mv;
   if (!make_kv_map(&mk, p.fp16 != 0, p.D, k, p.T, p.Hkv, p.sk_t, p.sk_h, kBN) || !make_kv_map(&mv, p.fp16 != 0, p.D, v, p.T, p.Hkv, p.sv_t, p.sv_h, kBN))
     return cudaErrorNotSupported;
-  if (p.D != 64 && p.D != 128) return cudaErrorInvalidValue;
+  if (p.D != 64 && p.D != 96 && p.D != 128) return cudaErrorInvalidValue;
   auto kernel = p.D == 128 ? (p.fp16 ? attend_tc5_kernel<true, 128> : attend_tc5_kernel<false, 128>)
+              : p.D == 96  ? (p.fp16 ? attend_tc5_kernel<true, 96> : attend_tc5_kernel<false, 96>)
                            : (p.fp16 ? attend_tc5_kernel<true, 64> : attend_tc5_kernel<false, 64>);
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   if (e != cudaSuccess) return e;

@@ -184,6 +184,8 @@ cudaError_t launch_attend_tc5(const Params& p, const __nv_bfloat16* q, const __n
                               const int32_t* row_list, float* partial_out, float* partial_lse,
                               int32_t* work_counter, int32_t* status, cudaStream_t st);
 
+cudaError_t launch_bounded_wait_probe(int32_t* status, unsigned long long limit_ns, cudaStream_t st);
+
 // ---- backward (training path), attend_bwd.cu ---------------------------------
 cudaError_t launch_count_lists(const Params& p, const int32_t* selected, int32_t* list_counts, cudaStream_t st);
 cudaError_t launch_bwd_delta(const Params& p, const __nv_bfloat16* out, const __nv_bfloat16* dout, int64_t do_t,

@@ -68,8 +68,8 @@ def _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, windo
 
 
 def default_attend_impl(head_dim: int) -> int:
-    """The tcgen05 dense stage exists for head_dim 64 and 128; 96 and 256 run the mma.sync stage."""
-    return _lib.ATTEND_TCGEN05 if head_dim in (64, 128) else _lib.ATTEND_MMA_SYNC
+    """The tcgen05 dense stage exists for head_dim 64, 96 and 128; 256 runs the mma.sync stage."""
+    return _lib.ATTEND_TCGEN05 if head_dim in (64, 96, 128) else _lib.ATTEND_MMA_SYNC
 
 
 def make_problem(q, k, v, out, cu_seqlens, max_seqlen, chunk, topk, attend_impl=None,
@@ -111,7 +111,8 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 def moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, *,
                  return_lse: bool = False, return_selected: bool = False,
                  attend_impl: Optional[int] = None, workspace: Optional[torch.Tensor] = None,
-                 q_token_begin: Optional[int] = None, workspace_limit: Optional[int] = None
+                 q_token_begin: Optional[int] = None, workspace_limit: Optional[int] = None,
+                 means_cache: Optional[torch.Tensor] = None, cached_slots: int = 0
                  ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
     """Runs the operator and optionally returns the final LSE [Hq, T] (fp32) and
     the routing decision selected[hist, Hq, T] (int32, -1 padded).
@@ -122,7 +123,11 @@ def moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, *,
     cover the window.  `workspace_limit` (bytes) bounds the scratch memory: the kv heads
     are then processed in groups, with identical results.  Scratch memory is allocated per
     call through torch's caching allocator unless `workspace` (a uint8 tensor the caller
-    keeps alive and does not share between unordered streams) is given."""
+    keeps alive and does not share between unordered streams) is given.
+
+    `means_cache` (incremental prefill): a [slots, Hkv, D] tensor the caller keeps between calls;
+    slots below `cached_slots` are taken from it, the others are computed and stored into it
+    (moba_forward_cached in include/moba_b200.h has the rule for `cached_slots`)."""
     _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, windowed=q_token_begin is not None)
     out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     prob = make_problem(q, k, v, out, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, attend_impl,
@@ -137,11 +142,18 @@ def moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, *,
         sel = torch.empty((max(dims.hist, 0), q.shape[1], q.shape[0]), dtype=torch.int32, device=q.device)
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream(q.device).cuda_stream
-        rc = _lib.lib().moba_forward(
-            C.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(),
-            lse.data_ptr() if lse is not None else None,
-            sel.data_ptr() if sel is not None and sel.numel() else None,
-            ws.data_ptr(), ws.numel() * ws.element_size(), stream)
+        common = (C.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(),
+                  lse.data_ptr() if lse is not None else None,
+                  sel.data_ptr() if sel is not None and sel.numel() else None)
+        if means_cache is not None:
+            if means_cache.shape != (dims.slots, k.shape[1], k.shape[2]) or means_cache.dtype != k.dtype \
+                    or not means_cache.is_contiguous():
+                raise ValueError(f"means_cache must be a contiguous {k.dtype} tensor of shape "
+                                 f"{(dims.slots, k.shape[1], k.shape[2])}")
+            rc = _lib.lib().moba_forward_cached(*common, means_cache.data_ptr(), cached_slots,
+                                                ws.data_ptr(), ws.numel() * ws.element_size(), stream)
+        else:
+            rc = _lib.lib().moba_forward(*common, ws.data_ptr(), ws.numel() * ws.element_size(), stream)
     _lib.check(rc)
     return out, lse, sel
 

@@ -20,7 +20,7 @@
  *     (the head dims of the reference's benchmark suite, moba_compare.py:63, :70),
  *     innermost dimension contiguous; token and head strides are given in
  *     elements (the reference kernels also take strides, attention.py:431-439).
- *     The tcgen05 dense stage exists for head_dim 64 and 128; 96 and 256 run
+ *     The tcgen05 dense stage exists for head_dim 64, 96 and 128; 256 runs
  *     the mma.sync dense stage (attend_impl = MOBA_ATTEND_MMA_SYNC).  Anything
  *     else returns MOBA_E_UNSUPPORTED: there is no fallback path.
  */
@@ -49,7 +49,7 @@ enum {
 
 /* Which implementation of the dense stage moba_attend/moba_forward run. */
 enum {
-  MOBA_ATTEND_TCGEN05 = 0,  /* tcgen05.mma + TMEM accumulators + TMA K/V tiles (head_dim 64, 128) */
+  MOBA_ATTEND_TCGEN05 = 0,  /* tcgen05.mma + TMEM accumulators + TMA K/V tiles (head_dim 64, 96, 128) */
   MOBA_ATTEND_MMA_SYNC = 1  /* legacy mma.sync tensor path, kept as cross-check  */
 };
 
@@ -137,6 +137,27 @@ int moba_forward_events(const moba_problem_t* p, const void* q, const void* k, c
                         const int32_t* cu_seqlens, void* out, float* lse_out, int32_t* selected_out,
                         void* workspace, size_t workspace_bytes, void* stream, void* const* events);
 
+/* moba_forward with a caller-held cache of chunk means, for incremental prefill: a sequence
+ * (or batch) is prefilled in several calls, each with a later, chunk-aligned query window
+ * (q_token_begin / q_tokens) over a longer K/V prefix, and the means of chunks that were
+ * complete at an earlier call are not computed again.  The reference recomputes all chunk means
+ * on every call (parallel.py:306-311); it has no incremental mode.
+ *   means_cache   [slots, Hkv, D] in the tensors' dtype, slots = batch * ceil(max_seqlen / chunk)
+ *                 (use the same max_seqlen, the capacity, for every call so that slots keep their
+ *                 place); 16-byte aligned
+ *   cached_slots  slots [0, cached_slots) of the cache hold final means and are read only; the
+ *                 means of the slots from there on are computed from k and stored into the cache.
+ *                 A chunk's mean is final once its sequence has grown past the chunk: with batch 1
+ *                 and a prefix of T tokens (a multiple of the chunk size) the next call may pass
+ *                 cached_slots = T / chunk - 1 (the prefix's last chunk was the sequence's last
+ *                 chunk, which is never a candidate, so its slot still holds zeros).
+ * Results are bit-identical to moba_forward on the same window.  The workspace must have the
+ * full moba_workspace_size (one pass over all kv heads). */
+int moba_forward_cached(const moba_problem_t* p, const void* q, const void* k, const void* v,
+                        const int32_t* cu_seqlens, void* out, float* lse_out, int32_t* selected_out,
+                        void* means_cache, int32_t cached_slots, void* workspace, size_t workspace_bytes,
+                        void* stream);
+
 /* Same call with HOST buffers (pinned memory; cu_seqlens_host is also read by the
  * CPU): copies q, k, v to staging buffers inside `workspace`, runs the operator
  * and copies `out` back.  The caller synchronises `stream`, which completes after
@@ -223,6 +244,15 @@ int moba_attend(const moba_problem_t* p, const void* q, const void* k, const voi
  * when it is non-zero the output is filled with NaN instead of partial data. */
 int moba_merge(const moba_problem_t* p, const float* partial_out, const float* partial_lse,
                const int32_t* status, void* out, float* lse_out, void* stream);
+
+/* Self-test of the device-side wait limit (no counterpart in the reference, whose kernels
+ * never wait on one another).  Every wait inside the dense-stage and gradient kernels is
+ * bounded; one that gives up sets the status word next to the work counter, the kernel drains
+ * and moba_merge then writes NaN instead of partial data.  This call launches one warp that
+ * waits `limit_us` microseconds (1 .. 100000) on a barrier nothing will ever arrive on and then
+ * sets `*status` (device int32, zero on entry) the way the kernels do.  Nothing faults, traps
+ * or spins without limit. */
+int moba_selftest_bounded_wait(int32_t* status, uint32_t limit_us, void* stream);
 
 /* Routing without a workspace.  No counterpart in the reference, whose stages
  * all allocate through torch; it exists for callers that cannot give the library

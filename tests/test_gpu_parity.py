@@ -5,6 +5,7 @@ Routing (slot tables, chunk means, selected chunks) must be bit-exact.
 Outputs must be within max-abs 2e-2 and mean-abs 2e-3 of the fp32 evaluation of
 the same selection (BASELINE.json north_star); the reference's own limits are
 max < 0.04, mean < 4e-4 against float64 (test_moba_topk.py:117-118)."""
+import ctypes as C
 import glob
 import zlib
 from pathlib import Path
@@ -147,7 +148,7 @@ def test_routing_bit_exact(case, dtype):
 @pytest.mark.parametrize("case", HEAD_DIM_CASES, ids=lambda c: c[0])
 def test_other_head_dims(case, dtype):
     """head_dim 64, 96 and 256: chunk means and selection bit-exact, output within tolerance
-    (64 on both dense stages, 96 and 256 on the mma.sync one)."""
+    (64 and 96 on both dense stages, 256 on the mma.sync one)."""
     name, d, lens, hq, hkv, chunk, topk = case
     q, k, v, cu = _case_inputs(lens, hq, hkv, chunk, zlib.crc32(name.encode()) % 1000, dtype=dtype, d=d)
     max_seqlen = max(lens)
@@ -155,12 +156,12 @@ def test_other_head_dims(case, dtype):
     qd, kd, vd = G.to_dev(q, k, v)
     cud = torch.from_numpy(cu).cuda()
     prob, _ = G.problem_for(qd, kd, vd, cud, max_seqlen, chunk, topk)
-    assert prob.attend_impl == (_lib.ATTEND_TCGEN05 if d == 64 else _lib.ATTEND_MMA_SYNC)
+    assert prob.attend_impl == (_lib.ATTEND_TCGEN05 if d in (64, 96) else _lib.ATTEND_MMA_SYNC)
     cu_chunk_o, _, valid_o, _ = O.chunk_slots(cu, max_seqlen, chunk)
     means_o = O.chunk_means(k, cu_chunk_o, valid_o, chunk)
     m = G.means(prob, kd, cud)
     assert torch.equal(m.cpu().view(torch.int16), means_o.view(torch.int16))
-    for impl in ((_lib.ATTEND_TCGEN05, _lib.ATTEND_MMA_SYNC) if d == 64 else (_lib.ATTEND_MMA_SYNC,)):
+    for impl in ((_lib.ATTEND_TCGEN05, _lib.ATTEND_MMA_SYNC) if d in (64, 96) else (_lib.ATTEND_MMA_SYNC,)):
         out, lse, sel = parallel.moba_forward(qd, kd, vd, cud, max_seqlen, chunk, topk, return_lse=True,
                                               return_selected=True, attend_impl=impl)
         torch.cuda.synchronize()
@@ -168,8 +169,8 @@ def test_other_head_dims(case, dtype):
         mx, mean = G.rel_stats(out.cpu(), ref)
         assert mx < MAX_ABS and mean < MEAN_ABS, (impl, mx, mean)
         assert (lse.cpu() - ref_lse).abs().max().item() < 2e-3
-    if d != 64:
-        with pytest.raises(_lib.MobaError):                   # the tcgen05 stage is built for head_dim 64 and 128
+    if d == 256:
+        with pytest.raises(_lib.MobaError):                   # the tcgen05 stage is built for head_dim 64, 96 and 128
             parallel.moba_forward(qd, kd, vd, cud, max_seqlen, chunk, topk, attend_impl=_lib.ATTEND_TCGEN05)
 
 
@@ -695,3 +696,85 @@ def test_forward_is_capturable_in_a_cuda_graph():
         with torch.no_grad():
             eager = parallel.parallel_moba(sq, sk, sv, cud, 1290, 128, 4)
         assert torch.equal(out, eager)
+
+
+def test_bounded_wait_gives_up_and_the_merge_poisons_the_output():
+    """A device-side wait that nothing satisfies runs out after its limit (1 ms here), sets the
+    status word and returns; the merge then writes NaN instead of partial results.  The failure
+    is made by a barrier nobody arrives on: no fault, no trap, no unbounded spin, and the context
+    stays usable (a normal forward afterwards is checked)."""
+    status = torch.zeros(2, dtype=torch.int32, device="cuda")
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    _lib.check(_lib.lib().moba_selftest_bounded_wait(status.data_ptr(), 1000, G.stream()))
+    t1.record()
+    torch.cuda.synchronize()
+    assert status[0].item() != 0
+    assert 0.9 < t0.elapsed_time(t1) < 50.0                                # waited its millisecond, not the 2 s default
+    assert _lib.lib().moba_selftest_bounded_wait(status.data_ptr(), 0, G.stream()) == -1
+    # merge of arbitrary finite partials under that status: NaN everywhere
+    q, k, v, cu = _case_inputs((512,), 4, 2, 128, seed=1)
+    qd, kd, vd = G.to_dev(q, k, v)
+    cud = torch.from_numpy(cu).cuda()
+    prob, out = G.problem_for(qd, kd, vd, cud, 512, 128, 3)
+    d = G.dims_of(prob)
+    pout = torch.randn(d.rows * d.partials * 128, dtype=torch.float32, device="cuda")
+    plse = torch.randn(d.rows * d.partials, dtype=torch.float32, device="cuda")
+    _lib.check(_lib.lib().moba_merge(C.byref(prob), pout.data_ptr(), plse.data_ptr(), status.data_ptr(), out.data_ptr(),
+                                     None, G.stream()))
+    torch.cuda.synchronize()
+    assert torch.isnan(out.float()).all()
+    status.zero_()
+    _lib.check(_lib.lib().moba_merge(C.byref(prob), pout.data_ptr(), plse.data_ptr(), status.data_ptr(), out.data_ptr(),
+                                     None, G.stream()))
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
+    good = parallel.moba_forward(qd, kd, vd, cud, 512, 128, 3)[0]
+    assert torch.isfinite(good.float()).all()
+
+
+def test_incremental_prefill_with_a_means_cache_equals_one_shot():
+    """Prefill of one sequence in three chunk-aligned increments, each call seeing a longer K/V
+    prefix and taking the means of the chunks completed earlier from a caller-held cache: outputs
+    and selections equal the one-shot run bit for bit, and so does the cache in the end."""
+    total, hq, hkv, chunk, topk = 3072, 8, 2, 256, 4
+    q, k, v, cu = _case_inputs((total,), hq, hkv, chunk, seed=12)
+    qd, kd, vd = G.to_dev(q, k, v)
+    full, _, full_sel = parallel.moba_forward(qd, kd, vd, torch.from_numpy(cu).cuda(), total, chunk, topk,
+                                              return_selected=True)
+    mc = total // chunk
+    cache = torch.full((mc, hkv, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    cached = 0
+    for lo, hi in ((0, 1024), (1024, 1792), (1792, 3072)):
+        cu_i = torch.tensor([0, hi], dtype=torch.int32, device="cuda")
+        out, _, sel = parallel.moba_forward(qd[lo:hi], kd[:hi], vd[:hi], cu_i, total, chunk, topk, return_selected=True,
+                                            q_token_begin=lo, means_cache=cache, cached_slots=cached)
+        torch.cuda.synchronize()
+        assert torch.equal(out, full[lo:hi]) and torch.equal(sel, full_sel[:, :, lo:hi]), (lo, hi)
+        cached = hi // chunk - 1                      # the prefix's last chunk is not final yet
+    cu_chunk, _, valid, _ = O.chunk_slots(cu, total, chunk)
+    want = O.chunk_means(k, cu_chunk, valid, chunk)
+    assert torch.equal(cache.cpu().view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.parametrize("cfg_id,seed", [(1, 43), (2, 44)])
+def test_config_selection_full_tensor(cfg_id, seed):
+    """BASELINE.json configs[1] and configs[2]: the WHOLE selected-chunk tensor (every token,
+    head and rank, 1.2 M and 7.3 M entries), the chunk means and the list sizes against the
+    oracle, bit for bit."""
+    cfg = O.CONFIGS[cfg_id]
+    lens = O.config_lengths(cfg_id)
+    q, k, v, cu = O.make_inputs(lens, cfg["hq"], cfg["hkv"], cfg["d"], cfg["chunk"], seed=seed)
+    cu_chunk, _, valid, mc = O.chunk_slots(cu, max(lens), cfg["chunk"])
+    hist = O.historical_topk(cfg["topk"], mc)
+    means_o = O.chunk_means(k, cu_chunk, valid, cfg["chunk"])
+    sel_o = O.select_chunks(q, means_o, cu, max(lens), cfg["chunk"], hist)
+    qd, kd = q.cuda(), k.cuda()
+    cud = torch.from_numpy(cu).cuda()
+    prob, _ = G.problem_for(qd, kd, kd, cud, max(lens), cfg["chunk"], cfg["topk"])
+    m = G.means(prob, kd, cud)
+    assert torch.equal(m.cpu().view(torch.int16), means_o.view(torch.int16))
+    sel, counts = G.gate(prob, qd, m, cud)
+    assert np.array_equal(sel.cpu().numpy(), sel_o)
+    assert counts.sum().item() == (sel_o >= 0).sum()
