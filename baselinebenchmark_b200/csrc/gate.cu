@@ -251,8 +251,10 @@ __device__ __forceinline__ float global_ssq(const __nv_bfloat16* row) {
 }
 
 // Score of row `r` (Q tile in shared memory) against the mean at `mrow` (global), in the contract order.
+// (not inlined: it is called from the two rarely taken recheck paths, and one copy keeps the
+// kernel's hot loop small in the instruction cache)
 template <bool kHalf, int D>
-__device__ __forceinline__ float contract_score(const unsigned char* sQ, int r, const __nv_bfloat16* mrow) {
+__device__ __noinline__ float contract_score(const unsigned char* sQ, int r, const __nv_bfloat16* mrow) {
   constexpr int kNB = D / 8;
   constexpr int kNBPad = kNB <= 8 ? 8 : (kNB <= 16 ? 16 : 32);
   uint4 mraw[kNB];
@@ -298,6 +300,8 @@ __device__ __forceinline__ void heap_replace_root(uint2* heap, int n, uint32_t k
 }
 
 enum { GATE_FORCE_EXACT = 1, GATE_FORCE_RECHECK = 2 };
+// marks in the chunk word of a list entry (chunk indices are below 2^24; an empty place is 0xFFFFFFFF)
+constexpr uint32_t kTied = 1u << 30, kRunStart = 1u << 29, kChunkMask = 0x00FFFFFFu;
 
 // Resident CTAs per SM the register budget is set for: four with the narrow network (its
 // working set is small and the kernel is bound by the latency of dependent instructions, which
@@ -583,7 +587,9 @@ gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, con
     constexpr float kKappa = (18.f * (D / 16) + 16.f) / 8388608.f + (kW > 0 ? 1.f / 262144.f : 0.f);
     const float eps = kKappa * 1.001f * sqrtf(q_ssq) * sqrtf(__int_as_float(c.mean_ssq_max)) + 7.9e-31f;
     const int n_keep = min(hist, ncand);
-    int mode = 0, n_surv = 0;                                 // 0: list is exact, 1: rank survivors, 2: rank all candidates
+    // 0: list is exact; 3: order the runs of near-ties (marked in the list); 1: rank all survivors;
+    // 2: rank all candidates
+    int mode = 0, n_surv = 0;
     if (ncand > 0) {
       int n_real = 0;
       for (int i = 0; i < list_len; ++i) n_real += (int32_t)mylist[i].x >= 0;
@@ -591,17 +597,59 @@ gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, con
         mode = 2;
       } else {
         const float eps2 = 2.f * eps;
-        bool amb = (flags & GATE_FORCE_RECHECK) != 0;
-        for (int i = 0; i < n_keep && i + 1 < n_real; ++i)
-          if (!(key_float(mylist[i].y) - key_float(mylist[i + 1].y) > eps2)) amb = true;
+        const bool all = (flags & GATE_FORCE_RECHECK) != 0;
+        // settled by the estimates alone? (the common case: nothing else is computed for the row)
+        bool amb = all;
+        {
+          float prev = key_float(mylist[0].y);
+          for (int i = 0; i < n_keep && i + 1 < n_real; ++i) {
+            const float next = key_float(mylist[i + 1].y);
+            if (!(prev - next > eps2)) amb = true;
+            prev = next;
+          }
+        }
+        // survivors: the only candidates that can be among the n_keep best exact scores
         if (amb) {
           const float theta = key_float(mylist[n_keep - 1].y) - eps2;
           while (n_surv < n_real && key_float(mylist[n_surv].y) >= theta) ++n_surv;
-          // the last place also survives and more candidates exist: the near-ties may go on below the list
-          mode = (n_surv == list_len && ncand > list_len) || !(eps2 < INFINITY) || n_surv < n_keep ? 2 : 1;
+        }
+        if (!amb) {
+          mode = 0;
+        } else if ((n_surv == list_len && ncand > list_len) || !(eps2 < INFINITY) || n_surv < n_keep) {
+          mode = 2;            // the near-ties may go on below the list, or eps is not finite
+        } else {
+          // Runs of neighbours closer than 2 eps: entries of different runs are certainly in the
+          // order of their estimates, entries of one run are ordered by their exact scores.  The
+          // members of a run are marked in the chunk word (kTied, kRunStart on its first member).
+          int tied = 0;
+          bool in_run = false;
+          float prev = key_float(mylist[0].y);
+          for (int i = 0; i + 1 < n_surv; ++i) {
+            const float next = key_float(mylist[i + 1].y);
+            if (all || !(prev - next > eps2)) {
+              if (!in_run) { mylist[i].x |= kTied | kRunStart; ++tied; }
+              mylist[i + 1].x |= kTied;
+              ++tied;
+              in_run = true;
+            } else {
+              in_run = false;
+            }
+            prev = next;
+          }
+          if (all && tied == 0) {                             // a single survivor, scored again on request
+            mylist[0].x |= kTied | kRunStart;
+            tied = 1;
+          }
+          if (tied > 32) {     // more near-ties than one round of the warp ranks: rank all survivors instead
+            for (int i = 0; i < n_surv; ++i) mylist[i].x &= kChunkMask;
+            mode = 1;
+          } else if (tied > 0) {
+            mode = 3;
+          }
         }
       }
     }
+    __syncwarp();                                             // the marks are visible to the warp
     unsigned need = __ballot_sync(0xffffffffu, mode != 0);
     unsigned long long* lx = c.exact[warp];
     while (need) {
@@ -613,6 +661,53 @@ gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, con
       const int r_keep = __shfl_sync(0xffffffffu, n_keep, src);
       const float r_eps = __shfl_sync(0xffffffffu, eps, src);
       uint2* rlist = lists + (size_t)r * lstride;
+      if (r_mode == 3) {
+        // runs of near-ties: one marked entry per lane (at most 32), exact keys, rank inside the run
+        int cnt = 0, runs = 0, my_e = -1, my_run = 0;
+        for (int e0 = 0; e0 < r_total; e0 += 32) {
+          const int e = e0 + lane;
+          const uint32_t x = e < r_total ? rlist[e].x : 0u;
+          const unsigned bt = __ballot_sync(0xffffffffu, (x & kTied) != 0 && x != 0xFFFFFFFFu);
+          const unsigned bs = __ballot_sync(0xffffffffu, (x & kRunStart) != 0 && x != 0xFFFFFFFFu);
+          if ((bt >> lane) & 1) {
+            const int slot = cnt + __popc(bt & ((1u << lane) - 1));
+            const int run = runs + __popc(bs & ((2u << lane) - 1));
+            lx[slot] = (unsigned long long)e | ((unsigned long long)run << 8);
+          }
+          cnt += __popc(bt);
+          runs += __popc(bs);
+        }
+        __syncwarp();
+        unsigned long long key = 0ull;
+        uint32_t cc = 0;
+        if (lane < cnt) {
+          my_e = (int)(lx[lane] & 0xFF);
+          my_run = (int)(lx[lane] >> 8);
+          const uint2 ent = rlist[my_e];
+          cc = ent.x & kChunkMask;
+          const float e = contract_score<kHalf, D>(sQ, r, means + ((int64_t)(slot0 + (int)cc) * p.Hkv + t.hk) * D);
+          key = ((unsigned long long)float_key(e) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)(slot0 + (int)cc));
+          if (stats != nullptr) {
+            const float diff = fabsf(key_float(ent.y) - e);
+            if (!(diff <= r_eps)) atomicAdd(&stats[2], 1);
+            atomicMax(&stats[1], (int)fminf(diff / r_eps * 65536.f, 1.0e9f));
+          }
+        }
+        int rank = 0, first = my_e;
+        for (int t2 = 0; t2 < cnt; ++t2) {
+          const unsigned long long kt = __shfl_sync(0xffffffffu, key, t2);
+          const int rt = __shfl_sync(0xffffffffu, my_run, t2), et = __shfl_sync(0xffffffffu, my_e, t2);
+          if (lane < cnt && rt == my_run) {
+            rank += kt > key;
+            first = min(first, et);
+          }
+        }
+        __syncwarp();
+        if (lane < cnt) rlist[first + rank].x = cc;          // a run occupies consecutive places; marks are cleared
+        __syncwarp();
+        if (stats != nullptr && lane == 0) atomicAdd(&stats[0], 1);
+        continue;
+      }
       lx[lane] = 0ull;
       lx[lane + 32] = 0ull;
       if (__shfl_sync(0xffffffffu, (int)failed, src)) {
@@ -679,7 +774,8 @@ gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, con
       const int tl = row / p.G, hl = row - tl * p.G;
       int32_t* dst = selected + (int64_t)(t.hk * p.G + hl) * p.Tq + (t.tok_lo - p.win_lo) + tl;
       for (int r = 0; r < hist; ++r) {
-        const int cc = (int32_t)mylist[r].x;
+        const uint32_t x = mylist[r].x;
+        const int cc = x == 0xFFFFFFFFu ? -1 : (int)(x & kChunkMask);
         dst[(int64_t)r * p.sel_rs] = cc >= 0 ? slot0 + cc : -1;
         if (cc >= 0 && list_counts != nullptr) {
           if (cnt_in_smem) atomicAdd(&cnt_s[cc], 1);

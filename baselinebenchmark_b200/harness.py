@@ -46,6 +46,7 @@ BASELINE_CASES = {
     "cfg1": Case("cfg1", (6144, 2560, 7168, 3584), 32, 32, 128, 512, 3, key_offsets=True),
     "cfg2": Case("cfg2", (32768,), 32, 8, 128, 4096, 12, key_offsets=True),
     "cfg3-unit": Case("cfg3-unit", (131072,), 4, 1, 128, 4096, 8, key_offsets=True),
+    "cfg3-seq": Case("cfg3-seq", (131072,), 32, 8, 128, 4096, 8, key_offsets=True),     # one of the 16 sequences
 }
 
 
