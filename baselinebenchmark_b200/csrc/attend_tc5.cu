@@ -86,29 +86,6 @@ constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + 6 * kTileBytes + sizeof
 #endif
 constexpr int kPolyPairs = MOBA_POLY_PAIRS;
 
-// Optional cycle accounting (build with -DMOBA_TC5_TRACE): sums over all CTAs are
-// added to status[2 + i]; status must then point at 64 zeroed ints.
-#ifdef MOBA_TC5_TRACE
-#define TRACE_T0(var) const long long var = clock64()
-#define TRACE_BASE(args) reinterpret_cast<unsigned long long*>(((uintptr_t)((args).status + 2) + 7) & ~(uintptr_t)7)
-#define TRACE_ADD(args, slot, t0) atomicAdd(TRACE_BASE(args) + (slot), (unsigned long long)(clock64() - (t0)))
-#else
-#define TRACE_T0(var)
-#define TRACE_ADD(args, slot, t0)
-#endif
-
-// Optional timeline (build with -DMOBA_TC5_TIMELINE): CTA 0 stores clock64 stamps of its
-// third item, tile steps 8-11, at status[64 + 16*j' + slot] (as 64-bit values).
-#ifdef MOBA_TC5_TIMELINE
-#define TL_STAMP(args, n, j, slot)                                                                          \
-  do {                                                                                                      \
-    if (blockIdx.x == 0 && (n) == 2 && (j) >= 8 && (j) < 12)                                                \
-      reinterpret_cast<long long*>(((uintptr_t)((args).status + 64) + 7) & ~(uintptr_t)7)[((j) - 8) * 16 + (slot)] = clock64(); \
-  } while (0)
-#else
-#define TL_STAMP(args, n, j, slot)
-#endif
-
 struct KernelArgs {
   const __nv_bfloat16* q;
   const int32_t* cu;
@@ -216,11 +193,10 @@ __device__ __forceinline__ bool next_item(const KernelArgs& a, Ctrl& c, unsigned
 // -> P (bf16, written over the first 64 columns), running max / sum updated.
 template <bool kMasked, bool kHalf, int D>
 __device__ __forceinline__ void softmax_row(uint32_t tS, uint32_t tO, int j, int key0, int lim, float sl2,
-                                            float& m_ref, float& l, const KernelArgs& a, int n) {
+                                            float& m_ref, float& l) {
   uint32_t v[128];
   tmem_ld128(tS, v);
   tmem_wait_ld();
-  if (threadIdx.x == 128) TL_STAMP(a, n, j, 11);            // S loaded
   if (kMasked) {
 #pragma unroll
     for (int i = 0; i < 128; ++i) v[i] = (key0 + i < lim) ? v[i] : 0xff800000u;   // -inf
@@ -235,7 +211,6 @@ __device__ __forceinline__ void softmax_row(uint32_t tS, uint32_t tO, int j, int
   }
   const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
   const float m_new = fmaxf(m_ref, mx * sl2);
-  if (threadIdx.x == 128) TL_STAMP(a, n, j, 12);            // row max known
   if (__any_sync(0xffffffffu, m_new > m_ref + 8.f)) {
     const float alpha = (m_new == -INFINITY) ? 1.f : ex2_approx(m_ref - m_new);
     if (j > 0) {
@@ -275,9 +250,7 @@ __device__ __forceinline__ void softmax_row(uint32_t tS, uint32_t tO, int j, int
   }
   const uint64_t sum = add2(sum_a, sum_b);
   l += lo2(sum) + hi2(sum);
-  if (threadIdx.x == 128) TL_STAMP(a, n, j, 13);            // exponentials done, stores issued
   tmem_wait_st();
-  if (threadIdx.x == 128) TL_STAMP(a, n, j, 14);            // stores complete
 }
 
 // Descriptor words.  Low word: start address >> 4 | (leading byte offset >> 4) << 16;
@@ -417,7 +390,6 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         // costs a dozen dependent vector instructions and the issuer starves for
         // issue slots next to the softmax warps of its scheduler partition.
         bool ok = true;
-        TRACE_T0(t_item);
         tc_fence_after();
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.k_full[kc & 1]), (kc >> 1) & 1));
         if (ok) {
@@ -435,25 +407,17 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         for (int j = 0; ok && j < ntiles; ++j) {
           const bool more = j + 1 < ntiles;
           const uint32_t vs = vc & 1, ks = vs ^ 1;
-          TRACE_T0(t_v);
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.v_full[vs]), (vc >> 1) & 1));
           if (!ok) break;
-          if (lane == 0) TRACE_ADD(a, 0, t_v);
-          TRACE_T0(t_pa);
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.p_full[0]), pph0));
           if (!ok) break;
-          if (lane == 0) TRACE_ADD(a, 1, t_pa);
           pph0 ^= 1;
           tc_fence_after();
-          if (lane == 0) TL_STAMP(a, n, j, 0);               // P_A seen
           if (el) { if (vs) issue_pv<0, 1, kHalf, D>(tm, dv, j == 0); else issue_pv<0, 0, kHalf, D>(tm, dv, j == 0); }
           __syncwarp();
-          if (lane == 0) TL_STAMP(a, n, j, 1);               // PV_A issued
           if (more) {
-            TRACE_T0(t_k);
             ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.k_full[ks]), (kc >> 1) & 1));
             if (!ok) break;
-            if (lane == 0) TRACE_ADD(a, 2, t_k);
             tc_fence_after();
             if (el) {
               if (ks) issue_qk<0, 1, kHalf, D>(tm, dq, dk); else issue_qk<0, 0, kHalf, D>(tm, dq, dk);
@@ -463,14 +427,10 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
             tc_commit(smem_u32(&c.o_full[0]));
           }
           __syncwarp();
-          if (lane == 0) TL_STAMP(a, n, j, 2);               // QK_A issued
-          TRACE_T0(t_pb);
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.p_full[1]), pph1));
           if (!ok) break;
-          if (lane == 0) TRACE_ADD(a, 3, t_pb);
           pph1 ^= 1;
           tc_fence_after();
-          if (lane == 0) TL_STAMP(a, n, j, 3);               // P_B seen
           if (el) {
             if (vs) issue_pv<1, 1, kHalf, D>(tm, dv, j == 0); else issue_pv<1, 0, kHalf, D>(tm, dv, j == 0);
             tc_commit(smem_u32(&c.v_empty[vs]));
@@ -483,12 +443,10 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
             }
           }
           __syncwarp();
-          if (lane == 0) TL_STAMP(a, n, j, 4);               // PV_B + QK_B issued
           ++vc;
           if (more) ++kc;
         }
         if (!ok && lane == 0) { atomicExch(a.status, ST_MMA); c.abort = 1; }
-        if (lane == 0) TRACE_ADD(a, 4, t_item);
       }
       __syncwarp();
     }
@@ -502,14 +460,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     const uint32_t tO = tmem + lane_base + 256 + x * 128;
     const float sl2 = rsqrtf((float)D) * 1.4426950408889634f;
     uint32_t sph = 0, oph = 0;                           // s_full / o_full phases of this tile
-#ifdef MOBA_TC5_TRACE
-    long long t_next = clock64();
-    const long long t_kernel = t_next;
-#endif
     for (int n = 0; next_item<true, D>(a, c, smem, n & 1, it); ++n) {
-#ifdef MOBA_TC5_TRACE
-      if (threadIdx.x == 128) { TRACE_ADD(a, 8, t_next); atomicAdd(TRACE_BASE(a) + 9, 1ull); }
-#endif
       const int32_t* entries = c.entry[n & 1];
       const int ntiles = (it.kv_len + kBN - 1) / kBN;
       const int qpos = it.tok0 + x * kTileM + row;
@@ -517,27 +468,18 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
       float m_ref = -INFINITY, l = 0.f;
       bool ok = true;
       for (int j = 0; ok && j < ntiles; ++j) {
-        TRACE_T0(t_s);
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.s_full[x]), sph));   // warp-uniform exit
         if (!ok) break;
-        if (threadIdx.x == 128) TRACE_ADD(a, 5, t_s);
-        TRACE_T0(t_c);
         sph ^= 1;
         tc_fence_after();
-        if (threadIdx.x == 128) TL_STAMP(a, n, j, 5);        // S_A seen
-        if (threadIdx.x == 256) TL_STAMP(a, n, j, 9);        // S_B seen
         const int key0 = j * kBN;
         const bool masked = key0 + kBN > it.kv_len ||
                             (it.causal && it.kv_tok0 + key0 + kBN - 1 > it.tok0 + x * kTileM);
-        if (masked) softmax_row<true, kHalf, D>(tS, tO, j, key0, lim, sl2, m_ref, l, a, n);
-        else softmax_row<false, kHalf, D>(tS, tO, j, key0, lim, sl2, m_ref, l, a, n);
+        if (masked) softmax_row<true, kHalf, D>(tS, tO, j, key0, lim, sl2, m_ref, l);
+        else softmax_row<false, kHalf, D>(tS, tO, j, key0, lim, sl2, m_ref, l);
         tc_fence_before();
         mbar_arrive(smem_u32(&c.p_full[x]));
-        if (threadIdx.x == 128) TL_STAMP(a, n, j, 6);        // P_A arrived
-        if (threadIdx.x == 256) TL_STAMP(a, n, j, 10);       // P_B arrived
-        if (threadIdx.x == 128) TRACE_ADD(a, 6, t_c);
       }
-      TRACE_T0(t_e);
       if (ok) ok = mbar_wait(smem_u32(&c.o_full[x]), oph);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
@@ -571,18 +513,11 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         }
         if (e >= 0) a.partial_lse[e] = (m_ref + log2f(l)) * 0.6931471805599453f;
         tc_fence_before();
-        if (threadIdx.x == 128) TRACE_ADD(a, 7, t_e);
       } else {
         atomicExch(a.status, ST_SOFTMAX);
         c.abort = 1;
       }
-#ifdef MOBA_TC5_TRACE
-      t_next = clock64();
-#endif
     }
-#ifdef MOBA_TC5_TRACE
-    if (threadIdx.x == 128) TRACE_ADD(a, 10, t_kernel);
-#endif
   }
 
   // teardown: all roles are past their last wait; give in-flight copies time to

@@ -209,23 +209,31 @@ def timed_steps(runner, steps, warmup, barrier, calls=1):
 
 
 def pin_to_gpu_numa_node(index):
-    """Best effort: run this process on the CPUs of the NUMA node the GPU hangs off, so that the
-    pinned host buffers of the end-to-end leg are allocated next to it."""
+    """Best effort: run this process on the CPUs next to its GPU, so that the pinned host buffers
+    of the end-to-end leg are allocated (first touch) on the NUMA node the GPU hangs off and the
+    copies of eight ranks do not all cross the same socket link.  The CPU list comes from the
+    driver's topology table (`nvidia-smi topo -m`, column "CPU Affinity").  Returns the list it
+    pinned to (as text) or None."""
     try:
-        bus = torch.cuda.get_device_properties(index).pci_bus_id
-        dom = torch.cuda.get_device_properties(index).pci_domain_id
-        dev = torch.cuda.get_device_properties(index).pci_device_id
-        node = int(Path(f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node").read_text())
-        if node < 0:
-            return None
-        cpus = set()
-        for part in Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip().split(","):
-            lo, _, hi = part.partition("-")
-            cpus.update(range(int(lo), int(hi or lo) + 1))
-        cpus &= os.sched_getaffinity(0)
-        if cpus:
-            os.sched_setaffinity(0, cpus)
-            return node
+        out = subprocess.run(["nvidia-smi", "topo", "-m"], capture_output=True, text=True, timeout=20).stdout
+        header = None
+        for line in out.splitlines():
+            clean = line.replace("\x1b[4m", "").replace("\x1b[0m", "")
+            cells = [c.strip() for c in clean.split("\t")]
+            if header is None and any(c == "CPU Affinity" for c in cells):
+                header = cells
+                continue
+            if header is not None and cells and cells[0] == f"GPU{index}":
+                spec = cells[header.index("CPU Affinity")]
+                cpus = set()
+                for part in spec.split(","):
+                    lo, _, hi = part.partition("-")
+                    cpus.update(range(int(lo), int(hi or lo) + 1))
+                cpus &= os.sched_getaffinity(0)
+                if cpus:
+                    os.sched_setaffinity(0, cpus)
+                    return spec
+                return None
     except Exception:
         pass
     return None
@@ -621,7 +629,7 @@ def main():
                     "d2h_bytes_per_step": d2h * world, "ms_per_step": e2e_ms / args.e2e_steps, "steps": args.e2e_steps,
                     "host_buffers": "per rank one pinned two-sequence slab of inputs (3.2 GB) and one of results "
                                     "(2.1 GB), copied in and out by every call of the step",
-                    "numa_node_of_rank0": numa},
+                    "cpus_of_rank0": numa},
             "gpu_launches": KERNELS_PER_CALL * calls * args.steps,
             "roofline": {"kernel": "attend_tc5_kernel", "bound": "tensor", "achieved": achieved,
                          "peak": pk["sustained"], "unit": "TFLOP/s", "frac": achieved / pk["sustained"],
