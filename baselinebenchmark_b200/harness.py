@@ -116,6 +116,8 @@ def run_case(case: Case, args, device):
     call = (q, k, v, cu, max(case.seq_lens), case.chunk_size, case.topk)
     if args.backward:
         return run_backward_case(case, args, call)
+    if args.stage == "gating":
+        return run_gating_case(case, args, call)
     with torch.inference_mode():
         parallel_moba(*call)
         torch.cuda.synchronize()
@@ -136,6 +138,51 @@ def run_case(case: Case, args, device):
             "native_sparse_path_eligible": bool(native_moba._supported(q)) and case.topk > 1
             and max(case.seq_lens) > case.chunk_size,
             "latency": stats, "tokens_per_s": tokens / (stats["median_ms"] * 1e-3)}
+
+
+def run_gating_case(case: Case, args, call):
+    """Latency of the gating stage alone through the staged C entry points (chunk means, then
+    scores + mask + top-k: routing.py:740-775, :1185-1262), with the counters of the gating
+    kernel's decision paths."""
+    import ctypes as C
+    from . import _lib
+    from .parallel import make_problem
+    q, k, v, cu, max_seqlen, chunk, topk = call
+    prob = make_problem(q, k, v, q, cu, max_seqlen, chunk, topk)          # no output tensor: q stands in for its strides
+    dims = _lib.Dims()
+    _lib.check(_lib.lib().moba_problem_dims(C.byref(prob), C.byref(dims)))
+    if dims.hist <= 0:
+        return {**asdict(case), "status": "skipped", "reason": "nothing to select (top-k 1 or one chunk)"}
+    means = torch.empty(dims.slots, k.shape[1], k.shape[2], dtype=k.dtype, device=k.device)
+    sel = torch.empty(dims.hist, q.shape[1], q.shape[0], dtype=torch.int32, device=q.device)
+    counts = torch.zeros(dims.lists, dtype=torch.int32, device=q.device)
+    stats = torch.zeros(4, dtype=torch.int32, device=q.device)
+    lib = _lib.lib()
+
+    def call_once(with_stats=False):
+        st = torch.cuda.current_stream().cuda_stream
+        counts.zero_()
+        _lib.check(lib.moba_chunk_means(C.byref(prob), k.data_ptr(), cu.data_ptr(), means.data_ptr(), st))
+        _lib.check(lib.moba_gate_topk_stats(C.byref(prob), q.data_ptr(), means.data_ptr(), cu.data_ptr(), sel.data_ptr(),
+                                            counts.data_ptr(), stats.data_ptr() if with_stats else None, 0, st))
+
+    call_once(True)
+    torch.cuda.synchronize()
+    st = stats.cpu().tolist()
+    samples = []
+    for _ in range(args.rounds):
+        for _ in range(args.warmup):
+            call_once()
+        torch.cuda.synchronize()
+        for _ in range(args.iterations):
+            t0 = time.perf_counter()
+            call_once()
+            torch.cuda.synchronize()
+            samples.append((time.perf_counter() - t0) * 1e3)
+    rows = q.shape[0] * q.shape[1]
+    return {**asdict(case), "status": "measured", "pass": "gating", "latency": summary(samples), "rows": rows,
+            "rows_rechecked": st[0], "rows_ranked_over_all_candidates": st[3],
+            "largest_estimate_error_over_bound": st[1] / 65536.0, "bound_violations": st[2]}
 
 
 def run_backward_case(case: Case, args, call):
@@ -169,6 +216,8 @@ def main(argv=None):
     ap.add_argument("--iterations", type=int, default=25)
     ap.add_argument("--rounds", type=int, default=4)
     ap.add_argument("--backward", action="store_true", help="time moba_backward instead of the forward")
+    ap.add_argument("--stage", choices=["all", "gating"], default="all",
+                    help="gating: time chunk means + scores + top-k alone (staged entry points)")
     ap.add_argument("--output")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():

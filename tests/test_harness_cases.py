@@ -24,7 +24,7 @@ def test_every_suite_case_is_supported():
 
 
 def test_baseline_cases_match_their_names():
-    assert set(harness.BASELINE_CASES) == {"cfg0", "cfg1", "cfg2", "cfg3-unit"}
+    assert set(harness.BASELINE_CASES) == {"cfg0", "cfg1", "cfg2", "cfg3-unit", "cfg3-seq"}
     cfg2 = harness.BASELINE_CASES["cfg2"]
     assert (cfg2.seq_lens, cfg2.q_heads, cfg2.kv_heads, cfg2.chunk_size, cfg2.topk) == ((32768,), 32, 8, 4096, 12)
 
@@ -37,10 +37,10 @@ def test_summary_reports_p99_only_with_enough_samples():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("extra", [[], ["--backward"]], ids=["forward", "backward"])
+@pytest.mark.parametrize("extra", [[], ["--backward"], ["--stage", "gating"]], ids=["forward", "backward", "gating"])
 def test_harness_measures_a_baseline_case(extra, tmp_path):
     """The harness end to end on BASELINE.json configs[0]: one measured case with a latency
-    summary, written as JSON (forward and --backward)."""
+    summary, written as JSON (forward, --backward and the gating stage alone)."""
     import json
     out = tmp_path / "report.json"
     report = harness.main(["--case", "cfg0", "--rounds", "1", "--iterations", "2", "--warmup", "1",
