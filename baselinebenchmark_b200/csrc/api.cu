@@ -16,6 +16,11 @@ using namespace moba;
 
 namespace {
 
+// rows per work item of the dense stage: the tcgen05 kernel takes two 128-row tiles per item up to
+// head_dim 128 and one at head_dim 256, the mma.sync kernel one
+int tile_rows_of(int impl, int head_dim) {
+  return impl == MOBA_ATTEND_MMA_SYNC ? kMmaTileRows : (head_dim > 128 ? kTileRowsWide : kTc5TileRows);
+}
 constexpr size_t kAlign = 256;
 inline size_t align_up(size_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
 
@@ -30,8 +35,6 @@ int check_problem(const moba_problem_t* p) {
   if (p->topk < 1 || p->topk > kMaxTopk) return MOBA_E_TOPK;               // :432-437
   if (p->head_dim > 256) return MOBA_E_SHAPE;                              // :445-446
   if (p->head_dim != 64 && p->head_dim != 96 && p->head_dim != 128 && p->head_dim != 256) return MOBA_E_UNSUPPORTED;
-  // the tcgen05 dense stage is built for head_dim 64, 96 and 128; 256 runs the mma.sync one
-  if (p->attend_impl == MOBA_ATTEND_TCGEN05 && p->head_dim == 256) return MOBA_E_UNSUPPORTED;
   if (p->num_q_heads / p->num_kv_heads > 128) return MOBA_E_UNSUPPORTED;
   if (p->attend_impl != MOBA_ATTEND_TCGEN05 && p->attend_impl != MOBA_ATTEND_MMA_SYNC) return MOBA_E_UNSUPPORTED;
   if ((p->dtype != MOBA_DTYPE_BF16 && p->dtype != MOBA_DTYPE_FP16) || p->reserved != 0) return MOBA_E_UNSUPPORTED;
@@ -60,7 +63,7 @@ int check_problem(const moba_problem_t* p) {
   // tiles = slots * Hq * tiles per chunk, per pass of one kv-head group at least)
   if (p->batch > 65535 || p->num_kv_heads > 65535) return MOBA_E_UNSUPPORTED;
   const int64_t g = p->num_q_heads / p->num_kv_heads;
-  const int64_t tile = p->attend_impl == MOBA_ATTEND_MMA_SYNC ? kMmaTileRows : kTc5TileRows;
+  const int64_t tile = tile_rows_of(p->attend_impl, p->head_dim);
   const int64_t own_items = mc * p->batch * g * ((p->chunk_size + tile - 1) / tile);
   const int64_t routed_items = (hist > 0 ? hist : 0) * tq * g / tile + mc * p->batch;
   if (own_items + routed_items >= ((int64_t)1 << 31)) return MOBA_E_UNSUPPORTED;
@@ -139,7 +142,7 @@ Workspace carve(const Params& r, void* base) {
   return w;
 }
 
-int tile_rows_of(int impl) { return impl == MOBA_ATTEND_MMA_SYNC ? kMmaTileRows : kTc5TileRows; }
+
 
 int attend_dispatch(const moba_problem_t* p, const Params& r, const void* q, const void* k, const void* v,
                     const int32_t* cu, const int32_t* list_counts, const int32_t* list_offsets,
@@ -218,7 +221,7 @@ const char* moba_b200_strerror(int code) {
   switch (code) {
     case MOBA_OK: return "ok";
     case MOBA_E_SHAPE: return "q, k, v, cu_seqlens or the integer arguments have an invalid shape or value";
-    case MOBA_E_UNSUPPORTED: return "configuration outside this build (bf16 or fp16; head_dim 64, 96, 128 or 256, tcgen05 dense stage up to 128 only)";
+    case MOBA_E_UNSUPPORTED: return "configuration outside this build (bf16 or fp16; head_dim 64, 96, 128 or 256, backward up to 128 only)";
     case MOBA_E_WORKSPACE: return "workspace is null or too small";
     case MOBA_E_NULL: return "a required pointer is null";
     case MOBA_E_TOPK: return "moba_topk must be in 1..64";
@@ -246,7 +249,8 @@ int moba_problem_dims(const moba_problem_t* p, moba_dims_t* d) {
   return MOBA_OK;
 }
 
-int moba_attend_tile_rows(int impl) { return tile_rows_of(impl); }
+int moba_attend_tile_rows(int impl) { return tile_rows_of(impl, 128); }
+int moba_attend_tile_rows_for(int impl, int head_dim) { return tile_rows_of(impl, head_dim); }
 
 int moba_workspace_size(const moba_problem_t* p, size_t* bytes) {
   const int rc = check_problem(p);
@@ -378,7 +382,7 @@ static int forward_pass(const moba_problem_t* p, int64_t sel_rs, const void* q, 
     if ((e = launch_gate_topk(r, qb, means, cu, sel, w.list_counts, st)) != cudaSuccess) return (int)e;
     if (last && (e = mark(2)) != cudaSuccess) return (int)e;
     if ((e = launch_compact(r, cu, sel, w.list_counts, w.list_offsets, w.tile_prefix, w.cursors, w.row_list,
-                            w.partial_lse, tile_rows_of(p->attend_impl), st)) != cudaSuccess)
+                            w.partial_lse, tile_rows_of(p->attend_impl, p->head_dim), st)) != cudaSuccess)
       return (int)e;
   } else if (last) {
     if ((e = mark(1)) != cudaSuccess || (e = mark(2)) != cudaSuccess) return (int)e;

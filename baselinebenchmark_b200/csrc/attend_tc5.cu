@@ -73,6 +73,7 @@ struct Ctrl {
   // tile_prefix copied once per CTA when it fits: decoding an item searches it, and with
   // short items (small chunks) eleven dependent global loads per item were the critical path
   int32_t prefix_cache[kPrefixCache];
+  float row_inv[kTileM];                   // head dim 256: 1 / row sum, handed to the warps that write the second half of O
 };
 
 constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + 6 * kTileBytes + sizeof(Ctrl);
@@ -102,6 +103,7 @@ struct KernelArgs {
 // Runs in one spare warp while the other warps work on the current item: draws the
 // next item from the global queue (skipping empty own-chunk tiles), decodes it and
 // resolves its rows (output entry and Q row offset) into prefetch slot `slot`.
+template <int kItemRows>
 __device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs& a, Ctrl& c, int slot,
                                               int n_routed, int n_items) {
   const int lane = threadIdx.x & 31;
@@ -113,16 +115,16 @@ __device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs&
     if (lane == 0) idx = c.abort ? 0x7fffffff : atomicAdd(a.work_counter, 1);
     idx = __shfl_sync(0xffffffffu, idx, 0);
     if (idx >= n_items) { done = 1; break; }
-    it = decode_item(p, idx, n_routed, 2 * kTileM, a.cu, a.list_counts, a.list_offsets,
+    it = decode_item(p, idx, n_routed, kItemRows, a.cu, a.list_counts, a.list_offsets,
                      p.lists < kPrefixCache ? c.prefix_cache : a.tile_prefix);
     if (it.valid) break;
   }
   if (lane == 0) { c.item[slot] = it; c.done[slot] = done; }
   if (!done) {
-    // the 8 rows of a lane: all row_list loads in flight before any of them is used
-    int32_t ent[2 * kTileM / 32];
+    // the rows of a lane: all row_list loads in flight before any of them is used
+    int32_t ent[kItemRows / 32];
 #pragma unroll
-    for (int u = 0; u < 2 * kTileM / 32; ++u) {
+    for (int u = 0; u < kItemRows / 32; ++u) {
       const int r = lane + 32 * u;
       ent[u] = -1;
       if (r < it.nrows) {
@@ -131,7 +133,7 @@ __device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs&
       }
     }
 #pragma unroll
-    for (int u = 0; u < 2 * kTileM / 32; ++u) {
+    for (int u = 0; u < kItemRows / 32; ++u) {
       const int r = lane + 32 * u;
       const int32_t e = ent[u];
       int64_t off = 0;
@@ -145,6 +147,10 @@ __device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs&
       if (e >= 0) {                                            // the gather of the next item then hits L2
         asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + off));
         if (p.D > 64) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + off + 64));
+        if (p.D > 128) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + off + 128));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + off + 192));
+        }
       }
     }
   }
@@ -155,7 +161,7 @@ __device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs&
 // Common head of an item, executed by all 384 threads: take the prefetched item
 // of slot `slot`; the softmax warps (kGather) gather its Q rows into the two swizzled Q tiles.  Returns
 // false when the queue is empty (or the kernel is aborting).
-template <bool kGather, int D>
+template <bool kGather, int D, int kItemRows = 2 * kTileM>
 __device__ __forceinline__ bool next_item(const KernelArgs& a, Ctrl& c, unsigned char* smem, int slot, Item& it) {
   __syncthreads();                         // every role has finished the previous item; slot is filled
   if (c.done[slot]) return false;
@@ -166,17 +172,18 @@ __device__ __forceinline__ bool next_item(const KernelArgs& a, Ctrl& c, unsigned
   // produce; the 256 softmax threads do it, each with its D/8 loads in flight at once
   if (kGather) {
     constexpr int kChunks = D / 8;                  // 16-byte pieces of a row
+    constexpr int kPieces = kItemRows * kChunks / 256;   // pieces per thread
     const int t = threadIdx.x - 128;
-    uint4 val[kChunks];
+    uint4 val[kPieces];
 #pragma unroll
-    for (int u = 0; u < kChunks; ++u) {
+    for (int u = 0; u < kPieces; ++u) {
       const int i = t + u * 256;
       const int r = i / kChunks, ch = i % kChunks;
       val[u] = make_uint4(0, 0, 0, 0);
       if (entry[r] >= 0) val[u] = __ldg(reinterpret_cast<const uint4*>(a.q + qoff[r] + ch * 8));
     }
 #pragma unroll
-    for (int u = 0; u < kChunks; ++u) {
+    for (int u = 0; u < kPieces; ++u) {
       const int i = t + u * 256;
       const int r = i / kChunks, ch = i % kChunks;
       const uint32_t dst = (uint32_t)((r >> 7) * kTileBytes + (ch >> 3) * kHalfBytes + (r & 127) * 128 +
@@ -191,9 +198,11 @@ __device__ __forceinline__ bool next_item(const KernelArgs& a, Ctrl& c, unsigned
 
 // One softmax step of one row: S (128 fp32 columns of this thread's TMEM lane)
 // -> P (bf16, written over the first 64 columns), running max / sum updated.
-template <bool kMasked, bool kHalf, int D>
+// `before_rescale` runs (warp-uniformly) before the accumulator O is rescaled: a kernel whose
+// previous P.V may still be executing at that point waits for it there.
+template <bool kMasked, bool kHalf, int D, typename F>
 __device__ __forceinline__ void softmax_row(uint32_t tS, uint32_t tO, int j, int key0, int lim, float sl2,
-                                            float& m_ref, float& l) {
+                                            float& m_ref, float& l, F&& before_rescale) {
   uint32_t v[128];
   tmem_ld128(tS, v);
   tmem_wait_ld();
@@ -214,6 +223,7 @@ __device__ __forceinline__ void softmax_row(uint32_t tS, uint32_t tO, int j, int
   if (__any_sync(0xffffffffu, m_new > m_ref + 8.f)) {
     const float alpha = (m_new == -INFINITY) ? 1.f : ex2_approx(m_ref - m_new);
     if (j > 0) {
+      before_rescale();
       uint32_t o[32];
 #pragma unroll
       for (int ch = 0; ch < D / 32; ++ch) {
@@ -341,7 +351,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     const uint32_t el = elect_one();
     for (int n = 0;; ++n) {
       // warp 2 runs one item ahead: it fills slot n & 1 while the others still work on item n - 1
-      if (warp == 2) prefetch_item(p, a, c, n & 1, n_routed, n_items);
+      if (warp == 2) prefetch_item<2 * kTileM>(p, a, c, n & 1, n_routed, n_items);
       if (!next_item<false, D>(a, c, smem, n & 1, it)) break;
       const int ntiles = (it.kv_len + kBN - 1) / kBN;
       if (warp == 0 && lane == 0) {
@@ -475,8 +485,9 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         const int key0 = j * kBN;
         const bool masked = key0 + kBN > it.kv_len ||
                             (it.causal && it.kv_tok0 + key0 + kBN - 1 > it.tok0 + x * kTileM);
-        if (masked) softmax_row<true, kHalf, D>(tS, tO, j, key0, lim, sl2, m_ref, l);
-        else softmax_row<false, kHalf, D>(tS, tO, j, key0, lim, sl2, m_ref, l);
+        // S of the next step is only computed after this tile's P.V: O is quiet here
+        if (masked) softmax_row<true, kHalf, D>(tS, tO, j, key0, lim, sl2, m_ref, l, [] {});
+        else softmax_row<false, kHalf, D>(tS, tO, j, key0, lim, sl2, m_ref, l, [] {});
         tc_fence_before();
         mbar_arrive(smem_u32(&c.p_full[x]));
       }
@@ -522,6 +533,292 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
 
   // teardown: all roles are past their last wait; give in-flight copies time to
   // land after an abort, then release tensor memory
+  if (c.abort) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+// ---------------------------------------------------------------------------
+// head dim 256
+//
+// One 128-row tile per work item.  Operands keep the shapes of the kernel above: Q, K and V are
+// handled as two 128-dim halves ("lo", "hi"); S = Q_lo.K_lo^T + Q_hi.K_hi^T (16 k-steps into one
+// accumulator), O_lo += P.V_lo and O_hi += P.V_hi (two 128-column accumulators).
+// TMEM columns: S buffers 0-127 and 128-255 (tile g of the CTA uses buffer g & 1), O 256-511.
+// Shared memory: Q 64 KB (lo, hi), the K halves in two 32 KB slots, the V halves in two.
+// With S double-buffered Q.K^T of tile j+1 runs while the softmax of tile j does.  Per tile the
+// tensor core has 2048 cycles of MMAs against about 1700 of softmax, so one softmax warpgroup
+// keeps it busy.  Order on the tensor core: QK(0) QK(1) PV(0) QK(2) PV(1) ...; the producer
+// requests K and V in that order.  The P.V of a tile may still be executing when the softmax
+// of the next tile wants to rescale O: that (rare) path waits for it first.
+// Warps 8-11 take no part in the softmax: they gather Q rows and write the hi half of O.
+// ---------------------------------------------------------------------------
+template <int SB, int H, bool kHalf>
+__device__ __forceinline__ void issue_qk_wide(uint32_t tmem, uint32_t dq, uint32_t dk) {
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    constexpr int kBlock = kHalfBytes >> 4, kTile = kTileBytes >> 4;
+    const uint32_t koff = (uint32_t)(H * kTile + (ks >> 2) * kBlock + (ks & 3) * 2);
+    mma_ss(tmem + SB * kBN, desc64(dq + koff), desc64(dk + koff), kIdescQK<kHalf>, (H | ks) > 0);
+  }
+}
+template <int SB, int H, bool kHalf>
+__device__ __forceinline__ void issue_pv_wide(uint32_t tmem, uint32_t dv, bool first) {
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks)
+    mma_ts(tmem + 256 + H * 128, tmem + SB * kBN + ks * 8,
+           desc64(dv + H * (kTileBytes >> 4) + ks * (2048 >> 4)), kIdescPV<kHalf, 128>, (!first) || ks > 0);
+}
+
+__device__ __forceinline__ void bar_sync_256() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+template <bool kHalf>
+__global__ void __launch_bounds__(kThreads, 1)
+attend_tc5_wide_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
+                       const __grid_constant__ CUtensorMap tmap_v, const KernelArgs a) {
+  constexpr int D = 256;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sQ = smem_u32(smem);                       // lo, hi
+  const uint32_t sK = sQ + 2 * kTileBytes;                  // lo, hi
+  const uint32_t sV = sK + 2 * kTileBytes;                  // lo, hi
+  Ctrl& c = *reinterpret_cast<Ctrl*>(smem + 6 * kTileBytes);
+
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&c.k_full[i]), 1);
+      mbar_init(smem_u32(&c.k_empty[i]), 1);
+      mbar_init(smem_u32(&c.v_full[i]), 1);
+      mbar_init(smem_u32(&c.v_empty[i]), 1);
+      mbar_init(smem_u32(&c.s_full[i]), 1);
+      mbar_init(smem_u32(&c.p_full[i]), kTileM);
+      mbar_init(smem_u32(&c.o_full[i]), 1);
+      mbar_init(smem_u32(&c.item_ready[i]), 1);
+    }
+    c.abort = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&c.tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  if (p.hist > 0 && p.lists < kPrefixCache)
+    for (int i = threadIdx.x; i <= (int)p.lists; i += kThreads) c.prefix_cache[i] = a.tile_prefix[i];
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = c.tmem_slot;
+
+  const int n_routed = p.hist > 0 ? a.tile_prefix[p.lists] : 0;
+  const int n_items = n_routed + own_item_count(p.slots, p.Hq, p.C, kTileM);
+  Item it;
+  // c.o_full[0] completes once per tile, when its P.V has executed; "tile g" counts the CTA's tiles
+
+  if (warp < 4) {
+    setmaxnreg_dec<72>();
+    uint32_t kt = 0, vt = 0;               // K / V tiles produced (warp 0) or consumed (warp 1) so far
+    uint32_t g = 0, gp = 0;                // tiles whose Q.K^T / P.V has been issued (warp 1)
+    bool pre_k0 = false, pre_v0 = false;   // producer: K(0) / V(0) of the coming item already requested
+    const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+    const uint32_t dq = __shfl_sync(0xffffffffu, desc_lo(sQ, 16), 0);
+    const uint32_t dk = __shfl_sync(0xffffffffu, desc_lo(sK, 16), 0);
+    const uint32_t dv = __shfl_sync(0xffffffffu, desc_lo(sV, kHalfBytes), 0);
+    const uint32_t el = elect_one();
+    for (int n = 0;; ++n) {
+      if (warp == 2) prefetch_item<kTileM>(p, a, c, n & 1, n_routed, n_items);
+      if (!next_item<false, D, kTileM>(a, c, smem, n & 1, it)) break;
+      const int ntiles = (it.kv_len + kBN - 1) / kBN;
+      if (warp == 0 && lane == 0) {
+        // both halves of K (V) tile `j` of item `w`, each into its slot; false after a timeout
+        auto load_k = [&](const Item& w, int j) -> bool {
+          const int tok = w.kv_tok0 + j * kBN;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (!mbar_wait(smem_u32(&c.k_empty[h]), (kt & 1) ^ 1)) return false;
+            const uint32_t bar = smem_u32(&c.k_full[h]);
+            mbar_expect_tx(bar, kTileBytes);
+            tma_load_3d(sK + h * kTileBytes, &tmap_k, bar, h * 128, w.kv_head, tok);
+            tma_load_3d(sK + h * kTileBytes + kHalfBytes, &tmap_k, bar, h * 128 + 64, w.kv_head, tok);
+          }
+          ++kt;
+          return true;
+        };
+        auto load_v = [&](const Item& w, int j) -> bool {
+          const int tok = w.kv_tok0 + j * kBN;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (!mbar_wait(smem_u32(&c.v_empty[h]), (vt & 1) ^ 1)) return false;
+            const uint32_t bar = smem_u32(&c.v_full[h]);
+            mbar_expect_tx(bar, kTileBytes);
+            tma_load_3d(sV + h * kTileBytes, &tmap_v, bar, h * 128, w.kv_head, tok);
+            tma_load_3d(sV + h * kTileBytes + kHalfBytes, &tmap_v, bar, h * 128 + 64, w.kv_head, tok);
+          }
+          ++vt;
+          return true;
+        };
+        // in the order the tensor core consumes them: K(0), then K(j + 1), V(j) for every tile j
+        bool alive = pre_k0 ? true : load_k(it, 0);
+        for (int j = 0; alive && j < ntiles; ++j) {
+          if (j + 1 < ntiles) alive = load_k(it, j + 1);
+          if (alive && !(j == 0 && pre_v0)) alive = load_v(it, j);
+        }
+        pre_k0 = pre_v0 = false;
+        // K(0) and V(0) of the next item go into the slots the tail of this item frees (K(1)
+        // would need a slot that only the next item's own first MMAs free: not before it starts)
+        if (alive) {
+          const int s1 = (n + 1) & 1;
+          alive = mbar_wait(smem_u32(&c.item_ready[s1]), ((n + 1) >> 1) & 1);
+          if (alive && !c.done[s1]) {
+            const Item nx = c.item[s1];
+            alive = load_k(nx, 0);
+            pre_k0 = alive;
+            if (alive) { alive = load_v(nx, 0); pre_v0 = alive; }
+          }
+        }
+        if (!alive) { atomicExch(a.status, ST_PRODUCER); c.abort = 1; }
+      } else if (warp == 1) {
+        bool ok = true;
+        tc_fence_after();
+        // S(g & 1) = Q.K^T for the next K tile
+        auto qk = [&]() -> bool {
+          if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&c.k_full[0]), kt & 1))) return false;
+          tc_fence_after();
+          if (el) {
+            if (g & 1) issue_qk_wide<1, 0, kHalf>(tm, dq, dk); else issue_qk_wide<0, 0, kHalf>(tm, dq, dk);
+            tc_commit(smem_u32(&c.k_empty[0]));
+          }
+          __syncwarp();
+          if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&c.k_full[1]), kt & 1))) return false;
+          tc_fence_after();
+          if (el) {
+            if (g & 1) issue_qk_wide<1, 1, kHalf>(tm, dq, dk); else issue_qk_wide<0, 1, kHalf>(tm, dq, dk);
+            tc_commit(smem_u32(&c.k_empty[1]));
+            tc_commit(smem_u32(&c.s_full[g & 1]));
+          }
+          __syncwarp();
+          ++kt;
+          ++g;
+          return true;
+        };
+        ok = qk();
+        if (ok && ntiles > 1) ok = qk();
+        for (int j = 0; ok && j < ntiles; ++j) {
+          // O += P.V: P of tile gp sits in S buffer gp & 1
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.v_full[0]), vt & 1));
+          if (!ok) break;
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.p_full[0]), gp & 1));
+          if (!ok) break;
+          tc_fence_after();
+          if (el) {
+            if (gp & 1) issue_pv_wide<1, 0, kHalf>(tm, dv, j == 0); else issue_pv_wide<0, 0, kHalf>(tm, dv, j == 0);
+            tc_commit(smem_u32(&c.v_empty[0]));
+          }
+          __syncwarp();
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.v_full[1]), vt & 1));
+          if (!ok) break;
+          tc_fence_after();
+          if (el) {
+            if (gp & 1) issue_pv_wide<1, 1, kHalf>(tm, dv, j == 0); else issue_pv_wide<0, 1, kHalf>(tm, dv, j == 0);
+            tc_commit(smem_u32(&c.v_empty[1]));
+            tc_commit(smem_u32(&c.o_full[0]));
+          }
+          __syncwarp();
+          ++vt;
+          ++gp;
+          if (j + 2 < ntiles) ok = qk();
+        }
+        if (!ok && lane == 0) { atomicExch(a.status, ST_MMA); c.abort = 1; }
+      }
+      __syncwarp();
+    }
+  } else {
+    setmaxnreg_inc<216>();
+    const int xg = (warp - 4) >> 2;                      // 0: softmax + lo half of O, 1: hi half of O
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tO = tmem + lane_base + 256;
+    const float sl2 = rsqrtf((float)D) * 1.4426950408889634f;
+    uint32_t g = 0;                                      // tiles of this CTA before the current one
+    for (int n = 0; next_item<true, D, kTileM>(a, c, smem, n & 1, it); ++n) {
+      const int32_t* entries = c.entry[n & 1];
+      const int ntiles = (it.kv_len + kBN - 1) / kBN;
+      float m_ref = -INFINITY, l = 0.f;
+      bool ok = true;
+      if (xg == 0) {
+        const int qpos = it.tok0 + row;
+        const int lim = it.causal ? min(it.kv_len, qpos - it.kv_tok0 + 1) : it.kv_len;
+        for (int j = 0; ok && j < ntiles; ++j, ++g) {
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.s_full[g & 1]), (g >> 1) & 1));
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t tS = tmem + lane_base + (g & 1) * kBN;
+          const int key0 = j * kBN;
+          const bool masked = key0 + kBN > it.kv_len || (it.causal && it.kv_tok0 + key0 + kBN - 1 > it.tok0);
+          // the P.V of tile g - 1 must have executed before O is touched (tile g - 2 is known to have)
+          auto wait_pv = [&] {
+            if (!mbar_wait(smem_u32(&c.o_full[0]), (g - 1) & 1)) ok = false;
+            tc_fence_after();
+          };
+          if (masked) softmax_row<true, kHalf, D>(tS, tO, j, key0, lim, sl2, m_ref, l, wait_pv);
+          else softmax_row<false, kHalf, D>(tS, tO, j, key0, lim, sl2, m_ref, l, wait_pv);
+          // keeps the completions of o_full at most one behind, so that a wait on the parity of a
+          // tile index can never be answered by an older phase
+          if (j > 0 && !mbar_wait(smem_u32(&c.o_full[0]), (g - 1) & 1)) ok = false;
+          ok = __all_sync(0xffffffffu, ok);
+          tc_fence_before();
+          mbar_arrive(smem_u32(&c.p_full[0]));
+        }
+        c.row_inv[row] = 1.f / l;
+      } else {
+        g += (uint32_t)ntiles;
+      }
+      bar_sync_256();                                    // row sums are visible; the last P has been published
+      if (ok) ok = mbar_wait(smem_u32(&c.o_full[0]), (g - 1) & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tc_fence_after();
+        const int32_t e = entries[row];
+        const float inv = c.row_inv[row];
+        // as above: O rows pass through this warp's 8 KB of the idle Q tile; warps 4-7 write
+        // dims 0-127, warps 8-11 dims 128-255
+        unsigned char* stage = smem + xg * kTileBytes + (warp & 3) * 8192;
+        uint32_t v[32];
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          tmem_ld32(tO + xg * 128 + ch * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<float4*>(stage + lane * 144 + i * 16) =
+                make_float4(__uint_as_float(v[4 * i]) * inv, __uint_as_float(v[4 * i + 1]) * inv,
+                            __uint_as_float(v[4 * i + 2]) * inv, __uint_as_float(v[4 * i + 3]) * inv);
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rl = i * 4 + (lane >> 3), c16 = lane & 7;
+            const int32_t er = __shfl_sync(0xffffffffu, e, rl);
+            const float4 val = *reinterpret_cast<const float4*>(stage + rl * 144 + c16 * 16);
+            if (er >= 0) *reinterpret_cast<float4*>(a.partial_out + (int64_t)er * D + xg * 128 + ch * 32 + c16 * 4) = val;
+          }
+          __syncwarp();
+        }
+        if (xg == 0 && e >= 0) a.partial_lse[e] = (m_ref + log2f(l)) * 0.6931471805599453f;
+        tc_fence_before();
+      } else {
+        atomicExch(a.status, ST_SOFTMAX);
+        c.abort = 1;
+      }
+    }
+  }
+
   if (c.abort) {
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
@@ -595,8 +892,9 @@ cudaError_t launch_attend_tc5(const Params& p, const __nv_bfloat16* q, const __n
   CUtensorMap mk, mv;
   if (!make_kv_map(&mk, p.fp16 != 0, p.D, k, p.T, p.Hkv, p.sk_t, p.sk_h, kBN) || !make_kv_map(&mv, p.fp16 != 0, p.D, v, p.T, p.Hkv, p.sv_t, p.sv_h, kBN))
     return cudaErrorNotSupported;
-  if (p.D != 64 && p.D != 96 && p.D != 128) return cudaErrorInvalidValue;
-  auto kernel = p.D == 128 ? (p.fp16 ? attend_tc5_kernel<true, 128> : attend_tc5_kernel<false, 128>)
+  if (p.D != 64 && p.D != 96 && p.D != 128 && p.D != 256) return cudaErrorInvalidValue;
+  auto kernel = p.D == 256 ? (p.fp16 ? attend_tc5_wide_kernel<true> : attend_tc5_wide_kernel<false>)
+              : p.D == 128 ? (p.fp16 ? attend_tc5_kernel<true, 128> : attend_tc5_kernel<false, 128>)
               : p.D == 96  ? (p.fp16 ? attend_tc5_kernel<true, 96> : attend_tc5_kernel<false, 96>)
                            : (p.fp16 ? attend_tc5_kernel<true, 64> : attend_tc5_kernel<false, 64>);
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);

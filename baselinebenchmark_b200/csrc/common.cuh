@@ -172,6 +172,7 @@ cudaError_t launch_merge(const Params& p, const float* partial_out, const float*
 
 constexpr int kMmaTileRows = 128;        // rows per work item, mma.sync kernel
 constexpr int kTc5TileRows = 256;        // rows per work item, tcgen05 kernel (two 128-row MMA tiles)
+constexpr int kTileRowsWide = 128;       // rows per work item, tcgen05 kernel at head_dim 256 (one tile)
 
 cudaError_t launch_attend_mma(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* k,
                               const __nv_bfloat16* v, const int32_t* cu, const int32_t* list_counts,

@@ -212,6 +212,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--case", action="append", choices=sorted(BASELINE_CASES), help="BASELINE.json workload(s)")
     ap.add_argument("--suite", action="store_true", help="the reference's 40-case list")
+    ap.add_argument("--only", action="append", help="with --suite: only the cases of this name (repeatable)")
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--iterations", type=int, default=25)
     ap.add_argument("--rounds", type=int, default=4)
@@ -223,7 +224,13 @@ def main(argv=None):
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device")
     device = torch.device("cuda", torch.cuda.current_device())
-    cases = [BASELINE_CASES[c] for c in (args.case or [])] + (reference_suite() if args.suite else [])
+    suite = reference_suite() if args.suite else []
+    if args.only:
+        unknown = set(args.only) - {c.name for c in suite}
+        if unknown:
+            raise SystemExit(f"--only: not in the suite: {sorted(unknown)}")
+        suite = [c for c in suite if c.name in args.only]
+    cases = [BASELINE_CASES[c] for c in (args.case or [])] + suite
     if not cases:
         cases = [BASELINE_CASES["cfg0"]]
     report = {"schema_version": 4, "timing": "perf_counter + device synchronize per call; inference only",

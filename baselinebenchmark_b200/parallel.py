@@ -68,8 +68,8 @@ def _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, windo
 
 
 def default_attend_impl(head_dim: int) -> int:
-    """The tcgen05 dense stage exists for head_dim 64, 96 and 128; 256 runs the mma.sync stage."""
-    return _lib.ATTEND_TCGEN05 if head_dim in (64, 96, 128) else _lib.ATTEND_MMA_SYNC
+    """The tcgen05 dense stage for every supported head_dim (its own kernel at 256)."""
+    return _lib.ATTEND_TCGEN05 if head_dim in HEAD_DIMS else _lib.ATTEND_MMA_SYNC
 
 
 def make_problem(q, k, v, out, cu_seqlens, max_seqlen, chunk, topk, attend_impl=None,

@@ -20,9 +20,9 @@
  *     (the head dims of the reference's benchmark suite, moba_compare.py:63, :70),
  *     innermost dimension contiguous; token and head strides are given in
  *     elements (the reference kernels also take strides, attention.py:431-439).
- *     The tcgen05 dense stage exists for head_dim 64, 96 and 128; 256 runs
- *     the mma.sync dense stage (attend_impl = MOBA_ATTEND_MMA_SYNC).  Anything
- *     else returns MOBA_E_UNSUPPORTED: there is no fallback path.
+ *     Both dense stages exist for all four head dims (the tcgen05 one with its own
+ *     kernel at 256).  Anything else returns MOBA_E_UNSUPPORTED: there is no
+ *     fallback path.
  */
 #ifndef MOBA_B200_H_
 #define MOBA_B200_H_
@@ -49,7 +49,7 @@ enum {
 
 /* Which implementation of the dense stage moba_attend/moba_forward run. */
 enum {
-  MOBA_ATTEND_TCGEN05 = 0,  /* tcgen05.mma + TMEM accumulators + TMA K/V tiles (head_dim 64, 96, 128) */
+  MOBA_ATTEND_TCGEN05 = 0,  /* tcgen05.mma + TMEM accumulators + TMA K/V tiles                   */
   MOBA_ATTEND_MMA_SYNC = 1  /* legacy mma.sync tensor path, kept as cross-check  */
 };
 
@@ -323,8 +323,11 @@ int moba_cp_poll(void* nccl_comm, int32_t* async_error);
 int moba_cp_abort(void* nccl_comm);
 
 /* Rows per routed work item that the selected attend implementation wants
- * (the tile_rows argument of moba_compact_routes). */
+ * (the tile_rows argument of moba_compact_routes): moba_attend_tile_rows answers for
+ * head_dim <= 128, moba_attend_tile_rows_for for any head_dim (the tcgen05 stage takes
+ * 256 rows per item up to head_dim 128 and 128 at head_dim 256). */
 int moba_attend_tile_rows(int attend_impl);
+int moba_attend_tile_rows_for(int attend_impl, int head_dim);
 
 #ifdef __cplusplus
 }

@@ -45,7 +45,7 @@ def test_problem_check_codes(lib):
     assert lib.moba_problem_check(C.byref(_problem(topk=65))) == -5
     wide = dict(q_stride_token=2048, q_stride_head=256, k_stride_token=2048, k_stride_head=256,
                 v_stride_token=2048, v_stride_head=256, o_stride_token=2048, o_stride_head=256)
-    assert lib.moba_problem_check(C.byref(_problem(head_dim=256, **wide))) == -2            # tcgen05 stage: 64, 96, 128
+    assert lib.moba_problem_check(C.byref(_problem(head_dim=256, **wide))) == 0             # its own tcgen05 kernel
     assert lib.moba_problem_check(C.byref(_problem(head_dim=512))) == -1                    # parallel.py:445
     assert lib.moba_problem_check(C.byref(_problem(max_seqlen=0))) == -1
     assert lib.moba_problem_check(C.byref(_problem(q_stride_head=132))) == -6
@@ -58,7 +58,7 @@ def test_head_dims_and_dtypes_accepted(lib):
         stride = dict(q_stride_token=8 * d, q_stride_head=d, k_stride_token=8 * d, k_stride_head=d,
                       v_stride_token=8 * d, v_stride_head=d, o_stride_token=8 * d, o_stride_head=d)
         assert lib.moba_problem_check(C.byref(_problem(head_dim=d, attend_impl=1, **stride))) == 0      # mma.sync stage
-        assert lib.moba_problem_check(C.byref(_problem(head_dim=d, attend_impl=0, **stride))) == (-2 if d == 256 else 0)
+        assert lib.moba_problem_check(C.byref(_problem(head_dim=d, attend_impl=0, **stride))) == 0
     assert lib.moba_problem_check(C.byref(_problem(head_dim=32, attend_impl=1))) == -2
     assert lib.moba_problem_check(C.byref(_problem(dtype=1))) == 0                           # fp16
     assert lib.moba_problem_check(C.byref(_problem(dtype=2))) == -2
@@ -135,6 +135,8 @@ def test_workspace_size_and_null_handling(lib):
     assert lib.moba_forward(C.byref(_problem()), None, None, None, None, None, None, None, None, 0, None) == -4
     assert lib.moba_attend_tile_rows(_lib.ATTEND_TCGEN05) == 256
     assert lib.moba_attend_tile_rows(_lib.ATTEND_MMA_SYNC) == 128
+    assert [lib.moba_attend_tile_rows_for(_lib.ATTEND_TCGEN05, d) for d in (64, 96, 128, 256)] == [256, 256, 256, 128]
+    assert lib.moba_attend_tile_rows_for(_lib.ATTEND_MMA_SYNC, 256) == 128
 
 
 def _cpu_args(t=64, hq=4, hkv=2, d=128, dtype=torch.bfloat16):
