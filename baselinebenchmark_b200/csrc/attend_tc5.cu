@@ -138,9 +138,11 @@ __device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs&
       const int32_t e = ent[u];
       int64_t off = 0;
       if (e >= 0) {
-        const int64_t row = e / p.NP;
-        const int64_t t = row / p.Hq;
-        off = t * p.sq_t + (row - t * p.Hq) * p.sq_h;
+        // entries and rows fit 32 bits (checked on the host): unsigned 32-bit divisions, not the
+        // 64-bit ones, which are a subroutine of a hundred instructions each
+        const uint32_t row = (uint32_t)e / (uint32_t)p.NP;
+        const uint32_t t = row / (uint32_t)p.Hq;
+        off = (int64_t)t * p.sq_t + (int64_t)(row - t * (uint32_t)p.Hq) * p.sq_h;
       }
       c.entry[slot][r] = e;
       c.qoff[slot][r] = off;
@@ -518,7 +520,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
             const int rl = i * 4 + (lane >> 3), c16 = lane & 7;
             const int32_t er = __shfl_sync(0xffffffffu, e, rl);
             const float4 val = *reinterpret_cast<const float4*>(stage + rl * 144 + c16 * 16);
-            if (er >= 0) *reinterpret_cast<float4*>(a.partial_out + (int64_t)er * D + ch * 32 + c16 * 4) = val;
+            if (er >= 0) __stcs(reinterpret_cast<float4*>(a.partial_out + (int64_t)er * D + ch * 32 + c16 * 4), val);
           }
           __syncwarp();
         }
@@ -806,7 +808,7 @@ attend_tc5_wide_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_
             const int rl = i * 4 + (lane >> 3), c16 = lane & 7;
             const int32_t er = __shfl_sync(0xffffffffu, e, rl);
             const float4 val = *reinterpret_cast<const float4*>(stage + rl * 144 + c16 * 16);
-            if (er >= 0) *reinterpret_cast<float4*>(a.partial_out + (int64_t)er * D + xg * 128 + ch * 32 + c16 * 4) = val;
+            if (er >= 0) __stcs(reinterpret_cast<float4*>(a.partial_out + (int64_t)er * D + xg * 128 + ch * 32 + c16 * 4), val);
           }
           __syncwarp();
         }
