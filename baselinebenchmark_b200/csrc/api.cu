@@ -111,13 +111,13 @@ struct Workspace {
   int32_t* tile_prefix;
   int32_t* cursors;
   int32_t* row_list;
-  float* partial_out;
-  float* partial_lse;
+  void* partial_out;         // forward: fp16 [rows * NP][D]; backward: fp32 dq contributions of the same shape
+  float2* partial_lse;       // {lse, 1 / scale} per entry
   size_t zero_bytes;
   size_t total;
 };
 
-Workspace carve(const Params& r, void* base) {
+Workspace carve(const Params& r, void* base, bool backward = false) {
   Workspace w;
   size_t off = 0;
   auto take = [&](size_t bytes) {
@@ -136,8 +136,8 @@ Workspace carve(const Params& r, void* base) {
   w.means = static_cast<__nv_bfloat16*>(take((size_t)r.slots * r.Hkv * r.D * 2));
   w.selected = static_cast<int32_t*>(take((size_t)r.hist * r.rows * sizeof(int32_t)));
   w.row_list = static_cast<int32_t*>(take((size_t)r.hist * r.rows * sizeof(int32_t)));
-  w.partial_lse = static_cast<float*>(take((size_t)r.rows * r.NP * sizeof(float)));
-  w.partial_out = static_cast<float*>(take((size_t)r.rows * r.NP * r.D * sizeof(float)));
+  w.partial_lse = static_cast<float2*>(take((size_t)r.rows * r.NP * sizeof(float2)));
+  w.partial_out = take((size_t)r.rows * r.NP * r.D * (backward ? sizeof(float) : sizeof(__half)));
   w.total = off;
   return w;
 }
@@ -146,8 +146,8 @@ Workspace carve(const Params& r, void* base) {
 
 int attend_dispatch(const moba_problem_t* p, const Params& r, const void* q, const void* k, const void* v,
                     const int32_t* cu, const int32_t* list_counts, const int32_t* list_offsets,
-                    const int32_t* tile_prefix, const int32_t* row_list, float* partial_out,
-                    float* partial_lse, int32_t* work_counter, int32_t* status, cudaStream_t st) {
+                    const int32_t* tile_prefix, const int32_t* row_list, __half* partial_out,
+                    float2* partial_lse, int32_t* work_counter, int32_t* status, cudaStream_t st) {
   const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(q);
   const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(k);
   const __nv_bfloat16* vb = static_cast<const __nv_bfloat16*>(v);
@@ -320,28 +320,32 @@ int moba_compact_routes(const moba_problem_t* p, const int32_t* cu, const int32_
   const Params r = make_params(p);
   if (r.hist <= 0) return MOBA_OK;
   return (int)launch_compact(r, cu, selected, list_counts, list_offsets, tile_prefix, cursors, row_list,
-                             partial_lse, tile_rows, (cudaStream_t)stream);
+                             reinterpret_cast<float2*>(partial_lse), tile_rows, (cudaStream_t)stream);
 }
 
 int moba_attend(const moba_problem_t* p, const void* q, const void* k, const void* v, const int32_t* cu,
                 const int32_t* list_counts, const int32_t* list_offsets, const int32_t* tile_prefix,
-                const int32_t* row_list, float* partial_out, float* partial_lse, int32_t* work_counter,
+                const int32_t* row_list, void* partial_out, float* partial_lse, int32_t* work_counter,
                 void* stream) {
   const int rc = check_problem(p);
   if (rc != MOBA_OK) return rc;
   if (!q || !k || !v || !cu || !partial_out || !partial_lse || !work_counter) return MOBA_E_NULL;
   const Params r = make_params(p);
   if (r.hist > 0 && (!list_counts || !list_offsets || !tile_prefix || !row_list)) return MOBA_E_NULL;
-  return attend_dispatch(p, r, q, k, v, cu, list_counts, list_offsets, tile_prefix, row_list, partial_out,
-                         partial_lse, work_counter, work_counter + 1, (cudaStream_t)stream);
+  if (((uintptr_t)partial_out & 15) || ((uintptr_t)partial_lse & 7)) return MOBA_E_ALIGN;
+  return attend_dispatch(p, r, q, k, v, cu, list_counts, list_offsets, tile_prefix, row_list,
+                         static_cast<__half*>(partial_out), reinterpret_cast<float2*>(partial_lse), work_counter,
+                         work_counter + 1, (cudaStream_t)stream);
 }
 
-int moba_merge(const moba_problem_t* p, const float* partial_out, const float* partial_lse,
+int moba_merge(const moba_problem_t* p, const void* partial_out, const float* partial_lse,
                const int32_t* status, void* out, float* lse_out, void* stream) {
   const int rc = check_problem(p);
   if (rc != MOBA_OK) return rc;
   if (!partial_out || !partial_lse || !out) return MOBA_E_NULL;
-  return (int)launch_merge(make_params(p), partial_out, partial_lse, status, static_cast<__nv_bfloat16*>(out),
+  if ((((uintptr_t)partial_out | (uintptr_t)out) & 15) || ((uintptr_t)partial_lse & 7)) return MOBA_E_ALIGN;
+  return (int)launch_merge(make_params(p), static_cast<const __half*>(partial_out),
+                           reinterpret_cast<const float2*>(partial_lse), status, static_cast<__nv_bfloat16*>(out),
                            lse_out, (cudaStream_t)stream);
 }
 
@@ -390,10 +394,11 @@ static int forward_pass(const moba_problem_t* p, int64_t sel_rs, const void* q, 
   if (opt.kv_ready != nullptr && (e = cudaStreamWaitEvent(st, opt.kv_ready, 0)) != cudaSuccess) return (int)e;
   if (last && (e = mark(3)) != cudaSuccess) return (int)e;
   const int arc = attend_dispatch(p, r, q, k, v, cu, w.list_counts, w.list_offsets, w.tile_prefix, w.row_list,
-                                  w.partial_out, w.partial_lse, w.work_counter, w.status, st);
+                                  static_cast<__half*>(w.partial_out), w.partial_lse, w.work_counter, w.status, st);
   if (arc != 0) return arc;
   if (last && (e = mark(4)) != cudaSuccess) return (int)e;
-  e = launch_merge(r, w.partial_out, w.partial_lse, w.status, static_cast<__nv_bfloat16*>(out), lse_out, st);
+  e = launch_merge(r, static_cast<const __half*>(w.partial_out), w.partial_lse, w.status,
+                   static_cast<__nv_bfloat16*>(out), lse_out, st);
   if (e != cudaSuccess) return (int)e;
   return last ? (int)mark(5) : MOBA_OK;
 }
@@ -494,7 +499,7 @@ int moba_backward_workspace_size(const moba_problem_t* p, size_t* bytes) {
   if (rc != MOBA_OK) return rc;
   if (bytes == nullptr) return MOBA_E_NULL;
   const Params r = make_params(p);
-  *bytes = carve(r, nullptr).total + 2 * align_up((size_t)r.rows * sizeof(float));
+  *bytes = carve(r, nullptr, true).total + 2 * align_up((size_t)r.rows * sizeof(float));
   return MOBA_OK;
 }
 
@@ -512,7 +517,8 @@ int moba_backward(const moba_problem_t* p, const void* q, const void* k, const v
   const Params r = make_params(p);
   if (r.hist > 0 && selected == nullptr) return MOBA_E_NULL;
   cudaStream_t st = (cudaStream_t)stream;
-  const Workspace w = carve(r, workspace);
+  const Workspace w = carve(r, workspace, true);
+  float* partial_dq = static_cast<float*>(w.partial_out);
   float* delta = reinterpret_cast<float*>(static_cast<char*>(workspace) + w.total);
   float* lse2 = reinterpret_cast<float*>(reinterpret_cast<char*>(delta) + align_up((size_t)r.rows * sizeof(float)));
   const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(q);
@@ -536,12 +542,12 @@ int moba_backward(const moba_problem_t* p, const void* q, const void* k, const v
     return (int)e;
   if (dq_tc5)
     e = launch_bwd_dq_tc5(r, qb, kb, vb, gb, cu, w.list_counts, w.list_offsets, w.tile_prefix, w.row_list, lse2, delta,
-                          w.partial_out, w.work_counter, w.status, st);
+                          partial_dq, w.work_counter, w.status, st);
   else
     e = launch_bwd_dq(r, qb, kb, vb, gb, qt, hd, cu, w.list_counts, w.list_offsets, w.tile_prefix, w.row_list, lse2,
-                      delta, w.partial_out, w.work_counter, st);
+                      delta, partial_dq, w.work_counter, st);
   if (e != cudaSuccess) return (int)e;
-  if ((e = launch_bwd_sum_dq(r, w.partial_out, selected, w.status, static_cast<__nv_bfloat16*>(dq), qt, hd, st)) !=
+  if ((e = launch_bwd_sum_dq(r, partial_dq, selected, w.status, static_cast<__nv_bfloat16*>(dq), qt, hd, st)) !=
       cudaSuccess)
     return (int)e;
   if (dq_tc5)

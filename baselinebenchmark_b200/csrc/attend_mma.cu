@@ -95,7 +95,7 @@ attend_mma_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bflo
                   const __nv_bfloat16* __restrict__ v, const int32_t* __restrict__ cu,
                   const int32_t* __restrict__ list_counts, const int32_t* __restrict__ list_offsets,
                   const int32_t* __restrict__ tile_prefix, const int32_t* __restrict__ row_list,
-                  float* __restrict__ partial_out, float* __restrict__ partial_lse,
+                  __half* __restrict__ partial_out, float2* __restrict__ partial_lse,
                   int32_t* __restrict__ work_counter) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   Smem<D>& s = *reinterpret_cast<Smem<D>*>(smem_raw);
@@ -232,26 +232,39 @@ attend_mma_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bflo
       __syncthreads();
     }
     cp_async_wait<0>();
-    // epilogue: normalise, write fp32 partials and natural-log LSE
+    // epilogue: normalise, write the partial rows (fp16, scaled by a power of two per row)
+    // and {natural-log LSE, 1 / scale}; a row lives in the four lanes of a quad
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     const int e0 = s.entry[row0], e1 = s.entry[row0 + 8];
     const float i0 = 1.f / l0, i1 = 1.f / l1;
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+      a0 = fmaxf(a0, fmaxf(fabsf(o[dt][0]), fabsf(o[dt][1])));
+      a1 = fmaxf(a1, fmaxf(fabsf(o[dt][2]), fabsf(o[dt][3])));
+    }
+    a0 = fmaxf(a0, __shfl_xor_sync(0xffffffffu, a0, 1));
+    a0 = fmaxf(a0, __shfl_xor_sync(0xffffffffu, a0, 2));
+    a1 = fmaxf(a1, __shfl_xor_sync(0xffffffffu, a1, 1));
+    a1 = fmaxf(a1, __shfl_xor_sync(0xffffffffu, a1, 2));
+    const PartialScale ps0 = partial_scale(a0 * i0), ps1 = partial_scale(a1 * i1);
+    const float f0 = i0 * ps0.scale, f1 = i1 * ps1.scale;
     if (e0 >= 0) {
-      float* dst = partial_out + (int64_t)e0 * D + 2 * (lane & 3);
+      __half* dst = partial_out + (int64_t)e0 * D + 2 * (lane & 3);
 #pragma unroll
       for (int dt = 0; dt < D / 8; ++dt)
-        *reinterpret_cast<float2*>(dst + dt * 8) = make_float2(o[dt][0] * i0, o[dt][1] * i0);
-      if ((lane & 3) == 0) partial_lse[e0] = (m0 + log2f(l0)) * 0.6931471805599453f;
+        *reinterpret_cast<uint32_t*>(dst + dt * 8) = pack2_half(o[dt][0] * f0, o[dt][1] * f0);
+      if ((lane & 3) == 0) partial_lse[e0] = make_float2((m0 + log2f(l0)) * 0.6931471805599453f, ps0.inv);
     }
     if (e1 >= 0) {
-      float* dst = partial_out + (int64_t)e1 * D + 2 * (lane & 3);
+      __half* dst = partial_out + (int64_t)e1 * D + 2 * (lane & 3);
 #pragma unroll
       for (int dt = 0; dt < D / 8; ++dt)
-        *reinterpret_cast<float2*>(dst + dt * 8) = make_float2(o[dt][2] * i1, o[dt][3] * i1);
-      if ((lane & 3) == 0) partial_lse[e1] = (m1 + log2f(l1)) * 0.6931471805599453f;
+        *reinterpret_cast<uint32_t*>(dst + dt * 8) = pack2_half(o[dt][2] * f1, o[dt][3] * f1);
+      if ((lane & 3) == 0) partial_lse[e1] = make_float2((m1 + log2f(l1)) * 0.6931471805599453f, ps1.inv);
     }
   }
 }
@@ -261,10 +274,10 @@ attend_mma_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bflo
 cudaError_t launch_attend_mma(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* k,
                               const __nv_bfloat16* v, const int32_t* cu, const int32_t* list_counts,
                               const int32_t* list_offsets, const int32_t* tile_prefix,
-                              const int32_t* row_list, float* partial_out, float* partial_lse,
+                              const int32_t* row_list, __half* partial_out, float2* partial_lse,
                               int32_t* work_counter, cudaStream_t st) {
   void (*kernel)(Params, const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*, const int32_t*,
-                 const int32_t*, const int32_t*, const int32_t*, const int32_t*, float*, float*, int32_t*);
+                 const int32_t*, const int32_t*, const int32_t*, const int32_t*, __half*, float2*, int32_t*);
   size_t smem;
   switch (p.D) {
     case 64:  kernel = p.fp16 ? attend_mma_kernel<true, 64>  : attend_mma_kernel<false, 64>;  smem = sizeof(Smem<64>);  break;

@@ -73,7 +73,7 @@ struct Ctrl {
   // tile_prefix copied once per CTA when it fits: decoding an item searches it, and with
   // short items (small chunks) eleven dependent global loads per item were the critical path
   int32_t prefix_cache[kPrefixCache];
-  float row_inv[kTileM];                   // head dim 256: 1 / row sum, handed to the warps that write the second half of O
+  float row_inv[kTileM];                   // head dim 256: the row's factor (scale / row sum), handed to the warps that write the second half of O
 };
 
 constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + 6 * kTileBytes + sizeof(Ctrl);
@@ -94,8 +94,8 @@ struct KernelArgs {
   const int32_t* list_offsets;
   const int32_t* tile_prefix;
   const int32_t* row_list;
-  float* partial_out;
-  float* partial_lse;
+  __half* partial_out;                     // fp16 rows scaled by a power of two per row
+  float2* partial_lse;                     // {natural-log LSE, 1 / scale}
   int32_t* work_counter;
   int32_t* status;
 };
@@ -499,32 +499,53 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         oph ^= 1;
         tc_fence_after();
         const int32_t e = entries[x * kTileM + row];
-        const float inv = 1.f / l;
-        // O rows go through this warp's 8 KB of the (now idle) Q tile so that every global
-        // store instruction writes whole 128-byte pieces of four rows: 32 columns at a
-        // time, rows 144 bytes apart in shared memory (conflict-free both ways).
-        unsigned char* stage = smem + x * kTileBytes + (warp & 3) * 8192;
-        uint32_t v[32];
+        // the row's largest magnitude decides the power of two its fp16 copy is scaled by
+        uint32_t v0[32], v1[32];
+        float amax = 0.f;
 #pragma unroll
         for (int ch = 0; ch < D / 32; ++ch) {
-          tmem_ld32(tO + ch * 32, v);
+          tmem_ld32(tO + ch * 32, v0);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2)
+            amax = max3(amax, fabsf(__uint_as_float(v0[i])), fabsf(__uint_as_float(v0[i + 1])));
+        }
+        const float inv = 1.f / l;
+        const PartialScale ps = partial_scale(amax * inv);
+        const float mul = inv * ps.scale;
+        // O rows go through this warp's 8 KB of the (now idle) Q tile so that every global
+        // store instruction writes whole 128-byte pieces of four rows: 64 columns at a
+        // time, rows 144 bytes apart in shared memory (conflict-free both ways).
+        unsigned char* stage = smem + x * kTileBytes + (warp & 3) * 8192;
+#pragma unroll
+        for (int ch = 0; ch < (D + 63) / 64; ++ch) {
+          constexpr int kLast = D % 64 == 0 ? 64 : D % 64;      // columns of the last piece (head dim 96: 32)
+          const int cols = ch == (D + 63) / 64 - 1 ? kLast : 64;
+          tmem_ld32(tO + ch * 64, v0);
+          if (cols > 32) tmem_ld32(tO + ch * 64 + 32, v1);
           tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < 8; ++i)
-            *reinterpret_cast<float4*>(stage + lane * 144 + i * 16) =
-                make_float4(__uint_as_float(v[4 * i]) * inv, __uint_as_float(v[4 * i + 1]) * inv,
-                            __uint_as_float(v[4 * i + 2]) * inv, __uint_as_float(v[4 * i + 3]) * inv);
+            if (i * 8 < cols) {
+              const uint32_t* s8 = i < 4 ? v0 + 8 * i : v1 + 8 * (i - 4);
+              *reinterpret_cast<uint4*>(stage + lane * 144 + i * 16) =
+                  make_uint4(pack2_half(__uint_as_float(s8[0]) * mul, __uint_as_float(s8[1]) * mul),
+                             pack2_half(__uint_as_float(s8[2]) * mul, __uint_as_float(s8[3]) * mul),
+                             pack2_half(__uint_as_float(s8[4]) * mul, __uint_as_float(s8[5]) * mul),
+                             pack2_half(__uint_as_float(s8[6]) * mul, __uint_as_float(s8[7]) * mul));
+            }
           __syncwarp();
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int rl = i * 4 + (lane >> 3), c16 = lane & 7;
             const int32_t er = __shfl_sync(0xffffffffu, e, rl);
-            const float4 val = *reinterpret_cast<const float4*>(stage + rl * 144 + c16 * 16);
-            if (er >= 0) __stcs(reinterpret_cast<float4*>(a.partial_out + (int64_t)er * D + ch * 32 + c16 * 4), val);
+            const uint4 val = *reinterpret_cast<const uint4*>(stage + rl * 144 + c16 * 16);
+            if (er >= 0 && c16 * 8 < cols)
+              __stcs(reinterpret_cast<uint4*>(a.partial_out + (int64_t)er * D + ch * 64 + c16 * 8), val);
           }
           __syncwarp();
         }
-        if (e >= 0) a.partial_lse[e] = (m_ref + log2f(l)) * 0.6931471805599453f;
+        if (e >= 0) a.partial_lse[e] = make_float2((m_ref + log2f(l)) * 0.6931471805599453f, ps.inv);
         tc_fence_before();
       } else {
         atomicExch(a.status, ST_SOFTMAX);
@@ -778,41 +799,62 @@ attend_tc5_wide_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_
           tc_fence_before();
           mbar_arrive(smem_u32(&c.p_full[0]));
         }
-        c.row_inv[row] = 1.f / l;
       } else {
         g += (uint32_t)ntiles;
       }
-      bar_sync_256();                                    // row sums are visible; the last P has been published
+      bar_sync_256();                                    // the last P has been published
       if (ok) ok = mbar_wait(smem_u32(&c.o_full[0]), (g - 1) & 1);
       ok = __all_sync(0xffffffffu, ok);
+      const int32_t e = entries[row];
+      uint32_t v0[32], v1[32];
+      if (ok) tc_fence_after();
+      if (ok && xg == 0) {
+        // the row's largest magnitude over all 256 dims decides the power of two of its fp16 copy
+        float amax = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < D / 32; ++ch) {
+          tmem_ld32(tO + ch * 32, v0);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2)
+            amax = max3(amax, fabsf(__uint_as_float(v0[i])), fabsf(__uint_as_float(v0[i + 1])));
+        }
+        const float inv = 1.f / l;
+        const PartialScale ps = partial_scale(amax * inv);
+        c.row_inv[row] = inv * ps.scale;
+        if (e >= 0) a.partial_lse[e] = make_float2((m_ref + log2f(l)) * 0.6931471805599453f, ps.inv);
+      }
+      bar_sync_256();                                    // the rows' factors are visible to warps 8-11
       if (ok) {
-        tc_fence_after();
-        const int32_t e = entries[row];
-        const float inv = c.row_inv[row];
+        const float mul = c.row_inv[row];
         // as above: O rows pass through this warp's 8 KB of the idle Q tile; warps 4-7 write
         // dims 0-127, warps 8-11 dims 128-255
         unsigned char* stage = smem + xg * kTileBytes + (warp & 3) * 8192;
-        uint32_t v[32];
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          tmem_ld32(tO + xg * 128 + ch * 32, v);
+        for (int ch = 0; ch < 2; ++ch) {
+          tmem_ld32(tO + xg * 128 + ch * 64, v0);
+          tmem_ld32(tO + xg * 128 + ch * 64 + 32, v1);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            *reinterpret_cast<float4*>(stage + lane * 144 + i * 16) =
-                make_float4(__uint_as_float(v[4 * i]) * inv, __uint_as_float(v[4 * i + 1]) * inv,
-                            __uint_as_float(v[4 * i + 2]) * inv, __uint_as_float(v[4 * i + 3]) * inv);
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t* s8 = i < 4 ? v0 + 8 * i : v1 + 8 * (i - 4);
+            *reinterpret_cast<uint4*>(stage + lane * 144 + i * 16) =
+                make_uint4(pack2_half(__uint_as_float(s8[0]) * mul, __uint_as_float(s8[1]) * mul),
+                           pack2_half(__uint_as_float(s8[2]) * mul, __uint_as_float(s8[3]) * mul),
+                           pack2_half(__uint_as_float(s8[4]) * mul, __uint_as_float(s8[5]) * mul),
+                           pack2_half(__uint_as_float(s8[6]) * mul, __uint_as_float(s8[7]) * mul));
+          }
           __syncwarp();
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int rl = i * 4 + (lane >> 3), c16 = lane & 7;
             const int32_t er = __shfl_sync(0xffffffffu, e, rl);
-            const float4 val = *reinterpret_cast<const float4*>(stage + rl * 144 + c16 * 16);
-            if (er >= 0) __stcs(reinterpret_cast<float4*>(a.partial_out + (int64_t)er * D + xg * 128 + ch * 32 + c16 * 4), val);
+            const uint4 val = *reinterpret_cast<const uint4*>(stage + rl * 144 + c16 * 16);
+            if (er >= 0)
+              __stcs(reinterpret_cast<uint4*>(a.partial_out + (int64_t)er * D + xg * 128 + ch * 64 + c16 * 8), val);
           }
           __syncwarp();
         }
-        if (xg == 0 && e >= 0) a.partial_lse[e] = (m_ref + log2f(l)) * 0.6931471805599453f;
         tc_fence_before();
       } else {
         atomicExch(a.status, ST_SOFTMAX);
@@ -889,7 +931,7 @@ cudaError_t launch_bounded_wait_probe(int32_t* status, unsigned long long limit_
 cudaError_t launch_attend_tc5(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* k,
                               const __nv_bfloat16* v, const int32_t* cu, const int32_t* list_counts,
                               const int32_t* list_offsets, const int32_t* tile_prefix,
-                              const int32_t* row_list, float* partial_out, float* partial_lse,
+                              const int32_t* row_list, __half* partial_out, float2* partial_lse,
                               int32_t* work_counter, int32_t* status, cudaStream_t st) {
   CUtensorMap mk, mv;
   if (!make_kv_map(&mk, p.fp16 != 0, p.D, k, p.T, p.Hkv, p.sk_t, p.sk_h, kBN) || !make_kv_map(&mv, p.fp16 != 0, p.D, v, p.T, p.Hkv, p.sv_t, p.sv_h, kBN))

@@ -55,6 +55,26 @@ __device__ __forceinline__ void unpack8(const uint4 x, float (&f)[8]) {
   f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
 }
 
+// Partial results of the dense stage (one per row and attended chunk; the reference keeps them
+// in the input dtype, attention.py:727).  The normalised O row is stored as fp16 scaled by a
+// power of two chosen per row, so that its largest magnitude lands in [2^13, 2^14): 11
+// significant bits on every element whatever the range of V, no overflow.  partial_lse holds
+// two floats per entry: the natural-log LSE (-inf: the entry contributes nothing) and 1 / scale.
+struct PartialScale { float scale, inv; };
+__device__ __forceinline__ PartialScale partial_scale(float amax) {
+  // floor(log2 amax) from the exponent field: -127 for zero and subnormals, 128 for inf / NaN
+  int s = 13 - ((int)((__float_as_uint(amax) >> 23) & 0xFF) - 127);
+  s = s < -100 ? -100 : (s > 100 ? 100 : s);
+  PartialScale r;
+  r.scale = __uint_as_float((uint32_t)(127 + s) << 23);
+  r.inv = __uint_as_float((uint32_t)(127 - s) << 23);
+  return r;
+}
+__device__ __forceinline__ uint32_t pack2_half(float lo, float hi) {
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 // Chunk slot geometry (routing.py:565-579).
 struct Slot {
   int start, end;        // token range [start, end)
@@ -165,9 +185,9 @@ cudaError_t launch_gate_topk_stats(const Params& p, const __nv_bfloat16* q, cons
 bool gate_topk_fits(const Params& p);
 cudaError_t launch_compact(const Params& p, const int32_t* cu, const int32_t* selected,
                            const int32_t* list_counts, int32_t* list_offsets, int32_t* tile_prefix,
-                           int32_t* cursors, int32_t* row_list, float* partial_lse, int tile_rows,
+                           int32_t* cursors, int32_t* row_list, float2* partial_lse, int tile_rows,
                            cudaStream_t st);
-cudaError_t launch_merge(const Params& p, const float* partial_out, const float* partial_lse,
+cudaError_t launch_merge(const Params& p, const __half* partial_out, const float2* partial_lse,
                          const int32_t* status, __nv_bfloat16* out, float* lse_out, cudaStream_t st);
 
 constexpr int kMmaTileRows = 128;        // rows per work item, mma.sync kernel
@@ -177,12 +197,12 @@ constexpr int kTileRowsWide = 128;       // rows per work item, tcgen05 kernel a
 cudaError_t launch_attend_mma(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* k,
                               const __nv_bfloat16* v, const int32_t* cu, const int32_t* list_counts,
                               const int32_t* list_offsets, const int32_t* tile_prefix,
-                              const int32_t* row_list, float* partial_out, float* partial_lse,
+                              const int32_t* row_list, __half* partial_out, float2* partial_lse,
                               int32_t* work_counter, cudaStream_t st);
 cudaError_t launch_attend_tc5(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* k,
                               const __nv_bfloat16* v, const int32_t* cu, const int32_t* list_counts,
                               const int32_t* list_offsets, const int32_t* tile_prefix,
-                              const int32_t* row_list, float* partial_out, float* partial_lse,
+                              const int32_t* row_list, __half* partial_out, float2* partial_lse,
                               int32_t* work_counter, int32_t* status, cudaStream_t st);
 
 cudaError_t launch_bounded_wait_probe(int32_t* status, unsigned long long limit_ns, cudaStream_t st);

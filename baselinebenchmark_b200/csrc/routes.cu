@@ -75,7 +75,7 @@ constexpr int kScatterTokens = 64;
 __global__ void __launch_bounds__(kScatterThreads)
 scatter_routes_kernel(Params p, const int32_t* __restrict__ cu, const int32_t* __restrict__ selected,
                       const int32_t* __restrict__ offsets, int32_t* __restrict__ cursors,
-                      int32_t* __restrict__ row_list, float* __restrict__ partial_lse) {
+                      int32_t* __restrict__ row_list, float2* __restrict__ partial_lse) {
   extern __shared__ int32_t sm[];
   int32_t* cnt_s = sm;               // [mc] rows of this CTA per list, then running index
   int32_t* base_s = sm + p.mc;       // [mc] first position reserved for this CTA
@@ -114,14 +114,14 @@ scatter_routes_kernel(Params p, const int32_t* __restrict__ cu, const int32_t* _
       const int pos = offsets[(int64_t)slot * p.Hkv + hk] + base_s[c] + atomicAdd(&cnt_s[c], 1);
       row_list[pos] = (int32_t)entry;
     } else {
-      partial_lse[entry] = -INFINITY;            // this rank contributes nothing to the merge
+      partial_lse[entry] = make_float2(-INFINITY, 0.f);   // this rank contributes nothing to the merge
     }
   }
 }
 
 cudaError_t launch_compact(const Params& p, const int32_t* cu, const int32_t* selected,
                            const int32_t* list_counts, int32_t* list_offsets, int32_t* tile_prefix,
-                           int32_t* cursors, int32_t* row_list, float* partial_lse, int tile_rows,
+                           int32_t* cursors, int32_t* row_list, float2* partial_lse, int tile_rows,
                            cudaStream_t st) {
   scan_lists_kernel<<<1, kScanThreads, 0, st>>>(p.lists, tile_rows, list_counts, list_offsets, tile_prefix, cursors);
   cudaError_t e = cudaGetLastError();
@@ -138,62 +138,90 @@ cudaError_t launch_compact(const Params& p, const int32_t* cu, const int32_t* se
 // ---------------------------------------------------------------------------
 // merge: one warp per (token, head) row.
 //   lse_tot = log sum_j exp(lse_j);  out = sum_j O_j * exp(lse_j - lse_tot)
+// (exponentials through ex2.approx: relative error 2^-22, far below the rounding of the output)
 // ---------------------------------------------------------------------------
 constexpr int kMergeThreads = 256;
 
-// A row has D/4 float4 pieces: one per lane for D <= 128 (lanes beyond D/4 idle), two for D = 256.
+// A partial row is D/8 pieces of eight fp16 values (16 bytes), one per lane: 32 / (D/8) rows fit
+// one load instruction of the warp (2 at head dim 128 and 96, 4 at 64, 1 at 256), so the lanes form
+// that many groups, group g takes the partials g, g + groups, ... of the row, four of them in
+// flight at a time, and the groups' sums are added at the end.
 template <bool kHalf, int D>
 __global__ void __launch_bounds__(kMergeThreads)
-merge_kernel(Params p, const float* __restrict__ partial_out, const float* __restrict__ partial_lse,
+merge_kernel(Params p, const __half* __restrict__ partial_out, const float2* __restrict__ partial_lse,
              const int32_t* __restrict__ status, __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out) {
+  constexpr int kLanes = D / 8;                  // lanes per partial row
+  constexpr int kGroups = 32 / kLanes;
+  constexpr int kAhead = 4;                      // partial rows a group has in flight
   const int lane = threadIdx.x & 31;
+  const int grp = lane / kLanes, piece = lane - grp * kLanes;
+  const bool active = grp < kGroups;             // head dim 96: lanes 24-31 idle
   // a dense stage that gave up on a wait leaves a non-zero status: poison the result
   const bool failed = status != nullptr && *status != 0;
   const int64_t warps = (int64_t)gridDim.x * (kMergeThreads / 32);
   for (int64_t row = (int64_t)blockIdx.x * (kMergeThreads / 32) + (threadIdx.x >> 5); row < p.rows; row += warps) {
-    const float* lse = partial_lse + row * p.NP;
+    const float2* lse = partial_lse + row * p.NP;
     float mx = -INFINITY;
-    for (int j = lane; j < p.NP; j += 32) mx = fmaxf(mx, lse[j]);
+    for (int j = lane; j < p.NP; j += 32) mx = fmaxf(mx, lse[j].x);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     float tot = 0.f;
-    for (int j = lane; j < p.NP; j += 32) tot += expf(lse[j] - mx);
+    for (int j = lane; j < p.NP; j += 32) tot += __expf(lse[j].x - mx);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
     const float inv = failed ? __int_as_float(0x7fc00000) : 1.f / tot;
-    constexpr int nvec = D / 4, kVecs = (nvec + 31) / 32;
-    float4 acc[kVecs];
+    float acc[8];
 #pragma unroll
-    for (int u = 0; u < kVecs; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4* src = reinterpret_cast<const float4*>(partial_out + row * p.NP * D) + lane;
-    for (int j = 0; j < p.NP; ++j) {
-      const float lj = lse[j];                                // same address for all lanes
-      if (lj == -INFINITY) continue;
-      const float w = expf(lj - mx) * inv;
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    const uint4* src = reinterpret_cast<const uint4*>(partial_out + row * p.NP * D) + piece;
+    for (int j0 = 0; j0 < p.NP; j0 += kGroups * kAhead) {
+      float w[kAhead];
+      uint4 o[kAhead];
 #pragma unroll
-      for (int u = 0; u < kVecs; ++u) {
-        if (nvec % 32 == 0 || lane + 32 * u < nvec) {
-          const float4 o = __ldg(src + j * nvec + 32 * u);
-          acc[u].x += w * o.x; acc[u].y += w * o.y; acc[u].z += w * o.z; acc[u].w += w * o.w;
+      for (int u = 0; u < kAhead; ++u) {
+        const int j = j0 + u * kGroups + grp;
+        w[u] = 0.f;
+        o[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (active && j < p.NP) {
+          const float2 lj = lse[j];
+          if (lj.x != -INFINITY) {
+            w[u] = __expf(lj.x - mx) * inv * lj.y;            // the row's power-of-two scale is undone with the weight
+            o[u] = __ldg(src + j * kLanes);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) {
+        const uint32_t words[4] = {o[u].x, o[u].y, o[u].z, o[u].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&words[i]));
+          acc[2 * i] += w[u] * a.x;
+          acc[2 * i + 1] += w[u] * a.y;
         }
       }
     }
+    // sum of the groups into group 0
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (kGroups == 4) acc[i] += __shfl_down_sync(0xffffffffu, acc[i], 2 * kLanes);
+      if (kGroups >= 2) acc[i] += __shfl_down_sync(0xffffffffu, acc[i], kLanes);
+    }
     const int64_t t = row / p.Hq;
     const int h = (int)(row - t * p.Hq);
-#pragma unroll
-    for (int u = 0; u < kVecs; ++u) {
-      if (nvec % 32 == 0 || lane + 32 * u < nvec) {
-        uint2 pk;
-        pk.x = pack2_16<kHalf>(acc[u].x, acc[u].y);
-        pk.y = pack2_16<kHalf>(acc[u].z, acc[u].w);
-        *reinterpret_cast<uint2*>(out + t * p.so_t + (int64_t)h * p.so_h + (lane + 32 * u) * 4) = pk;
-      }
+    if (grp == 0) {
+      uint4 pk;
+      pk.x = pack2_16<kHalf>(acc[0], acc[1]);
+      pk.y = pack2_16<kHalf>(acc[2], acc[3]);
+      pk.z = pack2_16<kHalf>(acc[4], acc[5]);
+      pk.w = pack2_16<kHalf>(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(out + t * p.so_t + (int64_t)h * p.so_h + piece * 8) = pk;
     }
     if (lse_out != nullptr && lane == 0) lse_out[(int64_t)h * p.Tq + t] = logf(tot) + mx;
   }
 }
 
-cudaError_t launch_merge(const Params& p, const float* partial_out, const float* partial_lse,
+cudaError_t launch_merge(const Params& p, const __half* partial_out, const float2* partial_lse,
                          const int32_t* status, __nv_bfloat16* out, float* lse_out, cudaStream_t st) {
   int64_t blocks = (p.rows + (kMergeThreads / 32) - 1) / (kMergeThreads / 32);
   if (blocks > 148 * 64) blocks = 148 * 64;

@@ -42,12 +42,12 @@ sys.path.insert(0, str(ROOT))
 
 SEQ_LEN = 131072
 NUM_SEQS = 16             # BASELINE.json configs[3]
-SEQS_PER_CALL = 2         # sequences per operator call (16 units: 35 GB of partial results)
+SEQS_PER_CALL = 2         # sequences per operator call (16 units: 18 GB of partial results)
 HQ, HKV, D, CHUNK, TOPK = 32, 8, 128, 4096, 8
 KERNELS_PER_CALL = 6      # chunk_mean, gate_topk, scan_lists, scatter_routes, attend, merge
 # dram__bytes_read.sum + dram__bytes_write.sum of one attend_tc5_kernel launch on configs[2]
 # (32768 tokens x 32 heads, 8 partial results per row), from an ncu capture of that launch
-ATTEND_TRAFFIC_CFG2 = 2.713171e9 + 2.517811e9
+ATTEND_TRAFFIC_CFG2 = 2.610216e9 + 1.323296e9
 PARTIALS = min(TOPK - 1, SEQ_LEN // CHUNK - 1) + 1
 
 
@@ -639,8 +639,8 @@ def main():
                          "launches_per_step": calls,
                          "traffic": ATTEND_TRAFFIC_CFG2 * (call_tokens * HQ * PARTIALS) / (32768 * 32 * 8),
                          "traffic_unit": "bytes of DRAM read + write per launch, scaled from one ncu capture of "
-                                         "configs[2] (5.231e9 B for 32768 x 32 rows x 8 partial results) by "
-                                         "rows x partial results: the traffic is fp32 partial writes and Q gathers"},
+                                         "configs[2] (3.934e9 B for 32768 x 32 rows x 8 partial results) by "
+                                         "rows x partial results: the traffic is fp16 partial writes and Q gathers"},
             "stage_ms": {"means": float(stage_ms[0]), "gate_topk": float(stage_ms[1]), "compact": float(stage_ms[2]),
                          "attend": float(stage_ms[3]), "merge": float(stage_ms[4]), "per": "operator call"},
             "gating": gating_roofline(float(stage_ms[0]) + float(stage_ms[1]), pk),

@@ -217,8 +217,8 @@ int moba_gate_topk_stats(const moba_problem_t* p, const void* q, const void* mea
  *   list_offsets  int32[lists+1]  exclusive prefix of list_counts
  *   tile_prefix   int32[lists+1]  exclusive prefix of ceil(count / tile_rows)
  *   row_list      int32[hist*T*Hq] entry ids  (t*Hq + h) * partials + rank + 1
- *   partial_lse   fp32 [T*Hq, partials]; entries of ranks that selected nothing
- *                 are set to -inf here
+ *   partial_lse   fp32 [T*Hq, partials, 2] = {natural-log LSE, 1 / scale of the partial row};
+ *                 entries of ranks that selected nothing are set to {-inf, 0} here
  *   cursors       int32[lists] scratch */
 int moba_compact_routes(const moba_problem_t* p, const int32_t* cu_seqlens,
                         const int32_t* selected, const int32_t* list_counts,
@@ -228,21 +228,26 @@ int moba_compact_routes(const moba_problem_t* p, const int32_t* cu_seqlens,
 /* Dense stage: own-chunk causal attention (replaces _varlen_attn_fwd_kernel,
  * attention.py:53-160) and the routed historical-chunk attention (replaces
  * native_moba.routed / _routed_gqa_attn_fwd_kernel, native_moba.py:120-135,
- * attention.py:610-707) in one persistent launch.  Writes normalised fp32
- * partial outputs [T*Hq, partials, D] and their natural-log LSE.
+ * attention.py:610-707) in one persistent launch.  Writes the normalised
+ * partial outputs [T*Hq, partials, D] as fp16 (the reference keeps them in the
+ * input dtype, attention.py:727), each row scaled by a power of two that puts
+ * its largest magnitude into [2^13, 2^14) - 11 significant bits on every
+ * element whatever the range of V - and {natural-log LSE, 1 / scale} per row
+ * into partial_lse [T*Hq, partials, 2].  partial_out 16-byte, partial_lse
+ * 8-byte aligned.
  *   work_counter int32[2] must be zero on entry: [0] is the item counter, [1]
  *   receives a non-zero status if a bounded device-side wait gave up. */
 int moba_attend(const moba_problem_t* p, const void* q, const void* k, const void* v,
                 const int32_t* cu_seqlens, const int32_t* list_counts,
                 const int32_t* list_offsets, const int32_t* tile_prefix,
-                const int32_t* row_list, float* partial_out, float* partial_lse,
+                const int32_t* row_list, void* partial_out, float* partial_lse,
                 int32_t* work_counter, void* stream);
 
 /* LSE-weighted combine: replaces _fused_merge_softmax_triton
- * (attention.py:892-945), all partials of a row in one pass, fp32 throughout,
- * one rounding to bf16.  `status` (optional) is work_counter + 1 of moba_attend:
+ * (attention.py:892-945), all partials of a row in one pass, fp32 arithmetic,
+ * one rounding to the output dtype.  `status` (optional) is work_counter + 1 of moba_attend:
  * when it is non-zero the output is filled with NaN instead of partial data. */
-int moba_merge(const moba_problem_t* p, const float* partial_out, const float* partial_lse,
+int moba_merge(const moba_problem_t* p, const void* partial_out, const float* partial_lse,
                const int32_t* status, void* out, float* lse_out, void* stream);
 
 /* Self-test of the device-side wait limit (no counterpart in the reference, whose kernels

@@ -74,7 +74,7 @@ def compact(prob, cu, sel, counts, tile_rows):
     tiles = torch.empty(d.lists + 1, dtype=torch.int32, device="cuda")
     cursors = torch.empty(d.lists, dtype=torch.int32, device="cuda")
     row_list = torch.full((max(d.hist, 0) * d.rows,), -7, dtype=torch.int32, device="cuda")
-    plse = torch.zeros(d.rows * d.partials, dtype=torch.float32, device="cuda")
+    plse = torch.zeros(d.rows * d.partials, 2, dtype=torch.float32, device="cuda")   # {lse, 1 / scale}
     _lib.check(_lib.lib().moba_compact_routes(
         C.byref(prob), cu.data_ptr(), sel.data_ptr(), counts.data_ptr(), offsets.data_ptr(), tiles.data_ptr(),
         cursors.data_ptr(), row_list.data_ptr(), plse.data_ptr(), tile_rows, stream()))

@@ -141,7 +141,7 @@ def test_routing_bit_exact(case, dtype):
         list_id = np.repeat(np.arange(len(want.ravel())), want.ravel())
         np.testing.assert_array_equal(slot_of_entry * hkv + head // g, list_id)
         # ranks without a chunk are marked -inf for the merge
-        plse = plse.cpu().numpy().reshape(-1, npart)
+        plse = plse.cpu().numpy()[:, 0].reshape(-1, npart)
         empty = np.transpose(sel_o < 0, (2, 1, 0)).reshape(-1, hist)        # [row, rank]
         assert np.all(np.isneginf(plse[:, 1:][empty])) and np.all(plse[:, 1:][~empty] == 0)
 
@@ -719,8 +719,8 @@ def test_bounded_wait_gives_up_and_the_merge_poisons_the_output():
     cud = torch.from_numpy(cu).cuda()
     prob, out = G.problem_for(qd, kd, vd, cud, 512, 128, 3)
     d = G.dims_of(prob)
-    pout = torch.randn(d.rows * d.partials * 128, dtype=torch.float32, device="cuda")
-    plse = torch.randn(d.rows * d.partials, dtype=torch.float32, device="cuda")
+    pout = torch.randn(d.rows * d.partials * 128, dtype=torch.float16, device="cuda")
+    plse = torch.randn(d.rows * d.partials, 2, dtype=torch.float32, device="cuda")      # {lse, 1 / scale}
     _lib.check(_lib.lib().moba_merge(C.byref(prob), pout.data_ptr(), plse.data_ptr(), status.data_ptr(), out.data_ptr(),
                                      None, G.stream()))
     torch.cuda.synchronize()
