@@ -37,23 +37,27 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// A waiting thread is suspended by the hardware until the phase completes or this many
+// nanoseconds have passed (then the poll returns false and is repeated): long enough that a
+// waiting warp does not compete for issue slots with the warps it waits for.
+constexpr uint32_t kSuspendHintNs = 20000;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(kSuspendHintNs) : "memory");
   return ok != 0;
 }
 // Waits for the phase with the given parity to complete.  Gives up after
-// `limit_ns` (checked every 1024 polls) and returns false.
+// `limit_ns` (checked every 8 polls, each of which may sleep for the hint) and returns false.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_t limit_ns = 2000000000ull) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 1024; ++i)
+    for (int i = 0; i < 8; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (globaltimer_ns() - t0 > limit_ns) return false;
   }
