@@ -40,14 +40,25 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 // A waiting thread is suspended by the hardware until the phase completes or this many
 // nanoseconds have passed (then the poll returns false and is repeated): long enough that a
 // waiting warp does not compete for issue slots with the warps it waits for.
-constexpr uint32_t kSuspendHintNs = 20000;
+#ifndef MOBA_SUSPEND_NS
+#define MOBA_SUSPEND_NS 20000
+#endif
+constexpr uint32_t kSuspendHintNs = MOBA_SUSPEND_NS;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
+#if MOBA_SUSPEND_NS > 0
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok) : "r"(bar), "r"(parity), "r"(kSuspendHintNs) : "memory");
+#else
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+#endif
   return ok != 0;
 }
 // Waits for the phase with the given parity to complete.  Gives up after
@@ -75,7 +86,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
-
 // ---- tensor memory --------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {   // whole warp
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols)
