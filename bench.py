@@ -269,21 +269,18 @@ class HostRunner:
 
 
 def cpu_sample(threads):
-    """CPU baseline on a bounded sample of the workload: one (sequence, KV-head
-    group) unit with 4 of its 32 query chunks evaluated (chunks 3, 11, 19, 27:
-    6.0 selected chunks per query on average, 6.1 in the full unit)."""
+    """CPU baseline on a bounded sample of the workload: one whole (sequence,
+    KV-head group) unit of the 128, about 15 s on 16 host threads."""
     from oracle import moba_cpu, moba_oracle
     torch.set_num_threads(threads)
     q, k, v, cu = moba_oracle.make_inputs([SEQ_LEN], HQ // HKV, 1, D, CHUNK, seed=7)
-    chunks = (3, 11, 19, 27)
     t0 = time.perf_counter()
-    _, done = moba_cpu.moba_forward_cpu(q, k, v, cu, SEQ_LEN, CHUNK, TOPK, query_chunks=chunks)
+    _, done = moba_cpu.moba_forward_cpu(q, k, v, cu, SEQ_LEN, CHUNK, TOPK)
     dt = time.perf_counter() - t0
     # a benchmark token carries all 32 query heads; the sample evaluated 4 of them
     tokens_equiv = int(done.sum()) * (HQ // HKV) / HQ
-    return tokens_equiv / dt, dt, ("one (sequence, KV-group) unit of the 128: 131072 keys, 4 query heads, query chunks "
-                                   "3/11/19/27 of 32 evaluated (16384 tokens x 4 heads); rate extrapolated to "
-                                   "whole tokens (32 heads)")
+    return tokens_equiv / dt, dt, ("one whole (sequence, KV-group) unit of the 128: 131072 tokens, 4 query heads, "
+                                   "1 kv head; rate counted in whole tokens (32 heads)")
 
 
 def reference_arm(args, rank):
