@@ -21,7 +21,7 @@ SYMBOLS = (
     "moba_b200_abi_version", "moba_b200_strerror", "moba_problem_check", "moba_problem_dims",
     "moba_workspace_size", "moba_workspace_size_min", "moba_forward", "moba_forward_events", "moba_forward_cached", "moba_workspace_size_host", "moba_forward_host",
     "moba_chunk_metadata", "moba_chunk_means", "moba_gate_topk", "moba_gate_topk_stats", "moba_compact_routes",
-    "moba_attend", "moba_merge", "moba_attend_tile_rows", "moba_attend_tile_rows_for", "moba_route_static",
+    "moba_attend", "moba_merge", "moba_attend_tile_rows", "moba_attend_tile_rows_for", "moba_problem_tile_rows", "moba_route_static",
     "moba_backward_workspace_size", "moba_backward",
     "moba_cp_workspace_size", "moba_cp_forward", "moba_cp_poll", "moba_cp_abort", "moba_selftest_bounded_wait",
 )
@@ -90,6 +90,7 @@ def lib() -> C.CDLL:
         handle.moba_merge.argtypes = [pp, vp, vp, i32p, vp, vp, vp]
         handle.moba_attend_tile_rows.argtypes = [C.c_int]
         handle.moba_attend_tile_rows_for.argtypes = [C.c_int, C.c_int]
+        handle.moba_problem_tile_rows.argtypes = [pp]
         handle.moba_route_static.argtypes = [pp, vp, vp, i32p, i32p, vp]
         handle.moba_backward_workspace_size.argtypes = [pp, C.POINTER(sz)]
         handle.moba_backward.argtypes = [pp, vp, vp, vp, i32p, vp, vp, i32p, vp, vp, vp, vp, vp, sz, vp]

@@ -18,8 +18,9 @@ namespace {
 
 // rows per work item of the dense stage: the tcgen05 kernel takes two 128-row tiles per item up to
 // head_dim 128 and one at head_dim 256, the mma.sync kernel one
-int tile_rows_of(int impl, int head_dim) {
-  return impl == MOBA_ATTEND_MMA_SYNC ? kMmaTileRows : (head_dim > 128 ? kTileRowsWide : kTc5TileRows);
+int tile_rows_of(int impl, int head_dim, int chunk = 1 << 30) {
+  if (impl == MOBA_ATTEND_MMA_SYNC) return kMmaTileRows;
+  return head_dim > 128 || tc5_small_items(head_dim, chunk) ? kTileRowsWide : kTc5TileRows;
 }
 constexpr size_t kAlign = 256;
 inline size_t align_up(size_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
@@ -63,7 +64,7 @@ int check_problem(const moba_problem_t* p) {
   // tiles = slots * Hq * tiles per chunk, per pass of one kv-head group at least)
   if (p->batch > 65535 || p->num_kv_heads > 65535) return MOBA_E_UNSUPPORTED;
   const int64_t g = p->num_q_heads / p->num_kv_heads;
-  const int64_t tile = tile_rows_of(p->attend_impl, p->head_dim);
+  const int64_t tile = tile_rows_of(p->attend_impl, p->head_dim, p->chunk_size);
   const int64_t own_items = mc * p->batch * g * ((p->chunk_size + tile - 1) / tile);
   const int64_t routed_items = (hist > 0 ? hist : 0) * tq * g / tile + mc * p->batch;
   if (own_items + routed_items >= ((int64_t)1 << 31)) return MOBA_E_UNSUPPORTED;
@@ -251,6 +252,10 @@ int moba_problem_dims(const moba_problem_t* p, moba_dims_t* d) {
 
 int moba_attend_tile_rows(int impl) { return tile_rows_of(impl, 128); }
 int moba_attend_tile_rows_for(int impl, int head_dim) { return tile_rows_of(impl, head_dim); }
+int moba_problem_tile_rows(const moba_problem_t* p) {
+  const int rc = check_problem(p);
+  return rc != MOBA_OK ? rc : tile_rows_of(p->attend_impl, p->head_dim, p->chunk_size);
+}
 
 int moba_workspace_size(const moba_problem_t* p, size_t* bytes) {
   const int rc = check_problem(p);
@@ -386,7 +391,7 @@ static int forward_pass(const moba_problem_t* p, int64_t sel_rs, const void* q, 
     if ((e = launch_gate_topk(r, qb, means, cu, sel, w.list_counts, st)) != cudaSuccess) return (int)e;
     if (last && (e = mark(2)) != cudaSuccess) return (int)e;
     if ((e = launch_compact(r, cu, sel, w.list_counts, w.list_offsets, w.tile_prefix, w.cursors, w.row_list,
-                            w.partial_lse, tile_rows_of(p->attend_impl, p->head_dim), st)) != cudaSuccess)
+                            w.partial_lse, tile_rows_of(p->attend_impl, p->head_dim, p->chunk_size), st)) != cudaSuccess)
       return (int)e;
   } else if (last) {
     if ((e = mark(1)) != cudaSuccess || (e = mark(2)) != cudaSuccess) return (int)e;

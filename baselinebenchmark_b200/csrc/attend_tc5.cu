@@ -59,6 +59,7 @@ constexpr int kPrefixCache = 6144;       // ints of tile_prefix kept in shared m
 enum { ST_OK = 0, ST_PRODUCER = 1, ST_MMA = 2, ST_SOFTMAX = 3 };
 
 struct Ctrl {
+  static constexpr int kPrefix = kPrefixCache;
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
   uint64_t s_full[2], p_full[2], o_full[2];
   uint64_t item_ready[2];                  // slot filled by the prefetch warp (phase = fill count)
@@ -103,8 +104,8 @@ struct KernelArgs {
 // Runs in one spare warp while the other warps work on the current item: draws the
 // next item from the global queue (skipping empty own-chunk tiles), decodes it and
 // resolves its rows (output entry and Q row offset) into prefetch slot `slot`.
-template <int kItemRows>
-__device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs& a, Ctrl& c, int slot,
+template <int kItemRows, typename CtrlT>
+__device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs& a, CtrlT& c, int slot,
                                               int n_routed, int n_items) {
   const int lane = threadIdx.x & 31;
   Item it;
@@ -116,7 +117,7 @@ __device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs&
     idx = __shfl_sync(0xffffffffu, idx, 0);
     if (idx >= n_items) { done = 1; break; }
     it = decode_item(p, idx, n_routed, kItemRows, a.cu, a.list_counts, a.list_offsets,
-                     p.lists < kPrefixCache ? c.prefix_cache : a.tile_prefix);
+                     p.lists < CtrlT::kPrefix ? c.prefix_cache : a.tile_prefix);
     if (it.valid) break;
   }
   if (lane == 0) { c.item[slot] = it; c.done[slot] = done; }
@@ -872,6 +873,288 @@ attend_tc5_wide_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_
   if (warp == 1) tmem_dealloc(tmem, kTmemCols);
 }
 
+// ---------------------------------------------------------------------------
+// small chunks (at most kSmallChunk keys): one 128-row tile per work item, two CTAs per SM
+//
+// With one or two key tiles per item the kernels above spend most of an item on its hand-over
+// (description, Q gather, epilogue; see the cycle stamps in the design notes), during which the
+// tensor pipe idles.  This variant halves every per-CTA resource - 192 threads (one softmax
+// warpgroup, warps 0-3; warp 4 describes the next item and requests K/V tiles, warp 5 issues the
+// MMAs), one Q tile, one K and one V stage, 256 TMEM columns (S 0-127, O 128-255), about 110 KB
+// of shared memory, 168 registers per thread - so that two CTAs share an SM and one works while
+// the other changes items.  Per tile: QK -> softmax -> PV in sequence (S is single-buffered; P
+// overwrites it), K(j+1) is requested when QK(j) has executed, V(j+1) when PV(j) has.
+// ---------------------------------------------------------------------------
+constexpr int kSmallThreads = 192;
+constexpr int kSmallPrefix = 2048;
+
+struct SmallCtrl {
+  static constexpr int kPrefix = kSmallPrefix;
+  uint64_t k_full, k_empty, v_full, v_empty, s_full, p_full, o_full;
+  uint64_t item_ready[2];
+  uint32_t tmem_slot;
+  volatile int32_t abort;
+  Item item[2];
+  int32_t done[2];
+  int64_t qoff[2][kTileM];
+  int32_t entry[2][kTileM];
+  int32_t prefix_cache[kSmallPrefix];
+};
+constexpr size_t kSmallSmemBytes = 1024 + 3 * kTileBytes + sizeof(SmallCtrl);
+static_assert(2 * (kSmallSmemBytes + 1024) <= 232448, "two CTAs per SM");
+
+template <bool kHalf, int D>
+__global__ void __launch_bounds__(kSmallThreads, 2)
+attend_tc5_small_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
+                        const __grid_constant__ CUtensorMap tmap_v, const KernelArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sQ = smem_u32(smem);
+  const uint32_t sK = sQ + kTileBytes;
+  const uint32_t sV = sK + kTileBytes;
+  SmallCtrl& c = *reinterpret_cast<SmallCtrl*>(smem + 3 * kTileBytes);
+  constexpr uint32_t kCols = 256;
+
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&c.k_full), 1);
+    mbar_init(smem_u32(&c.k_empty), 1);
+    mbar_init(smem_u32(&c.v_full), 1);
+    mbar_init(smem_u32(&c.v_empty), 1);
+    mbar_init(smem_u32(&c.s_full), 1);
+    mbar_init(smem_u32(&c.p_full), kTileM);
+    mbar_init(smem_u32(&c.o_full), 1);
+    mbar_init(smem_u32(&c.item_ready[0]), 1);
+    mbar_init(smem_u32(&c.item_ready[1]), 1);
+    c.abort = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&c.tmem_slot), kCols);
+    tmem_relinquish();
+  }
+  if (p.hist > 0 && p.lists < kSmallPrefix)
+    for (int i = threadIdx.x; i <= (int)p.lists; i += kSmallThreads) c.prefix_cache[i] = a.tile_prefix[i];
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = c.tmem_slot;
+
+  const int n_routed = p.hist > 0 ? a.tile_prefix[p.lists] : 0;
+  const int n_items = n_routed + own_item_count(p.slots, p.Hq, p.C, kTileM);
+
+  // Head of item n for every thread: the slot filled by warp 4; warps 0-3 gather the Q rows.  Warp 4
+  // does not wait for the gather: it goes on to describe item n + 1 at once (its chain of
+  // dependent global loads is as long as an item).
+  auto next_item = [&](int n, Item& it) -> bool {
+    const int slot = n & 1;
+    __syncthreads();
+    if (c.done[slot]) return false;
+    it = c.item[slot];
+    if (warp < 4) {
+      constexpr int kChunks = D / 8;
+      const int32_t* entry = c.entry[slot];
+      const int64_t* qoff = c.qoff[slot];
+      const int t = threadIdx.x;
+      uint4 val[kChunks];
+#pragma unroll
+      for (int u = 0; u < kChunks; ++u) {
+        const int i = t + u * 128;
+        const int r = i / kChunks, ch = i % kChunks;
+        val[u] = make_uint4(0, 0, 0, 0);
+        if (entry[r] >= 0) val[u] = __ldg(reinterpret_cast<const uint4*>(a.q + qoff[r] + ch * 8));
+      }
+#pragma unroll
+      for (int u = 0; u < kChunks; ++u) {
+        const int i = t + u * 128;
+        const int r = i / kChunks, ch = i % kChunks;
+        const uint32_t dst = (uint32_t)((ch >> 3) * kHalfBytes + r * 128 + (((ch & 7) ^ (r & 7)) << 4));
+        *reinterpret_cast<uint4*>(smem + dst) = val[u];
+      }
+    }
+    fence_proxy_async_smem();
+    if (warp != 4) asm volatile("bar.sync 1, 160;" ::: "memory");
+    return true;
+  };
+  Item it;
+
+  if (warp >= 4) {
+    uint32_t kt = 0, vt = 0;               // K / V tiles produced (warp 4) or consumed (warp 5) so far
+    uint32_t pph = 0;                      // p_full phase
+    int pre = 0;                           // warp 4: 1 when K(0) and V(0) of the coming item are requested
+    const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+    const uint32_t dq = __shfl_sync(0xffffffffu, desc_lo(sQ, 16), 0);
+    const uint32_t dk = __shfl_sync(0xffffffffu, desc_lo(sK, 16), 0);
+    const uint32_t dv = __shfl_sync(0xffffffffu, desc_lo(sV, kHalfBytes), 0);
+    const uint32_t el = elect_one();
+    if (warp == 4) prefetch_item<kTileM>(p, a, c, 0, n_routed, n_items);
+    for (int n = 0;; ++n) {
+      if (!next_item(n, it)) break;
+      const int ntiles = (it.kv_len + kBN - 1) / kBN;
+      if (warp == 4) {
+        // K and V tile `j` of item `w`; false after a timeout (lane 0 only)
+        auto load_tile = [&](const Item& w, int j) -> bool {
+          const int tok = w.kv_tok0 + j * kBN;
+          if (!mbar_wait(smem_u32(&c.k_empty), (kt & 1) ^ 1)) return false;
+          uint32_t bar = smem_u32(&c.k_full);
+          mbar_expect_tx(bar, ((D + 63) / 64) * kHalfBytes);
+          tma_load_3d(sK, &tmap_k, bar, 0, w.kv_head, tok);
+          if (D > 64) tma_load_3d(sK + kHalfBytes, &tmap_k, bar, 64, w.kv_head, tok);
+          ++kt;
+          if (!mbar_wait(smem_u32(&c.v_empty), (vt & 1) ^ 1)) return false;
+          bar = smem_u32(&c.v_full);
+          mbar_expect_tx(bar, ((D + 63) / 64) * kHalfBytes);
+          tma_load_3d(sV, &tmap_v, bar, 0, w.kv_head, tok);
+          if (D > 64) tma_load_3d(sV + kHalfBytes, &tmap_v, bar, 64, w.kv_head, tok);
+          ++vt;
+          return true;
+        };
+        bool alive = true;
+        if (lane == 0)
+          for (int j = pre; alive && j < ntiles; ++j) alive = load_tile(it, j);
+        pre = 0;
+        __syncwarp();
+        // the next item: described by the whole warp, its first tiles requested as soon as the
+        // stages free up
+        const int s1 = (n + 1) & 1;
+        prefetch_item<kTileM>(p, a, c, s1, n_routed, n_items);
+        if (lane == 0 && alive && !c.done[s1]) {
+          const Item nx = c.item[s1];
+          alive = load_tile(nx, 0);
+          pre = alive ? 1 : 0;
+        }
+        pre = __shfl_sync(0xffffffffu, pre, 0);
+        if (lane == 0 && !alive) { atomicExch(a.status, ST_PRODUCER); c.abort = 1; }
+      } else {
+        bool ok = true;
+        tc_fence_after();
+        for (int j = 0; ok && j < ntiles; ++j) {
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.k_full), kt & 1));
+          if (!ok) break;
+          tc_fence_after();
+          if (el) {
+            issue_qk<0, 0, kHalf, D>(tm, dq, dk);
+            tc_commit(smem_u32(&c.s_full));
+            tc_commit(smem_u32(&c.k_empty));
+          }
+          __syncwarp();
+          ++kt;
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.v_full), vt & 1));
+          if (!ok) break;
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.p_full), pph));
+          if (!ok) break;
+          pph ^= 1;
+          tc_fence_after();
+          if (el) {
+            // O in columns 128-255: the P.V of the kernels above with the accumulator moved
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+              mma_ts(tm + 128, tm + ks * 8, desc64(dv + ks * (2048 >> 4)), kIdescPV<kHalf, D>, j > 0 || ks > 0);
+            tc_commit(smem_u32(&c.v_empty));
+            if (j + 1 == ntiles) tc_commit(smem_u32(&c.o_full));
+          }
+          __syncwarp();
+          ++vt;
+        }
+        if (!ok && lane == 0) { atomicExch(a.status, ST_MMA); c.abort = 1; }
+      }
+      __syncwarp();
+    }
+  } else {
+    const int row = warp * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t tS = tmem + lane_base;
+    const uint32_t tO = tmem + lane_base + 128;
+    const float sl2 = rsqrtf((float)D) * 1.4426950408889634f;
+    uint32_t sph = 0, oph = 0;
+    for (int n = 0; next_item(n, it); ++n) {
+      const int32_t* entries = c.entry[n & 1];
+      const int ntiles = (it.kv_len + kBN - 1) / kBN;
+      const int qpos = it.tok0 + row;
+      const int lim = it.causal ? min(it.kv_len, qpos - it.kv_tok0 + 1) : it.kv_len;
+      float m_ref = -INFINITY, l = 0.f;
+      bool ok = true;
+      for (int j = 0; ok && j < ntiles; ++j) {
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&c.s_full), sph));
+        if (!ok) break;
+        sph ^= 1;
+        tc_fence_after();
+        const int key0 = j * kBN;
+        const bool masked = key0 + kBN > it.kv_len || (it.causal && it.kv_tok0 + key0 + kBN - 1 > it.tok0);
+        if (masked) softmax_row<true, kHalf, D>(tS, tO, j, key0, lim, sl2, m_ref, l, [] {});
+        else softmax_row<false, kHalf, D>(tS, tO, j, key0, lim, sl2, m_ref, l, [] {});
+        tc_fence_before();
+        mbar_arrive(smem_u32(&c.p_full));
+      }
+      if (ok) ok = mbar_wait(smem_u32(&c.o_full), oph);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        oph ^= 1;
+        tc_fence_after();
+        const int32_t e = entries[row];
+        uint32_t v0[32], v1[32];
+        float amax = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < D / 32; ++ch) {
+          tmem_ld32(tO + ch * 32, v0);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2)
+            amax = max3(amax, fabsf(__uint_as_float(v0[i])), fabsf(__uint_as_float(v0[i + 1])));
+        }
+        const float inv = 1.f / l;
+        const PartialScale ps = partial_scale(amax * inv);
+        const float mul = inv * ps.scale;
+        unsigned char* stage = smem + warp * 8192;            // this warp's part of the idle Q tile
+#pragma unroll
+        for (int ch = 0; ch < (D + 63) / 64; ++ch) {
+          constexpr int kLast = D % 64 == 0 ? 64 : D % 64;
+          const int cols = ch == (D + 63) / 64 - 1 ? kLast : 64;
+          tmem_ld32(tO + ch * 64, v0);
+          if (cols > 32) tmem_ld32(tO + ch * 64 + 32, v1);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (i * 8 < cols) {
+              const uint32_t* s8 = i < 4 ? v0 + 8 * i : v1 + 8 * (i - 4);
+              *reinterpret_cast<uint4*>(stage + lane * 144 + i * 16) =
+                  make_uint4(pack2_half(__uint_as_float(s8[0]) * mul, __uint_as_float(s8[1]) * mul),
+                             pack2_half(__uint_as_float(s8[2]) * mul, __uint_as_float(s8[3]) * mul),
+                             pack2_half(__uint_as_float(s8[4]) * mul, __uint_as_float(s8[5]) * mul),
+                             pack2_half(__uint_as_float(s8[6]) * mul, __uint_as_float(s8[7]) * mul));
+            }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rl = i * 4 + (lane >> 3), c16 = lane & 7;
+            const int32_t er = __shfl_sync(0xffffffffu, e, rl);
+            const uint4 val = *reinterpret_cast<const uint4*>(stage + rl * 144 + c16 * 16);
+            if (er >= 0 && c16 * 8 < cols)
+              __stcs(reinterpret_cast<uint4*>(a.partial_out + (int64_t)er * D + ch * 64 + c16 * 8), val);
+          }
+          __syncwarp();
+        }
+        if (e >= 0) a.partial_lse[e] = make_float2((m_ref + log2f(l)) * 0.6931471805599453f, ps.inv);
+        tc_fence_before();
+      } else {
+        atomicExch(a.status, ST_SOFTMAX);
+        c.abort = 1;
+      }
+    }
+  }
+
+  if (c.abort) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, kCols);
+}
+
 // One warp waits, with the same bounded wait every role of the dense stage uses, on a barrier
 // nobody ever arrives on: the wait gives up after `limit_ns`, the status word is set like the
 // kernel would set it, and the warp returns.  Lets a test see the give-up path without a fault.
@@ -948,6 +1231,15 @@ cudaError_t launch_attend_tc5(const Params& p, const __nv_bfloat16* q, const __n
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const KernelArgs args{q, cu, list_counts, list_offsets, tile_prefix, row_list, partial_out, partial_lse,
                         work_counter, status};
+  if (tc5_small_items(p.D, p.C)) {
+    auto small = p.D == 128 ? (p.fp16 ? attend_tc5_small_kernel<true, 128> : attend_tc5_small_kernel<false, 128>)
+               : p.D == 96  ? (p.fp16 ? attend_tc5_small_kernel<true, 96> : attend_tc5_small_kernel<false, 96>)
+                            : (p.fp16 ? attend_tc5_small_kernel<true, 64> : attend_tc5_small_kernel<false, 64>);
+    e = cudaFuncSetAttribute(small, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmallSmemBytes);
+    if (e != cudaSuccess) return e;
+    small<<<2 * sms, kSmallThreads, kSmallSmemBytes, st>>>(p, mk, mv, args);
+    return cudaGetLastError();
+  }
   kernel<<<sms, kThreads, kSmemBytes, st>>>(p, mk, mv, args);
   return cudaGetLastError();
 }

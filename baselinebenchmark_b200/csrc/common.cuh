@@ -193,6 +193,12 @@ cudaError_t launch_merge(const Params& p, const __half* partial_out, const float
 constexpr int kMmaTileRows = 128;        // rows per work item, mma.sync kernel
 constexpr int kTc5TileRows = 256;        // rows per work item, tcgen05 kernel (two 128-row MMA tiles)
 constexpr int kTileRowsWide = 128;       // rows per work item, tcgen05 kernel at head_dim 256 (one tile)
+// Chunks of at most this many keys run the tcgen05 kernel for short items (128-row items, two CTAs per SM).
+#ifndef MOBA_SMALL_CHUNK
+#define MOBA_SMALL_CHUNK 256
+#endif
+constexpr int kSmallChunk = MOBA_SMALL_CHUNK;
+__host__ __device__ inline bool tc5_small_items(int head_dim, int chunk) { return head_dim <= 128 && chunk <= kSmallChunk; }
 
 cudaError_t launch_attend_mma(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* k,
                               const __nv_bfloat16* v, const int32_t* cu, const int32_t* list_counts,

@@ -327,12 +327,15 @@ int moba_cp_forward(const moba_problem_t* p, void* nccl_comm, int32_t rank, int3
 int moba_cp_poll(void* nccl_comm, int32_t* async_error);
 int moba_cp_abort(void* nccl_comm);
 
-/* Rows per routed work item that the selected attend implementation wants
- * (the tile_rows argument of moba_compact_routes): moba_attend_tile_rows answers for
- * head_dim <= 128, moba_attend_tile_rows_for for any head_dim (the tcgen05 stage takes
- * 256 rows per item up to head_dim 128 and 128 at head_dim 256). */
+/* Rows per routed work item that the dense stage wants (the tile_rows argument of
+ * moba_compact_routes).  moba_problem_tile_rows answers for a problem and is what callers
+ * of the staged entry points should use: the tcgen05 stage takes 256 rows per item, 128 at
+ * head_dim 256 and for chunks of at most 256 keys (its kernel for short items), the
+ * mma.sync stage 128.  moba_attend_tile_rows / _for answer for long chunks at head_dim
+ * <= 128 / any head_dim. */
 int moba_attend_tile_rows(int attend_impl);
 int moba_attend_tile_rows_for(int attend_impl, int head_dim);
+int moba_problem_tile_rows(const moba_problem_t* p);
 
 #ifdef __cplusplus
 }

@@ -139,6 +139,10 @@ def test_workspace_size_and_null_handling(lib):
     assert lib.moba_attend_tile_rows(_lib.ATTEND_MMA_SYNC) == 128
     assert [lib.moba_attend_tile_rows_for(_lib.ATTEND_TCGEN05, d) for d in (64, 96, 128, 256)] == [256, 256, 256, 128]
     assert lib.moba_attend_tile_rows_for(_lib.ATTEND_MMA_SYNC, 256) == 128
+    assert lib.moba_problem_tile_rows(C.byref(_problem())) == 256                       # chunk 512
+    assert lib.moba_problem_tile_rows(C.byref(_problem(chunk_size=128))) == 128         # short items: their own kernel
+    assert lib.moba_problem_tile_rows(C.byref(_problem(chunk_size=128, attend_impl=1))) == 128
+    assert lib.moba_problem_tile_rows(C.byref(_problem(topk=0))) == -5
 
 
 def _cpu_args(t=64, hq=4, hkv=2, d=128, dtype=torch.bfloat16):
