@@ -504,7 +504,9 @@ int moba_backward_workspace_size(const moba_problem_t* p, size_t* bytes) {
   if (rc != MOBA_OK) return rc;
   if (bytes == nullptr) return MOBA_E_NULL;
   const Params r = make_params(p);
-  *bytes = carve(r, nullptr, true).total + 2 * align_up((size_t)r.rows * sizeof(float));
+  // + delta and lse per row + the packed Q / dO rows of the routed lists (tcgen05 dk/dv kernel)
+  *bytes = carve(r, nullptr, true).total + 2 * align_up((size_t)r.rows * sizeof(float)) +
+           align_up((size_t)bwd_packed_elems(r) * 2);
   return MOBA_OK;
 }
 
@@ -526,6 +528,8 @@ int moba_backward(const moba_problem_t* p, const void* q, const void* k, const v
   float* partial_dq = static_cast<float*>(w.partial_out);
   float* delta = reinterpret_cast<float*>(static_cast<char*>(workspace) + w.total);
   float* lse2 = reinterpret_cast<float*>(reinterpret_cast<char*>(delta) + align_up((size_t)r.rows * sizeof(float)));
+  __nv_bfloat16* packed =
+      reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(lse2) + align_up((size_t)r.rows * sizeof(float)));
   const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(q);
   const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(k);
   const __nv_bfloat16* vb = static_cast<const __nv_bfloat16*>(v);
@@ -557,8 +561,8 @@ int moba_backward(const moba_problem_t* p, const void* q, const void* k, const v
     return (int)e;
   if (dq_tc5)
     e = launch_bwd_dkdv_tc5(r, qb, kb, vb, gb, cu, w.list_counts, w.list_offsets, w.row_list, lse2, delta,
-                            static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), w.work_counter + 8,
-                            w.status, st);
+                            static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), packed,
+                            w.work_counter + 8, w.status, st);
   else
     e = launch_bwd_dkdv(r, qb, kb, vb, gb, qt, hd, cu, w.list_counts, w.list_offsets, w.row_list, lse2, delta,
                         static_cast<__nv_bfloat16*>(dk), kt, hd, static_cast<__nv_bfloat16*>(dv), kt, hd,

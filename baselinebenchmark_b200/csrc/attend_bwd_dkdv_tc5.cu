@@ -12,7 +12,12 @@
 // Key-stationary: a unit is 128 keys of one (chunk, kv head); its K and V tiles stay in shared
 // memory (TMA) and dK, dV stay in tensor memory while the CTA visits every query row that
 // attends the keys - the routed list of the chunk, then the chunk's own rows of every query
-// head of the group - in steps of 64 rows gathered into a four-stage ring.  Per step
+// head of the group - in steps of 64 rows brought into a four-stage ring by TMA.  The rows of
+// a routed list are scattered over q and dO, so a pre-pass (pack_rows_kernel) first copies
+// them, in list order, into two packed arrays [entries, D]: a step of a routed list is then
+// a 64-row box of those, a step of own-chunk rows a 64-token box of q / dO themselves.  (A
+// list is read once per 128-key tile of its chunk; gathered with cp.async every time, the
+// 16-byte copies kept the load/store pipe busier than the tensor pipe.)  Per step
 //   S^T  = K . Q^T      (128 keys x 64 rows, operands in shared memory)
 //   dP^T = V . dO^T     (128 x 64)
 //   one thread per key turns them into P^T and dS^T (input dtype) in tensor memory
@@ -22,9 +27,9 @@
 // the compaction's (unspecified), so dK and dV vary in their last bits from run to run.
 //
 // Warp roles (384 threads): warp 0 lane 0 loads K/V by TMA, warp 1 issues the MMAs and owns
-// the TMEM allocation, warps 2-3 describe the rows of the coming steps, warps 4-7 handle the even
-// steps (S buffer 0) and write dK, warps 8-11 the odd steps (S buffer 1) and write dV; after a
-// step a group copies the Q / dO rows of the step three ahead with cp.async.
+// the TMEM allocation, warps 2-3 describe the rows of the coming steps (LSE, delta, token), warps
+// 4-7 handle the even steps (S buffer 0) and write dK, warps 8-11 the odd steps (S buffer 1) and
+// write dV; after a step one thread of the group requests the Q / dO boxes of the step three ahead.
 // TMEM columns: buffer X: S^T 128X..+63 (P^T, 16-bit, over the first 32), dP^T 128X+64..+127
 // (dS^T over its first 32); dK 256.., dV 384...
 // Every wait is bounded; a wait that gives up sets a status word, the CTAs stop drawing units
@@ -36,6 +41,8 @@ namespace moba {
 
 bool make_kv_map(CUtensorMap* m, bool fp16, int D, const __nv_bfloat16* base, int64_t T, int Hkv, int64_t st,
                  int64_t sh, int box_rows);
+bool make_tile_map(CUtensorMap* m, bool fp16, int D, const __nv_bfloat16* base, int64_t T, int H, int64_t st,
+                   int64_t sh, int box_heads, int box_rows);
 
 namespace {
 
@@ -66,8 +73,6 @@ struct Ctrl {
   int32_t unit;
   alignas(16) float2 meta[kStages][kStep];     // {lse * log2 e, delta} of the row; {0, 0}: no row
   alignas(16) int32_t tok[kStages][kStep];                 // query token of an own-chunk row (causal limit), else INT_MAX
-  int64_t qoff[kStages][kStep];                // element offset of the row in q, -1: no row
-  int32_t grow[kStages][kStep];                // row index t * Hq + h
   int32_t ent[4][kStep];                       // routed-list entries of the steps ahead (0: no row)
 };
 
@@ -253,7 +258,9 @@ __device__ __forceinline__ bool next_unit(const Params& p, const KernelArgs& a, 
 template <bool kHalf, int D>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
-                    const __grid_constant__ CUtensorMap tmap_v, const KernelArgs a) {
+                    const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_q,
+                    const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__ CUtensorMap tmap_qp,
+                    const __grid_constant__ CUtensorMap tmap_gp, const KernelArgs a) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sK = smem_u32(smem);
@@ -267,7 +274,7 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     mbar_init(smem_u32(&c.kv_full), 1);
     mbar_init(smem_u32(&c.acc_full), 1);
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(smem_u32(&c.row_full[i]), 64 + kKeys);     // lse / delta of 64 rows + the copies of 128 threads
+      mbar_init(smem_u32(&c.row_full[i]), 64 + 1);         // lse / delta of 64 rows + the thread that requests the boxes
       mbar_init(smem_u32(&c.row_empty[i]), 1);
       mbar_init(smem_u32(&c.meta_full[i]), 64);
     }
@@ -279,6 +286,10 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     fence_barrier_init();
     prefetch_tmap(&tmap_k);
     prefetch_tmap(&tmap_v);
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_g);
+    prefetch_tmap(&tmap_qp);
+    prefetch_tmap(&tmap_gp);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&c.tmem_slot), kTmemCols);
@@ -399,17 +410,16 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         if (threadIdx.x == 64) TR_ADD(a, 4, t_e);
         TR_T0(t_i);
         {
-          int64_t off = -1;
-          if (row >= 0) {
-            const int t = row / p.Hq;
-            off = (int64_t)t * p.sq_t + (int64_t)(row - t * p.Hq) * p.sq_h;
-          }
           c.tok[st][r] = tokq;
-          c.qoff[st][r] = off;
-          c.grow[st][r] = row;
-          const int rs = row >= 0 ? row : 0;
-          cp_async4(smem_u32(&c.meta[st][r].x), a.lse2 + rs, row >= 0);      // absent rows: {0, 0}, their Q and
-          cp_async4(smem_u32(&c.meta[st][r].y), a.delta + rs, row >= 0);     // dO rows are zero as well
+          // A place of the step without a row still holds data in the stage (the box goes on into
+          // the next list, the next chunk, or the zero rows behind the last list): an LSE of
+          // +inf makes its p = 2^(s - inf) = 0, and with it its share of dV and dS.
+          if (row >= 0) {
+            cp_async4(smem_u32(&c.meta[st][r].x), a.lse2 + row, true);
+            cp_async4(smem_u32(&c.meta[st][r].y), a.delta + row, true);
+          } else {
+            c.meta[st][r] = make_float2(INFINITY, 0.f);
+          }
         }
         // lse and delta travel asynchronously and count on the stage's barrier when they land;
         // the offsets are there now: the row threads may start copying the rows
@@ -438,28 +448,35 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
       const bool key_ok = key < u.nkeys;
       const int key_tok = u.key0 + key;
       bool ok = true;
-      // The Q and dO rows of step j are copied by the 128 threads of one of the two groups in
-      // 16-byte pieces with the 128-byte swizzle of the tile.  Two dedicated warps issue such
-      // copies too slowly to feed the tensor core; the eight row warps keep up.
+      // The Q and dO rows of step j: 64-row boxes requested by one thread of the group.  It first
+      // waits for the step's description, which the describing warps only write once the stage
+      // is free again.
       auto copy_rows = [&](int j) -> bool {
         if (j >= u.steps) return true;
         const uint32_t gj = g0 + j, sj = gj & 3;
         if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&c.meta_full[sj]), (gj >> 2) & 1))) return false;
-        // a warp takes 16 rows of Q and the same 16 rows of dO; an instruction covers whole rows
-        // (D / 8 lanes per row), so every 32-byte sector it asks for is used in full
-        constexpr int kChunks = D / 8, kRowsPerInstr = 32 / kChunks;
-        const int ch = lane % kChunks;
-        const uint32_t qb = sRows + sj * 2 * kRowTileBytes + (ch >> 3) * kRowBlockBytes, gb = qb + kRowTileBytes;
+        if ((warp & 3) == 0 && lane == 0) {
+          const uint32_t bar = smem_u32(&c.row_full[sj]);
+          const uint32_t qb = sRows + sj * 2 * kRowTileBytes, gb = qb + kRowTileBytes;
+          mbar_expect_tx(bar, 2 * (D / 64) * kRowBlockBytes);
+          if (j < u.routed_steps) {
+            const int pos = (int)u.list_off + j * kStep;
 #pragma unroll
-        for (int it = 0; it < 16 / kRowsPerInstr; ++it) {
-          const int rr = (warp & 3) * 16 + it * kRowsPerInstr + lane / kChunks;
-          const int64_t off = c.qoff[sj][rr];
-          const bool valid = off >= 0;
-          const uint32_t dst = (uint32_t)(rr * 128 + (((ch & 7) ^ (rr & 7)) << 4));
-          cp_async16(qb + dst, a.q + (valid ? off : 0) + ch * 8, valid);
-          cp_async16(gb + dst, a.dout + (valid ? (int64_t)c.grow[sj][rr] * D : 0) + ch * 8, valid);
+            for (int blk = 0; blk < D / 64; ++blk) {
+              tma_load_3d(qb + blk * kRowBlockBytes, &tmap_qp, bar, blk * 64, 0, pos);
+              tma_load_3d(gb + blk * kRowBlockBytes, &tmap_gp, bar, blk * 64, 0, pos);
+            }
+          } else {
+            const int o = j - u.routed_steps;
+            const int hl = o / u.own_steps, ot = o - hl * u.own_steps;
+            const int tok = u.key0 + ot * kStep, head = u.kvh * p.G + hl;
+#pragma unroll
+            for (int blk = 0; blk < D / 64; ++blk) {
+              tma_load_3d(qb + blk * kRowBlockBytes, &tmap_q, bar, blk * 64, head, tok);
+              tma_load_3d(gb + blk * kRowBlockBytes, &tmap_g, bar, blk * 64, head, tok);
+            }
+          }
         }
-        cp_async_arrive(smem_u32(&c.row_full[sj]));
         return true;
       };
       const int first = ((g0 & 1) == (uint32_t)x) ? 0 : 1;
@@ -493,7 +510,6 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         ok = copy_rows(i + 3);
         if (threadIdx.x == 128) TR_ADD(a, 10, t_w);
       }
-      cp_async_wait_all();
       TR_T0(t_a);
       if (ok) ok = mbar_wait(smem_u32(&c.acc_full), nu & 1);
       ok = __all_sync(0xffffffffu, ok);
@@ -541,6 +557,32 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
   if (warp == 1) tmem_dealloc(tmem, kTmemCols);
 }
 
+// Pre-pass: the Q and dO rows of every routed list, in list order, into qp / gp [entries, D];
+// 64 rows of zeros behind the last list (a 64-row box may reach past it).  One 16-byte piece per
+// thread and tensor: a warp copies whole rows.
+template <int D>
+__global__ void __launch_bounds__(256)
+pack_rows_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ dout,
+                 const int32_t* __restrict__ list_offsets, const int32_t* __restrict__ row_list,
+                 __nv_bfloat16* __restrict__ qp, __nv_bfloat16* __restrict__ gp) {
+  constexpr int kChunks = D / 8;
+  const int64_t total = list_offsets[p.lists];
+  const int64_t pieces = (total + kStep) * kChunks;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < pieces; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t pos = i / kChunks;
+    const int ch = (int)(i - pos * kChunks);
+    uint4 vq = make_uint4(0, 0, 0, 0), vg = vq;
+    if (pos < total) {
+      const uint32_t row = (uint32_t)row_list[pos] / (uint32_t)p.NP;
+      const uint32_t t = row / (uint32_t)p.Hq;
+      vq = __ldg(reinterpret_cast<const uint4*>(q + (int64_t)t * p.sq_t + (int64_t)(row - t * (uint32_t)p.Hq) * p.sq_h) + ch);
+      vg = __ldg(reinterpret_cast<const uint4*>(dout + (int64_t)row * D) + ch);
+    }
+    reinterpret_cast<uint4*>(qp + pos * D)[ch] = vq;
+    reinterpret_cast<uint4*>(gp + pos * D)[ch] = vg;
+  }
+}
+
 // dk, dv <- NaN when a kernel of the call gave up on a wait
 __global__ void poison_kernel(const int32_t* __restrict__ status, uint32_t* dk, uint32_t* dv, int64_t words) {
   if (*status == 0) return;
@@ -556,21 +598,36 @@ cudaError_t launch_bwd_dkdv_tc5(const Params& p, const __nv_bfloat16* q, const _
                                 const __nv_bfloat16* v, const __nv_bfloat16* dout, const int32_t* cu,
                                 const int32_t* list_counts, const int32_t* list_offsets, const int32_t* row_list,
                                 const float* lse2, const float* delta, __nv_bfloat16* dk, __nv_bfloat16* dv,
-                                int32_t* work_counter, int32_t* status, cudaStream_t st) {
+                                __nv_bfloat16* packed, int32_t* work_counter, int32_t* status, cudaStream_t st) {
   if (p.D != 64 && p.D != 128) return cudaErrorInvalidValue;
-  CUtensorMap mk, mv;
-  if (!make_kv_map(&mk, p.fp16 != 0, p.D, k, p.T, p.Hkv, p.sk_t, p.sk_h, kKeys) ||
-      !make_kv_map(&mv, p.fp16 != 0, p.D, v, p.T, p.Hkv, p.sv_t, p.sv_h, kKeys))
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // packed rows of the routed lists: qp, then gp, each [hist * rows + 64, D]
+  const int64_t cap = (int64_t)p.hist * p.rows + kStep;
+  __nv_bfloat16* qp = packed;
+  __nv_bfloat16* gp = packed + cap * p.D;
+  if (p.hist > 0) {
+    if (p.D == 128) pack_rows_kernel<128><<<sms * 8, 256, 0, st>>>(p, q, dout, list_offsets, row_list, qp, gp);
+    else pack_rows_kernel<64><<<sms * 8, 256, 0, st>>>(p, q, dout, list_offsets, row_list, qp, gp);
+    const cudaError_t pe = cudaGetLastError();
+    if (pe != cudaSuccess) return pe;
+  }
+  CUtensorMap mk, mv, mq, mg, mqp, mgp;
+  const bool half = p.fp16 != 0;
+  if (!make_kv_map(&mk, half, p.D, k, p.T, p.Hkv, p.sk_t, p.sk_h, kKeys) ||
+      !make_kv_map(&mv, half, p.D, v, p.T, p.Hkv, p.sv_t, p.sv_h, kKeys) ||
+      !make_tile_map(&mq, half, p.D, q, p.T, p.Hq, p.sq_t, p.sq_h, 1, kStep) ||
+      !make_tile_map(&mg, half, p.D, dout, p.T, p.Hq, (int64_t)p.Hq * p.D, p.D, 1, kStep) ||
+      !make_tile_map(&mqp, half, p.D, qp, cap, 1, p.D, p.D, 1, kStep) ||
+      !make_tile_map(&mgp, half, p.D, gp, cap, 1, p.D, p.D, 1, kStep))
     return cudaErrorNotSupported;
   auto kernel = p.D == 128 ? (p.fp16 ? bwd_dkdv_tc5_kernel<true, 128> : bwd_dkdv_tc5_kernel<false, 128>)
                            : (p.fp16 ? bwd_dkdv_tc5_kernel<true, 64> : bwd_dkdv_tc5_kernel<false, 64>);
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   if (e != cudaSuccess) return e;
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const KernelArgs args{q, dout, cu, list_counts, list_offsets, row_list, lse2, delta, dk, dv, work_counter, status};
-  kernel<<<sms, kThreads, kSmemBytes, st>>>(p, mk, mv, args);
+  kernel<<<sms, kThreads, kSmemBytes, st>>>(p, mk, mv, mq, mg, mqp, mgp, args);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   poison_kernel<<<sms, 256, 0, st>>>(status, reinterpret_cast<uint32_t*>(dk), reinterpret_cast<uint32_t*>(dv),
                                      (int64_t)p.T * p.Hkv * p.D / 2);

@@ -231,7 +231,9 @@ cudaError_t launch_bwd_dkdv_tc5(const Params& p, const __nv_bfloat16* q, const _
                                 const __nv_bfloat16* v, const __nv_bfloat16* dout, const int32_t* cu,
                                 const int32_t* list_counts, const int32_t* list_offsets, const int32_t* row_list,
                                 const float* lse2, const float* delta, __nv_bfloat16* dk, __nv_bfloat16* dv,
-                                int32_t* work_counter, int32_t* status, cudaStream_t st);
+                                __nv_bfloat16* packed, int32_t* work_counter, int32_t* status, cudaStream_t st);
+// 16-bit elements of the `packed` scratch of launch_bwd_dkdv_tc5 (Q and dO rows of the routed lists)
+inline int64_t bwd_packed_elems(const Params& p) { return 2 * ((int64_t)p.hist * p.rows + 64) * p.D; }
 cudaError_t launch_bwd_sum_dq(const Params& p, const float* partial_dq, const int32_t* selected, const int32_t* status,
                               __nv_bfloat16* dq, int64_t dq_t, int64_t dq_h, cudaStream_t st);
 cudaError_t launch_bwd_dkdv(const Params& p, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,

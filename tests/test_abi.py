@@ -72,7 +72,8 @@ def test_backward_argument_checks(lib):
     assert lib.moba_workspace_size(C.byref(_problem(attend_impl=1)), C.byref(fwd)) == 0
     # the forward keeps its partial rows in fp16, the backward its dq contributions in fp32
     # (same shape: rows x partials x head_dim); + delta and lse per row
-    assert need.value == fwd.value + 4096 * 8 * 3 * 128 * 2 + 2 * 4096 * 8 * 4
+    packed = 2 * (2 * 4096 * 8 + 64) * 128 * 2                      # Q and dO rows of the routed lists (hist 2)
+    assert need.value == fwd.value + 4096 * 8 * 3 * 128 * 2 + 2 * 4096 * 8 * 4 + packed
     assert lib.moba_backward_workspace_size(C.byref(_problem(q_token_begin=0, q_tokens=512)), C.byref(need)) == -2
     wide = dict(q_stride_token=2048, q_stride_head=256, k_stride_token=2048, k_stride_head=256,
                 v_stride_token=2048, v_stride_head=256, o_stride_token=2048, o_stride_head=256)
