@@ -778,3 +778,42 @@ def test_config_selection_full_tensor(cfg_id, seed):
     sel, counts = G.gate(prob, qd, m, cud)
     assert np.array_equal(sel.cpu().numpy(), sel_o)
     assert counts.sum().item() == (sel_o >= 0).sum()
+
+
+@pytest.mark.parametrize("case", [("long_items", (2048, 900), 8, 2, 128, 512, 4),
+                                  ("short_items", (1500, 700), 8, 2, 128, 128, 5),
+                                  ("d256", (1024, 300), 4, 2, 256, 128, 3),
+                                  ("mma_sync", (1024, 300), 4, 2, 64, 128, 3)], ids=lambda c: c[0])
+def test_stage_entry_points_chain_to_the_forward_result(case):
+    """moba_chunk_means -> moba_gate_topk -> moba_compact_routes -> moba_attend -> moba_merge with
+    caller-held buffers (work items of moba_problem_tile_rows rows, fp16 partial rows, {lse,
+    1 / scale} pairs) give bit for bit what moba_forward gives: the three tcgen05 kernels and
+    the mma.sync one."""
+    name, lens, hq, hkv, d, chunk, topk = case
+    q, k, v, cu = _case_inputs(lens, hq, hkv, chunk, seed=11, d=d)
+    qd, kd, vd = G.to_dev(q, k, v)
+    cud = torch.from_numpy(cu).cuda()
+    impl = _lib.ATTEND_MMA_SYNC if name == "mma_sync" else _lib.ATTEND_TCGEN05
+    prob, out = G.problem_for(qd, kd, vd, cud, max(lens), chunk, topk, impl)
+    lib = _lib.lib()
+    dims = G.dims_of(prob)
+    tile_rows = lib.moba_problem_tile_rows(C.byref(prob))
+    assert tile_rows == (256 if name == "long_items" else 128)
+    m = G.means(prob, kd, cud)
+    sel, counts = G.gate(prob, qd, m, cud)
+    offsets, tiles, row_list, plse = G.compact(prob, cud, sel, counts, tile_rows)
+    pout = torch.empty(dims.rows * dims.partials * d, dtype=torch.float16, device="cuda")
+    work = torch.zeros(2, dtype=torch.int32, device="cuda")
+    _lib.check(lib.moba_attend(C.byref(prob), qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), cud.data_ptr(),
+                               counts.data_ptr(), offsets.data_ptr(), tiles.data_ptr(), row_list.data_ptr(),
+                               pout.data_ptr(), plse.data_ptr(), work.data_ptr(), G.stream()))
+    lse = torch.empty(hq, sum(lens), dtype=torch.float32, device="cuda")
+    _lib.check(lib.moba_merge(C.byref(prob), pout.data_ptr(), plse.data_ptr(), work[1:].data_ptr(), out.data_ptr(),
+                              lse.data_ptr(), G.stream()))
+    torch.cuda.synchronize()
+    assert work[1].item() == 0
+    want, want_lse, want_sel = parallel.moba_forward(qd, kd, vd, cud, max(lens), chunk, topk, return_lse=True,
+                                                     return_selected=True, attend_impl=impl)
+    assert torch.equal(sel, want_sel)
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    assert torch.equal(lse, want_lse)
