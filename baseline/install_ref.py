@@ -17,6 +17,7 @@ Both skip when the folder is absent.
 """
 from __future__ import annotations
 
+import os
 import shutil
 import sys
 from pathlib import Path
@@ -25,8 +26,14 @@ FILES = ("__init__.py", "attention.py", "native_moba.py", "parallel.py", "routin
 DEST = Path(__file__).resolve().parent / "_ref" / "moba"
 
 
-def install(reference_root: str | Path = "/root/reference") -> Path | None:
-    src = Path(reference_root) / "backends" / "_mthreads" / "ops" / "moba"
+def default_root() -> Path:
+    """$MOBA_REFERENCE_ROOT, else a checkout named `reference` next to this repository."""
+    env = os.environ.get("MOBA_REFERENCE_ROOT")
+    return Path(env) if env else Path(__file__).resolve().parents[2] / "reference"
+
+
+def install(reference_root: str | Path | None = None) -> Path | None:
+    src = Path(reference_root or default_root()) / "backends" / "_mthreads" / "ops" / "moba"
     if not src.is_dir():
         return None
     DEST.mkdir(parents=True, exist_ok=True)
@@ -37,5 +44,5 @@ def install(reference_root: str | Path = "/root/reference") -> Path | None:
 
 
 if __name__ == "__main__":
-    where = install(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    where = install(sys.argv[1] if len(sys.argv) > 1 else None)
     print(where if where else "reference checkout not found: nothing installed")
