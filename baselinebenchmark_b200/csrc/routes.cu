@@ -159,14 +159,26 @@ merge_kernel(Params p, const __half* __restrict__ partial_out, const float2* __r
   // a dense stage that gave up on a wait leaves a non-zero status: poison the result
   const bool failed = status != nullptr && *status != 0;
   const int64_t warps = (int64_t)gridDim.x * (kMergeThreads / 32);
-  for (int64_t row = (int64_t)blockIdx.x * (kMergeThreads / 32) + (threadIdx.x >> 5); row < p.rows; row += warps) {
+  // Up to 32 partials per row (top-k up to 32): lane j holds {lse, 1 / scale} of partial j, and the
+  // pair of the warp's next row is requested before this row is worked on, so that a row starts
+  // with its partial rows as the only loads it has to wait for.
+  const bool in_regs = p.NP <= 32;
+  const int64_t row0 = (int64_t)blockIdx.x * (kMergeThreads / 32) + (threadIdx.x >> 5);
+  float2 mine = make_float2(-INFINITY, 0.f);
+  if (in_regs && row0 < p.rows && lane < p.NP) mine = __ldg(partial_lse + row0 * p.NP + lane);
+  for (int64_t row = row0; row < p.rows; row += warps) {
     const float2* lse = partial_lse + row * p.NP;
+    const float2 cur = mine;
+    if (in_regs && row + warps < p.rows && lane < p.NP) mine = __ldg(partial_lse + (row + warps) * p.NP + lane);
     float mx = -INFINITY;
-    for (int j = lane; j < p.NP; j += 32) mx = fmaxf(mx, lse[j].x);
+    if (in_regs) mx = cur.x;
+    else for (int j = lane; j < p.NP; j += 32) mx = fmaxf(mx, lse[j].x);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     float tot = 0.f;
-    for (int j = lane; j < p.NP; j += 32) tot += __expf(lse[j].x - mx);
+    if (in_regs) tot = __expf(cur.x - mx);                    // 0 for lanes past the partials (lse -inf)
+    else for (int j = lane; j < p.NP; j += 32) tot += __expf(lse[j].x - mx);
+    const float wlane = tot * cur.y;                          // in_regs: weight of partial `lane` up to 1 / sum
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
     const float inv = failed ? __int_as_float(0x7fc00000) : 1.f / tot;
@@ -182,10 +194,17 @@ merge_kernel(Params p, const __half* __restrict__ partial_out, const float2* __r
         const int j = j0 + u * kGroups + grp;
         w[u] = 0.f;
         o[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (active && j < p.NP) {
+        // the row's power-of-two scale is undone with the weight
+        const float wj = __shfl_sync(0xffffffffu, wlane, j & 31) * inv;
+        if (in_regs) {
+          if (active && j < p.NP && wj != 0.f) {
+            w[u] = wj;
+            o[u] = __ldg(src + j * kLanes);
+          }
+        } else if (active && j < p.NP) {
           const float2 lj = lse[j];
           if (lj.x != -INFINITY) {
-            w[u] = __expf(lj.x - mx) * inv * lj.y;            // the row's power-of-two scale is undone with the weight
+            w[u] = __expf(lj.x - mx) * inv * lj.y;
             o[u] = __ldg(src + j * kLanes);
           }
         }
