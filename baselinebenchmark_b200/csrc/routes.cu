@@ -147,7 +147,8 @@ constexpr int kMergeThreads = 256;
 // that many groups, group g takes the partials g, g + groups, ... of the row, four of them in
 // flight at a time, and the groups' sums are added at the end.
 template <bool kHalf, int D>
-__global__ void __launch_bounds__(kMergeThreads)
+// five CTAs per SM (at most 51 registers): more warps to wait for partial rows; six would spill
+__global__ void __launch_bounds__(kMergeThreads, 5)
 merge_kernel(Params p, const __half* __restrict__ partial_out, const float2* __restrict__ partial_lse,
              const int32_t* __restrict__ status, __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out) {
   constexpr int kLanes = D / 8;                  // lanes per partial row
