@@ -71,7 +71,7 @@ struct Ctrl {
   int32_t done[2];
   int64_t qoff[2][2 * kTileM];
   int32_t entry[2][2 * kTileM];
-  // tile_prefix copied once per CTA when it fits: decoding an item searches it, and with
+  // tile_prefix sampled once per CTA (whole when it fits): decoding an item searches it, and with
   // short items (small chunks) eleven dependent global loads per item were the critical path
   int32_t prefix_cache[kPrefixCache];
   float row_inv[kTileM];                   // head dim 256: the row's factor (scale / row sum), handed to the warps that write the second half of O
@@ -101,6 +101,38 @@ struct KernelArgs {
   int32_t* status;
 };
 
+// tile_prefix is kept in shared memory sampled every 2^shift entries (shift 0: whole), so that
+// finding the list of a routed item costs `shift` dependent global loads instead of log2(lists).
+__host__ __device__ inline int prefix_shift(int64_t lists, int cache_entries) {
+  int shift = 0;
+  while ((lists >> shift) + 2 > cache_entries) ++shift;
+  return shift;
+}
+template <typename CtrlT>
+__device__ __forceinline__ void fill_prefix_cache(CtrlT& c, const int32_t* __restrict__ tile_prefix, int64_t lists,
+                                                  int nthreads) {
+  const int shift = prefix_shift(lists, CtrlT::kPrefix);
+  const int n = (int)(lists >> shift) + 1;                   // samples 0, 2^shift, ..., the last one <= lists
+  for (int i = threadIdx.x; i < n; i += nthreads) c.prefix_cache[i] = tile_prefix[(int64_t)i << shift];
+}
+// last l in [0, lists) with tile_prefix[l] <= i (i is a routed item: tile_prefix[lists] > i)
+template <typename CtrlT>
+__device__ __forceinline__ int find_list(const CtrlT& c, const int32_t* __restrict__ tile_prefix, int64_t lists, int i) {
+  const int shift = prefix_shift(lists, CtrlT::kPrefix);
+  int lo = 0, hi = (int)(lists >> shift) + 1;                // samples: last k with cache[k] <= i
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (c.prefix_cache[mid] <= i) lo = mid; else hi = mid;
+  }
+  int l = lo << shift;
+  int r = min(l + (1 << shift), (int)lists);                 // tile_prefix[r] > i, or r == lists
+  while (r - l > 1) {
+    const int mid = (l + r) >> 1;
+    if (__ldg(tile_prefix + mid) <= i) l = mid; else r = mid;
+  }
+  return l;
+}
+
 // Runs in one spare warp while the other warps work on the current item: draws the
 // next item from the global queue (skipping empty own-chunk tiles), decodes it and
 // resolves its rows (output entry and Q row offset) into prefetch slot `slot`.
@@ -116,8 +148,8 @@ __device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs&
     if (lane == 0) idx = c.abort ? 0x7fffffff : atomicAdd(a.work_counter, 1);
     idx = __shfl_sync(0xffffffffu, idx, 0);
     if (idx >= n_items) { done = 1; break; }
-    it = decode_item(p, idx, n_routed, kItemRows, a.cu, a.list_counts, a.list_offsets,
-                     p.lists < CtrlT::kPrefix ? c.prefix_cache : a.tile_prefix);
+    it = decode_item(p, idx, n_routed, kItemRows, a.cu, a.list_counts, a.list_offsets, a.tile_prefix,
+                     idx < n_routed ? find_list(c, a.tile_prefix, p.lists, idx) : 0);
     if (it.valid) break;
   }
   if (lane == 0) { c.item[slot] = it; c.done[slot] = done; }
@@ -327,8 +359,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     tmem_alloc(smem_u32(&c.tmem_slot), kTmemCols);
     tmem_relinquish();
   }
-  if (p.hist > 0 && p.lists < kPrefixCache)
-    for (int i = threadIdx.x; i <= (int)p.lists; i += kThreads) c.prefix_cache[i] = a.tile_prefix[i];
+  if (p.hist > 0) fill_prefix_cache(c, a.tile_prefix, p.lists, kThreads);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -634,8 +665,7 @@ attend_tc5_wide_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_
     tmem_alloc(smem_u32(&c.tmem_slot), kTmemCols);
     tmem_relinquish();
   }
-  if (p.hist > 0 && p.lists < kPrefixCache)
-    for (int i = threadIdx.x; i <= (int)p.lists; i += kThreads) c.prefix_cache[i] = a.tile_prefix[i];
+  if (p.hist > 0) fill_prefix_cache(c, a.tile_prefix, p.lists, kThreads);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -936,8 +966,7 @@ attend_tc5_small_kernel(const Params p, const __grid_constant__ CUtensorMap tmap
     tmem_alloc(smem_u32(&c.tmem_slot), kCols);
     tmem_relinquish();
   }
-  if (p.hist > 0 && p.lists < kSmallPrefix)
-    for (int i = threadIdx.x; i <= (int)p.lists; i += kSmallThreads) c.prefix_cache[i] = a.tile_prefix[i];
+  if (p.hist > 0) fill_prefix_cache(c, a.tile_prefix, p.lists, kSmallThreads);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();

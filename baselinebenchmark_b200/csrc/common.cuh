@@ -106,20 +106,25 @@ struct Item {
 
 // Decode work item `i`.  Routed items come first (list-major, tiles of
 // `tile_rows` rows), own-chunk items follow with the longest tiles first.
+// `list_hint` >= 0: the list of a routed item, found by the caller (the last l with
+// tile_prefix[l] <= i); otherwise it is searched for in tile_prefix.
 __device__ __forceinline__ Item decode_item(const Params& p, int i, int n_routed, int tile_rows,
                                             const int32_t* __restrict__ cu,
                                             const int32_t* __restrict__ list_counts,
                                             const int32_t* __restrict__ list_offsets,
-                                            const int32_t* __restrict__ tile_prefix) {
+                                            const int32_t* __restrict__ tile_prefix, int list_hint = -1) {
   Item it;
   it.valid = 0;
   if (i < n_routed) {
-    int lo = 0, hi = (int)p.lists;           // last l with tile_prefix[l] <= i
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (tile_prefix[mid] <= i) lo = mid; else hi = mid;
+    int l = list_hint;
+    if (l < 0) {
+      int lo = 0, hi = (int)p.lists;         // last l with tile_prefix[l] <= i
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (tile_prefix[mid] <= i) lo = mid; else hi = mid;
+      }
+      l = lo;
     }
-    const int l = lo;
     const int tile = i - tile_prefix[l];
     const int slot = l / p.Hkv;
     const int b = slot / p.mc, j = slot - b * p.mc;
