@@ -315,18 +315,18 @@ CP_TOKENS, CP_TOPK, CP_WINDOWS = 1048576, 16, 8
 def context_block(steps, warmup, rank, world, local, dev, dist):
     """BASELINE.json configs[4]: one sequence of 1048576 tokens, 32/8 heads, chunk 4096, top-k 16,
     as 8 contiguous query windows of 131072 tokens.  With 8 GPUs every rank owns one window and
-    its K/V rows (with 4: two windows each) and a step = exchange of K and V over NCCL + the
-    operator on the rank's windows.  With 1 or 2 GPUs the partial results of more than two
-    windows do not fit next to a full copy of Q, so each rank runs its 8 / N windows in turn on
-    K and V that are resident in full (no exchange): the same work, which gives the 1 -> 8 curve
-    its base.  Returns the dict for `also` (all ranks must call; rank 0 gets the numbers)."""
+    its K/V rows (with 4 or 2: two or four windows each) and a step = exchange of K and V over
+    NCCL + the operator on the rank's windows.  With 1 GPU the partial results of all eight
+    windows do not fit, so the rank runs the windows in turn on K and V that are resident in
+    full (no exchange): the same work, which gives the 1 -> 8 curve its base.  Returns the dict
+    for `also` (all ranks must call; rank 0 gets the numbers)."""
     from baselinebenchmark_b200 import sharding
     per_rank = CP_WINDOWS // world if world <= CP_WINDOWS else 0
     if per_rank == 0:
         return None
     win = CP_TOKENS // CP_WINDOWS
     tq = win * per_rank
-    exchange = world >= 4
+    exchange = world >= 2
     q, k_loc, v_loc, _ = make_inputs_device([tq], HQ, HKV, D, CHUNK, 46000 + rank, dev)
     out = torch.empty_like(q)
     if exchange:
@@ -394,8 +394,8 @@ def context_block(steps, warmup, rank, world, local, dev, dist):
                     f"4096, top-k 16, causal; 8 query windows of 131072 tokens, {per_rank} per GPU on {world} GPU(s); "
                     + ("through moba_cp_forward: chunk means exchanged, then K and V rows of the earlier ranks "
                        "received over NCCL on a side stream while the gating runs" if exchange else
-                       "K and V resident in full on every GPU, no exchange (too few GPUs to hold a rank's partial "
-                       "results next to a split context)"),
+                       "K and V resident in full, no exchange; the windows run in turn (the partial results of all "
+                       "eight at once would not fit)"),
         "n_gpus": world, "steps": steps, "warmup": warmup, "scaling": "strong",
         "tokens_per_s": CP_TOKENS / (step_ms * 1e-3), "ms_per_step": step_ms,
         "tflops_effective": flops / (step_ms * 1e-3) / 1e12,
