@@ -538,7 +538,7 @@ int moba_backward(const moba_problem_t* p, const void* q, const void* k, const v
   const int64_t qt = (int64_t)r.Hq * r.D, kt = (int64_t)r.Hkv * r.D, hd = r.D;
   // the gradient kernels run on the tcgen05 path where the forward's dense stage does, on
   // mma.sync otherwise
-  const bool dq_tc5 = p->attend_impl == MOBA_ATTEND_TCGEN05 && (r.D == 64 || r.D == 128);
+  const bool dq_tc5 = p->attend_impl == MOBA_ATTEND_TCGEN05 && r.D <= 128;
   cudaError_t e;
   if ((e = cudaMemsetAsync(w.list_counts, 0, w.zero_bytes, st)) != cudaSuccess) return (int)e;
   if (r.hist > 0) {

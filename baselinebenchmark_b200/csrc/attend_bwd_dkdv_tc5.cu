@@ -315,7 +315,7 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
       // ------------------------------------------------ K and V of the unit
       if (lane == 0) {
         const uint32_t bar = smem_u32(&c.kv_full);
-        mbar_expect_tx(bar, 2 * (D / 64) * kKvBlockBytes);
+        mbar_expect_tx(bar, 2 * ((D + 63) / 64) * kKvBlockBytes);
         tma_load_3d(sK, &tmap_k, bar, 0, u.kvh, u.key0);
         if (D > 64) tma_load_3d(sK + kKvBlockBytes, &tmap_k, bar, 64, u.kvh, u.key0);
         tma_load_3d(sV, &tmap_v, bar, 0, u.kvh, u.key0);
@@ -458,11 +458,11 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         if ((warp & 3) == 0 && lane == 0) {
           const uint32_t bar = smem_u32(&c.row_full[sj]);
           const uint32_t qb = sRows + sj * 2 * kRowTileBytes, gb = qb + kRowTileBytes;
-          mbar_expect_tx(bar, 2 * (D / 64) * kRowBlockBytes);
+          mbar_expect_tx(bar, 2 * ((D + 63) / 64) * kRowBlockBytes);
           if (j < u.routed_steps) {
             const int pos = (int)u.list_off + j * kStep;
 #pragma unroll
-            for (int blk = 0; blk < D / 64; ++blk) {
+            for (int blk = 0; blk < (D + 63) / 64; ++blk) {
               tma_load_3d(qb + blk * kRowBlockBytes, &tmap_qp, bar, blk * 64, 0, pos);
               tma_load_3d(gb + blk * kRowBlockBytes, &tmap_gp, bar, blk * 64, 0, pos);
             }
@@ -471,7 +471,7 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
             const int hl = o / u.own_steps, ot = o - hl * u.own_steps;
             const int tok = u.key0 + ot * kStep, head = u.kvh * p.G + hl;
 #pragma unroll
-            for (int blk = 0; blk < D / 64; ++blk) {
+            for (int blk = 0; blk < (D + 63) / 64; ++blk) {
               tma_load_3d(qb + blk * kRowBlockBytes, &tmap_q, bar, blk * 64, head, tok);
               tma_load_3d(gb + blk * kRowBlockBytes, &tmap_g, bar, blk * 64, head, tok);
             }
@@ -599,7 +599,7 @@ cudaError_t launch_bwd_dkdv_tc5(const Params& p, const __nv_bfloat16* q, const _
                                 const int32_t* list_counts, const int32_t* list_offsets, const int32_t* row_list,
                                 const float* lse2, const float* delta, __nv_bfloat16* dk, __nv_bfloat16* dv,
                                 __nv_bfloat16* packed, int32_t* work_counter, int32_t* status, cudaStream_t st) {
-  if (p.D != 64 && p.D != 128) return cudaErrorInvalidValue;
+  if (p.D != 64 && p.D != 96 && p.D != 128) return cudaErrorInvalidValue;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -609,6 +609,7 @@ cudaError_t launch_bwd_dkdv_tc5(const Params& p, const __nv_bfloat16* q, const _
   __nv_bfloat16* gp = packed + cap * p.D;
   if (p.hist > 0) {
     if (p.D == 128) pack_rows_kernel<128><<<sms * 8, 256, 0, st>>>(p, q, dout, list_offsets, row_list, qp, gp);
+    else if (p.D == 96) pack_rows_kernel<96><<<sms * 8, 256, 0, st>>>(p, q, dout, list_offsets, row_list, qp, gp);
     else pack_rows_kernel<64><<<sms * 8, 256, 0, st>>>(p, q, dout, list_offsets, row_list, qp, gp);
     const cudaError_t pe = cudaGetLastError();
     if (pe != cudaSuccess) return pe;
@@ -623,6 +624,7 @@ cudaError_t launch_bwd_dkdv_tc5(const Params& p, const __nv_bfloat16* q, const _
       !make_tile_map(&mgp, half, p.D, gp, cap, 1, p.D, p.D, 1, kStep))
     return cudaErrorNotSupported;
   auto kernel = p.D == 128 ? (p.fp16 ? bwd_dkdv_tc5_kernel<true, 128> : bwd_dkdv_tc5_kernel<false, 128>)
+              : p.D == 96  ? (p.fp16 ? bwd_dkdv_tc5_kernel<true, 96> : bwd_dkdv_tc5_kernel<false, 96>)
                            : (p.fp16 ? bwd_dkdv_tc5_kernel<true, 64> : bwd_dkdv_tc5_kernel<false, 64>);
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   if (e != cudaSuccess) return e;

@@ -338,7 +338,7 @@ bwd_dq_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
             const uint32_t s = g % kKStages, par = ((g / kKStages) & 1) ^ 1;
             if (!mbar_wait(smem_u32(&c.k_empty[s]), par)) return false;
             const uint32_t bar = smem_u32(&c.k_full[s]);
-            mbar_expect_tx(bar, (D / 64) * kKvBlockBytes);
+            mbar_expect_tx(bar, ((D + 63) / 64) * kKvBlockBytes);
             tma_load_3d(sK + s * kKvTileBytes, &tmap_k, bar, 0, w.kv_head, tok);
             if (D > 64) tma_load_3d(sK + s * kKvTileBytes + kKvBlockBytes, &tmap_k, bar, 64, w.kv_head, tok);
           }
@@ -346,7 +346,7 @@ bwd_dq_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
             const uint32_t s = g & 1, par = ((g >> 1) & 1) ^ 1;
             if (!mbar_wait(smem_u32(&c.v_empty[s]), par)) return false;
             const uint32_t bar = smem_u32(&c.v_full[s]);
-            mbar_expect_tx(bar, (D / 64) * kKvBlockBytes);
+            mbar_expect_tx(bar, ((D + 63) / 64) * kKvBlockBytes);
             tma_load_3d(sV + s * kKvTileBytes, &tmap_v, bar, 0, w.kv_head, tok);
             if (D > 64) tma_load_3d(sV + s * kKvTileBytes + kKvBlockBytes, &tmap_v, bar, 64, w.kv_head, tok);
           }
@@ -521,12 +521,13 @@ cudaError_t launch_bwd_dq_tc5(const Params& p, const __nv_bfloat16* q, const __n
                               const int32_t* list_counts, const int32_t* list_offsets, const int32_t* tile_prefix,
                               const int32_t* row_list, const float* lse2, const float* delta, float* partial_dq,
                               int32_t* work_counter, int32_t* status, cudaStream_t st) {
-  if (p.D != 64 && p.D != 128) return cudaErrorInvalidValue;
+  if (p.D != 64 && p.D != 96 && p.D != 128) return cudaErrorInvalidValue;
   CUtensorMap mk, mv;
   if (!make_kv_map(&mk, p.fp16 != 0, p.D, k, p.T, p.Hkv, p.sk_t, p.sk_h, kBN) ||
       !make_kv_map(&mv, p.fp16 != 0, p.D, v, p.T, p.Hkv, p.sv_t, p.sv_h, kBN))
     return cudaErrorNotSupported;
   auto kernel = p.D == 128 ? (p.fp16 ? bwd_dq_tc5_kernel<true, 128> : bwd_dq_tc5_kernel<false, 128>)
+              : p.D == 96  ? (p.fp16 ? bwd_dq_tc5_kernel<true, 96> : bwd_dq_tc5_kernel<false, 96>)
                            : (p.fp16 ? bwd_dq_tc5_kernel<true, 64> : bwd_dq_tc5_kernel<false, 64>);
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   if (e != cudaSuccess) return e;

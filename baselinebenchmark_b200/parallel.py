@@ -163,8 +163,7 @@ def moba_backward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, o
     """Gradients (dq, dk, dv) of the operator for the output gradient `dout`, given what
     `moba_forward(..., return_lse=True, return_selected=True)` returned
     (MixedAttention.backward, parallel.py:149-250: merged LSE and output, constant selection).
-    `attend_impl` picks the dq and dk/dv kernels: tcgen05 at head_dim 64 and 128 by default,
-    mma.sync otherwise (head_dim 96, or when asked for)."""
+    `attend_impl` picks the dq and dk/dv kernels: tcgen05 by default, mma.sync when asked for."""
     _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)
     if q.shape[2] > 128:
         raise NotImplementedError("the backward is built for head_dim <= 128")

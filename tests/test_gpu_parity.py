@@ -536,6 +536,7 @@ BACKWARD_CASES = [
     ("bwd_mqa_k8", 128, (900,), 8, 1, 64, 8),
     ("bwd_d64", 64, (700, 333), 8, 2, 128, 4),
     ("bwd_d96", 96, (640,), 4, 4, 64, 3),
+    ("bwd_d96_gqa", 96, (900, 257), 8, 2, 128, 4),
 ]
 
 
@@ -614,7 +615,7 @@ def test_backward_config2_dq_sampled_and_dkdv_finite():
 
 
 # the last case has 2502 route lists: more than the dq kernel keeps of the tile prefix in shared memory
-AGREE_CASES = [c for c in BACKWARD_CASES if c[1] in (64, 128)] + [("bwd_many_lists", 64, (20010,), 2, 2, 16, 4)]
+AGREE_CASES = BACKWARD_CASES + [("bwd_many_lists", 64, (20010,), 2, 2, 16, 4)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
