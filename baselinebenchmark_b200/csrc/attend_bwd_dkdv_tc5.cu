@@ -12,12 +12,13 @@
 // Key-stationary: a unit is 128 keys of one (chunk, kv head); its K and V tiles stay in shared
 // memory (TMA) and dK, dV stay in tensor memory while the CTA visits every query row that
 // attends the keys - the routed list of the chunk, then the chunk's own rows of every query
-// head of the group - in steps of 64 rows brought into a four-stage ring by TMA.  The rows of
-// a routed list are scattered over q and dO, so a pre-pass (pack_rows_kernel) first copies
-// them, in list order, into two packed arrays [entries, D]: a step of a routed list is then
-// a 64-row box of those, a step of own-chunk rows a 64-token box of q / dO themselves.  (A
-// list is read once per 128-key tile of its chunk; gathered with cp.async every time, the
-// 16-byte copies kept the load/store pipe busier than the tensor pipe.)  Per step
+// head of the group - in steps of 64 rows brought into a four-stage ring.  A step of own-chunk
+// rows is a 64-token box of q / dO (TMA).  The rows of a routed list are scattered over q and
+// dO and are read once per 128-key tile of the chunk: with chunks of kPackMinTiles tiles or
+// more a pre-pass (pack_rows_kernel) copies them, in list order, into two packed arrays
+// [entries, D] and a step is a 64-row box of those (gathered with cp.async every time, the
+// 16-byte copies kept the load/store pipe busier than the tensor pipe); with shorter chunks the
+// copy would cost more than it saves and the rows are gathered with cp.async.  Per step
 //   S^T  = K . Q^T      (128 keys x 64 rows, operands in shared memory)
 //   dP^T = V . dO^T     (128 x 64)
 //   one thread per key turns them into P^T and dS^T (input dtype) in tensor memory
@@ -29,7 +30,8 @@
 // Warp roles (384 threads): warp 0 lane 0 loads K/V by TMA, warp 1 issues the MMAs and owns
 // the TMEM allocation, warps 2-3 describe the rows of the coming steps (LSE, delta, token), warps
 // 4-7 handle the even steps (S buffer 0) and write dK, warps 8-11 the odd steps (S buffer 1) and
-// write dV; after a step one thread of the group requests the Q / dO boxes of the step three ahead.
+// write dV; after a step the group brings in the Q / dO rows of the step three ahead (one thread
+// requests the boxes, or all 128 gather).
 // TMEM columns: buffer X: S^T 128X..+63 (P^T, 16-bit, over the first 32), dP^T 128X+64..+127
 // (dS^T over its first 32); dK 256.., dV 384...
 // Every wait is bounded; a wait that gives up sets a status word, the CTAs stop drawing units
@@ -52,6 +54,10 @@ constexpr int kThreads = 384;
 constexpr int kKeys = 128;                    // keys per unit
 constexpr int kStep = 64;                     // rows per step
 constexpr int kStages = 4;
+// Chunks of at least this many 128-key tiles have their routed rows packed.  Measured backward of
+// 32768 tokens x 32/8 heads, packed against gathered: 4 tiles 21.7 / 20.1 ms, 8 tiles 17.0 / 17.2,
+// 16 tiles 26.1 / 27.3, 32 tiles (config 2) 33.5 / 35.8.
+constexpr int kPackMinTiles = 8;
 constexpr int kKvBlockBytes = kKeys * 64 * 2; // [128 keys][64 dims]
 constexpr int kKvTileBytes = 2 * kKvBlockBytes;
 constexpr int kRowBlockBytes = kStep * 64 * 2;  // [64 rows][64 dims]
@@ -74,6 +80,8 @@ struct Ctrl {
   alignas(16) float2 meta[kStages][kStep];     // {lse * log2 e, delta} of the row; {0, 0}: no row
   alignas(16) int32_t tok[kStages][kStep];                 // query token of an own-chunk row (causal limit), else INT_MAX
   int32_t ent[4][kStep];                       // routed-list entries of the steps ahead (0: no row)
+  int64_t qoff[kStages][kStep];                // gathered routed rows: element offset of the row in q, -1: no row
+  int32_t grow[kStages][kStep];                // ... and row index t * Hq + h
 };
 
 constexpr size_t kSmemBytes = 1024 + 2 * kKvTileBytes + kStages * 2 * kRowTileBytes + sizeof(Ctrl);
@@ -92,6 +100,7 @@ struct KernelArgs {
   __nv_bfloat16* dv;
   int32_t* work_counter;
   int32_t* status;
+  int packed;                                  // routed rows come from the packed arrays (TMA), else gathered
 };
 
 // What every thread derives from the unit index.
@@ -274,7 +283,7 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     mbar_init(smem_u32(&c.kv_full), 1);
     mbar_init(smem_u32(&c.acc_full), 1);
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(smem_u32(&c.row_full[i]), 64 + 1);         // lse / delta of 64 rows + the thread that requests the boxes
+      mbar_init(smem_u32(&c.row_full[i]), 64 + kKeys);     // lse / delta of 64 rows + the 128 threads of the group that copies
       mbar_init(smem_u32(&c.row_empty[i]), 1);
       mbar_init(smem_u32(&c.meta_full[i]), 64);
     }
@@ -411,6 +420,15 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         TR_T0(t_i);
         {
           c.tok[st][r] = tokq;
+          if (!a.packed && i < u.routed_steps) {
+            int64_t off = -1;
+            if (row >= 0) {
+              const int t = row / p.Hq;
+              off = (int64_t)t * p.sq_t + (int64_t)(row - t * p.Hq) * p.sq_h;
+            }
+            c.qoff[st][r] = off;
+            c.grow[st][r] = row;
+          }
           // A place of the step without a row still holds data in the stage (the box goes on into
           // the next list, the next chunk, or the zero rows behind the last list): an LSE of
           // +inf makes its p = 2^(s - inf) = 0, and with it its share of dV and dS.
@@ -455,7 +473,27 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         if (j >= u.steps) return true;
         const uint32_t gj = g0 + j, sj = gj & 3;
         if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&c.meta_full[sj]), (gj >> 2) & 1))) return false;
-        if ((warp & 3) == 0 && lane == 0) {
+        if (!a.packed && j < u.routed_steps) {
+          // a warp takes 16 rows of Q and the same 16 rows of dO; an instruction covers whole rows
+          // (D / 8 lanes per row), so every 32-byte sector it asks for is used in full
+          constexpr int kChunks = D / 8, kRowsPerInstr = 32 / kChunks;
+          const int ch = lane % kChunks;
+          const uint32_t qb = sRows + sj * 2 * kRowTileBytes + (ch >> 3) * kRowBlockBytes, gb = qb + kRowTileBytes;
+          if (lane / kChunks < kRowsPerInstr) {                // head dim 96: 24 of the 32 lanes copy
+#pragma unroll
+            for (int it = 0; it < 16 / kRowsPerInstr; ++it) {
+              const int rr = (warp & 3) * 16 + it * kRowsPerInstr + lane / kChunks;
+              const int64_t off = c.qoff[sj][rr];
+              const bool valid = off >= 0;
+              const uint32_t dst = (uint32_t)(rr * 128 + (((ch & 7) ^ (rr & 7)) << 4));
+              cp_async16(qb + dst, a.q + (valid ? off : 0) + ch * 8, valid);
+              cp_async16(gb + dst, a.dout + (valid ? (int64_t)c.grow[sj][rr] * D : 0) + ch * 8, valid);
+            }
+          }
+          cp_async_arrive(smem_u32(&c.row_full[sj]));
+        } else if ((warp & 3) != 0 || lane != 0) {
+          mbar_arrive(smem_u32(&c.row_full[sj]));
+        } else {
           const uint32_t bar = smem_u32(&c.row_full[sj]);
           const uint32_t qb = sRows + sj * 2 * kRowTileBytes, gb = qb + kRowTileBytes;
           mbar_expect_tx(bar, 2 * ((D + 63) / 64) * kRowBlockBytes);
@@ -510,6 +548,7 @@ bwd_dkdv_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
         ok = copy_rows(i + 3);
         if (threadIdx.x == 128) TR_ADD(a, 10, t_w);
       }
+      cp_async_wait_all();
       TR_T0(t_a);
       if (ok) ok = mbar_wait(smem_u32(&c.acc_full), nu & 1);
       ok = __all_sync(0xffffffffu, ok);
@@ -607,7 +646,9 @@ cudaError_t launch_bwd_dkdv_tc5(const Params& p, const __nv_bfloat16* q, const _
   const int64_t cap = (int64_t)p.hist * p.rows + kStep;
   __nv_bfloat16* qp = packed;
   __nv_bfloat16* gp = packed + cap * p.D;
-  if (p.hist > 0) {
+  // chunks of at least this many 128-key tiles: their lists are read often enough to pay for packing
+  const int use_packed = (p.C + kKeys - 1) / kKeys >= kPackMinTiles ? 1 : 0;
+  if (p.hist > 0 && use_packed) {
     if (p.D == 128) pack_rows_kernel<128><<<sms * 8, 256, 0, st>>>(p, q, dout, list_offsets, row_list, qp, gp);
     else if (p.D == 96) pack_rows_kernel<96><<<sms * 8, 256, 0, st>>>(p, q, dout, list_offsets, row_list, qp, gp);
     else pack_rows_kernel<64><<<sms * 8, 256, 0, st>>>(p, q, dout, list_offsets, row_list, qp, gp);
@@ -628,7 +669,8 @@ cudaError_t launch_bwd_dkdv_tc5(const Params& p, const __nv_bfloat16* q, const _
                            : (p.fp16 ? bwd_dkdv_tc5_kernel<true, 64> : bwd_dkdv_tc5_kernel<false, 64>);
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   if (e != cudaSuccess) return e;
-  const KernelArgs args{q, dout, cu, list_counts, list_offsets, row_list, lse2, delta, dk, dv, work_counter, status};
+  const KernelArgs args{q, dout, cu, list_counts, list_offsets, row_list, lse2, delta, dk, dv, work_counter, status,
+                        use_packed};
   kernel<<<sms, kThreads, kSmemBytes, st>>>(p, mk, mv, mq, mg, mqp, mgp, args);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   poison_kernel<<<sms, 256, 0, st>>>(status, reinterpret_cast<uint32_t*>(dk), reinterpret_cast<uint32_t*>(dv),
