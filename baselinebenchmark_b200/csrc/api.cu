@@ -493,7 +493,6 @@ static int check_backward(const moba_problem_t* p) {
   const int rc = check_problem(p);
   if (rc != MOBA_OK) return rc;
   if (p->q_tokens != 0) return MOBA_E_UNSUPPORTED;           // whole problems only
-  if (p->head_dim > 128) return MOBA_E_UNSUPPORTED;
   const Params r = make_params(p);
   if (r.rows * r.NP >= ((int64_t)1 << 31)) return MOBA_E_UNSUPPORTED;
   return MOBA_OK;

@@ -162,10 +162,11 @@ __global__ void count_lists_kernel(Params p, const int32_t* __restrict__ selecte
 // ---------------------------------------------------------------------------
 template <int D>
 struct DqSmem {
+  static constexpr int kBuf = D > 128 ? 1 : 2;  // K / V tiles in flight (head dim 256: one, 192 KB of tiles)
   unsigned char q[kRows * row_bytes(D)];
   unsigned char g[kRows * row_bytes(D)];        // dO rows
-  unsigned char k[2][kBN * row_bytes(D)];
-  unsigned char v[2][kBN * row_bytes(D)];
+  unsigned char k[kBuf][kBN * row_bytes(D)];
+  unsigned char v[kBuf][kBN * row_bytes(D)];
   int64_t qoff[kRows];
   int64_t goff[kRows];
   float lse2[kRows];
@@ -261,12 +262,18 @@ bwd_dq_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const int row0 = warp * 16 + (lane >> 2);          // this thread's rows: row0 and row0 + 8
     const int qpos0 = it.tok0 + row0, qpos1 = qpos0 + 8;
 
+    constexpr int kBuf = DqSmem<D>::kBuf;
     for (int j = 0; j < ntiles; ++j) {
-      if (j + 1 < ntiles) load_kv_tile<D>(p, it.kv_tok0, it.kv_len, it.kv_head, j + 1, s, (j + 1) & 1, k, v);
-      cp_async_commit();
-      cp_async_wait<1>();
+      // two buffers: tile j + 1 travels while tile j is used; one: it is requested behind tile j
+      if (kBuf == 2) {
+        if (j + 1 < ntiles) load_kv_tile<D>(p, it.kv_tok0, it.kv_len, it.kv_head, j + 1, s, (j + 1) & 1, k, v);
+        cp_async_commit();
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
       __syncthreads();
-      const uint32_t kb = smem_u32(s.k[j & 1]), vb = smem_u32(s.v[j & 1]);
+      const uint32_t kb = smem_u32(s.k[j & (kBuf - 1)]), vb = smem_u32(s.v[j & (kBuf - 1)]);
       float sc[8][4], dp[8][4];
       rows_times_keys<kHalf, D>(sc, smem_u32(s.q), kb, warp, lane);
       rows_times_keys<kHalf, D>(dp, smem_u32(s.g), vb, warp, lane);
@@ -301,6 +308,10 @@ bwd_dq_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         }
       }
       __syncthreads();
+      if (kBuf == 1 && j + 1 < ntiles) {
+        load_kv_tile<D>(p, it.kv_tok0, it.kv_len, it.kv_head, j + 1, s, 0, k, v);
+        cp_async_commit();
+      }
     }
     cp_async_wait<0>();
     const int e0 = s.entry[row0], e1 = s.entry[row0 + 8];
@@ -557,6 +568,203 @@ bwd_dkdv_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bfloat
   }
 }
 
+// ---------------------------------------------------------------------------
+// dK, dV at head dim 256: the tiles of the kernel above would need 320 KB of shared memory.
+// One buffer of row tiles (no prefetch of the next one), and P / dS take the place of the K tile,
+// which - with the V tile - is fetched again for every row tile.
+// ---------------------------------------------------------------------------
+struct DkvWideSmem {
+  unsigned char k[kBN * 512];                   // K tile; in the second phase P (16 KB) and dS (16 KB)
+  unsigned char v[kBN * 512];
+  unsigned char q[kRows * 512];
+  unsigned char g[kRows * 512];
+  int64_t qoff[kRows];
+  int64_t goff[kRows];
+  float lse2[kRows];
+  float delta[kRows];
+  int32_t tok[kRows];
+  int32_t unit;
+};
+
+template <bool kHalf>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_dkdv_wide_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                     const __nv_bfloat16* __restrict__ v, const __nv_bfloat16* __restrict__ dout, int64_t do_t,
+                     int64_t do_h, const int32_t* __restrict__ cu, const int32_t* __restrict__ list_counts,
+                     const int32_t* __restrict__ list_offsets, const int32_t* __restrict__ row_list,
+                     const float* __restrict__ lse2, const float* __restrict__ delta,
+                     __nv_bfloat16* __restrict__ dk, int64_t dk_t, int64_t dk_h,
+                     __nv_bfloat16* __restrict__ dv, int64_t dv_t, int64_t dv_h, int32_t* __restrict__ work_counter) {
+  constexpr int D = 256;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  DkvWideSmem& s = *reinterpret_cast<DkvWideSmem*>(smem_raw);
+  unsigned char* ps = s.k;                       // P  [128 rows][64 keys], 16-bit, swizzled
+  unsigned char* ds = s.k + kRows * 128;         // dS
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float scale = rsqrtf((float)D);
+  const float sl2 = scale * kLog2e;
+  constexpr int kChunks = D / 8;
+  const int key_tiles = (p.C + kBN - 1) / kBN;
+  const int64_t n_units = p.lists * key_tiles;
+  const int mt = warp & 3, dh = warp >> 2;       // second phase: keys mt*16 .. +15, dims dh*128 .. +127
+
+  for (;;) {
+    __syncthreads();
+    if (threadIdx.x == 0) s.unit = atomicAdd(work_counter, 1);
+    __syncthreads();
+    const int64_t u = s.unit;
+    if (u >= n_units) break;
+    const int l = (int)(u / key_tiles), kt = (int)(u - (int64_t)l * key_tiles);
+    const int slot = l / p.Hkv, kvh = l - slot * p.Hkv;
+    const int b = slot / p.mc, jc = slot - b * p.mc;
+    const Slot sl = slot_of(cu, b, jc, p.C);
+    const int key0 = sl.start + kt * kBN;
+    if (key0 >= sl.end) continue;
+    const int nkeys = min(kBN, sl.end - key0);
+    float acc_k[D / 16][4], acc_v[D / 16][4];
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) {
+      acc_k[i][0] = acc_k[i][1] = acc_k[i][2] = acc_k[i][3] = 0.f;
+      acc_v[i][0] = acc_v[i][1] = acc_v[i][2] = acc_v[i][3] = 0.f;
+    }
+    const int n_routed = p.hist > 0 ? list_counts[l] : 0;
+    const int routed_tiles = (n_routed + kRows - 1) / kRows;
+    const int own_rows = sl.end - key0;
+    const int own_tiles = (own_rows + kRows - 1) / kRows;
+    const int total_tiles = routed_tiles + own_tiles * p.G;
+    for (int rt = 0; rt < total_tiles; ++rt) {
+      // rows of the tile
+      {
+        const bool routed = rt < routed_tiles;
+        int hl = 0, ot = 0;
+        if (!routed) { hl = (rt - routed_tiles) / own_tiles; ot = (rt - routed_tiles) - hl * own_tiles; }
+        for (int r = threadIdx.x; r < kRows; r += kThreads) {
+          int64_t row = -1;
+          int tokq = -1;
+          if (routed) {
+            const int i = rt * kRows + r;
+            if (i < n_routed) { row = row_list[list_offsets[l] + i] / p.NP; tokq = 0x7fffffff; }
+          } else {
+            const int tok = key0 + ot * kRows + r;
+            if (tok < sl.end) { row = (int64_t)(tok - p.win_lo) * p.Hq + (kvh * p.G + hl); tokq = tok; }
+          }
+          int64_t off = 0, goff = 0;
+          float l2 = INFINITY, dl = 0.f;
+          if (row >= 0) {
+            const int64_t t = row / p.Hq;
+            const int64_t h = row - t * p.Hq;
+            off = t * p.sq_t + h * p.sq_h;
+            goff = t * do_t + h * do_h;
+            l2 = lse2[row];
+            dl = delta[row];
+          }
+          s.qoff[r] = off; s.goff[r] = goff; s.lse2[r] = l2; s.delta[r] = dl; s.tok[r] = tokq;
+        }
+      }
+      __syncthreads();                                       // rows described; the second phase of the tile before is over
+      {
+        const uint32_t kb = smem_u32(s.k), vb = smem_u32(s.v), qb = smem_u32(s.q), gb = smem_u32(s.g);
+        for (int i = threadIdx.x; i < kBN * kChunks; i += kThreads) {
+          const int r = i / kChunks, ch = i - r * kChunks;
+          const bool ok = r < nkeys;
+          const int64_t tok = key0 + (ok ? r : 0);
+          cp_async16(kb + swz<D>(r, ch), k + tok * p.sk_t + (int64_t)kvh * p.sk_h + ch * 8, ok);
+          cp_async16(vb + swz<D>(r, ch), v + tok * p.sv_t + (int64_t)kvh * p.sv_h + ch * 8, ok);
+        }
+        for (int i = threadIdx.x; i < kRows * kChunks; i += kThreads) {
+          const int r = i / kChunks, ch = i - r * kChunks;
+          cp_async16(qb + swz<D>(r, ch), q + s.qoff[r] + ch * 8, s.tok[r] >= 0);
+          cp_async16(gb + swz<D>(r, ch), dout + s.goff[r] + ch * 8, s.tok[r] >= 0);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+      }
+      __syncthreads();
+      // phase 1: this warp's 16 rows x 64 keys of P and dS, kept in registers until every warp has read K and V
+      uint32_t wp[8][2], wd[8][2];
+      const int row0 = warp * 16 + (lane >> 2);
+      {
+        float sc[8][4], dp[8][4];
+        rows_times_keys<kHalf, D>(sc, smem_u32(s.q), smem_u32(s.k), warp, lane);
+        rows_times_keys<kHalf, D>(dp, smem_u32(s.g), smem_u32(s.v), warp, lane);
+        const float l0 = s.lse2[row0], l1 = s.lse2[row0 + 8];
+        const float d0 = s.delta[row0], d1 = s.delta[row0 + 8];
+        const int t0 = s.tok[row0], t1 = s.tok[row0 + 8];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+          float pv[4], dsv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = nt * 8 + 2 * (lane & 3) + (e & 1);
+            const int tq = (e & 2) ? t1 : t0;
+            const bool ok = key < nkeys && key0 + key <= tq;
+            pv[e] = ok ? exp2f(sc[nt][e] * sl2 - ((e & 2) ? l1 : l0)) : 0.f;
+            dsv[e] = pv[e] * (dp[nt][e] - ((e & 2) ? d1 : d0));
+          }
+          wp[nt][0] = pack2_16<kHalf>(pv[0], pv[1]);
+          wp[nt][1] = pack2_16<kHalf>(pv[2], pv[3]);
+          wd[nt][0] = pack2_16<kHalf>(dsv[0], dsv[1]);
+          wd[nt][1] = pack2_16<kHalf>(dsv[2], dsv[3]);
+        }
+      }
+      __syncthreads();                                       // K is no longer needed: P and dS take its place
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const uint32_t c0 = (uint32_t)(((nt ^ row0) & 7) << 4) + 4 * (lane & 3);
+        const uint32_t c1 = (uint32_t)(((nt ^ (row0 + 8)) & 7) << 4) + 4 * (lane & 3);
+        *reinterpret_cast<uint32_t*>(ps + row0 * 128 + c0) = wp[nt][0];
+        *reinterpret_cast<uint32_t*>(ps + (row0 + 8) * 128 + c1) = wp[nt][1];
+        *reinterpret_cast<uint32_t*>(ds + row0 * 128 + c0) = wd[nt][0];
+        *reinterpret_cast<uint32_t*>(ds + (row0 + 8) * 128 + c1) = wd[nt][1];
+      }
+      __syncthreads();
+      // phase 2: dV += P^T . dO,  dK += dS^T . Q  over the 128 rows of the tile
+      {
+        const uint32_t pb = smem_u32(ps), sb = smem_u32(ds), qb = smem_u32(s.q), gb = smem_u32(s.g);
+#pragma unroll
+        for (int ks = 0; ks < kRows / 16; ++ks) {
+          const int ar = ks * 16 + (lane & 7) + ((lane >> 4) & 1) * 8;
+          const int ach = 2 * mt + ((lane >> 3) & 1);
+          const uint32_t aoff = (uint32_t)(ar * 128 + (((ach ^ ar) & 7) << 4));
+          uint32_t pa[4], sa[4];
+          ldsm_x4_t(pb + aoff, pa[0], pa[1], pa[2], pa[3]);
+          ldsm_x4_t(sb + aoff, sa[0], sa[1], sa[2], sa[3]);
+          const int br = ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+          for (int dpi = 0; dpi < D / 32; ++dpi) {
+            const int ch = dh * (D / 16) + 2 * dpi + (lane >> 4);
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_t(gb + swz<D>(br, ch), b0, b1, b2, b3);
+            mma_16<kHalf>(acc_v[2 * dpi], pa, b0, b1);
+            mma_16<kHalf>(acc_v[2 * dpi + 1], pa, b2, b3);
+            ldsm_x4_t(qb + swz<D>(br, ch), b0, b1, b2, b3);
+            mma_16<kHalf>(acc_k[2 * dpi], sa, b0, b1);
+            mma_16<kHalf>(acc_k[2 * dpi + 1], sa, b2, b3);
+          }
+        }
+      }
+      // the barrier at the top of the next tile (after its rows are described) ends this phase
+    }
+    const int kr0 = mt * 16 + (lane >> 2), kr1 = kr0 + 8;
+#pragma unroll
+    for (int nt = 0; nt < D / 16; ++nt) {
+      const int dim = dh * (D / 2) + nt * 8 + 2 * (lane & 3);
+      if (kr0 < nkeys) {
+        const int64_t tok = key0 + kr0;
+        *reinterpret_cast<uint32_t*>(dk + tok * dk_t + (int64_t)kvh * dk_h + dim) =
+            pack2_16<kHalf>(acc_k[nt][0] * scale, acc_k[nt][1] * scale);
+        *reinterpret_cast<uint32_t*>(dv + tok * dv_t + (int64_t)kvh * dv_h + dim) = pack2_16<kHalf>(acc_v[nt][0], acc_v[nt][1]);
+      }
+      if (kr1 < nkeys) {
+        const int64_t tok = key0 + kr1;
+        *reinterpret_cast<uint32_t*>(dk + tok * dk_t + (int64_t)kvh * dk_h + dim) =
+            pack2_16<kHalf>(acc_k[nt][2] * scale, acc_k[nt][3] * scale);
+        *reinterpret_cast<uint32_t*>(dv + tok * dv_t + (int64_t)kvh * dv_h + dim) = pack2_16<kHalf>(acc_v[nt][2], acc_v[nt][3]);
+      }
+    }
+  }
+}
+
 template <typename K>
 cudaError_t set_smem(K kernel, size_t bytes) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -611,6 +819,7 @@ cudaError_t launch_bwd_dq(const Params& p, const __nv_bfloat16* q, const __nv_bf
     case 64:  return p.fp16 ? MOBA_DQ(true, 64) : MOBA_DQ(false, 64);
     case 96:  return p.fp16 ? MOBA_DQ(true, 96) : MOBA_DQ(false, 96);
     case 128: return p.fp16 ? MOBA_DQ(true, 128) : MOBA_DQ(false, 128);
+    case 256: return p.fp16 ? MOBA_DQ(true, 256) : MOBA_DQ(false, 256);
     default: return cudaErrorInvalidValue;
   }
 #undef MOBA_DQ
@@ -652,6 +861,15 @@ cudaError_t launch_bwd_dkdv(const Params& p, const __nv_bfloat16* q, const __nv_
     case 64:  return p.fp16 ? MOBA_DKDV(true, 64) : MOBA_DKDV(false, 64);
     case 96:  return p.fp16 ? MOBA_DKDV(true, 96) : MOBA_DKDV(false, 96);
     case 128: return p.fp16 ? MOBA_DKDV(true, 128) : MOBA_DKDV(false, 128);
+    case 256: {
+      auto kernel = p.fp16 ? bwd_dkdv_wide_kernel<true> : bwd_dkdv_wide_kernel<false>;
+      const cudaError_t e = set_smem(kernel, sizeof(DkvWideSmem));
+      if (e != cudaSuccess) return e;
+      kernel<<<sm_count(), kThreads, sizeof(DkvWideSmem), st>>>(p, q, k, v, dout, do_t, do_h, cu, list_counts,
+                                                              list_offsets, row_list, lse2, delta, dk, dk_t, dk_h, dv,
+                                                              dv_t, dv_h, work_counter);
+      return cudaGetLastError();
+    }
     default: return cudaErrorInvalidValue;
   }
 #undef MOBA_DKDV

@@ -188,8 +188,6 @@ def run_gating_case(case: Case, args, call):
 def run_backward_case(case: Case, args, call):
     """Latency of `moba_backward` alone (gradients of the training path, parallel.py:149-250)
     on what one forward with LSE and selection returned; same timing protocol."""
-    if case.head_dim > 128:
-        return {**asdict(case), "status": "skipped", "reason": "backward: head_dim <= 128"}
     q = call[0]
     with torch.inference_mode():
         out, lse, sel = moba_forward(*call, return_lse=True, return_selected=True)

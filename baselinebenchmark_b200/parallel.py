@@ -165,8 +165,6 @@ def moba_backward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, o
     (MixedAttention.backward, parallel.py:149-250: merged LSE and output, constant selection).
     `attend_impl` picks the dq and dk/dv kernels: tcgen05 by default, mma.sync when asked for."""
     _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)
-    if q.shape[2] > 128:
-        raise NotImplementedError("the backward is built for head_dim <= 128")
     dout = dout.contiguous()
     if attend_impl is None:
         attend_impl = default_attend_impl(q.shape[2])
@@ -213,12 +211,10 @@ def parallel_moba(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens:
 
     Like the reference (parallel.py:447-456) the inference dataflow is taken when autograd is
     off; with autograd on and an input that requires grad the call goes through an
-    autograd.Function whose backward runs `moba_backward` (head_dim <= 128).
+    autograd.Function whose backward runs `moba_backward`.
     """
     if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
         _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)
-        if q.shape[2] > 128:
-            raise NotImplementedError("the training path is built for head_dim <= 128")
         return _MobaFunction.apply(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)
     return moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)[0]
 

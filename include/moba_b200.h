@@ -285,8 +285,8 @@ int moba_route_static(const moba_problem_t* p, const void* q, const void* k, con
  * chunk selection is a constant.  No atomic accumulation: dq is bit-identical run to run,
  * dk and dv up to the order in which the rows of a routed list are added.  With
  * attend_impl = MOBA_ATTEND_TCGEN05 the dq and dk/dv kernels run on tcgen05 (accumulators in
- * tensor memory), with MOBA_ATTEND_MMA_SYNC on mma.sync.
- * Whole problems only (q_tokens == 0), head_dim <= 128, T*Hq*(hist+1) < 2^31; otherwise
+ * tensor memory) up to head_dim 128; with MOBA_ATTEND_MMA_SYNC, and at head_dim 256, on mma.sync.
+ * Whole problems only (q_tokens == 0), T*Hq*(hist+1) < 2^31; otherwise
  * MOBA_E_UNSUPPORTED.  The workspace holds, besides the route lists, one fp32 [D] slot per
  * (row, partial) for dQ and the Q / dO rows of the routed lists packed in list order. */
 int moba_backward_workspace_size(const moba_problem_t* p, size_t* bytes);

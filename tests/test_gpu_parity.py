@@ -537,6 +537,8 @@ BACKWARD_CASES = [
     ("bwd_d64", 64, (700, 333), 8, 2, 128, 4),
     ("bwd_d96", 96, (640,), 4, 4, 64, 3),
     ("bwd_d96_gqa", 96, (900, 257), 8, 2, 128, 4),
+    ("bwd_d256", 256, (700, 333), 4, 2, 128, 3),              # mma.sync kernels whichever implementation is asked for
+    ("bwd_d256_mqa_c512", 256, (1500,), 4, 1, 512, 3),
 ]
 
 
