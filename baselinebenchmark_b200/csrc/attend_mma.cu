@@ -101,7 +101,8 @@ attend_mma_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bflo
   Smem<D>& s = *reinterpret_cast<Smem<D>*>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_routed = p.hist > 0 ? tile_prefix[p.lists] : 0;
-  const int n_items = n_routed + own_item_count(p.slots, p.Hq, p.C, kRows);
+  const SlotRange own = own_slot_range(p, cu);
+  const int n_items = n_routed + own_item_count(own.n, p.Hq, p.C, kRows);
   const float sl2 = rsqrtf((float)D) * 1.4426950408889634f;
   constexpr int kChunks = D / 8;
 
@@ -111,13 +112,13 @@ attend_mma_kernel(Params p, const __nv_bfloat16* __restrict__ q, const __nv_bflo
     __syncthreads();
     const int idx = s.item;
     if (idx >= n_items) break;
-    const Item it = decode_item(p, idx, n_routed, kRows, cu, list_counts, list_offsets, tile_prefix);
+    const Item it = decode_item(p, idx, n_routed, kRows, cu, list_counts, list_offsets, tile_prefix, -1, own);
     if (!it.valid) continue;
 
     for (int r = threadIdx.x; r < kRows; r += kThreads) {
       int32_t e = -1;
       int64_t off = 0;
-      if (r < it.nrows) {
+      if (r < it.nrows && !(it.causal && r < it.row_start)) {   // own chunk: rows before the query window stay absent
         if (it.causal) {
           const int64_t tl = it.tok0 - p.win_lo + r;          // window-relative token
           e = (int32_t)((tl * p.Hq + it.head) * p.NP);

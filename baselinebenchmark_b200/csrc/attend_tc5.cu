@@ -65,6 +65,8 @@ struct Ctrl {
   uint64_t item_ready[2];                  // slot filled by the prefetch warp (phase = fill count)
   uint32_t tmem_slot;
   volatile int32_t abort;
+  int32_t n_routed, n_items;               // work items of the launch (routed tiles first), set by thread 0
+  SlotRange own;                           // slots the own-chunk items run over
   // Work items are drawn and resolved one item ahead by a spare warp: slot (n & 1)
   // holds item n, its output entries and the offsets of its Q rows.
   Item item[2];
@@ -137,9 +139,10 @@ __device__ __forceinline__ int find_list(const CtrlT& c, const int32_t* __restri
 // next item from the global queue (skipping empty own-chunk tiles), decodes it and
 // resolves its rows (output entry and Q row offset) into prefetch slot `slot`.
 template <int kItemRows, typename CtrlT>
-__device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs& a, CtrlT& c, int slot,
-                                              int n_routed, int n_items) {
+__device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs& a, CtrlT& c, int slot) {
   const int lane = threadIdx.x & 31;
+  const int n_routed = c.n_routed, n_items = c.n_items;
+  const SlotRange own = c.own;
   Item it;
   it.valid = 0;
   int done = 0;
@@ -149,7 +152,7 @@ __device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs&
     idx = __shfl_sync(0xffffffffu, idx, 0);
     if (idx >= n_items) { done = 1; break; }
     it = decode_item(p, idx, n_routed, kItemRows, a.cu, a.list_counts, a.list_offsets, a.tile_prefix,
-                     idx < n_routed ? find_list(c, a.tile_prefix, p.lists, idx) : 0);
+                     idx < n_routed ? find_list(c, a.tile_prefix, p.lists, idx) : 0, own);
     if (it.valid) break;
   }
   if (lane == 0) { c.item[slot] = it; c.done[slot] = done; }
@@ -161,8 +164,9 @@ __device__ __forceinline__ void prefetch_item(const Params& p, const KernelArgs&
       const int r = lane + 32 * u;
       ent[u] = -1;
       if (r < it.nrows) {
-        if (it.causal) ent[u] = (int32_t)(((int64_t)(it.tok0 - p.win_lo + r) * p.Hq + it.head) * p.NP);
-        else ent[u] = __ldg(a.row_list + it.row_start + r);
+        if (!it.causal) ent[u] = __ldg(a.row_list + it.row_start + r);
+        else if (r >= it.row_start)                            // rows before the query window stay absent
+          ent[u] = (int32_t)(((int64_t)(it.tok0 - p.win_lo + r) * p.Hq + it.head) * p.NP);
       }
     }
 #pragma unroll
@@ -351,6 +355,9 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
       mbar_init(smem_u32(&c.item_ready[i]), 1);
     }
     c.abort = 0;
+    c.n_routed = p.hist > 0 ? a.tile_prefix[p.lists] : 0;
+    c.own = own_slot_range(p, a.cu);
+    c.n_items = c.n_routed + own_item_count(c.own.n, p.Hq, p.C, 2 * kTileM);
     fence_barrier_init();
     prefetch_tmap(&tmap_k);
     prefetch_tmap(&tmap_v);
@@ -364,9 +371,6 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = c.tmem_slot;
-
-  const int n_routed = p.hist > 0 ? a.tile_prefix[p.lists] : 0;
-  const int n_items = n_routed + own_item_count(p.slots, p.Hq, p.C, 2 * kTileM);
   Item it;
 
   if (warp < 4) {
@@ -385,7 +389,7 @@ attend_tc5_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_k,
     const uint32_t el = elect_one();
     for (int n = 0;; ++n) {
       // warp 2 runs one item ahead: it fills slot n & 1 while the others still work on item n - 1
-      if (warp == 2) prefetch_item<2 * kTileM>(p, a, c, n & 1, n_routed, n_items);
+      if (warp == 2) prefetch_item<2 * kTileM>(p, a, c, n & 1);
       if (!next_item<false, D>(a, c, smem, n & 1, it)) break;
       const int ntiles = (it.kv_len + kBN - 1) / kBN;
       if (warp == 0 && lane == 0) {
@@ -657,6 +661,9 @@ attend_tc5_wide_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_
       mbar_init(smem_u32(&c.item_ready[i]), 1);
     }
     c.abort = 0;
+    c.n_routed = p.hist > 0 ? a.tile_prefix[p.lists] : 0;
+    c.own = own_slot_range(p, a.cu);
+    c.n_items = c.n_routed + own_item_count(c.own.n, p.Hq, p.C, kTileM);
     fence_barrier_init();
     prefetch_tmap(&tmap_k);
     prefetch_tmap(&tmap_v);
@@ -670,9 +677,6 @@ attend_tc5_wide_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = c.tmem_slot;
-
-  const int n_routed = p.hist > 0 ? a.tile_prefix[p.lists] : 0;
-  const int n_items = n_routed + own_item_count(p.slots, p.Hq, p.C, kTileM);
   Item it;
   // c.o_full[0] completes once per tile, when its P.V has executed; "tile g" counts the CTA's tiles
 
@@ -687,7 +691,7 @@ attend_tc5_wide_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_
     const uint32_t dv = __shfl_sync(0xffffffffu, desc_lo(sV, kHalfBytes), 0);
     const uint32_t el = elect_one();
     for (int n = 0;; ++n) {
-      if (warp == 2) prefetch_item<kTileM>(p, a, c, n & 1, n_routed, n_items);
+      if (warp == 2) prefetch_item<kTileM>(p, a, c, n & 1);
       if (!next_item<false, D, kTileM>(a, c, smem, n & 1, it)) break;
       const int ntiles = (it.kv_len + kBN - 1) / kBN;
       if (warp == 0 && lane == 0) {
@@ -924,6 +928,8 @@ struct SmallCtrl {
   uint64_t item_ready[2];
   uint32_t tmem_slot;
   volatile int32_t abort;
+  int32_t n_routed, n_items;
+  SlotRange own;
   Item item[2];
   int32_t done[2];
   int64_t qoff[2][kTileM];
@@ -958,6 +964,9 @@ attend_tc5_small_kernel(const Params p, const __grid_constant__ CUtensorMap tmap
     mbar_init(smem_u32(&c.item_ready[0]), 1);
     mbar_init(smem_u32(&c.item_ready[1]), 1);
     c.abort = 0;
+    c.n_routed = p.hist > 0 ? a.tile_prefix[p.lists] : 0;
+    c.own = own_slot_range(p, a.cu);
+    c.n_items = c.n_routed + own_item_count(c.own.n, p.Hq, p.C, kTileM);
     fence_barrier_init();
     prefetch_tmap(&tmap_k);
     prefetch_tmap(&tmap_v);
@@ -971,9 +980,6 @@ attend_tc5_small_kernel(const Params p, const __grid_constant__ CUtensorMap tmap
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = c.tmem_slot;
-
-  const int n_routed = p.hist > 0 ? a.tile_prefix[p.lists] : 0;
-  const int n_items = n_routed + own_item_count(p.slots, p.Hq, p.C, kTileM);
 
   // Head of item n for every thread: the slot filled by warp 4; warps 0-3 gather the Q rows.  Warp 4
   // does not wait for the gather: it goes on to describe item n + 1 at once (its chain of
@@ -1019,7 +1025,7 @@ attend_tc5_small_kernel(const Params p, const __grid_constant__ CUtensorMap tmap
     const uint32_t dk = __shfl_sync(0xffffffffu, desc_lo(sK, 16), 0);
     const uint32_t dv = __shfl_sync(0xffffffffu, desc_lo(sV, kHalfBytes), 0);
     const uint32_t el = elect_one();
-    if (warp == 4) prefetch_item<kTileM>(p, a, c, 0, n_routed, n_items);
+    if (warp == 4) prefetch_item<kTileM>(p, a, c, 0);
     for (int n = 0;; ++n) {
       if (!next_item(n, it)) break;
       const int ntiles = (it.kv_len + kBN - 1) / kBN;
@@ -1049,7 +1055,7 @@ attend_tc5_small_kernel(const Params p, const __grid_constant__ CUtensorMap tmap
         // the next item: described by the whole warp, its first tiles requested as soon as the
         // stages free up
         const int s1 = (n + 1) & 1;
-        prefetch_item<kTileM>(p, a, c, s1, n_routed, n_items);
+        prefetch_item<kTileM>(p, a, c, s1);
         if (lane == 0 && alive && !c.done[s1]) {
           const Item nx = c.item[s1];
           alive = load_tile(nx, 0);

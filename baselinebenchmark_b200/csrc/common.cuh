@@ -30,6 +30,21 @@ struct Params {
 
 __host__ inline int cdiv_i(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 
+// Token tiles of `tile` tokens per sequence that the gating and scatter grids enumerate: those
+// of max_seqlen when every token is a query; with a query window only as many as Tq tokens can
+// overlap (one more than they fill), counted from window_tile0 of the sequence, so that a
+// decode step on a long prefix does not walk over the tiles of the whole prefix.
+__host__ __device__ inline int window_tiles(const Params& p, int tile) {
+  const int64_t all = ((int64_t)p.max_seqlen + tile - 1) / tile;
+  if (p.Tq == p.T) return (int)all;
+  const int64_t w = (p.Tq + tile - 1) / tile + 1;
+  return (int)(w < all ? w : all);
+}
+// First tile of the sequence starting at packed token s0 that can hold a token of the window.
+__device__ __forceinline__ int window_tile0(const Params& p, int s0, int tile) {
+  return (p.Tq == p.T || p.win_lo <= s0) ? 0 : (p.win_lo - s0) / tile;
+}
+
 __device__ __forceinline__ float bf16_lo(uint32_t x) { return __uint_as_float(x << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t x) { return __uint_as_float(x & 0xffff0000u); }
 
@@ -96,7 +111,7 @@ struct Item {
   int valid;             // 0: nothing to do
   int causal;            // 1: own chunk, rows are consecutive tokens of one head
   int nrows;             // rows in this item (<= tile rows)
-  int row_start;         // routed: first index into row_list
+  int row_start;         // routed: first index into row_list; own: first row inside the query window
   int tok0;              // own: first query token
   int head;              // own: query head
   int kv_head;
@@ -104,15 +119,43 @@ struct Item {
   int kv_len;            // keys to visit
 };
 
+// Slots that can hold tokens of the query window: [lo, lo + n).  All slots when every token
+// is a query; otherwise from the slot of the window's first token to that of its last one
+// (packed tokens rise with the slot index), so that a short window - a decode step is one
+// token - does not enumerate the own-chunk tiles of the whole batch.
+struct SlotRange { int lo, n; };
+__device__ __forceinline__ SlotRange own_slot_range(const Params& p, const int32_t* __restrict__ cu) {
+  SlotRange sr;
+  sr.lo = 0;
+  sr.n = (int)p.slots;
+  if (p.Tq == p.T) return sr;
+  int at[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int tok = e == 0 ? p.win_lo : p.win_lo + (int)p.Tq - 1;
+    int l = 0, r = p.B;                       // last sequence with cu[b] <= tok
+    while (r - l > 1) {
+      const int mid = (l + r) >> 1;
+      if (__ldg(cu + mid) <= tok) l = mid; else r = mid;
+    }
+    at[e] = l * p.mc + (tok - __ldg(cu + l)) / p.C;
+  }
+  sr.lo = at[0];
+  sr.n = at[1] - at[0] + 1;
+  return sr;
+}
+
 // Decode work item `i`.  Routed items come first (list-major, tiles of
-// `tile_rows` rows), own-chunk items follow with the longest tiles first.
+// `tile_rows` rows), own-chunk items follow with the longest tiles first, over the
+// slots [own.lo, own.lo + own.n) (own.n < 0: all slots).
 // `list_hint` >= 0: the list of a routed item, found by the caller (the last l with
 // tile_prefix[l] <= i); otherwise it is searched for in tile_prefix.
 __device__ __forceinline__ Item decode_item(const Params& p, int i, int n_routed, int tile_rows,
                                             const int32_t* __restrict__ cu,
                                             const int32_t* __restrict__ list_counts,
                                             const int32_t* __restrict__ list_offsets,
-                                            const int32_t* __restrict__ tile_prefix, int list_hint = -1) {
+                                            const int32_t* __restrict__ tile_prefix, int list_hint = -1,
+                                            SlotRange own = SlotRange{0, -1}) {
   Item it;
   it.valid = 0;
   if (i < n_routed) {
@@ -141,27 +184,32 @@ __device__ __forceinline__ Item decode_item(const Params& p, int i, int n_routed
     return it;
   }
   const int tiles_per_chunk = (p.C + tile_rows - 1) / tile_rows;
-  const int per_tile = p.slots * p.Hq;
+  const int per_tile = (own.n < 0 ? (int)p.slots : own.n) * p.Hq;
   int idx = i - n_routed;
   const int ti = tiles_per_chunk - 1 - idx / per_tile;
   idx -= (idx / per_tile) * per_tile;
-  const int slot = idx / p.Hq;
-  const int h = idx - slot * p.Hq;
+  const int slot = own.lo + idx / p.Hq;
+  const int h = idx - (slot - own.lo) * p.Hq;
   const int b = slot / p.mc, j = slot - b * p.mc;
   const Slot s = slot_of(cu, b, j, p.C);
   const int tok0 = s.start + ti * tile_rows;
-  if (ti < 0 || tok0 >= s.end) return it;
-  // the query window starts and ends on slot boundaries: a tile is inside or outside
-  if (tok0 < p.win_lo || tok0 >= p.win_lo + p.Tq) return it;
+  if (ti < 0) return it;
+  // the tile keeps its place in the chunk; of its rows, those inside the query window
+  // [first, nrows) are computed (a window may start and end anywhere)
+  const int win_hi = p.win_lo + (int)p.Tq;
+  const int tok_end = s.end < win_hi ? s.end : win_hi;
+  const int first = p.win_lo > tok0 ? p.win_lo - tok0 : 0;
+  const int nrows = tok_end - tok0 < tile_rows ? tok_end - tok0 : tile_rows;
+  if (first >= nrows) return it;
   it.valid = 1;
   it.causal = 1;
   it.tok0 = tok0;
-  it.nrows = s.end - tok0 < tile_rows ? s.end - tok0 : tile_rows;
+  it.nrows = nrows;
   it.head = h;
   it.kv_head = h / p.G;
   it.kv_tok0 = s.start;
-  it.kv_len = tok0 + it.nrows - s.start;
-  it.row_start = 0;
+  it.kv_len = tok0 + nrows - s.start;
+  it.row_start = first;
   return it;
 }
 

@@ -315,11 +315,12 @@ struct GateTile {
 __device__ __forceinline__ GateTile gate_tile(const Params& p, const int32_t* __restrict__ cu, int i, int tiles_x,
                                               int tokens_per_cta) {
   GateTile t;
-  const int x = i % tiles_x, rest = i / tiles_x;
+  const int rest = i / tiles_x;
   t.hk = rest % p.Hkv;
   t.b = rest / p.Hkv;
   t.s0 = cu[t.b];
   const int s1 = cu[t.b + 1];
+  const int x = i - rest * tiles_x + window_tile0(p, t.s0, tokens_per_cta);
   // tokens of the tile, clipped to the sequence and to the query window
   t.tok_lo = max(t.s0 + x * tokens_per_cta, p.win_lo);
   const int tok_hi = min(min(t.s0 + (x + 1) * tokens_per_cta, s1), p.win_lo + (int)p.Tq);
@@ -353,7 +354,7 @@ gate_topk_kernel(const Params p, const __grid_constant__ CUtensorMap tmap_q, con
   int32_t* cnt_s = reinterpret_cast<int32_t*>(&c + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int tiles_x = (p.max_seqlen + tokens_per_cta - 1) / tokens_per_cta;
+  const int tiles_x = window_tiles(p, tokens_per_cta);
   const int n_tiles = tiles_x * p.Hkv * p.B;
   const int rows_box = tokens_per_cta * p.G;           // rows one Q box brings
 
@@ -872,7 +873,7 @@ cudaError_t launch_gate_topk_stats(const Params& p, const __nv_bfloat16* q, cons
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int64_t n_tiles = (int64_t)cdiv_i(p.max_seqlen, tokens_per_cta) * p.Hkv * p.B;
+  const int64_t n_tiles = (int64_t)window_tiles(p, tokens_per_cta) * p.Hkv * p.B;
   if (n_tiles >= ((int64_t)1 << 31)) return cudaErrorInvalidConfiguration;
   // persistent CTAs: as many as are resident at once, by shared memory (1 KB per CTA is reserved),
   // registers (allocated in units of 8 per thread) and tensor memory (512 columns per SM)

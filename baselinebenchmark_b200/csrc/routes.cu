@@ -81,8 +81,9 @@ scatter_routes_kernel(Params p, const int32_t* __restrict__ cu, const int32_t* _
   int32_t* base_s = sm + p.mc;       // [mc] first position reserved for this CTA
   const int b = blockIdx.z, hk = blockIdx.y;
   const int s0 = cu[b], s1 = cu[b + 1];
-  const int tok_lo = max(s0 + blockIdx.x * kScatterTokens, p.win_lo);
-  const int tok_hi = min(min(s0 + (blockIdx.x + 1) * kScatterTokens, s1), p.win_lo + (int)p.Tq);
+  const int x = blockIdx.x + window_tile0(p, s0, kScatterTokens);
+  const int tok_lo = max(s0 + x * kScatterTokens, p.win_lo);
+  const int tok_hi = min(min(s0 + (x + 1) * kScatterTokens, s1), p.win_lo + (int)p.Tq);
   if (tok_lo >= tok_hi) return;
   const int ntok = tok_hi - tok_lo;
   const int loc = tok_lo - p.win_lo;             // window-relative token of the first row
@@ -130,7 +131,7 @@ cudaError_t launch_compact(const Params& p, const int32_t* cu, const int32_t* se
   if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
   e = cudaFuncSetAttribute(scatter_routes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  dim3 grid(cdiv_i(p.max_seqlen, kScatterTokens), p.Hkv, p.B);
+  dim3 grid(window_tiles(p, kScatterTokens), p.Hkv, p.B);
   scatter_routes_kernel<<<grid, kScatterThreads, smem, st>>>(p, cu, selected, list_offsets, cursors, row_list, partial_lse);
   return cudaGetLastError();
 }

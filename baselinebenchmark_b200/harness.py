@@ -7,6 +7,7 @@ report (:39-44).  Like the original it performs no correctness check.
 
     python -m baselinebenchmark_b200.harness --case cfg2 --rounds 1 --iterations 3
     python -m baselinebenchmark_b200.harness --suite --output results.json
+    python -m baselinebenchmark_b200.harness --case cfg3-seq --decode 64      # latency of decode steps
 
 `--suite` runs the reference's case list (moba_compare.py:59-99); a case outside
 what this build supports (bf16 or fp16; head_dim 64, 96, 128, 256) would be
@@ -114,6 +115,8 @@ def run_case(case: Case, args, device):
         return {**asdict(case), "status": "skipped", "reason": "this build: head_dim 64, 96, 128, 256"}
     q, k, v, cu = make_inputs(case, device)
     call = (q, k, v, cu, max(case.seq_lens), case.chunk_size, case.topk)
+    if args.decode:
+        return run_decode_case(case, args, call)
     if args.backward:
         return run_backward_case(case, args, call)
     if args.stage == "gating":
@@ -185,6 +188,47 @@ def run_gating_case(case: Case, args, call):
             "largest_estimate_error_over_bound": st[1] / 65536.0, "bound_violations": st[2]}
 
 
+def run_decode_case(case: Case, args, call):
+    """Latency of single-token decode steps at the end of the case's sequence (incremental.py):
+    the prefix is prefilled in one untimed call; then `--decode` steps are timed one by one
+    (perf_counter + synchronize per step, like the other cases) and as many again back to back
+    between two CUDA events, which gives the device time of a step without the host's launches."""
+    from .incremental import IncrementalMoba
+    q, k, v, _, _, chunk, topk = call
+    n, warm = args.decode, min(args.warmup, 8)
+    total = case.seq_lens[0]
+    if len(case.seq_lens) != 1 or total <= 2 * n + warm:
+        return {**asdict(case), "status": "skipped", "reason": "--decode wants one sequence longer than the steps"}
+    with torch.inference_mode():
+        inc = IncrementalMoba(total, case.kv_heads, case.head_dim, chunk, topk, dtype=q.dtype, device=q.device)
+        at = total - 2 * n - warm
+        inc.append(q[:at], k[:at], v[:at])
+
+        def step(t):
+            return inc.append(q[t:t + 1], k[t:t + 1], v[t:t + 1])
+
+        for _ in range(warm):
+            step(at)
+            at += 1
+        torch.cuda.synchronize()
+        samples = []
+        for _ in range(n):
+            t0 = time.perf_counter()
+            step(at)
+            torch.cuda.synchronize()
+            samples.append((time.perf_counter() - t0) * 1e3)
+            at += 1
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            step(at)
+            at += 1
+        e1.record()
+        torch.cuda.synchronize()
+    return {**asdict(case), "status": "measured", "pass": "decode", "prefix_tokens": total - 2 * n,
+            "latency": summary(samples), "back_to_back_ms_per_step": e0.elapsed_time(e1) / n}
+
+
 def run_backward_case(case: Case, args, call):
     """Latency of `moba_backward` alone (gradients of the training path, parallel.py:149-250)
     on what one forward with LSE and selection returned; same timing protocol."""
@@ -215,6 +259,8 @@ def main(argv=None):
     ap.add_argument("--iterations", type=int, default=25)
     ap.add_argument("--rounds", type=int, default=4)
     ap.add_argument("--backward", action="store_true", help="time moba_backward instead of the forward")
+    ap.add_argument("--decode", type=int, default=0, metavar="N",
+                    help="time N single-token decode steps at the end of the sequence instead of the prefill")
     ap.add_argument("--stage", choices=["all", "gating"], default="all",
                     help="gating: time chunk means + scores + top-k alone (staged entry points)")
     ap.add_argument("--output")

@@ -117,15 +117,15 @@ def moba_forward(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, *,
     """Runs the operator and optionally returns the final LSE [Hq, T] (fp32) and
     the routing decision selected[hist, Hq, T] (int32, -1 padded).
 
-    `q_token_begin` (context parallelism): q holds only the packed tokens
-    [q_token_begin, q_token_begin + q.shape[0]), a window that starts and ends on
-    chunk boundaries, while k, v and cu_seqlens describe every token; outputs
-    cover the window.  `workspace_limit` (bytes) bounds the scratch memory: the kv heads
+    `q_token_begin` (context parallelism, incremental prefill, decode): q holds only the
+    packed tokens [q_token_begin, q_token_begin + q.shape[0]), a window that may start and
+    end at any token, while k, v and cu_seqlens describe every token; outputs cover the
+    window and equal the rows of the run over all tokens bit for bit.  `workspace_limit` (bytes) bounds the scratch memory: the kv heads
     are then processed in groups, with identical results.  Scratch memory is allocated per
     call through torch's caching allocator unless `workspace` (a uint8 tensor the caller
     keeps alive and does not share between unordered streams) is given.
 
-    `means_cache` (incremental prefill): a [slots, Hkv, D] tensor the caller keeps between calls;
+    `means_cache` (incremental prefill and decode, see incremental.IncrementalMoba): a [slots, Hkv, D] tensor the caller keeps between calls;
     slots below `cached_slots` are taken from it, the others are computed and stored into it
     (moba_forward_cached in include/moba_b200.h has the rule for `cached_slots`)."""
     _validate(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, windowed=q_token_begin is not None)

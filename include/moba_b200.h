@@ -76,13 +76,16 @@ typedef struct moba_problem {
   int64_t k_stride_token, k_stride_head;
   int64_t v_stride_token, v_stride_head;
   int64_t o_stride_token, o_stride_head;
-  /* Query window, for context-parallel callers (the reference has none: it is
-   * rendered with enable_cp=False, native_moba.py:69).  With q_tokens > 0 only
-   * the packed tokens [q_token_begin, q_token_begin + q_tokens) are queries:
-   * q, out, lse_out and selected_out then hold q_tokens tokens (token 0 of q is
-   * packed token q_token_begin) while k, v and cu_seqlens still describe all
-   * total_tokens.  The window must start and end on chunk boundaries of its
-   * sequences (or at sequence ends).  q_tokens == 0: every token is a query. */
+  /* Query window, for context-parallel, incremental-prefill and decode callers
+   * (the reference has none: it is rendered with enable_cp=False,
+   * native_moba.py:69).  With q_tokens > 0 only the packed tokens
+   * [q_token_begin, q_token_begin + q_tokens) are queries: q, out, lse_out and
+   * selected_out then hold q_tokens tokens (token 0 of q is packed token
+   * q_token_begin) while k, v and cu_seqlens still describe all total_tokens.
+   * The window may start and end at any token (a decode step is a window of one
+   * token at the end of the prefix); its rows equal those of the run over all
+   * tokens bit for bit.  moba_cp_forward alone wants chunk-aligned windows.
+   * q_tokens == 0: every token is a query. */
   int64_t q_token_begin, q_tokens;
   int32_t dtype;            /* MOBA_DTYPE_*; 0 (bf16) in a zero-initialised struct */
   int32_t reserved;         /* must be 0                                         */
@@ -137,10 +140,11 @@ int moba_forward_events(const moba_problem_t* p, const void* q, const void* k, c
                         const int32_t* cu_seqlens, void* out, float* lse_out, int32_t* selected_out,
                         void* workspace, size_t workspace_bytes, void* stream, void* const* events);
 
-/* moba_forward with a caller-held cache of chunk means, for incremental prefill: a sequence
- * (or batch) is prefilled in several calls, each with a later, chunk-aligned query window
- * (q_token_begin / q_tokens) over a longer K/V prefix, and the means of chunks that were
- * complete at an earlier call are not computed again.  The reference recomputes all chunk means
+/* moba_forward with a caller-held cache of chunk means, for incremental prefill and decode: a
+ * sequence (or batch) is processed in several calls, each with a later query window
+ * (q_token_begin / q_tokens; any number of tokens, down to the single token of a decode step)
+ * over a longer K/V prefix, and the means of chunks that were complete at an earlier call are
+ * not computed again.  The reference recomputes all chunk means
  * on every call (parallel.py:306-311); it has no incremental mode.
  *   means_cache   [slots, Hkv, D] in the tensors' dtype, slots = batch * ceil(max_seqlen / chunk)
  *                 (use the same max_seqlen, the capacity, for every call so that slots keep their
@@ -148,9 +152,9 @@ int moba_forward_events(const moba_problem_t* p, const void* q, const void* k, c
  *   cached_slots  slots [0, cached_slots) of the cache hold final means and are read only; the
  *                 means of the slots from there on are computed from k and stored into the cache.
  *                 A chunk's mean is final once its sequence has grown past the chunk: with batch 1
- *                 and a prefix of T tokens (a multiple of the chunk size) the next call may pass
- *                 cached_slots = T / chunk - 1 (the prefix's last chunk was the sequence's last
- *                 chunk, which is never a candidate, so its slot still holds zeros).
+ *                 and a prefix of T >= 1 tokens the next call may pass cached_slots =
+ *                 (T - 1) / chunk, the chunks before the prefix's last one (that one was the
+ *                 sequence's last chunk, which is never a candidate and is not computed).
  * Results are bit-identical to moba_forward on the same window.  The workspace must have the
  * full moba_workspace_size (one pass over all kv heads). */
 int moba_forward_cached(const moba_problem_t* p, const void* q, const void* k, const void* v,

@@ -433,6 +433,60 @@ def test_query_window_equals_full_run(impl, d, dtype):
         assert torch.equal(lse, full_lse[:, lo:hi])
 
 
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("d,chunk,topk", [(128, 512, 3), (128, 128, 4), (64, 1024, 2), (256, 512, 3), (96, 256, 3)],
+                         ids=["d128_c512", "d128_c128", "d64_c1024", "d256_c512", "d96_c256"])
+def test_query_window_at_any_token_equals_full_run(impl, d, chunk, topk):
+    """Decode building block: a query window may start and end at ANY token - inside a chunk,
+    inside a row tile, across a sequence boundary, a single token - and still returns exactly the
+    rows, LSE and selection of the full run (own-chunk tiles keep their place in the chunk and
+    compute only their rows inside the window)."""
+    lens = (2500, 1300)
+    total = sum(lens)
+    q, k, v, cu = _case_inputs(lens, 8, 2, chunk, seed=27, d=d)
+    qd, kd, vd = G.to_dev(q, k, v)
+    cud = torch.from_numpy(cu).cuda()
+    full, full_lse, full_sel = parallel.moba_forward(qd, kd, vd, cud, 2500, chunk, topk, return_lse=True,
+                                                     return_selected=True, attend_impl=impl)
+    windows = [(0, 1), (1, 2), (777, 778), (130, 1999), (chunk - 1, chunk + 1), (2499, 2501), (2300, 2900),
+               (total - 1, total), (2500 + 255, 2500 + 257), (3, total - 5)]
+    for lo, hi in windows:
+        out, lse, sel = parallel.moba_forward(qd[lo:hi].contiguous(), kd, vd, cud, 2500, chunk, topk, return_lse=True,
+                                              return_selected=True, attend_impl=impl, q_token_begin=lo)
+        torch.cuda.synchronize()
+        assert torch.equal(sel, full_sel[:, :, lo:hi]), (lo, hi)
+        assert torch.equal(out, full[lo:hi]), (lo, hi)
+        assert torch.equal(lse, full_lse[:, lo:hi]), (lo, hi)
+
+
+@pytest.mark.parametrize("d,chunk,topk,impl", [(128, 256, 4, None), (128, 512, 3, None), (256, 512, 3, None),
+                                               (64, 128, 3, _lib.ATTEND_MMA_SYNC)],
+                         ids=["d128_c256", "d128_c512", "d256_c512", "d64_c128_mma"])
+def test_decode_token_by_token_equals_one_shot(d, chunk, topk, impl):
+    """IncrementalMoba: an unaligned prefill block, 40 decode steps of one token, a second block
+    and more single tokens (crossing chunk boundaries on the way) give the rows of the one-shot
+    run over the final sequence bit for bit; the means cache ends as the oracle's means."""
+    from baselinebenchmark_b200.incremental import IncrementalMoba
+    total, capacity, hq, hkv = 1500, 2048, 8, 2
+    q, k, v, cu = _case_inputs((total,), hq, hkv, chunk, seed=31, d=d)
+    qd, kd, vd = G.to_dev(q, k, v)
+    full = parallel.moba_forward(qd, kd, vd, torch.from_numpy(cu).cuda(), capacity, chunk, topk, attend_impl=impl)[0]
+    inc = IncrementalMoba(capacity, hkv, d, chunk, topk, dtype=qd.dtype, attend_impl=impl)
+    steps = [700] + [1] * 40 + [300] + [1] * 30 + [total - 1070]
+    assert sum(steps) == total
+    at = 0
+    for n in steps:
+        out = inc.append(qd[at:at + n], kd[at:at + n], vd[at:at + n])
+        torch.cuda.synchronize()
+        assert torch.equal(out, full[at:at + n]), (at, n)
+        at += n
+    assert inc.length == total
+    cu_chunk, _, valid, mc = O.chunk_slots(cu, capacity, chunk)
+    want = O.chunk_means(k, cu_chunk, valid, chunk)
+    done = (total - 1) // chunk                        # chunks behind the last one hold final means
+    assert torch.equal(inc.means[:done].cpu().view(torch.int16), want[:done].view(torch.int16))
+
+
 def test_host_buffer_entry_point_matches_device_call():
     """moba_forward_host (pinned host tensors, pipelined query windows) returns the bits of moba_forward."""
     import ctypes as C
