@@ -65,6 +65,18 @@ def test_head_dims_and_dtypes_accepted(lib):
     assert lib.moba_problem_check(C.byref(_problem(reserved=1))) == -2
 
 
+def test_query_windows_at_any_token_are_accepted(lib):
+    """A query window may start and end at any token (decode: one token at the end of the prefix);
+    its workspace is sized by the window, not by the prefix."""
+    whole, one, odd = C.c_size_t(0), C.c_size_t(0), C.c_size_t(0)
+    assert lib.moba_workspace_size(C.byref(_problem()), C.byref(whole)) == 0
+    assert lib.moba_workspace_size(C.byref(_problem(q_token_begin=4095, q_tokens=1)), C.byref(one)) == 0
+    assert lib.moba_workspace_size(C.byref(_problem(q_token_begin=7, q_tokens=1001)), C.byref(odd)) == 0
+    assert 0 < one.value < odd.value < whole.value
+    assert lib.moba_problem_check(C.byref(_problem(q_token_begin=4095, q_tokens=2))) == -1     # past the last token
+    assert lib.moba_problem_check(C.byref(_problem(q_token_begin=3, q_tokens=0))) == -1
+
+
 def test_backward_argument_checks(lib):
     need = C.c_size_t(0)
     assert lib.moba_backward_workspace_size(C.byref(_problem(attend_impl=1)), C.byref(need)) == 0
