@@ -223,3 +223,23 @@ def test_oracle_gradients_match_reference_backward(path):
         err = (got - ref).abs()
         scale = ref.abs().max().item()
         assert err.max().item() < 4e-3 * scale and err.mean().item() < 2e-4 * scale, (name, err.max().item(), scale)
+
+
+def test_rows_of_a_prefix_equal_rows_of_the_whole_sequence():
+    """What incremental prefill and decode rest on, stated on the oracle: the rows of a prefix
+    of the sequence - selection, output and LSE - are those of the whole sequence.  A query only
+    sees keys at or before its own position, only chunks before its own are candidates, and a
+    complete chunk's mean depends on its own keys alone; the prefix's last, possibly partial,
+    chunk is nobody's candidate yet.  max_seqlen is the capacity in every call so that the
+    slots and the number of selected chunks keep their meaning.  The selection is compared
+    exactly; outputs and LSE to 1e-5 (the oracle's fp32 matrix products sum in an order that
+    depends on the shapes)."""
+    total, capacity, chunk, topk = 700, 1024, 64, 4
+    q, k, v, cu = O.make_inputs([total], 4, 2, 64, chunk, seed=19)
+    out, lse, sel = O.moba_forward(q, k, v, cu, capacity, chunk, topk)
+    for t in (1, 63, 64, 65, 300, 511, 699):
+        cu_t = np.array([0, t], dtype=np.int32)
+        out_t, lse_t, sel_t = O.moba_forward(q[:t], k[:t], v[:t], cu_t, capacity, chunk, topk)
+        assert np.array_equal(sel_t, sel[:, :, :t]), t
+        assert torch.allclose(out_t, out[:t], rtol=0, atol=1e-5), t
+        assert torch.allclose(lse_t, lse[:, :t], rtol=0, atol=1e-5), t
