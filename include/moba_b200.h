@@ -170,7 +170,11 @@ int moba_forward_cached(const moba_problem_t* p, const void* q, const void* k, c
  * K/V only up to its own end), and window w+1 is copied in and window w-1 copied
  * out on two internal streams (created once per device) while window w computes;
  * results are identical to moba_forward.  With lse_out / selected_out the whole
- * batch runs as one call on `stream`.  Use moba_workspace_size_host for sizing. */
+ * batch runs as one call on `stream`.  Calls on distinct (stream, workspace) pairs may
+ * be in flight together (they share the two internal copy streams, which keep the copies
+ * in order of the calls): alternating between two pairs hides the first copy in and the
+ * last copy out of every call behind its neighbours' kernels.  Use
+ * moba_workspace_size_host for sizing. */
 int moba_workspace_size_host(const moba_problem_t* p, size_t* bytes);
 int moba_forward_host(const moba_problem_t* p, const void* q_host, const void* k_host,
                       const void* v_host, const int32_t* cu_seqlens_host, void* out_host,

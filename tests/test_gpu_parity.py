@@ -516,6 +516,35 @@ def test_host_buffer_entry_point_matches_device_call():
             assert torch.equal(hlse, ref_lse.cpu()) and torch.equal(hsel, ref_sel.cpu())
 
 
+def test_host_calls_in_flight_on_two_streams_keep_their_results():
+    """moba_forward_host is re-entrant for distinct (stream, workspace, result buffer) sets: six
+    calls on two different problems, alternating between two streams without any host
+    synchronisation in between (the copies of one call then overlap the kernels of the other and
+    share the library's two copy streams), each leave the bits of the device call."""
+    import ctypes as C
+    sets = []
+    for i, (lens, topk) in enumerate((((3000, 1100, 2048), 4), ((2500, 3100), 3))):
+        q, k, v, cu = _case_inputs(lens, 8, 2, 128, seed=61 + i)
+        cud = torch.from_numpy(cu).cuda()
+        ref = parallel.moba_forward(*G.to_dev(q, k, v), cud, max(lens), 128, topk)[0].cpu()
+        prob, _ = G.problem_for(q.cuda(), k.cuda(), v.cuda(), cud, max(lens), 128, topk)
+        size = C.c_size_t(0)
+        _lib.check(_lib.lib().moba_workspace_size_host(C.byref(prob), C.byref(size)))
+        sets.append(dict(prob=prob, ref=ref, host=[t.pin_memory() for t in (q, k, v, torch.from_numpy(cu))],
+                         out=torch.zeros_like(q).pin_memory(), stream=torch.cuda.Stream(),
+                         ws=torch.empty(size.value, dtype=torch.uint8, device="cuda")))
+    torch.cuda.synchronize()
+    for _ in range(3):
+        for s in sets:
+            hq, hk, hv, hcu = s["host"]
+            _lib.check(_lib.lib().moba_forward_host(
+                C.byref(s["prob"]), hq.data_ptr(), hk.data_ptr(), hv.data_ptr(), hcu.data_ptr(), s["out"].data_ptr(),
+                None, None, s["ws"].data_ptr(), s["ws"].numel(), s["stream"].cuda_stream))
+    torch.cuda.synchronize()
+    for s in sets:
+        assert torch.equal(s["out"], s["ref"])
+
+
 def test_config3_unit_sampled():
     """BASELINE.json configs[3], one of its 128 (sequence, KV-head group) units at full size:
     131072 tokens, 4 query heads sharing 1 KV head, chunk 4096, top-k 8."""
