@@ -40,8 +40,9 @@ class IncrementalMoba:
     def reset(self) -> None:
         self.length = 0
 
-    def append(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
-        """q [n, Hq, D], k / v [n, Hkv, D]: the next n >= 1 tokens.  Returns their rows [n, Hq, D]."""
+    def append(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, return_selected: bool = False):
+        """q [n, Hq, D], k / v [n, Hkv, D]: the next n >= 1 tokens.  Returns their rows [n, Hq, D];
+        with `return_selected` also the chunks they selected, (out, selected[hist, Hq, n] int32)."""
         n, begin = q.shape[0], self.length
         if k.shape[0] != n or v.shape[0] != n:
             raise ValueError(f"q, k and v must hold the same number of new tokens, got {n}, {k.shape[0]}, {v.shape[0]}")
@@ -54,8 +55,9 @@ class IncrementalMoba:
         # a call on a prefix of `begin` tokens left final means in the slots of all chunks but the
         # prefix's last one (the last chunk of a sequence is no candidate and is not computed)
         cached = (begin - 1) // self.chunk if begin > 0 else 0
-        out, _, _ = parallel.moba_forward(q, self.k[:end], self.v[:end], self.cu, self.capacity, self.chunk, self.topk,
-                                          attend_impl=self.attend_impl, q_token_begin=begin,
-                                          means_cache=self.means, cached_slots=cached)
+        out, _, sel = parallel.moba_forward(q, self.k[:end], self.v[:end], self.cu, self.capacity, self.chunk,
+                                            self.topk, attend_impl=self.attend_impl, q_token_begin=begin,
+                                            means_cache=self.means, cached_slots=cached,
+                                            return_selected=return_selected)
         self.length = end
-        return out
+        return (out, sel) if return_selected else out

@@ -584,6 +584,46 @@ def test_config4_window_sampled():
     assert diff.max().item() < MAX_ABS and diff.mean().item() < MEAN_ABS
 
 
+def test_decode_on_config4_prefix_sampled():
+    """BASELINE.json configs[4] geometry for one KV-head group at full length: a cache of 1048576
+    tokens (chunk 4096, top-k 16: 255 candidate chunks, 15 selected) is prefilled in eight blocks,
+    the last one 24 tokens short, and the last 24 tokens are decoded one by one.  Their selection
+    against the oracle bit for bit, their rows against float64."""
+    from baselinebenchmark_b200.incremental import IncrementalMoba
+    cfg = O.CONFIGS[4]
+    total, chunk, topk, steps = 1048576, cfg["chunk"], cfg["topk"], 24
+    q, k, v, cu = O.make_inputs([total], 4, 1, 128, chunk, seed=47)
+    qd, kd, vd = G.to_dev(q, k, v)
+    inc = IncrementalMoba(total, 1, 128, chunk, topk)
+    at = 0
+    for n in [total // 8] * 7 + [total // 8 - steps]:
+        out = inc.append(qd[at:at + n], kd[at:at + n], vd[at:at + n])
+        at += n
+    assert torch.isfinite(out.float()).all()
+    del out
+    outs, sels = [], []
+    for _ in range(steps):
+        o, s = inc.append(qd[at:at + 1], kd[at:at + 1], vd[at:at + 1], return_selected=True)
+        outs.append(o)
+        sels.append(s)
+        at += 1
+    assert at == total == inc.length
+    out = torch.cat(outs, 0).cpu()
+    sel = torch.cat(sels, 2).cpu().numpy()
+    toks = list(range(total - steps, total))
+    cu_chunk, _, valid, mc = O.chunk_slots(cu, total, chunk)
+    hist = O.historical_topk(topk, mc)
+    assert (mc, hist) == (256, 15)
+    means = O.chunk_means(k, cu_chunk, valid, chunk)
+    sel_o = O.select_chunks(q, means, cu, total, chunk, hist, rows=toks)
+    np.testing.assert_array_equal(sel, sel_o[:, :, toks])
+    rows = [(t, h) for t in toks[::3] for h in range(4)]
+    ref, _ = O.attend_rows(q, k, v, cu, total, chunk, sel_o, rows)
+    got = torch.stack([out[t - (total - steps), h] for t, h in rows]).double()
+    diff = (got - ref).abs()
+    assert diff.max().item() < MAX_ABS and diff.mean().item() < MEAN_ABS
+
+
 @pytest.mark.parametrize("d,dtype", [(128, torch.bfloat16), (64, torch.float16), (96, torch.bfloat16)],
                          ids=["d128_bf16", "d64_fp16", "d96_bf16"])
 def test_bounded_workspace_runs_head_groups(d, dtype):
