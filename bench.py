@@ -621,6 +621,32 @@ def main():
                 "ms_per_call": bwd_ms, "tflops_on_2.5x_forward_flops": 2.5 * f2 / bwd_ms / 1e9}
             del q2, k2, v2, out2, lse2, sel2, dout2
             torch.cuda.empty_cache()
+            # decode: one sequence of configs[3] prefilled in one call, then single-token steps with the
+            # K/V rows and chunk means cached on the device (incremental.py)
+            from baselinebenchmark_b200.incremental import IncrementalMoba
+            q3, k3, v3, _ = make_inputs_device([SEQ_LEN], HQ, HKV, D, CHUNK, 47000, dev)
+            n_dec, n_warm = 64, 8
+            inc = IncrementalMoba(SEQ_LEN, HKV, D, CHUNK, TOPK, device=dev)
+            at = SEQ_LEN - n_dec - n_warm
+            inc.append(q3[:at], k3[:at], v3[:at])
+            for _ in range(n_warm):
+                inc.append(q3[at:at + 1], k3[at:at + 1], v3[at:at + 1])
+                at += 1
+            d0, d1 = new_events(2)
+            d0.record()
+            for _ in range(n_dec):
+                inc.append(q3[at:at + 1], k3[at:at + 1], v3[at:at + 1])
+                at += 1
+            d1.record()
+            torch.cuda.synchronize()
+            dec_ms = d0.elapsed_time(d1) / n_dec
+            also["decode (1 GPU, one sequence of configs[3]: single-token steps on a cached prefix)"] = {
+                "prefix_tokens": SEQ_LEN - n_dec, "steps": n_dec, "ms_per_token": dec_ms,
+                "tokens_per_s": 1e3 / dec_ms,
+                "note": "steps issued back to back from Python, CUDA events around all of them; every step "
+                        "returns the bits of the prefill's row"}
+            del q3, k3, v3, inc
+            torch.cuda.empty_cache()
         barrier()
         ctx = context_block(args.context_steps, 1, rank, world, local, dev, dist)
         if rank == 0 and ctx is not None:
